@@ -1,0 +1,933 @@
+// Host layer above the kernel-launch ABI: NArray objects and an ndloop-style
+// dispatcher.  See include/cumo_b200_host.h for what it mirrors in the reference.
+//
+// Everything here only prepares descriptors and calls the exported
+// `cumo_..._kernel_launch` symbols by the names the reference's generated code
+// uses; no arithmetic on array data happens on the host.
+#include "../common.cuh"
+#include "../../../include/cumo_b200_host.h"
+
+#include <dlfcn.h>
+#include <cstdarg>
+#include <cstdio>
+#include <cstring>
+#include <mutex>
+#include <string>
+#include <vector>
+
+namespace {
+
+constexpr int kMaxD = CUMO_NA_MAX_DIMENSION;
+const char* kTypeName[] = {"sfloat", "dfloat", "int32", "int64", "bit", "uint64"};
+const int kElemSize[] = {4, 8, 4, 8, 0, 8};
+
+thread_local std::string tl_class, tl_message;
+
+struct Storage {
+    char* ptr;
+    size_t bytes;
+    int refs;
+    bool owned;
+};
+
+}  // namespace
+
+struct cb200_na {
+    int dtype;
+    int ndim;
+    int64_t shape[kMaxD];
+    int64_t step[kMaxD];     // bytes; bits for CB200_BIT
+    int64_t offset;          // same unit, from the start of the buffer
+    Storage* st;
+    bool inplace;
+};
+
+namespace {
+
+std::mutex g_ref_mu;
+
+void* fail(const char* klass, const char* fmt, ...) {
+    char buf[512];
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(buf, sizeof buf, fmt, ap);
+    va_end(ap);
+    tl_class = klass;
+    tl_message = buf;
+    return nullptr;
+}
+
+bool cuda_ok(cudaError_t e, const char* what) {
+    if (e == cudaSuccess) return true;
+    fail("CudaError", "%s: %s", what, cudaGetErrorString(e));
+    return false;
+}
+
+// raise what the default launch check latched (a strong check supplied by a host
+// program reports through its own channel and leaves the latch empty)
+bool launch_ok() {
+    const char* msg = nullptr;
+    int e = cb200_last_error(&msg);
+    if (e == 0) return true;
+    fail("CudaError", "%s", msg);
+    return false;
+}
+
+int64_t size_of(const cb200_na* a) {
+    int64_t n = 1;
+    for (int d = 0; d < a->ndim; ++d) n *= a->shape[d];
+    return n;
+}
+
+size_t buffer_bytes(int dtype, int64_t n) {
+    if (dtype == CB200_BIT) return (size_t)((n + 31) / 32) * 4;
+    return (size_t)n * kElemSize[dtype];
+}
+
+void contiguous_steps(int dtype, int ndim, const int64_t* shape, int64_t* step) {
+    int64_t s = dtype == CB200_BIT ? 1 : kElemSize[dtype];
+    for (int d = ndim - 1; d >= 0; --d) { step[d] = s; s *= shape[d]; }
+}
+
+cb200_na* make(int dtype, int ndim, const int64_t* shape, bool zero) {
+    if (dtype < 0 || dtype > CB200_UINT64) return (cb200_na*)fail("TypeError", "unknown dtype %d", dtype);
+    if (ndim < 0 || ndim > kMaxD) return (cb200_na*)fail("ShapeError", "ndim %d out of range", ndim);
+    cb200_na* a = new cb200_na();
+    a->dtype = dtype;
+    a->ndim = ndim;
+    for (int d = 0; d < ndim; ++d) {
+        if (shape[d] < 0) { delete a; return (cb200_na*)fail("ShapeError", "negative extent"); }
+        a->shape[d] = shape[d];
+    }
+    contiguous_steps(dtype, ndim, a->shape, a->step);
+    a->offset = 0;
+    a->inplace = false;
+    size_t bytes = buffer_bytes(dtype, size_of(a));
+    char* p = cumo_cuda_runtime_malloc(bytes ? bytes : 4);
+    if (!p) { delete a; launch_ok(); if (tl_message.empty()) fail("CudaError", "out of device memory"); return nullptr; }
+    if (zero && bytes) {
+        if (!cuda_ok(cudaMemsetAsync(p, 0, bytes, cb200::current_stream()), "cudaMemsetAsync")) {
+            cumo_cuda_runtime_free(p); delete a; return nullptr;
+        }
+    }
+    a->st = new Storage{p, bytes, 1, true};
+    return a;
+}
+
+cb200_na* share(const cb200_na* src) {
+    cb200_na* v = new cb200_na(*src);
+    v->inplace = false;
+    std::lock_guard<std::mutex> lk(g_ref_mu);
+    ++v->st->refs;
+    return v;
+}
+
+char* data_ptr(const cb200_na* a) {   // value types only
+    return a->st->ptr + a->offset;
+}
+
+bool is_contiguous(const cb200_na* a) {
+    int64_t s = a->dtype == CB200_BIT ? 1 : kElemSize[a->dtype];
+    for (int d = a->ndim - 1; d >= 0; --d) {
+        if (a->shape[d] != 1 && a->step[d] != s) return false;
+        s *= a->shape[d];
+    }
+    return true;
+}
+
+// ---- symbol lookup ---------------------------------------------------------------------
+void* lib_handle() {
+    static void* h = [] {
+        Dl_info info;
+        if (dladdr((void*)&cb200_version, &info) && info.dli_fname) {
+            void* hh = dlopen(info.dli_fname, RTLD_NOW | RTLD_NOLOAD);
+            if (hh) return hh;
+        }
+        return dlopen(nullptr, RTLD_NOW);
+    }();
+    return h;
+}
+
+void* sym(const std::string& name) {
+    void* f = dlsym(lib_handle(), name.c_str());
+    if (!f) fail("NoMethodError", "libcumo_b200 has no entry point %s", name.c_str());
+    return f;
+}
+
+// ---- the int* flag of integer div/mod/reciprocal/abs ------------------------------------
+// One mapped pinned int per thread, as ext/cumo/cuda/runtime.c:22-47 allocates per call.
+struct Flag {
+    int* host = nullptr;
+    int* dev = nullptr;
+    bool ready() {
+        if (host) return true;
+        if (cudaHostAlloc((void**)&host, sizeof(int), cudaHostAllocMapped) != cudaSuccess) { host = nullptr; return false; }
+        if (cudaHostGetDevicePointer((void**)&dev, host, 0) != cudaSuccess) { cudaFreeHost(host); host = nullptr; return false; }
+        return true;
+    }
+};
+thread_local Flag tl_flag;
+
+// ---- descriptors ---------------------------------------------------------------------------
+struct Loop {
+    int ndim;
+    int64_t shape[kMaxD];
+};
+
+// broadcast rule of ndloop_check_shape: extents are aligned at the last dimension, an
+// extent of 1 repeats, anything else must match
+bool broadcast(const cb200_na* a, const cb200_na* b, Loop* lp) {
+    lp->ndim = a->ndim > b->ndim ? a->ndim : b->ndim;
+    for (int i = 0; i < lp->ndim; ++i) {
+        int da = i - (lp->ndim - a->ndim), db = i - (lp->ndim - b->ndim);
+        int64_t na = da >= 0 ? a->shape[da] : 1, nb = db >= 0 ? b->shape[db] : 1;
+        if (na != nb && na != 1 && nb != 1) {
+            fail("ShapeError", "shape1[%d](=%lld) != shape2[%d](=%lld)", da, (long long)na, db, (long long)nb);
+            return false;
+        }
+        lp->shape[i] = na == 1 ? nb : na;
+    }
+    return true;
+}
+
+void fill_indexer(cumo_na_indexer_t* ix, const Loop& lp) {
+    memset(ix, 0, sizeof *ix);
+    ix->ndim = (unsigned char)lp.ndim;
+    ix->total_size = 1;
+    for (int d = 0; d < lp.ndim; ++d) { ix->shape[d] = (size_t)lp.shape[d]; ix->total_size *= (size_t)lp.shape[d]; }
+}
+
+// operand steps against the loop shape: 0 where the operand's extent is 1 or missing
+void fill_iarray(cumo_na_iarray_t* ia, const cb200_na* a, const Loop& lp) {
+    memset(ia, 0, sizeof *ia);
+    ia->ptr = data_ptr(a);
+    for (int i = 0; i < lp.ndim; ++i) {
+        int d = i - (lp.ndim - a->ndim);
+        ia->step[i] = (d >= 0 && a->shape[d] != 1) ? (ssize_t)a->step[d] : 0;
+    }
+}
+
+void fill_bit_iarray(cumo_na_bit_iarray_t* ia, const cb200_na* a, const Loop& lp) {
+    memset(ia, 0, sizeof *ia);
+    ia->ptr = reinterpret_cast<CUMO_BIT_DIGIT*>(a->st->ptr);
+    ia->pos = (size_t)a->offset;
+    for (int i = 0; i < lp.ndim; ++i) {
+        int d = i - (lp.ndim - a->ndim);
+        ia->step[i] = (d >= 0 && a->shape[d] != 1) ? (ssize_t)a->step[d] : 0;
+    }
+}
+
+int upcast(int ta, int tb) {   // gen/def/{sfloat,dfloat,int32,int64}.rb
+    if (ta == tb) return ta;
+    if (ta == CB200_DFLOAT || tb == CB200_DFLOAT) return CB200_DFLOAT;
+    if (ta == CB200_SFLOAT || tb == CB200_SFLOAT) return CB200_SFLOAT;
+    return CB200_INT64;
+}
+
+bool is_value_type(int t) { return t >= CB200_SFLOAT && t <= CB200_INT64; }
+bool is_float_type(int t) { return t == CB200_SFLOAT || t == CB200_DFLOAT; }
+
+cb200_na* cast_to(cb200_na* a, int dtype) {
+    if (!is_value_type(a->dtype) || !is_value_type(dtype)) return (cb200_na*)fail("TypeError", "cannot cast %s to %s", kTypeName[a->dtype], kTypeName[dtype]);
+    cb200_na* out = make(dtype, a->ndim, a->shape, false);
+    if (!out) return nullptr;
+    using Fn = void (*)(cumo_na_iarray_t*, cumo_na_iarray_t*, cumo_na_indexer_t*);
+    Fn f = (Fn)sym(std::string("cumo_iter_") + kTypeName[dtype] + "_store_" + kTypeName[a->dtype] + "_kernel_launch");
+    if (!f) { cb200_na_release(out); return nullptr; }
+    Loop lp;
+    lp.ndim = a->ndim;
+    memcpy(lp.shape, a->shape, sizeof(int64_t) * a->ndim);
+    cumo_na_indexer_t ix;
+    cumo_na_iarray_t dst, src;
+    fill_indexer(&ix, lp);
+    fill_iarray(&dst, out, lp);
+    fill_iarray(&src, a, lp);
+    f(&dst, &src, &ix);
+    if (!launch_ok()) { cb200_na_release(out); return nullptr; }
+    return out;
+}
+
+// which family an operation name belongs to decides the symbol name and the signature
+enum Family { F_BINARY_S, F_MATH2, F_EWCOMP, F_POW, F_NONE };
+Family binary_family(const std::string& op, bool is_float) {
+    static const char* with_s[] = {"add", "sub", "mul", "div", "mod"};
+    for (auto s : with_s) if (op == s) return F_BINARY_S;
+    if (is_float && op == "copysign") return F_BINARY_S;
+    if (!is_float) for (auto s : {"bit_and", "bit_or", "bit_xor", "left_shift", "right_shift"}) if (op == s) return F_BINARY_S;
+    if (is_float) for (auto s : {"atan2", "hypot", "ldexp"}) if (op == s) return F_MATH2;
+    if (op == "maximum" || op == "minimum") return F_EWCOMP;
+    if (is_float && (op == "maximum_nan" || op == "minimum_nan")) return F_EWCOMP;
+    if (op == "pow") return F_POW;
+    return F_NONE;
+}
+
+bool needs_flag(const std::string& op, int dtype) {
+    if (is_float_type(dtype)) return false;
+    return op == "div" || op == "mod" || op == "reciprocal" || op == "abs";
+}
+
+// run `launch(flag_ptr)`, then apply the flag protocol: synchronise and raise
+template <typename L>
+bool with_flag(const std::string& op, int dtype, L launch) {
+    int* dev = nullptr;
+    if (needs_flag(op, dtype)) {
+        if (!tl_flag.ready()) { fail("CudaError", "cannot allocate the mapped error flag"); return false; }
+        *tl_flag.host = 0;
+        dev = tl_flag.dev;
+    }
+    launch(dev);
+    if (!launch_ok()) return false;
+    if (dev) {
+        if (!cuda_ok(cudaStreamSynchronize(cb200::current_stream()), "cudaStreamSynchronize")) return false;
+        if (*tl_flag.host) {
+            if (op == "abs") fail("ValueError", "cannot convert the minimum integer");
+            else fail("ZeroDivisionError", "divided by 0");
+            return false;
+        }
+    }
+    return true;
+}
+
+// output of an elementwise method: the in-place operand when it was marked and fits
+cb200_na* output_for(cb200_na* a, int dtype, const Loop& lp) {
+    if (a && a->inplace && a->dtype == dtype && a->ndim == lp.ndim) {
+        bool same = true;
+        for (int d = 0; d < lp.ndim; ++d) if (a->shape[d] != lp.shape[d]) same = false;
+        if (same) { a->inplace = false; return share(a); }
+    }
+    return make(dtype, lp.ndim, lp.shape, false);
+}
+
+template <typename C> C pick(double f, int64_t i);
+template <> float pick<float>(double f, int64_t) { return (float)f; }
+template <> double pick<double>(double f, int64_t) { return f; }
+template <> int32_t pick<int32_t>(double, int64_t i) { return (int32_t)i; }
+template <> int64_t pick<int64_t>(double, int64_t i) { return i; }
+
+template <typename C>
+bool call_binary_s(void* f, Family fam, cumo_na_iarray_t* a1, C sv, cumo_na_iarray_t* a3, cumo_na_indexer_t* ix, int* flag, int left) {
+    if (fam == F_BINARY_S) ((void (*)(cumo_na_iarray_t*, C, cumo_na_iarray_t*, cumo_na_indexer_t*, int*, int))f)(a1, sv, a3, ix, flag, left);
+    else if (fam == F_MATH2) ((void (*)(cumo_na_iarray_t*, cumo_na_iarray_t*, cumo_na_indexer_t*, C, int))f)(a1, a3, ix, sv, left);
+    else if (fam == F_POW) ((void (*)(cumo_na_iarray_t*, C, cumo_na_iarray_t*, cumo_na_indexer_t*, int))f)(a1, sv, a3, ix, left);
+    else return false;
+    return true;
+}
+
+template <typename C>
+void call_compare_s(void* f, cumo_na_iarray_t* a1, C sv, cumo_na_bit_iarray_t* a3, cumo_na_indexer_t* ix, int left) {
+    ((void (*)(cumo_na_iarray_t*, C, cumo_na_bit_iarray_t*, cumo_na_indexer_t*, int))f)(a1, sv, a3, ix, left);
+}
+
+std::string binary_symbol(const std::string& op, Family fam, int dtype, bool scalar) {
+    std::string t = kTypeName[dtype];
+    switch (fam) {
+    case F_BINARY_S: return "cumo_iter_" + t + "_" + op + (scalar ? "_s_kernel_launch" : "_kernel_launch");
+    case F_MATH2:    return "cumo_iter_" + t + "_math_s_" + op + (scalar ? "_s_kernel_launch" : "_kernel_launch");
+    case F_POW:      return "cumo_iter_" + t + "_pow" + (scalar ? "_s_kernel_launch" : "_kernel_launch");
+    case F_EWCOMP:   return "cumo_" + t + "_" + op + "_kernel_launch";
+    default: return "";
+    }
+}
+
+bool is_math_fn(const std::string& op) {
+    static const char* names[] = {"sqrt", "cbrt", "log", "log2", "log10", "exp", "exp2", "exp10", "sin", "cos", "tan",
+                                  "asin", "acos", "atan", "sinh", "cosh", "tanh", "asinh", "acosh", "atanh", "sinc",
+                                  "erf", "erfc", "log1p", "expm1"};
+    for (auto s : names) if (op == s) return true;
+    return false;
+}
+
+// ---- reductions ----------------------------------------------------------------------------
+struct ReducePlan {
+    int n_keep, n_red;
+    int keep[kMaxD], red[kMaxD];     // dimension numbers of `a`
+    int64_t out_shape[kMaxD];        // extents of the kept dims
+    int64_t keep_shape[kMaxD];       // result shape with keepdims
+};
+
+bool plan_reduce(const cb200_na* a, uint32_t mask, ReducePlan* rp) {
+    if (a->ndim > 0 && (mask >> a->ndim) != 0) { fail("ArgumentError", "axis out of range"); return false; }
+    if (mask == 0) mask = a->ndim >= 32 ? 0xffffffffu : ((1u << a->ndim) - 1u);
+    rp->n_keep = rp->n_red = 0;
+    for (int d = 0; d < a->ndim; ++d) {
+        if (mask & (1u << d)) { rp->red[rp->n_red++] = d; rp->keep_shape[d] = 1; }
+        else { rp->keep[rp->n_keep] = d; rp->out_shape[rp->n_keep++] = a->shape[d]; rp->keep_shape[d] = a->shape[d]; }
+    }
+    return true;
+}
+
+// cumo_na_make_reduction_arg (indexer.h:189-220) for `a` with the kept dims first
+void fill_reduction_arg(cumo_na_reduction_arg_t* arg, const cb200_na* a, const ReducePlan& rp, const cb200_na* out) {
+    memset(arg, 0, sizeof *arg);
+    arg->in.ptr = data_ptr(a);
+    arg->in_indexer.ndim = (unsigned char)a->ndim;
+    arg->in_indexer.total_size = 1;
+    int k = 0;
+    for (int i = 0; i < rp.n_keep; ++i, ++k) {
+        arg->in.step[k] = (ssize_t)a->step[rp.keep[i]];
+        arg->in_indexer.shape[k] = (size_t)a->shape[rp.keep[i]];
+    }
+    for (int i = 0; i < rp.n_red; ++i, ++k) {
+        arg->in.step[k] = (ssize_t)a->step[rp.red[i]];
+        arg->in_indexer.shape[k] = (size_t)a->shape[rp.red[i]];
+    }
+    for (int d = 0; d < a->ndim; ++d) arg->in_indexer.total_size *= arg->in_indexer.shape[d];
+    arg->out.ptr = data_ptr(out);
+    arg->out_indexer.ndim = (unsigned char)rp.n_keep;
+    arg->out_indexer.total_size = 1;
+    for (int i = 0; i < rp.n_keep; ++i) {
+        arg->out.step[i] = (ssize_t)out->step[i];
+        arg->out_indexer.shape[i] = (size_t)rp.out_shape[i];
+        arg->out_indexer.total_size *= (size_t)rp.out_shape[i];
+    }
+}
+
+void apply_keepdims(cb200_na* out, const cb200_na* a, const ReducePlan& rp, int keepdims) {
+    if (!keepdims) return;
+    out->ndim = a->ndim;
+    memcpy(out->shape, rp.keep_shape, sizeof(int64_t) * a->ndim);
+    contiguous_steps(out->dtype, out->ndim, out->shape, out->step);
+}
+
+// Host loop over the outer dims of a non-indexer ndloop (ndloop.c:1574-1613): dims are
+// ordered kept-first, neighbouring dims that every operand walks with one stride are
+// merged, the innermost dim is handed to `body(n, offsets...)` and the rest iterate here.
+struct StrideLoop {
+    int nd;
+    int64_t n[kMaxD];
+    int64_t s[3][kMaxD];
+};
+void contract(StrideLoop* L, int nops) {
+    int k = 0;
+    for (int d = 0; d < L->nd; ++d) {
+        if (L->n[d] == 1 && L->nd > 1) continue;
+        bool merge = k > 0;
+        for (int o = 0; o < nops && merge; ++o) if (L->s[o][k - 1] != L->s[o][d] * L->n[d]) merge = false;
+        if (merge) {
+            L->n[k - 1] *= L->n[d];
+            for (int o = 0; o < nops; ++o) L->s[o][k - 1] = L->s[o][d];
+        } else {
+            L->n[k] = L->n[d];
+            for (int o = 0; o < nops; ++o) L->s[o][k] = L->s[o][d];
+            ++k;
+        }
+    }
+    if (k == 0) { L->n[0] = 1; for (int o = 0; o < nops; ++o) L->s[o][0] = 0; k = 1; }
+    L->nd = k;
+}
+template <typename Body>
+void for_outer(const StrideLoop& L, int nops, Body body) {
+    int64_t outer = 1;
+    for (int d = 0; d < L.nd - 1; ++d) outer *= L.n[d];
+    for (int64_t o = 0; o < outer; ++o) {
+        int64_t off[3] = {0, 0, 0}, r = o;
+        for (int d = L.nd - 2; d >= 0; --d) {
+            int64_t i = r % L.n[d]; r /= L.n[d];
+            for (int k = 0; k < nops; ++k) off[k] += i * L.s[k][d];
+        }
+        body(off);
+    }
+}
+
+}  // namespace
+
+// =============================================================================================
+extern "C" {
+
+const char* cb200_host_error(const char** klass) {
+    if (klass) *klass = tl_class.c_str();
+    return tl_message.c_str();
+}
+
+cb200_na_t* cb200_na_new(int dtype, int ndim, const int64_t* shape) { return make(dtype, ndim, shape, false); }
+cb200_na_t* cb200_na_zeros(int dtype, int ndim, const int64_t* shape) { return make(dtype, ndim, shape, true); }
+
+cb200_na_t* cb200_na_wrap(int dtype, int ndim, const int64_t* shape, const int64_t* step, void* device_ptr, int64_t offset) {
+    if (dtype < 0 || dtype > CB200_UINT64) return (cb200_na*)fail("TypeError", "unknown dtype %d", dtype);
+    if (ndim < 0 || ndim > kMaxD) return (cb200_na*)fail("ShapeError", "ndim %d out of range", ndim);
+    cb200_na* a = new cb200_na();
+    a->dtype = dtype;
+    a->ndim = ndim;
+    for (int d = 0; d < ndim; ++d) { a->shape[d] = shape[d]; a->step[d] = step[d]; }
+    a->offset = offset;
+    a->inplace = false;
+    a->st = new Storage{(char*)device_ptr, 0, 1, false};
+    return a;
+}
+
+cb200_na_t* cb200_na_view(cb200_na_t* a, int ndim, const int64_t* shape, const int64_t* step, int64_t offset) {
+    if (ndim < 0 || ndim > kMaxD) return (cb200_na*)fail("ShapeError", "ndim %d out of range", ndim);
+    // every element of the view must lie inside the parent's buffer
+    int64_t lo = a->offset + offset, hi = lo;
+    bool empty = false;
+    for (int d = 0; d < ndim; ++d) {
+        if (shape[d] < 0) return (cb200_na*)fail("ShapeError", "negative extent");
+        if (shape[d] == 0) empty = true;
+        int64_t span = (shape[d] - 1) * step[d];
+        if (span < 0) lo += span; else hi += span;
+    }
+    if (a->st->owned && !empty) {
+        int64_t unit = a->dtype == CB200_BIT ? 1 : kElemSize[a->dtype];
+        int64_t limit = a->dtype == CB200_BIT ? (int64_t)a->st->bytes * 8 : (int64_t)a->st->bytes;
+        if (lo < 0 || hi + unit > limit) return (cb200_na*)fail("IndexError", "view reaches outside the array");
+    }
+    cb200_na* v = share(a);
+    v->ndim = ndim;
+    for (int d = 0; d < ndim; ++d) { v->shape[d] = shape[d]; v->step[d] = step[d]; }
+    v->offset = a->offset + offset;
+    return v;
+}
+
+void cb200_na_release(cb200_na_t* a) {
+    if (!a) return;
+    bool last;
+    { std::lock_guard<std::mutex> lk(g_ref_mu); last = --a->st->refs == 0; }
+    if (last) {
+        if (a->st->owned) cumo_cuda_runtime_free(a->st->ptr);
+        delete a->st;
+    }
+    delete a;
+}
+
+int cb200_na_dtype(const cb200_na_t* a) { return a->dtype; }
+int cb200_na_ndim(const cb200_na_t* a) { return a->ndim; }
+int64_t cb200_na_size(const cb200_na_t* a) { return size_of(a); }
+void cb200_na_shape(const cb200_na_t* a, int64_t* shape) { memcpy(shape, a->shape, sizeof(int64_t) * a->ndim); }
+void cb200_na_steps(const cb200_na_t* a, int64_t* step) { memcpy(step, a->step, sizeof(int64_t) * a->ndim); }
+int64_t cb200_na_offset(const cb200_na_t* a) { return a->offset; }
+void* cb200_na_base(const cb200_na_t* a) { return a->st->ptr; }
+int cb200_na_is_contiguous(const cb200_na_t* a) { return is_contiguous(a) ? 1 : 0; }
+void cb200_na_set_inplace(cb200_na_t* a, int on) { a->inplace = on != 0; }
+
+int cb200_na_store_host(cb200_na_t* a, const void* host, size_t bytes) {
+    if (!is_contiguous(a)) { fail("ValueError", "store_host needs a contiguous array"); return 1; }
+    if (a->dtype == CB200_BIT && (a->offset & 31)) { fail("ValueError", "store_host needs a word-aligned Bit array"); return 1; }
+    if (bytes != buffer_bytes(a->dtype, size_of(a))) { fail("ValueError", "store_host: %zu bytes given, %zu expected", bytes, buffer_bytes(a->dtype, size_of(a))); return 1; }
+    char* dst = a->dtype == CB200_BIT ? a->st->ptr + a->offset / 8 : data_ptr(a);
+    return cuda_ok(cudaMemcpyAsync(dst, host, bytes, cudaMemcpyHostToDevice, cb200::current_stream()), "cudaMemcpyAsync H2D") ? 0 : 1;
+}
+
+int cb200_na_read_host(cb200_na_t* a, void* host, size_t bytes) {
+    if (!is_contiguous(a)) { fail("ValueError", "read_host needs a contiguous array"); return 1; }
+    if (a->dtype == CB200_BIT && (a->offset & 31)) { fail("ValueError", "read_host needs a word-aligned Bit array"); return 1; }
+    if (bytes != buffer_bytes(a->dtype, size_of(a))) { fail("ValueError", "read_host: %zu bytes given, %zu expected", bytes, buffer_bytes(a->dtype, size_of(a))); return 1; }
+    const char* src = a->dtype == CB200_BIT ? a->st->ptr + a->offset / 8 : data_ptr(a);
+    if (!cuda_ok(cudaMemcpyAsync(host, src, bytes, cudaMemcpyDeviceToHost, cb200::current_stream()), "cudaMemcpyAsync D2H")) return 1;
+    return cuda_ok(cudaStreamSynchronize(cb200::current_stream()), "cudaStreamSynchronize") ? 0 : 1;
+}
+
+int cb200_synchronize(void) { return cuda_ok(cudaStreamSynchronize(cb200::current_stream()), "cudaStreamSynchronize") ? 0 : 1; }
+
+cb200_na_t* cb200_na_cast(cb200_na_t* a, int dtype) { return cast_to(a, dtype); }
+cb200_na_t* cb200_na_copy(cb200_na_t* a) {
+    if (a->dtype == CB200_UINT64) {   // a container type: copied as Int64 bit patterns
+        cb200_na tmp = *a; tmp.dtype = CB200_INT64;
+        cb200_na* c = cast_to(&tmp, CB200_INT64);
+        if (c) c->dtype = CB200_UINT64;
+        return c;
+    }
+    if (a->dtype == CB200_BIT) return (cb200_na*)fail("TypeError", "copy of a Bit view is not on this path");
+    return cast_to(a, a->dtype);
+}
+
+// ---- elementwise ---------------------------------------------------------------------------
+cb200_na_t* cb200_na_binary(const char* op_c, cb200_na_t* a, cb200_na_t* b) {
+    std::string op = op_c;
+    if (!is_value_type(a->dtype) || !is_value_type(b->dtype)) return (cb200_na*)fail("TypeError", "%s is not defined for %s and %s", op_c, kTypeName[a->dtype], kTypeName[b->dtype]);
+    int dtype = upcast(a->dtype, b->dtype);
+    Family fam = binary_family(op, is_float_type(dtype));
+    if (fam == F_NONE) return (cb200_na*)fail("NoMethodError", "undefined method %s for %s", op_c, kTypeName[dtype]);
+    Loop lp;
+    if (!broadcast(a, b, &lp)) return nullptr;
+    cb200_na *ca = nullptr, *cb = nullptr;
+    if (a->dtype != dtype) { ca = cast_to(a, dtype); if (!ca) return nullptr; }
+    if (b->dtype != dtype) { cb = cast_to(b, dtype); if (!cb) { cb200_na_release(ca); return nullptr; } }
+    cb200_na* x = ca ? ca : a;
+    cb200_na* y = cb ? cb : b;
+    cb200_na* out = output_for(ca ? nullptr : a, dtype, lp);
+    bool ok = out != nullptr;
+    if (ok) {
+        void* f = sym(binary_symbol(op, fam, dtype, false));
+        ok = f != nullptr;
+        if (ok) {
+            cumo_na_indexer_t ix;
+            cumo_na_iarray_t a1, a2, a3;
+            fill_indexer(&ix, lp);
+            fill_iarray(&a1, x, lp);
+            fill_iarray(&a2, y, lp);
+            fill_iarray(&a3, out, lp);
+            ok = with_flag(op, dtype, [&](int* flag) {
+                if (fam == F_BINARY_S) ((void (*)(cumo_na_iarray_t*, cumo_na_iarray_t*, cumo_na_iarray_t*, cumo_na_indexer_t*, int*))f)(&a1, &a2, &a3, &ix, flag);
+                else ((void (*)(cumo_na_iarray_t*, cumo_na_iarray_t*, cumo_na_iarray_t*, cumo_na_indexer_t*))f)(&a1, &a2, &a3, &ix);
+            });
+        }
+    }
+    cb200_na_release(ca);
+    cb200_na_release(cb);
+    if (!ok) { cb200_na_release(out); return nullptr; }
+    return out;
+}
+
+cb200_na_t* cb200_na_binary_scalar(const char* op_c, cb200_na_t* a, double sv_f, int64_t sv_i, int scalar_is_left) {
+    std::string op = op_c;
+    if (!is_value_type(a->dtype)) return (cb200_na*)fail("TypeError", "%s is not defined for %s", op_c, kTypeName[a->dtype]);
+    int dtype = a->dtype;
+    Family fam = binary_family(op, is_float_type(dtype));
+    if (fam == F_NONE || fam == F_EWCOMP) return (cb200_na*)fail("NoMethodError", "undefined scalar form of %s for %s", op_c, kTypeName[dtype]);
+    Loop lp;
+    lp.ndim = a->ndim;
+    memcpy(lp.shape, a->shape, sizeof(int64_t) * a->ndim);
+    cb200_na* out = output_for(a, dtype, lp);
+    if (!out) return nullptr;
+    void* f = sym(binary_symbol(op, fam, dtype, true));
+    bool ok = f != nullptr;
+    if (ok) {
+        cumo_na_indexer_t ix;
+        cumo_na_iarray_t a1, a3;
+        fill_indexer(&ix, lp);
+        fill_iarray(&a1, a, lp);
+        fill_iarray(&a3, out, lp);
+        ok = with_flag(op, dtype, [&](int* flag) {
+            switch (dtype) {
+            case CB200_SFLOAT: call_binary_s<float>(f, fam, &a1, pick<float>(sv_f, sv_i), &a3, &ix, flag, scalar_is_left); break;
+            case CB200_DFLOAT: call_binary_s<double>(f, fam, &a1, pick<double>(sv_f, sv_i), &a3, &ix, flag, scalar_is_left); break;
+            case CB200_INT32:  call_binary_s<int32_t>(f, fam, &a1, pick<int32_t>(sv_f, sv_i), &a3, &ix, flag, scalar_is_left); break;
+            default:           call_binary_s<int64_t>(f, fam, &a1, pick<int64_t>(sv_f, sv_i), &a3, &ix, flag, scalar_is_left); break;
+            }
+        });
+    }
+    if (!ok) { cb200_na_release(out); return nullptr; }
+    return out;
+}
+
+cb200_na_t* cb200_na_pow_int(cb200_na_t* a, int32_t exponent) {
+    if (!is_value_type(a->dtype)) return (cb200_na*)fail("TypeError", "pow is not defined for %s", kTypeName[a->dtype]);
+    Loop lp;
+    lp.ndim = a->ndim;
+    memcpy(lp.shape, a->shape, sizeof(int64_t) * a->ndim);
+    cb200_na* out = output_for(a, a->dtype, lp);
+    if (!out) return nullptr;
+    using Fn = void (*)(cumo_na_iarray_t*, int32_t, cumo_na_iarray_t*, cumo_na_indexer_t*);
+    Fn f = (Fn)sym(std::string("cumo_iter_") + kTypeName[a->dtype] + "_pow_int32_s_kernel_launch");
+    if (!f) { cb200_na_release(out); return nullptr; }
+    cumo_na_indexer_t ix;
+    cumo_na_iarray_t a1, a3;
+    fill_indexer(&ix, lp);
+    fill_iarray(&a1, a, lp);
+    fill_iarray(&a3, out, lp);
+    f(&a1, exponent, &a3, &ix);
+    if (!launch_ok()) { cb200_na_release(out); return nullptr; }
+    return out;
+}
+
+cb200_na_t* cb200_na_unary(const char* op_c, cb200_na_t* a) {
+    std::string op = op_c;
+    if (!is_value_type(a->dtype)) return (cb200_na*)fail("TypeError", "%s is not defined for %s", op_c, kTypeName[a->dtype]);
+    const bool fl = is_float_type(a->dtype);
+    std::string t = kTypeName[a->dtype];
+    std::string name;
+    bool has_flag_arg = true;
+    if (is_math_fn(op)) {
+        if (!fl) return (cb200_na*)fail("NoMethodError", "NMath.%s needs a float array", op_c);
+        name = "cumo_iter_" + t + "_math_s_" + op + "_kernel_launch";
+        has_flag_arg = false;
+    } else if (op == "minus" || op == "reciprocal" || op == "sign" || op == "square" || op == "abs" ||
+               (fl && (op == "floor" || op == "round" || op == "ceil" || op == "trunc" || op == "rint")) ||
+               (!fl && op == "bit_not")) {
+        name = "cumo_iter_" + t + "_" + op + "_kernel_launch";
+    } else if (!fl && (op == "floor" || op == "round" || op == "ceil" || op == "trunc" || op == "rint")) {
+        return share(a);   // aliases of `view` for the integer types (gen/spec.rb:248-254)
+    } else {
+        return (cb200_na*)fail("NoMethodError", "undefined method %s for %s", op_c, t.c_str());
+    }
+    Loop lp;
+    lp.ndim = a->ndim;
+    memcpy(lp.shape, a->shape, sizeof(int64_t) * a->ndim);
+    cb200_na* out = output_for(a, a->dtype, lp);
+    if (!out) return nullptr;
+    void* f = sym(name);
+    bool ok = f != nullptr;
+    if (ok) {
+        cumo_na_indexer_t ix;
+        cumo_na_iarray_t a1, a2;
+        fill_indexer(&ix, lp);
+        fill_iarray(&a1, a, lp);
+        fill_iarray(&a2, out, lp);
+        ok = with_flag(op, a->dtype, [&](int* flag) {
+            if (has_flag_arg) ((void (*)(cumo_na_iarray_t*, cumo_na_iarray_t*, cumo_na_indexer_t*, int*))f)(&a1, &a2, &ix, flag);
+            else ((void (*)(cumo_na_iarray_t*, cumo_na_iarray_t*, cumo_na_indexer_t*))f)(&a1, &a2, &ix);
+        });
+    }
+    if (!ok) { cb200_na_release(out); return nullptr; }
+    return out;
+}
+
+static cb200_na* new_bit_output(const Loop& lp) {
+    cb200_na* out = make(CB200_BIT, lp.ndim, lp.shape, false);
+    if (!out) return nullptr;
+    // bits past the end of the last word are padding; give them a defined value
+    if (out->st->bytes >= 4)
+        cudaMemsetAsync(out->st->ptr + out->st->bytes - 4, 0, 4, cb200::current_stream());
+    return out;
+}
+
+static bool is_cond_unary(const std::string& op) {
+    for (auto s : {"isnan", "isinf", "isposinf", "isneginf", "isfinite", "signbit"}) if (op == s) return true;
+    return false;
+}
+static bool is_cond_binary(const std::string& op, bool fl) {
+    for (auto s : {"eq", "ne", "gt", "ge", "lt", "le"}) if (op == s) return true;
+    return fl && op == "nearly_eq";
+}
+
+cb200_na_t* cb200_na_compare(const char* op_c, cb200_na_t* a, cb200_na_t* b) {
+    std::string op = op_c;
+    if (!is_value_type(a->dtype) || (b && !is_value_type(b->dtype))) return (cb200_na*)fail("TypeError", "%s needs numeric arrays", op_c);
+    if (!b) {
+        if (!is_float_type(a->dtype) || !is_cond_unary(op)) return (cb200_na*)fail("NoMethodError", "undefined method %s for %s", op_c, kTypeName[a->dtype]);
+        Loop lp;
+        lp.ndim = a->ndim;
+        memcpy(lp.shape, a->shape, sizeof(int64_t) * a->ndim);
+        cb200_na* out = new_bit_output(lp);
+        if (!out) return nullptr;
+        using Fn = void (*)(cumo_na_iarray_t*, cumo_na_bit_iarray_t*, cumo_na_indexer_t*);
+        Fn f = (Fn)sym(std::string("cumo_iter_") + kTypeName[a->dtype] + "_" + op + "_kernel_launch");
+        if (!f) { cb200_na_release(out); return nullptr; }
+        cumo_na_indexer_t ix;
+        cumo_na_iarray_t a1;
+        cumo_na_bit_iarray_t a2;
+        fill_indexer(&ix, lp);
+        fill_iarray(&a1, a, lp);
+        fill_bit_iarray(&a2, out, lp);
+        f(&a1, &a2, &ix);
+        if (!launch_ok()) { cb200_na_release(out); return nullptr; }
+        return out;
+    }
+    int dtype = upcast(a->dtype, b->dtype);
+    if (!is_cond_binary(op, is_float_type(dtype))) {
+        if (op == "nearly_eq") op = "eq";    // integer types alias nearly_eq to eq (gen/spec.rb:233-236)
+        else return (cb200_na*)fail("NoMethodError", "undefined method %s for %s", op_c, kTypeName[dtype]);
+    }
+    Loop lp;
+    if (!broadcast(a, b, &lp)) return nullptr;
+    cb200_na *ca = nullptr, *cb = nullptr;
+    if (a->dtype != dtype) { ca = cast_to(a, dtype); if (!ca) return nullptr; }
+    if (b->dtype != dtype) { cb = cast_to(b, dtype); if (!cb) { cb200_na_release(ca); return nullptr; } }
+    cb200_na* out = new_bit_output(lp);
+    bool ok = out != nullptr;
+    if (ok) {
+        using Fn = void (*)(cumo_na_iarray_t*, cumo_na_iarray_t*, cumo_na_bit_iarray_t*, cumo_na_indexer_t*);
+        Fn f = (Fn)sym(std::string("cumo_iter_") + kTypeName[dtype] + "_" + op + "_kernel_launch");
+        ok = f != nullptr;
+        if (ok) {
+            cumo_na_indexer_t ix;
+            cumo_na_iarray_t a1, a2;
+            cumo_na_bit_iarray_t a3;
+            fill_indexer(&ix, lp);
+            fill_iarray(&a1, ca ? ca : a, lp);
+            fill_iarray(&a2, cb ? cb : b, lp);
+            fill_bit_iarray(&a3, out, lp);
+            f(&a1, &a2, &a3, &ix);
+            ok = launch_ok();
+        }
+    }
+    cb200_na_release(ca);
+    cb200_na_release(cb);
+    if (!ok) { cb200_na_release(out); return nullptr; }
+    return out;
+}
+
+cb200_na_t* cb200_na_compare_scalar(const char* op_c, cb200_na_t* a, double sv_f, int64_t sv_i, int scalar_is_left) {
+    std::string op = op_c;
+    if (!is_value_type(a->dtype)) return (cb200_na*)fail("TypeError", "%s needs a numeric array", op_c);
+    if (!is_cond_binary(op, is_float_type(a->dtype))) {
+        if (op == "nearly_eq") op = "eq";
+        else return (cb200_na*)fail("NoMethodError", "undefined method %s for %s", op_c, kTypeName[a->dtype]);
+    }
+    Loop lp;
+    lp.ndim = a->ndim;
+    memcpy(lp.shape, a->shape, sizeof(int64_t) * a->ndim);
+    cb200_na* out = new_bit_output(lp);
+    if (!out) return nullptr;
+    void* f = sym(std::string("cumo_iter_") + kTypeName[a->dtype] + "_" + op + "_s_kernel_launch");
+    if (!f) { cb200_na_release(out); return nullptr; }
+    cumo_na_indexer_t ix;
+    cumo_na_iarray_t a1;
+    cumo_na_bit_iarray_t a3;
+    fill_indexer(&ix, lp);
+    fill_iarray(&a1, a, lp);
+    fill_bit_iarray(&a3, out, lp);
+    switch (a->dtype) {
+    case CB200_SFLOAT: call_compare_s<float>(f, &a1, pick<float>(sv_f, sv_i), &a3, &ix, scalar_is_left); break;
+    case CB200_DFLOAT: call_compare_s<double>(f, &a1, pick<double>(sv_f, sv_i), &a3, &ix, scalar_is_left); break;
+    case CB200_INT32:  call_compare_s<int32_t>(f, &a1, pick<int32_t>(sv_f, sv_i), &a3, &ix, scalar_is_left); break;
+    default:           call_compare_s<int64_t>(f, &a1, pick<int64_t>(sv_f, sv_i), &a3, &ix, scalar_is_left); break;
+    }
+    if (!launch_ok()) { cb200_na_release(out); return nullptr; }
+    return out;
+}
+
+// ---- reductions -----------------------------------------------------------------------------
+cb200_na_t* cb200_na_reduce(const char* op_c, cb200_na_t* a, uint32_t axis_mask, int keepdims, int nan) {
+    std::string op = op_c;
+    if (!is_value_type(a->dtype)) return (cb200_na*)fail("TypeError", "%s is not defined for %s", op_c, kTypeName[a->dtype]);
+    const bool fl = is_float_type(a->dtype);
+    const bool index_op = op == "max_index" || op == "min_index";
+    const bool arg_op = op == "argmax" || op == "argmin";
+    int out_dtype = a->dtype;
+    if (op == "sum" || op == "prod") { if (!fl) out_dtype = CB200_INT64; }
+    else if (op == "mean" || op == "var" || op == "stddev" || op == "rms") { if (!fl) return (cb200_na*)fail("NoMethodError", "undefined method %s for %s", op_c, kTypeName[a->dtype]); }
+    else if (op == "kahan_sum") { if (a->dtype != CB200_DFLOAT) return (cb200_na*)fail("NoMethodError", "undefined method kahan_sum for %s", kTypeName[a->dtype]); }
+    else if (op == "min" || op == "max" || op == "ptp") {}
+    else if (index_op || arg_op) { out_dtype = (uint64_t)size_of(a) > 0xffffffffull ? CB200_INT64 : CB200_INT32; }
+    else return (cb200_na*)fail("NoMethodError", "undefined method %s", op_c);
+    if (size_of(a) == 0 && op != "sum") return (cb200_na*)fail("ShapeError", "cannot reduce an empty array with %s", op_c);
+
+    ReducePlan rp;
+    if (!plan_reduce(a, axis_mask, &rp)) return nullptr;
+    // the index a (max|min)_index kernel answers counts along the operand's memory, so a
+    // non-contiguous operand is copied first (accum_index.c:121-129)
+    cb200_na* copy = nullptr;
+    if (index_op && !is_contiguous(a)) { copy = cast_to(a, a->dtype); if (!copy) return nullptr; }
+    const cb200_na* in = copy ? copy : a;
+    cb200_na* out = make(out_dtype, rp.n_keep, rp.out_shape, size_of(a) == 0);
+    if (!out) { cb200_na_release(copy); return nullptr; }
+    bool ok = true;
+    if (size_of(a) > 0) {
+        std::string name = std::string("cumo_") + kTypeName[a->dtype] + "_" + op + ((nan && fl) ? "_nan" : "");
+        if (index_op || arg_op) name += out_dtype == CB200_INT64 ? "_int64" : "_int32";
+        name += "_kernel_launch";
+        using Fn = void (*)(cumo_na_reduction_arg_t*);
+        Fn f = (Fn)sym(name);
+        ok = f != nullptr;
+        if (ok) {
+            cumo_na_reduction_arg_t arg;
+            fill_reduction_arg(&arg, in, rp, out);
+            f(&arg);
+            ok = launch_ok();
+        }
+    }
+    cb200_na_release(copy);
+    if (!ok) { cb200_na_release(out); return nullptr; }
+    apply_keepdims(out, a, rp, keepdims);
+    return out;
+}
+
+int cb200_na_minmax(cb200_na_t* a, uint32_t axis_mask, int keepdims, int nan, cb200_na_t** out_min, cb200_na_t** out_max) {
+    if (!is_value_type(a->dtype)) { fail("TypeError", "minmax is not defined for %s", kTypeName[a->dtype]); return 1; }
+    if (size_of(a) == 0) { fail("ShapeError", "cannot reduce an empty array with minmax"); return 1; }
+    ReducePlan rp;
+    if (!plan_reduce(a, axis_mask, &rp)) return 1;
+    cb200_na* o1 = make(a->dtype, rp.n_keep, rp.out_shape, false);
+    cb200_na* o2 = o1 ? make(a->dtype, rp.n_keep, rp.out_shape, false) : nullptr;
+    if (!o2) { cb200_na_release(o1); return 1; }
+    using Fn = void (*)(cumo_na_reduction_arg_t*, cumo_na_iarray_t*);
+    Fn f = (Fn)sym(std::string("cumo_") + kTypeName[a->dtype] + "_minmax" + ((nan && is_float_type(a->dtype)) ? "_nan" : "") + "_kernel_launch");
+    bool ok = f != nullptr;
+    if (ok) {
+        cumo_na_reduction_arg_t arg;
+        fill_reduction_arg(&arg, a, rp, o1);
+        cumo_na_iarray_t out2;
+        memset(&out2, 0, sizeof out2);
+        out2.ptr = data_ptr(o2);
+        for (int i = 0; i < rp.n_keep; ++i) out2.step[i] = (ssize_t)o2->step[i];
+        f(&arg, &out2);
+        ok = launch_ok();
+    }
+    if (!ok) { cb200_na_release(o1); cb200_na_release(o2); return 1; }
+    apply_keepdims(o1, a, rp, keepdims);
+    apply_keepdims(o2, a, rp, keepdims);
+    *out_min = o1;
+    *out_max = o2;
+    return 0;
+}
+
+cb200_na_t* cb200_na_count(cb200_na_t* a, uint32_t axis_mask, int keepdims, int want_false) {
+    if (a->dtype != CB200_BIT) return (cb200_na*)fail("TypeError", "count_true needs a Bit array");
+    ReducePlan rp;
+    if (!plan_reduce(a, axis_mask, &rp)) return nullptr;
+    cb200_na* out = make(CB200_UINT64, rp.n_keep, rp.out_shape, true);   // the `init` argument: filled with 0
+    if (!out) return nullptr;
+    if (size_of(a) > 0) {
+        StrideLoop L;
+        L.nd = a->ndim;
+        int k = 0;
+        for (int i = 0; i < rp.n_keep; ++i, ++k) { L.n[k] = a->shape[rp.keep[i]]; L.s[0][k] = a->step[rp.keep[i]]; L.s[1][k] = out->step[i]; }
+        for (int i = 0; i < rp.n_red; ++i, ++k) { L.n[k] = a->shape[rp.red[i]]; L.s[0][k] = a->step[rp.red[i]]; L.s[1][k] = 0; }
+        if (L.nd == 0) { L.nd = 1; L.n[0] = 1; L.s[0][0] = L.s[1][0] = 0; }
+        contract(&L, 2);
+        const char* nm = want_false ? "count_false" : "count_true";
+        using FnS = void (*)(size_t, char*, CUMO_BIT_DIGIT*, ssize_t, uint64_t);
+        using FnSS = void (*)(size_t, char*, CUMO_BIT_DIGIT*, ssize_t, ssize_t, uint64_t);
+        FnS fs = (FnS)sym(std::string("cumo_iter_bit_") + nm + "_stride_kernel_launch");
+        FnSS fss = (FnSS)sym(std::string("cumo_iter_bit_") + nm + "_stride_stride_kernel_launch");
+        if (!fs || !fss) { cb200_na_release(out); return nullptr; }
+        const int in = L.nd - 1;
+        CUMO_BIT_DIGIT* words = reinterpret_cast<CUMO_BIT_DIGIT*>(a->st->ptr);
+        for_outer(L, 2, [&](const int64_t* off) {
+            size_t p1 = (size_t)(a->offset + off[0]);
+            char* p2 = data_ptr(out) + off[1];
+            if (L.s[1][in] == 0) fs(p1, p2, words, (ssize_t)L.s[0][in], (uint64_t)L.n[in]);
+            else fss(p1, p2, words, (ssize_t)L.s[0][in], (ssize_t)L.s[1][in], (uint64_t)L.n[in]);
+        });
+        if (!launch_ok()) { cb200_na_release(out); return nullptr; }
+    }
+    apply_keepdims(out, a, rp, keepdims);
+    return out;
+}
+
+cb200_na_t* cb200_na_mulsum(cb200_na_t* a, cb200_na_t* b, uint32_t axis_mask, int keepdims, int nan) {
+    if (!is_value_type(a->dtype) || !is_value_type(b->dtype)) return (cb200_na*)fail("TypeError", "mulsum needs numeric arrays");
+    int dtype = upcast(a->dtype, b->dtype);
+    Loop lp;
+    if (!broadcast(a, b, &lp)) return nullptr;
+    cb200_na *ca = nullptr, *cb = nullptr;
+    if (a->dtype != dtype) { ca = cast_to(a, dtype); if (!ca) return nullptr; }
+    if (b->dtype != dtype) { cb = cast_to(b, dtype); if (!cb) { cb200_na_release(ca); return nullptr; } }
+    const cb200_na* x = ca ? ca : a;
+    const cb200_na* y = cb ? cb : b;
+    // reduce plan over the broadcast loop shape
+    cb200_na shape_only;
+    shape_only.ndim = lp.ndim;
+    memcpy(shape_only.shape, lp.shape, sizeof(int64_t) * lp.ndim);
+    ReducePlan rp;
+    cb200_na* out = nullptr;
+    bool ok = plan_reduce(&shape_only, axis_mask, &rp);
+    if (ok) { out = make(dtype, rp.n_keep, rp.out_shape, true); ok = out != nullptr; }
+    if (ok) {
+        cumo_na_iarray_t sx, sy;
+        fill_iarray(&sx, x, lp);
+        fill_iarray(&sy, y, lp);
+        StrideLoop L;
+        L.nd = lp.ndim;
+        int k = 0;
+        for (int i = 0; i < rp.n_keep; ++i, ++k) { L.n[k] = lp.shape[rp.keep[i]]; L.s[0][k] = sx.step[rp.keep[i]]; L.s[1][k] = sy.step[rp.keep[i]]; L.s[2][k] = out->step[i]; }
+        for (int i = 0; i < rp.n_red; ++i, ++k) { L.n[k] = lp.shape[rp.red[i]]; L.s[0][k] = sx.step[rp.red[i]]; L.s[1][k] = sy.step[rp.red[i]]; L.s[2][k] = 0; }
+        if (L.nd == 0) { L.nd = 1; L.n[0] = 1; L.s[0][0] = L.s[1][0] = L.s[2][0] = 0; }
+        contract(&L, 3);
+        std::string base = std::string("cumo_") + kTypeName[dtype] + "_mulsum" + ((nan && is_float_type(dtype)) ? "_nan" : "");
+        using FnR = void (*)(char*, char*, char*, ssize_t, ssize_t, uint64_t);
+        using FnE = void (*)(char*, char*, char*, ssize_t, ssize_t, ssize_t, uint64_t);
+        FnR fr = (FnR)sym(base + "_reduce_kernel_launch");
+        FnE fe = (FnE)sym(base + "_kernel_launch");
+        ok = fr && fe;
+        if (ok) {
+            const int in = L.nd - 1;
+            for_outer(L, 3, [&](const int64_t* off) {
+                char* p1 = sx.ptr + off[0];
+                char* p2 = sy.ptr + off[1];
+                char* p3 = data_ptr(out) + off[2];
+                if (L.s[2][in] == 0) fr(p1, p2, p3, (ssize_t)L.s[0][in], (ssize_t)L.s[1][in], (uint64_t)L.n[in]);
+                else fe(p1, p2, p3, (ssize_t)L.s[0][in], (ssize_t)L.s[1][in], (ssize_t)L.s[2][in], (uint64_t)L.n[in]);
+            });
+            ok = launch_ok();
+        }
+    }
+    cb200_na_release(ca);
+    cb200_na_release(cb);
+    if (!ok) { cb200_na_release(out); return nullptr; }
+    apply_keepdims(out, &shape_only, rp, keepdims);
+    return out;
+}
+
+}  // extern "C"

@@ -1,0 +1,256 @@
+/*
+ * cumo_b200.h -- the C ABI of libcumo_b200: hand-written sm_100a kernels behind
+ * the kernel-launch entry points of Cumo::NArray's data-parallel core.
+ *
+ * Every `cumo_..._kernel_launch` function declared here has the name, argument
+ * list and meaning of the function of the same name that the reference's
+ * generated type files declare on their host side and define in their `.cu`
+ * half.  The comment above each group names the reference template that
+ * declares it (paths are relative to the reference project root).  The host
+ * code of the Ruby extension (ndloop, the generated `iter_*` functions) calls
+ * these with descriptors that live on its stack; data pointers inside the
+ * descriptors must be device-accessible.
+ *
+ * Conventions shared by all entry points (reference: ext/cumo/include/cumo/
+ * template_kernel.h:83-90, ext/cumo/cuda/runtime.c:16-69):
+ *   - return type is void; after each launch the function calls
+ *     cumo_cuda_runtime_check_kernel_launch(), which the host program owns;
+ *   - scratch memory is taken from cumo_cuda_runtime_malloc() and given back
+ *     with cumo_cuda_runtime_free() before the function returns (stream-ordered
+ *     reuse is safe because all work is issued on one stream);
+ *   - kernels are launched asynchronously on the legacy default stream unless
+ *     cb200_set_stream() chose another one for the calling thread;
+ *   - data-dependent errors (integer division by zero, abs of the minimum
+ *     integer) store 1 through the caller's `int*` flag, which must be
+ *     device-writable (mapped pinned host memory in the reference), and skip
+ *     the element.  Nothing ever traps.
+ */
+#ifndef CUMO_B200_H
+#define CUMO_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+#include <sys/types.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* ---- descriptor layouts (ABI; reference: ext/cumo/include/cumo/indexer.h:16-68,
+ *      ext/cumo/include/cumo/narray_kernel.h CUMO_NA_MAX_DIMENSION) ---- */
+#ifndef CUMO_NA_MAX_DIMENSION
+#define CUMO_NA_MAX_DIMENSION 12
+#endif
+#ifndef CUMO_BIT_DIGIT
+#define CUMO_BIT_DIGIT unsigned int
+#endif
+
+#ifndef CUMO_INDEXER_H /* the reference's own header defines the same types */
+typedef struct {
+    unsigned char ndim;                      /* number of dimensions            */
+    size_t total_size;                       /* number of elements              */
+    size_t shape[CUMO_NA_MAX_DIMENSION];     /* extent of each dimension        */
+    uint64_t index[CUMO_NA_MAX_DIMENSION];   /* scratch of the reference kernels; ignored here */
+    uint64_t raw_index;                      /* idem                            */
+} cumo_na_indexer_t;
+
+typedef struct {
+    char* ptr;                               /* first element (view offset applied) */
+    ssize_t step[CUMO_NA_MAX_DIMENSION];     /* BYTE step per dimension; 0 = broadcast; may be negative */
+} cumo_na_iarray_t;
+
+typedef struct {
+    CUMO_BIT_DIGIT* ptr;                     /* first 32-bit word of the Bit array */
+    size_t pos;                              /* BIT position of the first element  */
+    ssize_t step[CUMO_NA_MAX_DIMENSION];     /* BIT step per dimension             */
+} cumo_na_bit_iarray_t;
+
+typedef struct {
+    cumo_na_iarray_t in;                     /* reduce dimensions are the LAST dims of `in` */
+    cumo_na_iarray_t out;                    /* steps for the leading out_indexer.ndim dims */
+    cumo_na_indexer_t in_indexer;
+    cumo_na_indexer_t out_indexer;
+} cumo_na_reduction_arg_t;
+#endif
+
+/* ---- callbacks owned by the host program (reference: template_kernel.h:83-90).
+ * libcumo_b200 carries weak default definitions (a per-device caching pool over
+ * cudaMalloc and an error latch read by cb200_last_error) so that it also
+ * works standalone; inside cumo.so the extension's own strong definitions win. */
+void  cumo_cuda_runtime_check_kernel_launch(void);
+char* cumo_cuda_runtime_malloc(size_t size);
+void  cumo_cuda_runtime_free(char* ptr);
+
+/* ---- library-level helpers (no counterpart in the reference) ---- */
+/* Stream used by the calling thread's launches; NULL = legacy default stream. */
+void  cb200_set_stream(void* cuda_stream);
+void* cb200_get_stream(void);
+/* Error latch of the default check_kernel_launch: 0 = ok, else the cudaError_t
+ * value; the message is valid until the next call on this thread.  Reading
+ * clears the latch. */
+int   cb200_last_error(const char** message);
+/* Number of kernels this library has launched in this process. */
+uint64_t cb200_launch_count(void);
+/* Bytes held by / handed out from the default scratch pool on the current device. */
+size_t cb200_pool_total_bytes(void);
+size_t cb200_pool_used_bytes(void);
+void   cb200_pool_free_all_blocks(void);
+const char* cb200_version(void);
+
+/* =====================================================================
+ * Per-dtype entry points.  T is one of sfloat, dfloat, int32, int64 and
+ * C the C element type (float, double, int32_t, int64_t).
+ * ===================================================================== */
+
+/* binary arithmetic, reference: gen/tmpl/binary.c:12-15, binary_kernel.cu:69-81.
+ * z = x op y; `_s` carries a host numeric by value, on the left when
+ * scalar_is_left != 0.  Integer div/mod by zero sets *divzero. */
+#define CB200_DECL_BINARY(T, C, op) \
+    void cumo_iter_##T##_##op##_kernel_launch(cumo_na_iarray_t* a1, cumo_na_iarray_t* a2, cumo_na_iarray_t* a3, cumo_na_indexer_t* indexer, int* divzero);
+#define CB200_DECL_BINARY_S(T, C, op) \
+    CB200_DECL_BINARY(T, C, op) \
+    void cumo_iter_##T##_##op##_s_kernel_launch(cumo_na_iarray_t* a1, C sv, cumo_na_iarray_t* a3, cumo_na_indexer_t* indexer, int* divzero, int scalar_is_left);
+
+/* unary arithmetic, reference: gen/tmpl/unary.c:3, unary_kernel.cu:28-42.
+ * Integer reciprocal of zero sets *divzero. */
+#define CB200_DECL_UNARY(T, C, op) \
+    void cumo_iter_##T##_##op##_kernel_launch(cumo_na_iarray_t* a1, cumo_na_iarray_t* a2, cumo_na_indexer_t* indexer, int* divzero);
+
+/* abs, reference: gen/tmpl/unary2.c:3, unary2_kernel.cu:26-38.  abs of the
+ * minimum signed integer sets *intmin. */
+#define CB200_DECL_ABS(T, C) \
+    void cumo_iter_##T##_abs_kernel_launch(cumo_na_iarray_t* a1, cumo_na_iarray_t* a2, cumo_na_indexer_t* indexer, int* intmin);
+
+/* NMath one-argument functions, reference: gen/tmpl/unary_s.c:2, unary_s_kernel.cu:14-28 */
+#define CB200_DECL_MATH(T, C, fn) \
+    void cumo_iter_##T##_math_s_##fn##_kernel_launch(cumo_na_iarray_t* a1, cumo_na_iarray_t* a2, cumo_na_indexer_t* indexer);
+
+/* NMath two-argument functions, reference: gen/tmpl/binary_s.c:2-3, binary_s_kernel.cu:38-51 */
+#define CB200_DECL_MATH2(T, C, fn) \
+    void cumo_iter_##T##_math_s_##fn##_kernel_launch(cumo_na_iarray_t* a1, cumo_na_iarray_t* a2, cumo_na_iarray_t* a3, cumo_na_indexer_t* indexer); \
+    void cumo_iter_##T##_math_s_##fn##_s_kernel_launch(cumo_na_iarray_t* a1, cumo_na_iarray_t* a3, cumo_na_indexer_t* indexer, C sv, int scalar_is_left);
+
+/* comparisons into a Bit array, reference: gen/tmpl/cond_binary.c:2-3, cond_binary_kernel.cu:41-53 */
+#define CB200_DECL_COND(T, C, op) \
+    void cumo_iter_##T##_##op##_kernel_launch(cumo_na_iarray_t* a1, cumo_na_iarray_t* a2, cumo_na_bit_iarray_t* a3, cumo_na_indexer_t* indexer); \
+    void cumo_iter_##T##_##op##_s_kernel_launch(cumo_na_iarray_t* a1, C sv, cumo_na_bit_iarray_t* a3, cumo_na_indexer_t* indexer, int scalar_is_left);
+
+/* float classification into a Bit array, reference: gen/tmpl/cond_unary.c:2, cond_unary_kernel.cu:15-29 */
+#define CB200_DECL_COND_UNARY(T, C, op) \
+    void cumo_iter_##T##_##op##_kernel_launch(cumo_na_iarray_t* a1, cumo_na_bit_iarray_t* a2, cumo_na_indexer_t* indexer);
+
+/* power, reference: gen/tmpl/pow.c:2-6, pow_kernel.cu:54-106.  The int32 forms
+ * take an Int32 exponent (array or host numeric) and multiply repeatedly. */
+#define CB200_DECL_POW(T, C) \
+    void cumo_iter_##T##_pow_kernel_launch(cumo_na_iarray_t* a1, cumo_na_iarray_t* a2, cumo_na_iarray_t* a3, cumo_na_indexer_t* indexer); \
+    void cumo_iter_##T##_pow_int32_kernel_launch(cumo_na_iarray_t* a1, cumo_na_iarray_t* a2, cumo_na_iarray_t* a3, cumo_na_indexer_t* indexer); \
+    void cumo_iter_##T##_pow_s_kernel_launch(cumo_na_iarray_t* a1, C sv, cumo_na_iarray_t* a3, cumo_na_indexer_t* indexer, int scalar_is_left); \
+    void cumo_iter_##T##_pow_int32_s_left_kernel_launch(C sv_base, cumo_na_iarray_t* a2, cumo_na_iarray_t* a3, cumo_na_indexer_t* indexer); \
+    void cumo_iter_##T##_pow_int32_s_kernel_launch(cumo_na_iarray_t* a1, int32_t sv, cumo_na_iarray_t* a3, cumo_na_indexer_t* indexer);
+
+/* elementwise maximum/minimum, reference: gen/tmpl/ewcomp.c:19, ewcomp_kernel.cu:16-32 */
+#define CB200_DECL_EWCOMP(T, C, op) \
+    void cumo_##T##_##op##_kernel_launch(cumo_na_iarray_t* a1, cumo_na_iarray_t* a2, cumo_na_iarray_t* a3, cumo_na_indexer_t* indexer);
+
+/* value reductions, reference: gen/tmpl/accum.c:6-9, real_accum_kernel.cu:166-226,
+ * float_accum_kernel.cu:155-206.  Integer sum/prod write int64_t. */
+#define CB200_DECL_ACCUM(T, C, op) \
+    void cumo_##T##_##op##_kernel_launch(cumo_na_reduction_arg_t* arg);
+
+/* minmax, reference: gen/tmpl/minmax.c:2-5, real_accum_kernel.cu:191-194 */
+#define CB200_DECL_MINMAX(T, C, sfx) \
+    void cumo_##T##_minmax##sfx##_kernel_launch(cumo_na_reduction_arg_t* arg, cumo_na_iarray_t* out2);
+
+/* index reductions, reference: gen/tmpl/accum_index.c:5 (max_index/min_index: flat
+ * element offset from arg->in.ptr) and gen/tmpl/accum_arg.c:5 (argmax/argmin: index
+ * along the reduced axes); accum_index_kernel.cu:121-144, accum_arg_kernel.cu:121-144.
+ * The output element type is int32_t or int64_t as the name says. */
+#define CB200_DECL_ACCUM_IDX(T, C, op) \
+    void cumo_##T##_##op##_int32_kernel_launch(cumo_na_reduction_arg_t* arg); \
+    void cumo_##T##_##op##_int64_kernel_launch(cumo_na_reduction_arg_t* arg);
+
+/* mulsum, reference: gen/tmpl/accum_binary.c:4-5, accum_binary_kernel.cu:69-92.
+ * `_reduce_`: *p3 += sum_i x[i]*y[i];  plain: p3[i] += x[i]*y[i] (all steps in bytes). */
+#define CB200_DECL_MULSUM(T, C, sfx) \
+    void cumo_##T##_mulsum##sfx##_reduce_kernel_launch(char* p1, char* p2, char* p3, ssize_t s1, ssize_t s2, uint64_t n); \
+    void cumo_##T##_mulsum##sfx##_kernel_launch(char* p1, char* p2, char* p3, ssize_t s1, ssize_t s2, ssize_t s3, uint64_t n);
+
+/* store / cast from another element type (also the plain strided copy when the types
+ * match), reference: gen/tmpl/store_from.c:2, store_from_kernel.cu:38-53.  NOTE the
+ * argument order: a1 is the DESTINATION, a2 the source. */
+#define CB200_DECL_STORE(T, F) \
+    void cumo_iter_##T##_store_##F##_kernel_launch(cumo_na_iarray_t* a1, cumo_na_iarray_t* a2, cumo_na_indexer_t* indexer);
+
+#define CB200_DECL_COMMON(T, C) \
+    CB200_DECL_STORE(T, sfloat) CB200_DECL_STORE(T, dfloat) CB200_DECL_STORE(T, int32) CB200_DECL_STORE(T, int64) \
+    CB200_DECL_BINARY_S(T, C, add) CB200_DECL_BINARY_S(T, C, sub) CB200_DECL_BINARY_S(T, C, mul) \
+    CB200_DECL_BINARY_S(T, C, div) CB200_DECL_BINARY_S(T, C, mod) \
+    CB200_DECL_UNARY(T, C, minus) CB200_DECL_UNARY(T, C, reciprocal) CB200_DECL_UNARY(T, C, sign) CB200_DECL_UNARY(T, C, square) \
+    CB200_DECL_ABS(T, C) CB200_DECL_POW(T, C) \
+    CB200_DECL_COND(T, C, eq) CB200_DECL_COND(T, C, ne) CB200_DECL_COND(T, C, gt) CB200_DECL_COND(T, C, ge) \
+    CB200_DECL_COND(T, C, lt) CB200_DECL_COND(T, C, le) \
+    CB200_DECL_EWCOMP(T, C, maximum) CB200_DECL_EWCOMP(T, C, minimum) \
+    CB200_DECL_ACCUM(T, C, sum) CB200_DECL_ACCUM(T, C, prod) CB200_DECL_ACCUM(T, C, min) CB200_DECL_ACCUM(T, C, max) CB200_DECL_ACCUM(T, C, ptp) \
+    CB200_DECL_MINMAX(T, C, ) \
+    CB200_DECL_ACCUM_IDX(T, C, max_index) CB200_DECL_ACCUM_IDX(T, C, min_index) \
+    CB200_DECL_ACCUM_IDX(T, C, argmax) CB200_DECL_ACCUM_IDX(T, C, argmin) \
+    CB200_DECL_MULSUM(T, C, )
+
+#define CB200_DECL_FLOAT(T, C) \
+    CB200_DECL_COMMON(T, C) \
+    CB200_DECL_BINARY_S(T, C, copysign) \
+    CB200_DECL_UNARY(T, C, floor) CB200_DECL_UNARY(T, C, round) CB200_DECL_UNARY(T, C, ceil) CB200_DECL_UNARY(T, C, trunc) CB200_DECL_UNARY(T, C, rint) \
+    CB200_DECL_COND(T, C, nearly_eq) \
+    CB200_DECL_COND_UNARY(T, C, isnan) CB200_DECL_COND_UNARY(T, C, isinf) CB200_DECL_COND_UNARY(T, C, isposinf) \
+    CB200_DECL_COND_UNARY(T, C, isneginf) CB200_DECL_COND_UNARY(T, C, isfinite) CB200_DECL_COND_UNARY(T, C, signbit) \
+    CB200_DECL_MATH(T, C, sqrt) CB200_DECL_MATH(T, C, cbrt) CB200_DECL_MATH(T, C, log) CB200_DECL_MATH(T, C, log2) \
+    CB200_DECL_MATH(T, C, log10) CB200_DECL_MATH(T, C, exp) CB200_DECL_MATH(T, C, exp2) CB200_DECL_MATH(T, C, exp10) \
+    CB200_DECL_MATH(T, C, sin) CB200_DECL_MATH(T, C, cos) CB200_DECL_MATH(T, C, tan) CB200_DECL_MATH(T, C, asin) \
+    CB200_DECL_MATH(T, C, acos) CB200_DECL_MATH(T, C, atan) CB200_DECL_MATH(T, C, sinh) CB200_DECL_MATH(T, C, cosh) \
+    CB200_DECL_MATH(T, C, tanh) CB200_DECL_MATH(T, C, asinh) CB200_DECL_MATH(T, C, acosh) CB200_DECL_MATH(T, C, atanh) \
+    CB200_DECL_MATH(T, C, sinc) CB200_DECL_MATH(T, C, erf) CB200_DECL_MATH(T, C, erfc) CB200_DECL_MATH(T, C, log1p) \
+    CB200_DECL_MATH(T, C, expm1) \
+    CB200_DECL_MATH2(T, C, atan2) CB200_DECL_MATH2(T, C, hypot) CB200_DECL_MATH2(T, C, ldexp) \
+    CB200_DECL_EWCOMP(T, C, maximum_nan) CB200_DECL_EWCOMP(T, C, minimum_nan) \
+    CB200_DECL_ACCUM(T, C, mean) CB200_DECL_ACCUM(T, C, var) CB200_DECL_ACCUM(T, C, stddev) CB200_DECL_ACCUM(T, C, rms) \
+    CB200_DECL_ACCUM(T, C, sum_nan) CB200_DECL_ACCUM(T, C, prod_nan) CB200_DECL_ACCUM(T, C, min_nan) CB200_DECL_ACCUM(T, C, max_nan) \
+    CB200_DECL_ACCUM(T, C, ptp_nan) CB200_DECL_ACCUM(T, C, mean_nan) CB200_DECL_ACCUM(T, C, var_nan) \
+    CB200_DECL_ACCUM(T, C, stddev_nan) CB200_DECL_ACCUM(T, C, rms_nan) \
+    CB200_DECL_MINMAX(T, C, _nan) \
+    CB200_DECL_ACCUM_IDX(T, C, max_index_nan) CB200_DECL_ACCUM_IDX(T, C, min_index_nan) \
+    CB200_DECL_ACCUM_IDX(T, C, argmax_nan) CB200_DECL_ACCUM_IDX(T, C, argmin_nan) \
+    CB200_DECL_MULSUM(T, C, _nan)
+
+#define CB200_DECL_INT(T, C) \
+    CB200_DECL_COMMON(T, C) \
+    CB200_DECL_BINARY_S(T, C, bit_and) CB200_DECL_BINARY_S(T, C, bit_or) CB200_DECL_BINARY_S(T, C, bit_xor) \
+    CB200_DECL_BINARY_S(T, C, left_shift) CB200_DECL_BINARY_S(T, C, right_shift) \
+    CB200_DECL_UNARY(T, C, bit_not)
+
+CB200_DECL_FLOAT(sfloat, float)
+CB200_DECL_FLOAT(dfloat, double)
+CB200_DECL_INT(int32, int32_t)
+CB200_DECL_INT(int64, int64_t)
+
+/* kahan_sum exists for the double-precision type only (reference: gen/spec.rb:321-323,
+ * float_accum_kernel.cu:196-206). */
+CB200_DECL_ACCUM(dfloat, double, kahan_sum)
+CB200_DECL_ACCUM(dfloat, double, kahan_sum_nan)
+
+/* Bit population counts, reference: gen/tmpl_bit/bit_count.c:4-7, bit_count_kernel.cu:48-78.
+ * p1: bit position of the first element; a1: first word; s1: bit step; n: number of
+ * bits looked at.  `stride`: *(uint64_t*)p2 += matches.  `stride_stride`:
+ * *(uint64_t*)(p2 + i*s2) += 1 for each matching bit i.  The `index` forms read the
+ * bit offsets from a device array of n size_t instead of using a step. */
+#define CB200_DECL_BITCOUNT(name) \
+    void cumo_iter_bit_##name##_index_kernel_launch(size_t p1, char* p2, CUMO_BIT_DIGIT* a1, size_t* idx1, uint64_t n); \
+    void cumo_iter_bit_##name##_stride_kernel_launch(size_t p1, char* p2, CUMO_BIT_DIGIT* a1, ssize_t s1, uint64_t n); \
+    void cumo_iter_bit_##name##_index_stride_kernel_launch(size_t p1, char* p2, CUMO_BIT_DIGIT* a1, size_t* idx1, ssize_t s2, uint64_t n); \
+    void cumo_iter_bit_##name##_stride_stride_kernel_launch(size_t p1, char* p2, CUMO_BIT_DIGIT* a1, ssize_t s1, ssize_t s2, uint64_t n);
+CB200_DECL_BITCOUNT(count_true)
+CB200_DECL_BITCOUNT(count_false)
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* CUMO_B200_H */

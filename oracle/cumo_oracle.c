@@ -1,0 +1,205 @@
+/*
+ * TEST INFRASTRUCTURE -- CPU oracle for the libcumo_b200 parity tests and the
+ * CPU-baseline leg of bench.py.  Nothing in the product may call into this file.
+ *
+ * It restates, as plain sequential C (OpenMP only across independent outputs /
+ * rows), the host loops that the reference keeps for its CPU path and inherited
+ * from Numo: elementwise loop shape and broadcasting
+ * (ext/cumo/narray/gen/tmpl/binary.c:22-112, unary.c:9-74), per-type operation
+ * macros (ext/cumo/include/cumo/types/float_macro.h:26-142, xint_macro.h:15-47,
+ * int_macro.h:3-67), reductions (types/real_accum.h:25-441, float_macro.h:150-193),
+ * Bit counting (ext/cumo/narray/gen/tmpl_bit/bit_count_cpu.c:4-67).  The per-type
+ * bodies are in oracle_type.inc, which cites the lines each function follows.
+ *
+ * Pinning: tests/test_oracle_golden.py checks this oracle against the literal
+ * expectations of the reference's own test suite (tests/golden/reference_cases.py
+ * transcribes them with file:line).  The reference itself (a CRuby extension
+ * generated from ERB templates) cannot be built or run here: no Ruby.
+ *
+ * Build: see oracle/Makefile (gcc -O3 -fopenmp, no -ffast-math).
+ */
+#define _GNU_SOURCE
+#include <math.h>
+#include <float.h>
+#include <stdint.h>
+#include <stddef.h>
+#include <string.h>
+#ifdef _OPENMP
+#include <omp.h>
+#endif
+
+enum { DT_SFLOAT = 0, DT_DFLOAT = 1, DT_INT32 = 2, DT_INT64 = 3 };
+enum { KIND_BINARY = 0, KIND_UNARY = 1, KIND_COMPARE = 2 };
+
+/* operation codes shared with oracle/cumo_oracle.py */
+enum {
+    OP_ADD = 0, OP_SUB, OP_MUL, OP_DIV, OP_MOD, OP_POW, OP_COPYSIGN, OP_ATAN2, OP_HYPOT, OP_LDEXP,
+    OP_MAXIMUM, OP_MINIMUM, OP_MAXIMUM_NAN, OP_MINIMUM_NAN,
+    OP_BIT_AND, OP_BIT_OR, OP_BIT_XOR, OP_LEFT_SHIFT, OP_RIGHT_SHIFT,
+    OP_MINUS = 100, OP_RECIPROCAL, OP_SIGN, OP_SQUARE, OP_ABS, OP_FLOOR, OP_ROUND, OP_CEIL, OP_TRUNC, OP_RINT,
+    OP_BIT_NOT,
+    OP_SQRT, OP_CBRT, OP_LOG, OP_LOG2, OP_LOG10, OP_EXP, OP_EXP2, OP_EXP10, OP_SIN, OP_COS, OP_TAN,
+    OP_ASIN, OP_ACOS, OP_ATAN, OP_SINH, OP_COSH, OP_TANH, OP_ASINH, OP_ACOSH, OP_ATANH, OP_SINC,
+    OP_ERF, OP_ERFC, OP_LOG1P, OP_EXPM1,
+    OP_EQ = 200, OP_NE, OP_GT, OP_GE, OP_LT, OP_LE, OP_NEARLY_EQ,
+    OP_ISNAN, OP_ISINF, OP_ISPOSINF, OP_ISNEGINF, OP_ISFINITE, OP_SIGNBIT
+};
+enum {
+    RED_SUM = 0, RED_PROD, RED_MEAN, RED_MIN, RED_MAX, RED_PTP, RED_MINMAX,
+    RED_MIN_INDEX, RED_MAX_INDEX, RED_ARGMIN, RED_ARGMAX, RED_VAR, RED_STDDEV, RED_RMS, RED_KAHAN
+};
+
+#define TN sfloat
+#define DT float
+#define ACC float
+#define IS_FP 1
+#define EPS_V FLT_EPSILON
+#include "oracle_type.inc"
+#undef TN
+#undef DT
+#undef ACC
+#undef IS_FP
+#undef EPS_V
+
+#define TN dfloat
+#define DT double
+#define ACC double
+#define IS_FP 1
+#define EPS_V DBL_EPSILON
+#include "oracle_type.inc"
+#undef TN
+#undef DT
+#undef ACC
+#undef IS_FP
+#undef EPS_V
+
+#define TN int32
+#define DT int32_t
+#define UDT uint32_t
+#define ACC int64_t
+#define IS_FP 0
+#define DATA_MIN_V INT32_MIN
+#include "oracle_type.inc"
+#undef TN
+#undef DT
+#undef UDT
+#undef ACC
+#undef IS_FP
+#undef DATA_MIN_V
+
+#define TN int64
+#define DT int64_t
+#define UDT uint64_t
+#define ACC int64_t
+#define IS_FP 0
+#define DATA_MIN_V INT64_MIN
+#include "oracle_type.inc"
+#undef TN
+#undef DT
+#undef UDT
+#undef ACC
+#undef IS_FP
+#undef DATA_MIN_V
+
+/* ---- exported API ------------------------------------------------------------------------ */
+
+/* kind: KIND_BINARY / KIND_UNARY / KIND_COMPARE.  Steps are in bytes (bits for the Bit
+ * output of a comparison).  a == NULL or b == NULL: that operand is the scalar `sv`
+ * (passed as double and as int64; the one matching the dtype is used). */
+int oracle_elementwise(int dtype, int kind, int op, int ndim, const int64_t* shape,
+                       const char* a, const int64_t* sa, const char* b, const int64_t* sb,
+                       char* c, const int64_t* sc, double sv_f, int64_t sv_i, int* flag,
+                       uint32_t* bits, uint64_t bitpos) {
+    switch (dtype) {
+    case DT_SFLOAT: return ew_loop_sfloat(kind, op, ndim, shape, a, sa, b, sb, c, sc, (float)sv_f, flag, bits, bitpos);
+    case DT_DFLOAT: return ew_loop_dfloat(kind, op, ndim, shape, a, sa, b, sb, c, sc, sv_f, flag, bits, bitpos);
+    case DT_INT32:  return ew_loop_int32(kind, op, ndim, shape, a, sa, b, sb, c, sc, (int32_t)sv_i, flag, bits, bitpos);
+    case DT_INT64:  return ew_loop_int64(kind, op, ndim, shape, a, sa, b, sb, c, sc, sv_i, flag, bits, bitpos);
+    }
+    return -1;
+}
+
+int oracle_pow_int32(int dtype, int ndim, const int64_t* shape, const char* a, const int64_t* sa,
+                     const char* b, const int64_t* sb, char* c, const int64_t* sc, double base_f,
+                     int64_t base_i, int32_t sv_exp) {
+    switch (dtype) {
+    case DT_SFLOAT: pow_int32_loop_sfloat(ndim, shape, a, sa, b, sb, c, sc, (float)base_f, sv_exp); return 0;
+    case DT_DFLOAT: pow_int32_loop_dfloat(ndim, shape, a, sa, b, sb, c, sc, base_f, sv_exp); return 0;
+    case DT_INT32:  pow_int32_loop_int32(ndim, shape, a, sa, b, sb, c, sc, (int32_t)base_i, sv_exp); return 0;
+    case DT_INT64:  pow_int32_loop_int64(ndim, shape, a, sa, b, sb, c, sc, base_i, sv_exp); return 0;
+    }
+    return -1;
+}
+
+/* out dims (oshape, in_ostep, out_step[, out2_step]) and reduce dims (rshape, in_rstep),
+ * all steps in bytes.  idx64 selects the output width of the index reductions. */
+int oracle_reduce(int dtype, int op, int nan, int n_od, const int64_t* oshape, const int64_t* in_ostep,
+                  const int64_t* out_step, const int64_t* out2_step, int n_rd, const int64_t* rshape,
+                  const int64_t* in_rstep, const char* in, char* out, char* out2, int idx64) {
+    switch (dtype) {
+    case DT_SFLOAT: reduce_all_sfloat(op, nan, n_od, oshape, in_ostep, out_step, out2_step, n_rd, rshape, in_rstep, in, out, out2, idx64); return 0;
+    case DT_DFLOAT: reduce_all_dfloat(op, nan, n_od, oshape, in_ostep, out_step, out2_step, n_rd, rshape, in_rstep, in, out, out2, idx64); return 0;
+    case DT_INT32:  reduce_all_int32(op, 0, n_od, oshape, in_ostep, out_step, out2_step, n_rd, rshape, in_rstep, in, out, out2, idx64); return 0;
+    case DT_INT64:  reduce_all_int64(op, 0, n_od, oshape, in_ostep, out_step, out2_step, n_rd, rshape, in_rstep, in, out, out2, idx64); return 0;
+    }
+    return -1;
+}
+
+int oracle_mulsum(int dtype, int nan, const char* p1, const char* p2, char* p3, int64_t s1, int64_t s2, int64_t s3, int64_t n) {
+    switch (dtype) {
+    case DT_SFLOAT: mulsum_sfloat(nan, p1, p2, p3, s1, s2, s3, n); return 0;
+    case DT_DFLOAT: mulsum_dfloat(nan, p1, p2, p3, s1, s2, s3, n); return 0;
+    case DT_INT32:  mulsum_int32(0, p1, p2, p3, s1, s2, s3, n); return 0;
+    case DT_INT64:  mulsum_int64(0, p1, p2, p3, s1, s2, s3, n); return 0;
+    }
+    return -1;
+}
+
+/* Bits at pos + i*step, i < n, LSB-first in 32-bit words (narray.h:492-496).  The
+ * contiguous case counts whole words the way bit_count_cpu.c:4-67 does. */
+uint64_t oracle_bit_count(const uint32_t* words, uint64_t pos, int64_t step, uint64_t n, int want_false) {
+    uint64_t c = 0;
+    if (step == 1) {
+        uint64_t i = 0;
+        while (i < n && ((pos + i) & 31)) { c += (words[(pos + i) >> 5] >> ((pos + i) & 31)) & 1u; ++i; }
+        for (; i + 32 <= n; i += 32) c += (uint64_t)__builtin_popcount(words[(pos + i) >> 5]);
+        for (; i < n; ++i) c += (words[(pos + i) >> 5] >> ((pos + i) & 31)) & 1u;
+    } else {
+        for (uint64_t i = 0; i < n; ++i) {
+            uint64_t b = pos + (uint64_t)((int64_t)i * step);
+            c += (words[b >> 5] >> (b & 31)) & 1u;
+        }
+    }
+    return want_false ? n - c : c;
+}
+
+/* float64 reference sum for tolerance checks: pairwise, so that its own error is
+ * far below the 1e-12 the double-precision kernels are held to. */
+static double pairwise_f64(const double* p, int64_t n) {
+    if (n <= 64) { double s = 0; for (int64_t i = 0; i < n; ++i) s += p[i]; return s; }
+    int64_t h = n / 2;
+    return pairwise_f64(p, h) + pairwise_f64(p + h, n - h);
+}
+static double pairwise_f32(const float* p, int64_t n) {
+    if (n <= 64) { double s = 0; for (int64_t i = 0; i < n; ++i) s += (double)p[i]; return s; }
+    int64_t h = n / 2;
+    return pairwise_f32(p, h) + pairwise_f32(p + h, n - h);
+}
+double oracle_sum_f64ref(int dtype, const char* p, int64_t n) {
+    return dtype == DT_SFLOAT ? pairwise_f32((const float*)p, n) : pairwise_f64((const double*)p, n);
+}
+
+int oracle_threads(void) {
+#ifdef _OPENMP
+    return omp_get_max_threads();
+#else
+    return 1;
+#endif
+}
+void oracle_set_threads(int n) {
+#ifdef _OPENMP
+    omp_set_num_threads(n > 0 ? n : 1);
+#else
+    (void)n;
+#endif
+}

@@ -1,0 +1,220 @@
+"""TEST INFRASTRUCTURE -- numpy-facing wrapper of the CPU oracle (oracle/cumo_oracle.c).
+
+Only tests/, __graft_entry__.smoke() and bench.py's CPU-baseline legs may import this.
+It restates nothing itself: arguments are turned into (pointer, shape, byte steps)
+and handed to the C loops, which cite the reference lines they follow.  The
+arrays may have any numpy strides; broadcasting follows ndloop's rule
+(ext/cumo/narray/ndloop.c:494-516) via numpy's zero strides.
+"""
+from __future__ import annotations
+
+import ctypes
+import subprocess
+from ctypes import POINTER, c_char_p, c_double, c_int, c_int32, c_int64, c_uint32, c_uint64, c_void_p
+from pathlib import Path
+
+import numpy as np
+
+HERE = Path(__file__).resolve().parent
+LIB = HERE / "libcumo_oracle.so"
+
+DT = {np.dtype(np.float32): 0, np.dtype(np.float64): 1, np.dtype(np.int32): 2, np.dtype(np.int64): 3}
+KIND_BINARY, KIND_UNARY, KIND_COMPARE = 0, 1, 2
+
+_BINARY = ["add", "sub", "mul", "div", "mod", "pow", "copysign", "atan2", "hypot", "ldexp", "maximum", "minimum",
+           "maximum_nan", "minimum_nan", "bit_and", "bit_or", "bit_xor", "left_shift", "right_shift"]
+_UNARY = ["minus", "reciprocal", "sign", "square", "abs", "floor", "round", "ceil", "trunc", "rint", "bit_not",
+          "sqrt", "cbrt", "log", "log2", "log10", "exp", "exp2", "exp10", "sin", "cos", "tan", "asin", "acos", "atan",
+          "sinh", "cosh", "tanh", "asinh", "acosh", "atanh", "sinc", "erf", "erfc", "log1p", "expm1"]
+_COMPARE = ["eq", "ne", "gt", "ge", "lt", "le", "nearly_eq", "isnan", "isinf", "isposinf", "isneginf", "isfinite", "signbit"]
+OPS = {n: i for i, n in enumerate(_BINARY)}
+OPS.update({n: 100 + i for i, n in enumerate(_UNARY)})
+OPS.update({n: 200 + i for i, n in enumerate(_COMPARE)})
+RED = {n: i for i, n in enumerate(["sum", "prod", "mean", "min", "max", "ptp", "minmax", "min_index", "max_index",
+                                   "argmin", "argmax", "var", "stddev", "rms", "kahan_sum"])}
+
+_lib = None
+
+
+def build() -> Path:
+    """Compile the oracle with the Makefile beside it (gcc, no fast-math)."""
+    if not LIB.exists() or any(p.stat().st_mtime > LIB.stat().st_mtime for p in (HERE / "cumo_oracle.c", HERE / "oracle_type.inc")):
+        subprocess.run(["make", "-C", str(HERE)], check=True, capture_output=True)
+    return LIB
+
+
+def lib():
+    global _lib
+    if _lib is None:
+        build()
+        L = ctypes.CDLL(str(LIB))
+        P = POINTER(c_int64)
+        L.oracle_elementwise.restype = c_int
+        L.oracle_elementwise.argtypes = [c_int, c_int, c_int, c_int, P, c_void_p, P, c_void_p, P, c_void_p, P,
+                                         c_double, c_int64, POINTER(c_int), c_void_p, c_uint64]
+        L.oracle_pow_int32.restype = c_int
+        L.oracle_pow_int32.argtypes = [c_int, c_int, P, c_void_p, P, c_void_p, P, c_void_p, P, c_double, c_int64, c_int32]
+        L.oracle_reduce.restype = c_int
+        L.oracle_reduce.argtypes = [c_int, c_int, c_int, c_int, P, P, P, P, c_int, P, P, c_void_p, c_void_p, c_void_p, c_int]
+        L.oracle_mulsum.restype = c_int
+        L.oracle_mulsum.argtypes = [c_int, c_int, c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int64]
+        L.oracle_bit_count.restype = c_uint64
+        L.oracle_bit_count.argtypes = [c_void_p, c_uint64, c_int64, c_uint64, c_int]
+        L.oracle_sum_f64ref.restype = c_double
+        L.oracle_sum_f64ref.argtypes = [c_int, c_void_p, c_int64]
+        L.oracle_threads.restype = c_int
+        L.oracle_set_threads.argtypes = [c_int]
+        _lib = L
+    return _lib
+
+
+def threads() -> int:
+    return int(lib().oracle_threads())
+
+
+def set_threads(n: int) -> None:
+    lib().oracle_set_threads(int(n))
+
+
+def _i64(values):
+    return (c_int64 * max(1, len(values)))(*[int(v) for v in values])
+
+
+def _scalar_args(value, dtype):
+    if np.issubdtype(dtype, np.floating):
+        return float(value), 0
+    return 0.0, int(value)
+
+
+def _is_array(x):
+    return isinstance(x, np.ndarray)
+
+
+def _elementwise(kind, op, a, b, out=None):
+    """a, b: ndarrays (same dtype) or python scalars (at most one of them)."""
+    arrs = [x for x in (a, b) if _is_array(x)]
+    dtype = arrs[0].dtype
+    shape = np.broadcast_shapes(*[x.shape for x in arrs])
+    sv = next((x for x in (a, b) if x is not None and not _is_array(x)), 0)
+    sv_f, sv_i = _scalar_args(sv, dtype)
+    va = np.broadcast_to(a, shape) if _is_array(a) else None
+    vb = np.broadcast_to(b, shape) if _is_array(b) else None
+    flag = c_int(0)
+    if kind == KIND_COMPARE:
+        n = int(np.prod(shape, dtype=np.int64))
+        words = np.zeros((n + 31) // 32, dtype=np.uint32)
+        steps, s = [], 1
+        for ext in reversed(shape):
+            steps.append(s); s *= ext
+        sc = _i64(list(reversed(steps)))
+        rc = lib().oracle_elementwise(DT[dtype], kind, OPS[op], len(shape), _i64(shape),
+                                      va.ctypes.data if va is not None else None, _i64(va.strides) if va is not None else _i64([]),
+                                      vb.ctypes.data if vb is not None else None, _i64(vb.strides) if vb is not None else _i64([]),
+                                      None, sc, sv_f, sv_i, ctypes.byref(flag), words.ctypes.data, 0)
+        if rc:
+            raise ValueError(f"oracle: {op} is not defined for {dtype}")
+        bits = np.unpackbits(words.view(np.uint8), bitorder="little")[:n].astype(bool).reshape(shape)
+        return bits, words
+    if out is None:
+        out = np.zeros(shape, dtype=dtype)
+    rc = lib().oracle_elementwise(DT[dtype], kind, OPS[op], len(shape), _i64(shape),
+                                  va.ctypes.data if va is not None else None, _i64(va.strides) if va is not None else _i64([]),
+                                  vb.ctypes.data if vb is not None else None, _i64(vb.strides) if vb is not None else _i64([]),
+                                  out.ctypes.data, _i64(out.strides), sv_f, sv_i, ctypes.byref(flag), None, 0)
+    if rc:
+        raise ValueError(f"oracle: {op} is not defined for {dtype}")
+    return out, flag.value
+
+
+def binary(op, a, b, out=None):
+    """(result, flag): flag is 1 when an integer division by zero was met (those elements are left alone)."""
+    return _elementwise(KIND_BINARY, op, a, b, out)
+
+
+def unary(op, a, out=None):
+    return _elementwise(KIND_UNARY, op, a, None, out)
+
+
+def compare(op, a, b=None):
+    """(bool array, packed uint32 words)."""
+    return _elementwise(KIND_COMPARE, op, a, b)
+
+
+def pow_int(a, exponent: int):
+    out = np.zeros(a.shape, dtype=a.dtype)
+    lib().oracle_pow_int32(DT[a.dtype], a.ndim, _i64(a.shape), a.ctypes.data, _i64(a.strides), None, _i64([]),
+                           out.ctypes.data, _i64(out.strides), 0.0, 0, int(exponent))
+    return out
+
+
+def reduce(op, a, axis=None, nan=False, keepdims=False, idx64=None):
+    """Reduction of `a` (any strides) over `axis` (None: all).  For max_index/min_index the
+    answer is the element offset from a's first element in units of elements, which for a
+    C-contiguous `a` is the flat index, as in the reference."""
+    nd = a.ndim
+    axes = tuple(range(nd)) if axis is None else ((axis,) if isinstance(axis, int) else tuple(axis))
+    axes = tuple(sorted(ax % nd for ax in axes)) if nd else ()
+    keep = [d for d in range(nd) if d not in axes]
+    out_shape = [a.shape[d] for d in keep]
+    index_op = op in ("max_index", "min_index", "argmax", "argmin")
+    if idx64 is None:
+        idx64 = a.size > 0xFFFFFFFF
+    if index_op:
+        out_dtype = np.int64 if idx64 else np.int32
+    elif op in ("sum", "prod") and np.issubdtype(a.dtype, np.integer):
+        out_dtype = np.int64
+    else:
+        out_dtype = a.dtype
+    out = np.zeros(out_shape, dtype=out_dtype)
+    out2 = np.zeros(out_shape, dtype=out_dtype) if op == "minmax" else None
+    lib().oracle_reduce(DT[a.dtype], RED[op], int(nan), len(keep), _i64(out_shape), _i64([a.strides[d] for d in keep]),
+                        _i64(out.strides), _i64(out2.strides) if out2 is not None else None,
+                        len(axes), _i64([a.shape[d] for d in axes]), _i64([a.strides[d] for d in axes]),
+                        a.ctypes.data, out.ctypes.data, out2.ctypes.data if out2 is not None else None, int(bool(idx64)))
+    if keepdims:
+        ks = [1 if d in axes else a.shape[d] for d in range(nd)]
+        out = out.reshape(ks)
+        if out2 is not None:
+            out2 = out2.reshape(ks)
+    return (out, out2) if op == "minmax" else out
+
+
+def mulsum(a, b, axis=None, nan=False):
+    """(a*b) summed over `axis`, accumulated the way the host loop does: one output at a time, z = x*y + z."""
+    shape = np.broadcast_shapes(a.shape, b.shape)
+    va, vb = np.broadcast_to(a, shape), np.broadcast_to(b, shape)
+    nd = len(shape)
+    axes = tuple(range(nd)) if axis is None else ((axis,) if isinstance(axis, int) else tuple(axis))
+    axes = tuple(sorted(ax % nd for ax in axes))
+    keep = [d for d in range(nd) if d not in axes]
+    out = np.zeros([shape[d] for d in keep], dtype=a.dtype)
+    red_shape = [shape[d] for d in axes]
+    for oi in np.ndindex(*out.shape):
+        for ri in np.ndindex(*red_shape):
+            idx = [0] * nd
+            for d, i in zip(keep, oi):
+                idx[d] = i
+            for d, i in zip(axes, ri):
+                idx[d] = i
+            pa = va.ctypes.data + sum(i * s for i, s in zip(idx, va.strides))
+            pb = vb.ctypes.data + sum(i * s for i, s in zip(idx, vb.strides))
+            po = out.ctypes.data + sum(i * s for i, s in zip(oi, out.strides))
+            lib().oracle_mulsum(DT[a.dtype], int(nan), pa, pb, po, 0, 0, 0, 1)
+    return out
+
+
+def mulsum_1d(a, b, nan=False):
+    """Full mulsum of two 1-D arrays in one C loop."""
+    out = np.zeros((), dtype=a.dtype)
+    lib().oracle_mulsum(DT[a.dtype], int(nan), a.ctypes.data, b.ctypes.data, out.ctypes.data, a.strides[0], b.strides[0], 0, a.size)
+    return out
+
+
+def bit_count(words: np.ndarray, pos: int, step: int, n: int, want_false: bool = False) -> int:
+    return int(lib().oracle_bit_count(words.ctypes.data, pos, step, n, int(want_false)))
+
+
+def sum_f64ref(a: np.ndarray) -> float:
+    """Pairwise float64 sum of a contiguous float array: the yardstick of the stated tolerances."""
+    a = np.ascontiguousarray(a)
+    return float(lib().oracle_sum_f64ref(DT[a.dtype], a.ctypes.data, a.size))

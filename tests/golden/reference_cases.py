@@ -1,0 +1,373 @@
+"""Known-answer cases transcribed from the reference's own test suite.
+
+Each function states literal inputs and the literal answers that the reference's
+tests assert (file:line under the reference project's test/ directory), written
+against a namespace `xp` that offers SFloat/DFloat/Int32/Int64/Bit/NMath.  They pin
+the CPU oracle (tests/test_oracle_golden.py, xp = tests/oracle_narray.OracleXP) and
+are run unchanged against the CUDA path (tests/test_gpu_golden.py, xp = cumo_b200).
+Ruby idioms map as: `a.sum(axis: 1)` -> `a.sum(axis=1)`, `a[true, 0..1]` ->
+`a[True, 0:2]`, `Cumo::SFloat[[1,2],[3,4]]` -> `xp.SFloat[[1, 2], [3, 4]]`.
+"""
+from __future__ import annotations
+
+import math
+
+NAN = float("nan")
+INF = float("inf")
+
+
+def tags(values):
+    """NaN -> 'nan' so that lists with NaN compare (test/narray_test.rb float_tags)."""
+    out = []
+    for v in (values if isinstance(values, list) else [values]):
+        out.append(tags(v) if isinstance(v, list) else ("nan" if isinstance(v, float) and math.isnan(v) else v))
+    return out
+
+
+def scalar(v):
+    """A reduction over everything answers a 0-d array; take its element."""
+    return v.extract()
+
+
+def value_types(xp):
+    return [xp.SFloat, xp.DFloat, xp.Int32, xp.Int64]
+
+
+def float_types(xp):
+    return [xp.SFloat, xp.DFloat]
+
+
+# ---- test/narray_test.rb:1009-1026 "element-wise" ------------------------------------------------
+def case_elementwise_broadcast(xp):
+    for T in value_types(xp):
+        x = T[[1, 2, 3], [5, 7, 11]]
+        assert (x + x).to_a() == [[2, 4, 6], [10, 14, 22]]
+        assert (x + 1).to_a() == [[2, 3, 4], [6, 8, 12]]
+        assert (x + T[1]).to_a() == [[2, 3, 4], [6, 8, 12]]
+        assert (x + T[[1], [2]]).to_a() == [[2, 3, 4], [7, 9, 13]]
+        assert (x + T[1, 2, 3]).to_a() == [[2, 4, 6], [6, 9, 14]]
+        assert (x + T[[1, 2], [3, 4], [5, 6]].transpose()).to_a() == [[2, 5, 8], [7, 11, 17]]
+        assert (x[0, 1:3] + x[1, 0:2]).to_a() == [7, 10]
+
+
+# ---- test/narray_test.rb:1028-1065 "reduction" ----------------------------------------------------
+def case_reduction_basic(xp):
+    for T in value_types(xp):
+        assert T.ones(2, 2, 3, 2).sum(axis=[0, 2, 3]).to_a() == [12, 12]
+        assert T.ones(5, 3, 4, 2, 1).sum(axis=[0, 3, 4]).to_a() == [[10] * 4] * 3
+        assert T[[1, 2, 3], [4, 5, 6]].sum(axis=1).to_a() == [6, 15]
+        assert T[[1, 2, 3], [4, 5, 6]].sum(axis=1, keepdims=True).to_a() == [[6], [15]]
+        T.ones(2, 3, 9, 4, 2).max_index(2)
+        a = T[[[6, 8, 5], [2, 5, 6], [4, 5, 5]], [[7, 4, 3], [9, 1, 0], [4, 1, 6]]]
+        # the last row of the first plane is [4, 5, 5]: a tie takes the earlier of the two
+        assert a.max_index(2).to_a() == [[1, 5, 7], [9, 12, 17]]
+        assert a.max(2).to_a() == [[8, 6, 5], [7, 9, 6]]
+        assert a.argmax(2).to_a() == [[1, 2, 1], [0, 0, 2]]
+        assert a.argmin(2).to_a() == [[2, 0, 0], [2, 2, 1]]
+        a = T[[[-6, -8, -5], [-2, 5, 6], [4, -5, 5]], [[-7, -4, -3], [9, 1, 0], [4, -1, -6]]]
+        assert a.max_index(2).to_a() == [[2, 5, 8], [11, 12, 15]]
+        assert a.max(2).to_a() == [[-5, 6, 5], [-3, 9, 4]]
+    for T in float_types(xp):
+        assert T[[-INF, 0, 1, INF]].max_index(0).to_a() == [0, 1, 2, 3]
+
+
+# ---- test/narray_test.rb:1388-1411 "argmax/argmin" -------------------------------------------------
+def case_argmax_argmin(xp):
+    for T in (xp.DFloat, xp.Int32):
+        a = T[3, 4, 1, 2]
+        assert scalar(a.argmax()) == 1
+        assert scalar(a.argmin()) == 2
+        b = T[[3, 4, 1], [2, 0, 5]]
+        assert scalar(b.argmax()) == 5
+        assert scalar(b.argmin()) == 4
+        assert b.argmax(axis=1).to_a() == [1, 2]
+        assert b.argmax(axis=0).to_a() == [0, 0, 1]
+        assert b.argmin(axis=1).to_a() == [2, 1]
+        assert b.argmin(axis=0).to_a() == [1, 1, 0]
+    c = xp.DFloat[3.0, NAN, 1.0, 5.0]
+    assert scalar(c.argmax()) == 3
+    assert scalar(c.argmax(nan=True)) == 1
+    assert scalar(c.argmin()) == 2
+    assert scalar(c.argmin(nan=True)) == 1
+
+
+# ---- test/narray_test.rb:1908-1941 "max_index/min_index with nan: true" ------------------------------
+def case_index_nan_true(xp):
+    a = xp.DFloat[3, 4, NAN, 2]
+    assert scalar(a.max_index(nan=True)) == 2
+    assert scalar(a.min_index(nan=True)) == 2
+    b = xp.DFloat[3, 4, 1, 2]
+    assert scalar(b.max_index(nan=True)) == 1
+    assert scalar(b.min_index(nan=True)) == 2
+    # the index is into the whole array, not into the axis
+    b = xp.DFloat[[3, 4, 1], [NAN, 2, 5]]
+    assert scalar(b.max_index(nan=True)) == 3
+    assert scalar(b.min_index(nan=True)) == 3
+    assert b.max_index(axis=0, nan=True).to_a() == [3, 1, 5]
+    assert b.max_index(axis=1, nan=True).to_a() == [1, 3]
+    assert b.min_index(axis=0, nan=True).to_a() == [3, 4, 2]
+    assert b.min_index(axis=1, nan=True).to_a() == [2, 3]
+    assert scalar(xp.SFloat[3, 4, NAN, 2].max_index(nan=True)) == 2
+    assert scalar(xp.DFloat[3, 4, NAN, 2, 9][0:4].max_index(nan=True)) == 2
+    a = xp.DFloat[[3, 4, 1], [9, 2, 5]]
+    assert scalar(a.max_index()) == 3
+    assert a.max_index(axis=1).to_a() == [1, 3]
+    assert scalar(a.min_index()) == 2
+
+
+# ---- test/narray_test.rb:1966-2025 "integer #sum widens to 64 bits" ------------------------------------
+def case_int_sum_widens(xp):
+    for T, bits in ((xp.Int32, 30), (xp.Int64, 50)):
+        for n in (4, 8, 64, 1024):
+            assert scalar(T.new(n).fill(2 ** bits).sum()) == n * 2 ** bits
+        a = T.new(100_000).seq()
+        assert scalar(a.sum()) == sum(range(100_000))
+        a = T.new(4, 256).seq()
+        rows = a.to_a()
+        assert a.sum(axis=1).to_a() == [sum(r) for r in rows]
+        assert a.sum(axis=0).to_a() == [sum(c) for c in zip(*rows)]
+        a = T.new(6).seq(1)
+        assert scalar(a.prod()) == 720
+
+
+# ---- test/narray_test.rb:2551-2568 "minmax of an all-NaN reduction" -----------------------------------
+def case_minmax_all_nan(xp):
+    for T in float_types(xp):
+        a = T[[1.0, NAN, -3.0, 2.0], [NAN, NAN, NAN, NAN]]
+        lo, hi = a.minmax(axis=1)
+        assert tags(lo.to_a()) == [-3.0, "nan"]
+        assert tags(hi.to_a()) == [2.0, "nan"]
+        assert tags(a.max(axis=1).to_a()) == tags(hi.to_a())
+        lo, hi = a.minmax(axis=1, nan=True)
+        assert tags(lo.to_a()) == ["nan", "nan"]
+        assert tags(hi.to_a()) == ["nan", "nan"]
+
+
+# ---- test/narray_test.rb:2570-2599 "nan:true reductions answer what the host rules say" ------------------
+def case_nan_true_table(xp):
+    for T in float_types(xp):
+        a = T[[1.0, NAN, -3.0], [4.0, -5.0, 2.0]]
+        assert a.sum(axis=1, nan=True).to_a() == [-2.0, 1.0]
+        assert a.prod(axis=1, nan=True).to_a() == [-3.0, -40.0]
+        assert tags(a.min(axis=1, nan=True).to_a()) == ["nan", -5.0]
+        assert tags(a.max(axis=1, nan=True).to_a()) == ["nan", 4.0]
+        assert tags(a.ptp(axis=1, nan=True).to_a()) == ["nan", 9.0]
+        assert a.argmin(axis=1, nan=True).to_a() == [1, 1]
+        assert a.argmax(axis=1, nan=True).to_a() == [1, 0]
+        assert a.min_index(axis=1, nan=True).to_a() == [1, 4]
+        assert a.max_index(axis=1, nan=True).to_a() == [1, 3]
+        assert scalar(a.sum(nan=True)) == -1.0
+        assert scalar(a.prod(nan=True)) == 120.0
+        assert tags(scalar(a.min(nan=True))) == ["nan"]
+        assert tags(scalar(a.max(nan=True))) == ["nan"]
+        assert scalar(a.argmin(nan=True)) == 1
+        assert tags(a.sum(axis=1).to_a()) == ["nan", 1.0]
+        assert tags(a.min(axis=1).to_a()) == [-3.0, -5.0]
+        assert tags(a.max(axis=1).to_a()) == [1.0, 4.0]
+
+
+# ---- test/narray_test.rb:2601-2620 "a reduction wide enough to be split across blocks" -------------------
+def case_split_reduction(xp):
+    n = (1 << 20) + 7
+    a = xp.DFloat.new(n).seq()
+    assert scalar(a.sum()) == 549_762_629_653.0
+    assert scalar(a.min()) == 0.0
+    assert scalar(a.max()) == n - 1.0
+    assert scalar(a.ptp()) == n - 1.0
+    lo, hi = a.minmax()
+    assert scalar(lo) == 0.0 and scalar(hi) == n - 1.0
+    rows, cols = 8, 300_000
+    b = xp.Int32.new(rows * cols).seq().reshape(rows, cols)
+    assert b.min(axis=1).to_a() == [r * cols for r in range(rows)]
+    assert b.max(axis=1).to_a() == [(r + 1) * cols - 1 for r in range(rows)]
+
+
+# ---- test/narray_test.rb:2622-2638 "a split reduction keeps the NaN rules" --------------------------------
+def case_split_nan_rules(xp):
+    n = 1 << 20
+    host = list(map(float, range(n)))
+    host[n // 2] = NAN
+    a = xp.DFloat.cast(host)
+    assert tags(scalar(a.sum())) == ["nan"]
+    assert scalar(a.min()) == 0.0
+    assert scalar(a.max()) == n - 1.0
+    all_nan = xp.DFloat.new(n).fill(NAN)
+    assert tags(scalar(all_nan.min())) == ["nan"]
+    assert tags(scalar(all_nan.max())) == ["nan"]
+    assert tags(scalar(all_nan.ptp())) == ["nan"]
+    lo, hi = all_nan.minmax()
+    assert tags(scalar(lo)) == ["nan"] and tags(scalar(hi)) == ["nan"]
+
+
+# ---- test/narray_test.rb:2640-2665 "an index reduction takes the earlier of two equal elements" -----------
+def case_index_ties(xp):
+    for T in (xp.DFloat, xp.Int32):
+        a = T[1, 0, 0, 2, 2]
+        assert scalar(a.min_index()) == 1
+        assert scalar(a.max_index()) == 3
+        assert scalar(a.argmin()) == 1
+        assert scalar(a.argmax()) == 3
+        long = T.cast([i % 3 for i in range(2000)])
+        assert scalar(long.min_index()) == 0
+        assert scalar(long.max_index()) == 2
+        assert scalar(long.argmin()) == 0
+        assert scalar(long.argmax()) == 2
+        grid = T.cast([i % 3 for i in range(2048)]).reshape(4, 512)
+        assert grid.min_index(axis=1).to_a() == [0, 513, 1026, 1536]
+        assert grid.max_index(axis=1).to_a() == [2, 512, 1025, 1538]
+        assert grid.argmin(axis=1).to_a() == [0, 1, 2, 0]
+        assert grid.argmax(axis=1).to_a() == [2, 0, 1, 2]
+
+
+# ---- test/narray_test.rb:3235-3274 "flat layout and a strided one" -----------------------------------------
+def case_flat_vs_strided(xp):
+    rows, cols = 96, 130
+    xs = [((i * 37) % 101) - 50.0 for i in range(rows * cols)]
+    a = xp.DFloat.cast(xs).reshape(rows, cols)
+    grid = [xs[r * cols:(r + 1) * cols] for r in range(rows)]
+    tgrid = [list(c) for c in zip(*grid)]
+    assert a.sum(axis=1).to_a() == [sum(r) for r in grid]
+    assert a.sum(axis=0).to_a() == [sum(c) for c in tgrid]
+    assert scalar(a.sum()) == sum(xs)
+    assert a.min(axis=1).to_a() == [min(r) for r in grid]
+    assert a.max(axis=1).to_a() == [max(r) for r in grid]
+    assert a.ptp(axis=1).to_a() == [max(r) - min(r) for r in grid]
+    t = a.transpose()
+    assert t.sum(axis=1).to_a() == [sum(c) for c in tgrid]
+    assert t.sum(axis=0).to_a() == [sum(r) for r in grid]
+    assert t.max(axis=1).to_a() == [max(c) for c in tgrid]
+    sel = list(range(0, cols, 3))
+    v = a[True, 0:cols:3]
+    assert v.sum(axis=1).to_a() == [sum(row[c] for c in sel) for row in grid]
+    assert v.min(axis=1).to_a() == [min(row[c] for c in sel) for row in grid]
+    deep = [4, 5, 6]
+    ys = [((i * 13) % 29) - 14.0 for i in range(4 * 5 * 6)]
+    b = xp.DFloat.cast(ys).reshape(*deep)
+    want = [[sum(ys[i * 30 + j * 6 + k] for j in range(5)) for k in range(6)] for i in range(4)]
+    assert b.sum(axis=1).to_a() == want
+    assert b.sum(axis=1, keepdims=True).shape == (4, 1, 6)
+
+
+# ---- test/narray_test.rb:3276-3291 "a split reduction answers the same as an unsplit one" -------------------
+def case_split_vs_unsplit(xp):
+    n = 300_000
+    xs = [((i * 7) % 13) - 6.0 for i in range(n)]
+    a = xp.DFloat.cast(xs)
+    assert scalar(a.sum()) == sum(xs)
+    assert scalar(a.min()) == min(xs)
+    assert scalar(a.max()) == max(xs)
+    b = xp.DFloat.cast(xs).reshape(300, n // 300)
+    assert sum(b.sum(axis=1).to_a()) == sum(xs)
+    assert min(b.min(axis=1).to_a()) == min(xs)
+
+
+# ---- test/narray_test.rb:4887-4893 "an integer divided or reduced by a numeric zero still raises" ------------
+def case_int_divmod_zero(xp):
+    def raises(f):
+        try:
+            f()
+        except ZeroDivisionError:
+            return True
+        return False
+
+    assert raises(lambda: xp.Int32[1, 2, 3] / 0)
+    assert raises(lambda: xp.Int32[[1, 2], [3, 4]][True, 0] / 0)
+    assert raises(lambda: xp.Int32[1, 2, 3] % 0)
+    assert (xp.Int32[1, 2, 3] / 2).to_a() == [0, 1, 1]
+    assert (xp.Int32[1, 2, 3] % 2).to_a() == [1, 0, 1]
+
+
+# ---- test/narray_test.rb:4895-4905 "the operators that take a numeric operand answer what Numo answers" --------
+def case_numeric_operand_operators(xp):
+    ints = xp.Int32[7, 3, 100]
+    assert (ints & 5).to_a() == [5, 1, 4]
+    assert (ints | 5).to_a() == [7, 7, 101]
+    assert (ints ^ 5).to_a() == [2, 6, 97]
+    assert (ints << 2).to_a() == [28, 12, 400]
+    assert (ints >> 2).to_a() == [1, 0, 25]
+    floats = xp.SFloat[7, -3, 100]
+    assert floats.copysign(-1).to_a() == [-7, -3, -100]
+    assert floats.copysign(1).to_a() == [7, 3, 100]
+
+
+# ---- test/narray_test.rb:4932-4939 "a reduction answering an index copies a strided view" ------------------------
+def case_index_on_view(xp):
+    a = xp.Int32.new(6, 5).seq()
+    v = a[True, 1:4]
+    assert v.max_index(axis=0).to_a() == [15, 16, 17]
+    assert v.max_index(axis=1).to_a() == [2, 5, 8, 11, 14, 17]
+
+
+# ---- test/narray_test.rb:5014-5086 "index reductions: earliest extreme, first NaN with nan" ------------------------
+def case_index_extremes(xp):
+    ops = ("max_index", "min_index", "argmax", "argmin")
+
+    def got(a, op, nan_aware=False):
+        return scalar(getattr(a, op)(nan=True) if nan_aware else getattr(a, op)())
+
+    def check(a, want):
+        for op, w in zip(ops, want):
+            assert got(a, op) == w, (op, got(a, op), w)
+
+    for T in float_types(xp):
+        n = 20_000
+        body = [(i * 7 % 101) - 50.0 for i in range(n)]
+        imax = max(range(n), key=lambda i: (body[i], -i))
+        imin = min(range(n), key=lambda i: (body[i], i))
+        check(T.cast(body), [imax, imin, imax, imin])
+        check(T.cast([-INF] * n), [0, 0, 0, 0])
+        check(T.cast([INF] * n), [0, 0, 0, 0])
+        check(T.cast([NAN] * n), [0, 0, 0, 0])
+        check(T.cast([-INF, 0.0, 1.0, INF]), [3, 0, 3, 0])
+        check(T.cast([1.0, 2.0, 2.0, 1.0]), [1, 0, 1, 0])
+        clean = T.cast(body)
+        for op in ops:
+            assert got(clean, op) == got(clean, op, True)
+        with_nan = T.cast([3.0, -1.0, NAN, 1.0, NAN])
+        for op in ops:
+            assert got(with_nan, op, True) == 2
+            assert got(with_nan, op) == (0 if "max" in op else 1)
+    for T, lo in ((xp.Int32, -(2 ** 31)), (xp.Int64, -(2 ** 63))):
+        check(T.cast([lo] * 100), [0, 0, 0, 0])
+        check(T.cast([1, 2, 2, 1]), [1, 0, 1, 0])
+    for src, want in (([[5.0, -INF], [6.0, -INF]], [[2, 1], [0, 1]]),
+                      ([[5.0, INF], [6.0, INF]], [[2, 1], [0, 1]]),
+                      ([[5.0, NAN], [6.0, NAN]], [[2, 1], [0, 1]])):
+        a = xp.DFloat.cast(src)
+        assert a.max_index(axis=0).to_a() == want[0]
+        assert a.min_index(axis=0).to_a() == want[1]
+    b = xp.DFloat.new(5, 24).seq()
+    for v in (b, b.transpose(), b[True, 23::-1]):
+        for ax in (0, 1):
+            for op in ops:
+                assert getattr(v, op)(axis=ax).to_a() == getattr(v, op)(axis=ax, nan=True).to_a()
+
+
+# ---- test/bit_test.rb:19-44 (count_true / count_false of the 8-bit literal, direct and through a view) ---------
+def case_bit_counts(xp):
+    src = [0, 1, 1, 0, 1, 0, 0, 1]
+    a = xp.Bit.cast(src)
+    assert a.to_a() == src
+    assert scalar(a.count_true()) == 4
+    assert scalar(a.count_false()) == 4
+
+
+# ---- test/math_test.rb (closeness of NMath functions on small literals) --------------------------------------------
+def case_math_closeness(xp):
+    vals = [0.25, 0.5, 1.0, 2.0, 3.5]
+    for T, rel in ((xp.SFloat, 2e-6), (xp.DFloat, 1e-14)):
+        x = T.cast(vals)
+        for name, f in (("sqrt", math.sqrt), ("exp", math.exp), ("log", math.log), ("sin", math.sin),
+                        ("cos", math.cos), ("tanh", math.tanh), ("log2", math.log2), ("log10", math.log10),
+                        ("atan", math.atan), ("sinh", math.sinh), ("erf", math.erf), ("expm1", math.expm1),
+                        ("log1p", math.log1p), ("cbrt", lambda v: v ** (1 / 3))):
+            out = getattr(xp.NMath, name)(x).to_a()
+            for o, v in zip(out, vals):
+                assert abs(o - f(v)) <= rel * max(1.0, abs(f(v))), (name, o, f(v))
+        assert (x ** 2).to_a() == [v * v for v in vals]
+        out = xp.NMath.atan2(x, T.cast([1.0] * 5)).to_a()
+        for o, v in zip(out, vals):
+            assert abs(o - math.atan(v)) <= rel * 2
+
+
+ALL_CASES = [v for k, v in sorted(globals().items()) if k.startswith("case_")]

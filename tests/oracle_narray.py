@@ -1,0 +1,349 @@
+"""TEST INFRASTRUCTURE -- the CPU oracle dressed in the same method names as
+cumo_b200.narray, so one test body can run against either: `xp.SFloat[[1, 2], [3, 4]].sum(axis=0)`.
+
+Arrays are numpy arrays (views keep their strides); every computation goes to
+oracle/cumo_oracle.py, none is done with numpy arithmetic.
+"""
+from __future__ import annotations
+
+import sys
+from pathlib import Path
+
+import numpy as np
+
+sys.path.insert(0, str(Path(__file__).resolve().parent.parent))
+from oracle import cumo_oracle as orc  # noqa: E402
+
+
+def _axes(axis):
+    return axis
+
+
+class ONArray:
+    np_dtype = None
+
+    def __init__(self, *shape):
+        if len(shape) == 1 and isinstance(shape[0], (tuple, list)):
+            shape = tuple(shape[0])
+        self.a = np.zeros(shape, dtype=self.np_dtype)
+
+    new = classmethod(lambda cls, *shape: cls(*shape))
+
+    @classmethod
+    def _wrap(cls, a):
+        klass = _BY_DTYPE[np.dtype(a.dtype)]
+        o = object.__new__(klass)
+        o.a = a
+        return o
+
+    def __class_getitem__(cls, item):
+        data = list(item) if isinstance(item, tuple) else [item]
+        return cls.cast(data)
+
+    @classmethod
+    def cast(cls, data):
+        if isinstance(data, ONArray):
+            return cls._wrap(data.a.astype(cls.np_dtype))
+        return cls._wrap(np.array(data, dtype=cls.np_dtype))
+
+    from_numpy = cast
+
+    @classmethod
+    def zeros(cls, *shape):
+        return cls(*shape)
+
+    @classmethod
+    def ones(cls, *shape):
+        return cls(*shape).fill(1)
+
+    def fill(self, v):
+        self.a[...] = v
+        return self
+
+    def seq(self, start=0, step=1):
+        self.a[...] = (start + step * np.arange(self.a.size)).astype(self.np_dtype).reshape(self.a.shape)
+        return self
+
+    # facts / host copies
+    shape = property(lambda self: tuple(self.a.shape))
+    ndim = property(lambda self: self.a.ndim)
+    size = property(lambda self: int(self.a.size))
+
+    def to_numpy(self):
+        return np.array(self.a)
+
+    def to_a(self):
+        return self.a.tolist()
+
+    def extract(self):
+        return self.a.reshape(()).item()
+
+    __float__ = lambda self: float(self.extract())
+    __int__ = lambda self: int(self.extract())
+
+    # views
+    def __getitem__(self, key):
+        if not isinstance(key, tuple):
+            key = (key,)
+        key = tuple(slice(None) if k is True else k for k in key)
+        return self._wrap(self.a[key])
+
+    def transpose(self, *perm):
+        return self._wrap(self.a.transpose(*perm) if perm else self.a.T)
+
+    def reverse(self, axis=None):
+        return self._wrap(np.flip(self.a, axis))
+
+    def reshape(self, *shape):
+        if len(shape) == 1 and isinstance(shape[0], (tuple, list)):
+            shape = tuple(shape[0])
+        return self._wrap(np.array(self.a).reshape(shape))
+
+    def flatten(self):
+        return self.reshape(self.a.size)
+
+    def dup(self):
+        return self._wrap(np.array(self.a))
+
+    copy = dup
+
+    def contiguous(self):
+        return bool(self.a.flags["C_CONTIGUOUS"])
+
+    def inplace(self):
+        self._inplace = True
+        return self
+
+    # elementwise
+    def _operand(self, o):
+        """(array_self, other) with the reference's casting: arrays upcast, a Python float
+        against an integer array upcasts the array to DFloat."""
+        a = self.a
+        if isinstance(o, ONArray):
+            t = _upcast(a.dtype, o.a.dtype)
+            return a.astype(t) if a.dtype != t else a, o.a.astype(t) if o.a.dtype != t else o.a
+        if isinstance(o, (list, tuple, np.ndarray)):
+            return a, np.array(o, dtype=a.dtype)
+        if isinstance(o, (float, np.floating)) and np.issubdtype(a.dtype, np.integer):
+            a = a.astype(np.float64)
+        return a, o
+
+    def _binary(self, op, o, reflected=False):
+        x, y = self._operand(o)
+        if reflected:
+            x, y = y, x
+        out = None
+        if getattr(self, "_inplace", False) and isinstance(x, np.ndarray) and x is self.a:
+            self._inplace = False
+            out = self.a
+        res, flag = orc.binary(op, x, y, out)
+        if flag:
+            raise ZeroDivisionError("divided by 0")
+        return self._wrap(res)
+
+    __add__ = lambda s, o: s._binary("add", o)
+    __radd__ = lambda s, o: s._binary("add", o, True)
+    __sub__ = lambda s, o: s._binary("sub", o)
+    __rsub__ = lambda s, o: s._binary("sub", o, True)
+    __mul__ = lambda s, o: s._binary("mul", o)
+    __rmul__ = lambda s, o: s._binary("mul", o, True)
+    __truediv__ = lambda s, o: s._binary("div", o)
+    __rtruediv__ = lambda s, o: s._binary("div", o, True)
+    __mod__ = lambda s, o: s._binary("mod", o)
+    __rmod__ = lambda s, o: s._binary("mod", o, True)
+    __and__ = lambda s, o: s._binary("bit_and", o)
+    __or__ = lambda s, o: s._binary("bit_or", o)
+    __xor__ = lambda s, o: s._binary("bit_xor", o)
+    __lshift__ = lambda s, o: s._binary("left_shift", o)
+    __rshift__ = lambda s, o: s._binary("right_shift", o)
+
+    def __pow__(self, o):
+        if isinstance(o, (int, np.integer)) and not isinstance(o, bool):
+            return self._wrap(orc.pow_int(self.a, int(o)))
+        return self._binary("pow", o)
+
+    __rpow__ = lambda s, o: s._binary("pow", o, True)
+    copysign = lambda s, o: s._binary("copysign", o)
+
+    @classmethod
+    def maximum(cls, a, b, nan=False):
+        return cls.cast(a)._binary("maximum_nan" if nan else "maximum", cls.cast(b))
+
+    @classmethod
+    def minimum(cls, a, b, nan=False):
+        return cls.cast(a)._binary("minimum_nan" if nan else "minimum", cls.cast(b))
+
+    def _unary(self, op):
+        if np.issubdtype(self.a.dtype, np.integer) and op in ("floor", "round", "ceil", "trunc", "rint"):
+            return self._wrap(self.a)
+        res, flag = orc.unary(op, self.a)
+        if flag:
+            if op == "abs":
+                raise ValueError("cannot convert the minimum integer")
+            raise ZeroDivisionError("divided by 0")
+        return self._wrap(res)
+
+    __neg__ = lambda s: s._unary("minus")
+    __abs__ = lambda s: s._unary("abs")
+    __invert__ = lambda s: s._unary("bit_not")
+    for _n in ("abs", "minus", "reciprocal", "sign", "square", "floor", "round", "ceil", "trunc", "rint"):
+        locals()[_n] = (lambda n: lambda s: s._unary(n))(_n)
+    del _n
+
+    def _compare(self, op, o, reflected=False):
+        x, y = self._operand(o)
+        if reflected:
+            x, y = y, x
+        if op == "nearly_eq" and np.issubdtype((x if isinstance(x, np.ndarray) else y).dtype, np.integer):
+            op = "eq"
+        bits, _ = orc.compare(op, x, y)
+        return OBit._wrap_bits(bits)
+
+    for _n in ("eq", "ne", "gt", "ge", "lt", "le", "nearly_eq"):
+        locals()[_n] = (lambda n: lambda s, o: s._compare(n, o))(_n)
+    del _n
+    __gt__ = lambda s, o: s._compare("gt", o)
+    __ge__ = lambda s, o: s._compare("ge", o)
+    __lt__ = lambda s, o: s._compare("lt", o)
+    __le__ = lambda s, o: s._compare("le", o)
+    for _n in ("isnan", "isinf", "isposinf", "isneginf", "isfinite", "signbit"):
+        locals()[_n] = (lambda n: lambda s: OBit._wrap_bits(orc.compare(n, s.a)[0]))(_n)
+    del _n
+
+    # reductions
+    def _reduce(self, op, axis=None, keepdims=False, nan=False):
+        if self.a.size == 0 and op != "sum":
+            raise ShapeErrorO("cannot reduce an empty array")
+        a = self.a
+        if op in ("max_index", "min_index") and not a.flags["C_CONTIGUOUS"]:
+            a = np.ascontiguousarray(a)        # accum_index.c:121-129 copies a non-contiguous operand
+        return self._wrap(orc.reduce(op, a, axis=axis, nan=nan, keepdims=keepdims))
+
+    for _n in ("sum", "prod", "mean", "var", "stddev", "rms", "kahan_sum", "min", "max", "ptp"):
+        locals()[_n] = (lambda n: lambda s, axis=None, keepdims=False, nan=False: s._reduce(n, axis, keepdims, nan))(_n)
+    for _n in ("max_index", "min_index", "argmax", "argmin"):
+        locals()[_n] = (lambda n: lambda s, axis=None, nan=False: s._reduce(n, axis, False, nan))(_n)
+    del _n
+
+    def minmax(self, axis=None, keepdims=False, nan=False):
+        lo, hi = orc.reduce("minmax", self.a, axis=axis, nan=nan, keepdims=keepdims)
+        return self._wrap(lo), self._wrap(hi)
+
+    def mulsum(self, other, axis=None, keepdims=False, nan=False):
+        x, y = self._operand(other)
+        return self._wrap(orc.mulsum(x, y, axis=axis, nan=nan))
+
+
+class ShapeErrorO(Exception):
+    pass
+
+
+class OSFloat(ONArray):
+    np_dtype = np.float32
+
+
+class ODFloat(ONArray):
+    np_dtype = np.float64
+
+
+class OInt32(ONArray):
+    np_dtype = np.int32
+
+
+class OInt64(ONArray):
+    np_dtype = np.int64
+
+
+class OUInt64(ONArray):
+    np_dtype = np.uint64
+
+
+class OBit:
+    """Bits kept unpacked for views, packed on demand for the counting loop."""
+
+    def __init__(self, bits):
+        self.b = np.asarray(bits, dtype=bool)
+
+    _wrap_bits = classmethod(lambda cls, bits: cls(bits))
+
+    def __class_getitem__(cls, item):
+        data = list(item) if isinstance(item, tuple) else [item]
+        return cls(np.array(data).astype(bool))
+
+    cast = classmethod(lambda cls, data: cls(np.array(data).astype(bool)))
+    from_numpy = cast
+    shape = property(lambda self: tuple(self.b.shape))
+    ndim = property(lambda self: self.b.ndim)
+    size = property(lambda self: int(self.b.size))
+
+    def to_numpy(self):
+        return np.array(self.b)
+
+    def to_a(self):
+        return self.b.astype(np.int64).tolist()
+
+    def _count(self, axis, keepdims, want_false):
+        nd = self.b.ndim
+        axes = tuple(range(nd)) if axis is None else ((axis,) if isinstance(axis, int) else tuple(axis))
+        axes = tuple(ax % nd for ax in axes)
+        keep = [d for d in range(nd) if d not in axes]
+        moved = np.ascontiguousarray(self.b.transpose(keep + list(axes)))
+        n_red = int(np.prod([self.b.shape[d] for d in axes], dtype=np.int64)) if axes else 1
+        flat = moved.reshape(-1)
+        pad = (-flat.size) % 32
+        words = np.packbits(np.concatenate([flat, np.zeros(pad, bool)]), bitorder="little").view(np.uint32)
+        n_out = flat.size // n_red if n_red else 0
+        out = np.array([orc.bit_count(words, o * n_red, 1, n_red, want_false) for o in range(n_out)], dtype=np.uint64)
+        out = out.reshape([self.b.shape[d] for d in keep])
+        if keepdims:
+            out = out.reshape([1 if d in axes else self.b.shape[d] for d in range(nd)])
+        return OUInt64._wrap(out)
+
+    def count_true(self, axis=None, keepdims=False):
+        return self._count(axis, keepdims, False)
+
+    def count_false(self, axis=None, keepdims=False):
+        return self._count(axis, keepdims, True)
+
+    count = count_1 = count_true
+    count_0 = count_false
+
+
+_BY_DTYPE = {np.dtype(np.float32): OSFloat, np.dtype(np.float64): ODFloat, np.dtype(np.int32): OInt32,
+             np.dtype(np.int64): OInt64, np.dtype(np.uint64): OUInt64}
+
+
+def _upcast(ta, tb):
+    """gen/def/{sfloat,dfloat,int32,int64}.rb: any float beats any integer; wider wins within a kind."""
+    ta, tb = np.dtype(ta), np.dtype(tb)
+    if ta == tb:
+        return ta
+    if np.float64 in (ta, tb):
+        return np.dtype(np.float64)
+    if np.float32 in (ta, tb):
+        return np.dtype(np.float32)
+    return np.dtype(np.int64)
+
+
+class _ONMath:
+    _one = ("sqrt cbrt log log2 log10 exp exp2 exp10 sin cos tan asin acos atan sinh cosh tanh "
+            "asinh acosh atanh sinc erf erfc log1p expm1").split()
+
+    def __getattr__(self, name):
+        if name in self._one:
+            def f(x):
+                if np.issubdtype(x.a.dtype, np.integer):
+                    x = ODFloat.cast(x)
+                return x._unary(name)
+            return f
+        if name in ("atan2", "hypot", "ldexp"):
+            return lambda x, y: x._binary(name, y) if isinstance(x, ONArray) else y._binary(name, x, True)
+        raise AttributeError(name)
+
+
+class OracleXP:
+    """Namespace with the same names as the cumo_b200 package."""
+    SFloat, DFloat, Int32, Int64, UInt64, Bit = OSFloat, ODFloat, OInt32, OInt64, OUInt64, OBit
+    NMath = _ONMath()
+    ShapeError = ShapeErrorO
+    name = "oracle"

@@ -1,0 +1,382 @@
+"""Benchmark of the hot path: effective HBM GB/s of the broadcast-elementwise chain.
+
+A step is one pass of BASELINE config 1 over one batch of synthetic input on each GPU:
+    t = x(8192,1) + y(1,16384);  u = NMath.exp(t);  r = u * 0.5          (fp32, 512 MiB outputs)
+i.e. three kernels of libcumo_b200 reached through the reference-facing API (cumo_b200.narray ->
+host layer -> `cumo_iter_sfloat_*_kernel_launch`).  `value` is the algorithmic bytes of the three
+kernels (each distinct input element once, each output element once) over all GPUs divided by
+the device time of the timed steps, inputs resident in HBM.  `e2e` is the same chain with the
+inputs coming from pinned host memory and the result read back to pinned host memory inside the
+timed region.  With --gpus N (launched by torch.distributed.run) every rank runs the same workload
+on its own GPU (weak scaling, no data-path collective: rows are independent), and rank 0 also
+times the row-sharded full reduction that does need a collective and reports it under `sharded`.
+
+`--impl reference` times the CPU restatement of the reference's host loops (oracle/, all host
+threads) on a bounded sample of the same workload and prints the same line with impl=reference.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+from pathlib import Path
+
+import numpy as np
+
+ROOT = Path(__file__).resolve().parent
+sys.path.insert(0, str(ROOT))
+
+R, C = 8192, 16384                      # BASELINE config 1
+ES = 4
+BYTES_ADD = R * C * ES + (R + C) * ES   # outer broadcast add: output + the two vectors
+BYTES_EXP = 2 * R * C * ES
+BYTES_MUL = 2 * R * C * ES
+BYTES_STEP = BYTES_ADD + BYTES_EXP + BYTES_MUL
+METRIC = "effective HBM GB/s, fp32 broadcast-elementwise chain x(8192,1)+y(1,16384) -> exp -> *0.5"
+NOMINAL_HBM_GBS = 8000.0
+FALLBACK_HBM_GBS = 6650.0
+# dram__bytes_read.sum + dram__bytes_write.sum of one ew_row_kernel<Exp<float>,4> launch on this
+# workload, from the ncu capture summarised in profiles/; None until a capture exists.
+EXP_KERNEL_DRAM_TRAFFIC_BYTES = None
+
+
+def measured_peak():
+    p = ROOT / "MEASURED_PEAKS.json"
+    if p.exists():
+        try:
+            return float(json.loads(p.read_text())["hbm_gbs"]), "measured"
+        except Exception:
+            pass
+    return FALLBACK_HBM_GBS, "fallback"
+
+
+class ClockSampler:
+    """nvidia-smi clocks and throttle reasons of one GPU while a region runs."""
+    Q = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+         "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index, self.rows, self.proc = index, [], None
+
+    def __enter__(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "100"],
+                                         stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.t = threading.Thread(target=self._read, daemon=True)
+            self.t.start()
+        except OSError:
+            self.proc = None
+        return self
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([c.strip() for c in line.split(",")])
+
+    def __exit__(self, *exc):
+        if self.proc:
+            time.sleep(0.15)
+            self.proc.terminate()
+            self.t.join(timeout=2)
+
+    def summary(self):
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for r in self.rows:
+            try:
+                sm.append(float(r[0])); mx.append(float(r[1]))
+            except (ValueError, IndexError):
+                continue
+            for n, v in zip(names, r[2:6]):
+                if v.lower().startswith("active"):
+                    reasons.add(n)
+        if not sm:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
+        return {"sm_mhz": float(np.median(sm)), "sm_max_mhz": max(mx), "reasons": sorted(reasons), "samples": len(sm)}
+
+
+def oracle_chain(hx, hy, rows):
+    """The chain on the first `rows` rows with the CPU oracle; returns seconds."""
+    sys.path.insert(0, str(ROOT / "tests"))
+    from oracle_narray import OracleXP as ox
+
+    x, y = ox.SFloat.cast(hx[:rows]), ox.SFloat.cast(hy)
+    t0 = time.perf_counter()
+    r = ox.NMath.exp(x + y) * 0.5
+    dt = time.perf_counter() - t0
+    assert r.shape == (rows, C)
+    return dt
+
+
+def sample_bytes(rows):
+    return (rows * C * ES + (rows + C) * ES) + 4 * rows * C * ES
+
+
+def run_reference(args):
+    """Reference arm: the reference's CPU algorithm (oracle port), all host threads, bounded sample per step."""
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    from oracle import cumo_oracle as orc
+
+    cores = os.cpu_count() or 1
+    orc.set_threads(cores)
+    rng = np.random.default_rng(1)
+    hx = rng.standard_normal((R, 1)).astype(np.float32)
+    hy = rng.standard_normal((1, C)).astype(np.float32)
+    rows = 1024                                    # 1/8 of the workload per step
+    for _ in range(args.warmup):
+        oracle_chain(hx, hy, rows)
+    t = [oracle_chain(hx, hy, rows) for _ in range(args.steps)]
+    sec = float(np.sum(t))
+    value = sample_bytes(rows) * args.steps / sec / 1e9
+    line = {"impl": "reference", "metric": METRIC, "value": value, "unit": "GB/s", "n_gpus": args.gpus, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": sec / args.steps * 1e3, "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "config": {"workload": "BASELINE config 1: x(8192,1)+y(1,16384), exp, *0.5 (fp32)", "sample": f"first {rows} of {R} rows per step"},
+            "cpu_baseline": {"value": value, "unit": "GB/s", "cores": orc.threads(), "kind": "port",
+                             "sample": f"{rows} of {R} rows per step, {args.steps} steps, CPU restatement of the reference's host loops (no Ruby here to run Numo)"},
+            "e2e": {"value": value, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
+    print(json.dumps(line), flush=True)
+
+
+def time_kernel(torch, fn, reps=10, warm=2):
+    """Median / min device time (ms) of fn() measured launch by launch with CUDA events on the launch stream."""
+    for _ in range(warm):
+        fn()
+    ts = []
+    for _ in range(reps):
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        fn()
+        b.record()
+        b.synchronize()
+        ts.append(a.elapsed_time(b))
+    return float(np.median(ts)), float(np.min(ts))
+
+
+def kernel_table(torch, xp, peak):
+    """Per-kernel effective GB/s at the BASELINE sizes (1 GPU, inputs resident, arrays >= 256 MB except C1)."""
+    rows = []
+
+    def add(config, name, nbytes, fn):
+        med, best = time_kernel(torch, fn)
+        gbs = nbytes / (med * 1e-3) / 1e9
+        rows.append({"config": config, "kernel": name, "bytes": int(nbytes), "ms": round(med, 4), "ms_min": round(best, 4),
+                     "GBps": round(gbs, 1), "frac_of_measured": round(gbs / peak, 3), "frac_of_nominal": round(gbs / NOMINAL_HBM_GBS, 3)})
+
+    g = torch.Generator(device="cuda").manual_seed(0)
+    MiB = 1 << 20
+    # C1 scaled to 16384^2 (1 GiB) and at its own 4096^2 (64 MiB, below the 256 MB bar: reported only)
+    for n, tag in ((16384, "C1x16"), (4096, "C1")):
+        a = xp.SFloat.from_torch(torch.rand(n, n, device="cuda", generator=g) * 2 - 1)
+        b = xp.SFloat.from_torch(torch.rand(n, n, device="cuda", generator=g) * 2 - 1)
+        s = n * n * 4
+        add(tag, "a*b", 3 * s, lambda: a * b)
+        add(tag, "a.sum(axis:1)", s + n * 4, lambda: a.sum(axis=1))
+        col = a.sum(axis=1).reshape(n, 1)
+        add(tag, "a + col(n,1)", 2 * s + n * 4, lambda: a + col)
+        add(tag, "c.sum(axis:0)", s + n * 4, lambda: a.sum(axis=0))
+        add(tag, "c.max_index(axis:1)", s + n * 4, lambda: a.max_index(axis=1))
+        del a, b, col
+    # C2
+    x = xp.SFloat.from_torch(torch.randn(R, 1, device="cuda", generator=g))
+    y = xp.SFloat.from_torch(torch.randn(1, C, device="cuda", generator=g))
+    t = x + y
+    add("C2", "x(8192,1)+y(1,16384)", BYTES_ADD, lambda: x + y)
+    add("C2", "exp", BYTES_EXP, lambda: xp.NMath.exp(t))
+    add("C2", "*0.5", BYTES_MUL, lambda: t * 0.5)
+    del t
+    # C3
+    for T, tt, es, tag in ((xp.SFloat, torch.float32, 4, "f32"), (xp.DFloat, torch.float64, 8, "f64")):
+        v = T.from_torch(torch.rand(1 << 28, device="cuda", dtype=tt, generator=g))
+        s = (1 << 28) * es
+        for op in ("sum", "mean", "max", "min", "argmax"):
+            add("C3", f"{tag} 2^28 {op}", s + (4 if op == "argmax" else es), lambda op=op: getattr(v, op)())
+        m = v.reshape(65536, 4096)
+        for ax, n_out in ((0, 4096), (1, 65536)):
+            for op in ("sum", "mean", "max", "min", "argmax"):
+                add("C3", f"{tag} (65536,4096) {op}(axis:{ax})", s + n_out * (4 if op == "argmax" else es), lambda op=op, ax=ax: getattr(m, op)(axis=ax))
+        del v, m
+    # C4
+    ia = xp.Int32.from_torch(torch.randint(-(1 << 20), 1 << 20, (1 << 27,), device="cuda", dtype=torch.int32, generator=g))
+    ib = xp.Int32.from_torch(torch.randint(-(1 << 20), 1 << 20, (1 << 27,), device="cuda", dtype=torch.int32, generator=g))
+    s = (1 << 27) * 4
+    add("C4", "a*3", 2 * s, lambda: ia * 3)
+    add("C4", "+b", 3 * s, lambda: ia + ib)
+    add("C4", "%7 (incl. the flag sync)", 2 * s, lambda: ia % 7)
+    add("C4", "a>0 -> Bit", s + s // 32, lambda: ia > 0)
+    mask = ia > 0
+    add("C4", "count_true", s // 32 + 8, lambda: mask.count_true())
+    im = ia.reshape(32768, 4096)
+    add("C4", "max_index(axis:1) (32768,4096)", s + 32768 * 4, lambda: im.max_index(axis=1))
+    add("C4", "Int32 sum -> Int64", s + 8, lambda: ia.sum())
+    return rows
+
+
+def run_ours(args):
+    import torch
+    import torch.distributed as dist
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if world != args.gpus and world > 1:
+        raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={world}")
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: libcumo_b200 has no CPU path (use --impl reference for the CPU arm)")
+    torch.cuda.set_device(local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+
+    import cumo_b200 as xp
+    from cumo_b200 import _lib
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    rng = np.random.default_rng(1 + rank)
+    hx = torch.from_numpy(rng.standard_normal((R, 1)).astype(np.float32)).pin_memory()
+    hy = torch.from_numpy(rng.standard_normal((1, C)).astype(np.float32)).pin_memory()
+    hout = torch.empty((R, C), dtype=torch.float32).pin_memory()
+
+    def upload():
+        return (xp.SFloat.from_host_pointer(hx.data_ptr(), (R, 1), R * ES), xp.SFloat.from_host_pointer(hy.data_ptr(), (1, C), C * ES))
+
+    def chain(x, y):
+        return xp.NMath.exp(x + y) * 0.5
+
+    gx, gy = upload()
+    xp.synchronize()
+    for _ in range(args.warmup):
+        chain(gx, gy)
+    barrier()
+    c0 = _lib.launch_count()
+    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    with ClockSampler(local) as clocks:
+        start.record()
+        for _ in range(args.steps):
+            chain(gx, gy)
+        stop.record()
+        barrier()
+    launches = _lib.launch_count() - c0
+    ms = torch.tensor([start.elapsed_time(stop)], device="cuda")
+    if world > 1:
+        dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+    ms = float(ms.item())
+    value = BYTES_STEP * world * args.steps / (ms * 1e-3) / 1e9
+
+    # end to end: host buffers in, host buffer out, copies inside the timed region
+    for _ in range(min(2, args.warmup)):
+        x, y = upload()
+        r = chain(x, y)
+        _lib.load().cb200_na_read_host(r._h, hout.data_ptr(), R * C * ES)
+    barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(args.steps):
+        x, y = upload()
+        r = chain(x, y)
+        if _lib.load().cb200_na_read_host(r._h, hout.data_ptr(), R * C * ES):
+            raise SystemExit("read_host failed")
+    e1.record()
+    barrier()
+    e2e_ms = torch.tensor([e0.elapsed_time(e1)], device="cuda")
+    if world > 1:
+        dist.all_reduce(e2e_ms, op=dist.ReduceOp.MAX)
+    e2e_value = BYTES_STEP * world * args.steps / (float(e2e_ms.item()) * 1e-3) / 1e9
+
+    peak, peak_kind = measured_peak()
+    line = None
+    if rank == 0:
+        # roofline of the dominant kernel (exp: 1 GiB algorithmic bytes per launch), timed launch by launch
+        t = gx + gy
+        med, _ = time_kernel(torch, lambda: xp.NMath.exp(t), reps=max(5, args.steps))
+        achieved = BYTES_EXP / (med * 1e-3) / 1e9
+        del t
+        line = {"metric": METRIC, "value": value, "unit": "GB/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+                "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+                "dtype": "f32", "data": "synthetic",
+                "config": {"workload": "BASELINE config 1: x(8192,1)+y(1,16384), exp, *0.5 (fp32), per GPU", "rows_per_gpu": R, "cols": C,
+                           "algorithmic_bytes_per_step_per_gpu": BYTES_STEP, "l2": "every kernel streams >= 512 MiB, 4x the 126 MB L2; no flush",
+                           "partition": "independent row blocks per GPU, no data-path collective"},
+                "gpu_launches": int(launches) * world,
+                "e2e": {"value": e2e_value, "unit": "GB/s", "h2d_bytes_per_step": (R + C) * ES, "d2h_bytes_per_step": R * C * ES,
+                        "ms_per_step": float(e2e_ms.item()) / args.steps},
+                "roofline": {"bound": "hbm", "kernel": "ew_row_kernel<Exp<float>,4>", "achieved": achieved, "peak": peak, "peak_kind": peak_kind,
+                             "unit": "GB/s", "frac": achieved / peak, "frac_of_nominal_8TBps": achieved / NOMINAL_HBM_GBS,
+                             "traffic": EXP_KERNEL_DRAM_TRAFFIC_BYTES, "algorithmic_bytes_per_launch": BYTES_EXP, "ms_per_launch": med},
+                "chain_frac_of_peak": value / world / peak,
+                "clocks": clocks.summary()}
+    if world > 1:
+        sharded = sharded_section(torch, dist, xp, rank, world)
+        if rank == 0:
+            line["sharded"] = sharded
+    if rank == 0 and world == 1:
+        rows = 2048
+        from oracle import cumo_oracle as orc
+        orc.set_threads(1)
+        sec = oracle_chain(hx.numpy(), hy.numpy(), rows)
+        line["cpu_baseline"] = {"value": sample_bytes(rows) / sec / 1e9, "unit": "GB/s", "cores": 1, "kind": "port",
+                                "sample": f"first {rows} of {R} rows of the same workload, one pass, single thread like Numo ({os.cpu_count()} host cores present)"}
+        if not args.no_kernels:
+            line["kernels"] = kernel_table(torch, xp, peak)
+    if rank == 0:
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def sharded_section(torch, dist, xp, rank, world):
+    """Row-sharded reductions that need a collective: 2^28 fp32 elements per GPU, and a (65536,4096) block per GPU."""
+    from cumo_b200.sharded import Comm, ShardedArray
+
+    comm = Comm(xp)
+    g = torch.Generator(device="cuda").manual_seed(100 + rank)
+    n = 1 << 28
+    v = xp.SFloat.from_torch(torch.rand(n, device="cuda", generator=g))
+    sv = ShardedArray(comm, v, n * world, n * rank)
+    m = v.reshape(65536, 4096)
+    sm = ShardedArray(comm, m, 65536 * world, 65536 * rank)
+    out = []
+    for name, fn, nbytes in (("sum 1-D 2^28/GPU", lambda: sv.sum(), n * 4), ("argmax 1-D 2^28/GPU", lambda: sv.argmax(), n * 4),
+                             ("sum(axis:0) (65536,4096)/GPU", lambda: sm.sum(axis=0), n * 4), ("max(axis:0) (65536,4096)/GPU", lambda: sm.max(axis=0), n * 4)):
+        for _ in range(2):
+            fn()
+        dist.barrier(); torch.cuda.synchronize()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        reps = 5
+        a.record()
+        for _ in range(reps):
+            fn()
+        b.record()
+        torch.cuda.synchronize()
+        ms = torch.tensor([a.elapsed_time(b) / reps], device="cuda")
+        dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+        out.append({"op": name, "ms": float(ms.item()), "aggregate_GBps": nbytes * world / (float(ms.item()) * 1e-3) / 1e9})
+    return out
+
+
+def main():
+    ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
+    ap.add_argument("--no-kernels", action="store_true", help="skip the per-kernel table of the other BASELINE configs")
+    args = ap.parse_args()
+    if args.warmup < 3:
+        args.warmup = 3
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()

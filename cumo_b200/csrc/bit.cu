@@ -3,12 +3,12 @@
 // Replaces ext/cumo/narray/gen/tmpl_bit/bit_count_kernel.cu:4-78, where one thread
 // looks at one bit and every set bit costs an atomicAdd on the single output word.
 // Here a contiguous run of bits (bit step 1) is read as 16-byte packets of four
-// 32-bit words, each masked at the run's two ends and counted with __popc; CTAs
-// write their partial counts to scratch and one warp adds them in CTA order, so
-// the count involves no atomics and no ordering question.  Strided bit runs take
-// one bit per thread but fold the same way.  The output is accumulated into
-// (`+=`), as the reference does, because ndloop pre-fills it with 0 and may call
-// once per outer index.
+// 32-bit words, each masked at the run's two ends and counted with __popc; every
+// CTA folds its count in registers/shared memory and adds it to the output with
+// ONE atomicAdd (integer addition commutes, so the total is exact in any order;
+// no scratch, no second launch).  Strided bit runs take one bit per thread but
+// fold the same way.  The output is accumulated into (`+=`), as the reference
+// does, because ndloop pre-fills it with 0 and may call once per outer index.
 #include "common.cuh"
 #include "reduce.cuh"
 
@@ -20,15 +20,26 @@ struct CountR {
     __device__ __forceinline__ Acc combine(Acc a, Acc b) const { return a + b; }
 };
 
+// count_false: CTA 0 adds the number of bits looked at and every CTA subtracts its
+// own count of set bits (arithmetic modulo 2^64, so the order still does not matter).
+__device__ __forceinline__ void add_count(unsigned long long* out, unsigned long long acc, unsigned long long n_bits, int want_false) {
+    if (want_false) {
+        if (blockIdx.x == 0) atomicAdd(out, n_bits);
+        if (acc) atomicAdd(out, 0ull - acc);
+    } else if (acc) {
+        atomicAdd(out, acc);
+    }
+}
+
 // bits [first, first+n) of the word array, contiguous.  Words are visited as
 // 16-byte packets starting from the 16-byte-aligned address at or below the first word.
 __global__ void __launch_bounds__(kBlock)
 bitcount_run_kernel(const uint32_t* __restrict__ words16, int64_t w_base, int64_t w_first, int64_t w_last,
-                    uint32_t head_mask, uint32_t tail_mask, int64_t n_packets, unsigned long long* partial) {
+                    uint32_t head_mask, uint32_t tail_mask, int64_t n_packets, int64_t per_cta,
+                    unsigned long long n_bits, int want_false, unsigned long long* out) {
     __shared__ unsigned long long smem[kWarpsPerBlock];
     CountR r;
     unsigned long long acc = 0;
-    const int64_t per_cta = (n_packets + gridDim.x - 1) / gridDim.x;
     const int64_t p_begin = (int64_t)blockIdx.x * per_cta;
     int64_t p_end = p_begin + per_cta; if (p_end > n_packets) p_end = n_packets;
     for (int64_t q0 = p_begin + threadIdx.x; q0 < p_end; q0 += (int64_t)kBlock * kUnroll) {
@@ -54,17 +65,16 @@ bitcount_run_kernel(const uint32_t* __restrict__ words16, int64_t w_base, int64_
         }
     }
     acc = group_fold<CountR, kBlock>(r, acc, smem);
-    if (threadIdx.x == 0) partial[blockIdx.x] = acc;
+    if (threadIdx.x == 0) add_count(out, acc, n_bits, want_false);
 }
 
 // bits at first + i*step (or first + idx[i]), one per thread
 __global__ void __launch_bounds__(kBlock)
 bitcount_strided_kernel(const uint32_t* __restrict__ words, uint64_t first, int64_t step, const size_t* __restrict__ idx,
-                        int64_t n, unsigned long long* partial) {
+                        int64_t n, int64_t per_cta, int want_false, unsigned long long* out) {
     __shared__ unsigned long long smem[kWarpsPerBlock];
     CountR r;
     unsigned long long acc = 0;
-    const int64_t per_cta = (n + gridDim.x - 1) / gridDim.x;
     const int64_t begin = (int64_t)blockIdx.x * per_cta;
     int64_t end = begin + per_cta; if (end > n) end = n;
     for (int64_t i = begin + threadIdx.x; i < end; i += kBlock) {
@@ -72,20 +82,7 @@ bitcount_strided_kernel(const uint32_t* __restrict__ words, uint64_t first, int6
         acc += (words[b >> 5] >> (b & 31)) & 1u;
     }
     acc = group_fold<CountR, kBlock>(r, acc, smem);
-    if (threadIdx.x == 0) partial[blockIdx.x] = acc;
-}
-
-// *out += (count_false ? n - total : total), partials added in CTA order
-__global__ void __launch_bounds__(32)
-bitcount_fold_kernel(const unsigned long long* __restrict__ partial, int n_part, unsigned long long n_bits,
-                     int want_false, unsigned long long* out) {
-    CountR r;
-    const int lane = threadIdx.x;
-    const int per = (n_part + 31) / 32;
-    unsigned long long acc = 0;
-    for (int k = 0; k < per; ++k) { int s = lane * per + k; if (s < n_part) acc += partial[s]; }
-    acc = warp_fold(r, acc);
-    if (lane == 0) *out += want_false ? n_bits - acc : acc;
+    if (threadIdx.x == 0) add_count(out, acc, (unsigned long long)n, want_false);
 }
 
 // out[i] += bit_i (or its complement): the loop dimension is not reduced
@@ -100,13 +97,19 @@ bitcount_each_kernel(const uint32_t* __restrict__ words, uint64_t first, int64_t
     }
 }
 
+// CTAs for `units` units of work at `base` units per CTA, growing the share so that at
+// most kMaxCtas CTAs (= atomics on the one output word) are launched
+static int64_t share_per_cta(int64_t units, int64_t base) {
+    constexpr int64_t kMaxCtas = 8192;
+    int64_t per = base;
+    if ((units + per - 1) / per > kMaxCtas) per = ((units + kMaxCtas - 1) / kMaxCtas + base - 1) / base * base;
+    return per;
+}
+
 static void count_total(size_t p1, char* p2, const uint32_t* a1, ssize_t s1, const size_t* idx, uint64_t n, int want_false) {
     if (n == 0) return;
     cudaStream_t st = current_stream();
     unsigned long long* out = reinterpret_cast<unsigned long long*>(p2);
-    const int64_t cap = (int64_t)sm_count() * 8;
-    unsigned long long* partial = nullptr;
-    int n_part = 1;
     if (!idx && s1 == 1) {
         const int64_t w_first = (int64_t)(p1 >> 5), w_last = (int64_t)((p1 + n - 1) >> 5);
         const uint32_t head = 0xffffffffu << (p1 & 31);
@@ -119,21 +122,16 @@ static void count_total(size_t p1, char* p2, const uint32_t* a1, ssize_t s1, con
         const uint32_t* words16 = a1 + w_first - back;
         const int64_t w_base = w_first - back;
         const int64_t n_packets = (w_last - w_base) / 4 + 1;
-        int64_t want = n_packets / (kBlock * kUnroll);
-        n_part = (int)(want < 1 ? 1 : (want > cap ? cap : want));
-        partial = reinterpret_cast<unsigned long long*>(cumo_cuda_runtime_malloc(sizeof(unsigned long long) * n_part));
-        if (!partial) { cumo_cuda_runtime_check_kernel_launch(); return; }
-        bitcount_run_kernel<<<n_part, kBlock, 0, st>>>(words16, w_base, w_first, w_last, head, tail, n_packets, partial);
+        const int64_t per_cta = share_per_cta(n_packets, (int64_t)kBlock * kUnroll);
+        const int64_t ctas = (n_packets + per_cta - 1) / per_cta;
+        bitcount_run_kernel<<<(unsigned)ctas, kBlock, 0, st>>>(words16, w_base, w_first, w_last, head, tail, n_packets, per_cta,
+                                                               (unsigned long long)n, want_false, out);
     } else {
-        int64_t want = (int64_t)n / (kBlock * kUnroll);
-        n_part = (int)(want < 1 ? 1 : (want > cap ? cap : want));
-        partial = reinterpret_cast<unsigned long long*>(cumo_cuda_runtime_malloc(sizeof(unsigned long long) * n_part));
-        if (!partial) { cumo_cuda_runtime_check_kernel_launch(); return; }
-        bitcount_strided_kernel<<<n_part, kBlock, 0, st>>>(a1, (uint64_t)p1, (int64_t)s1, idx, (int64_t)n, partial);
+        const int64_t per_cta = share_per_cta((int64_t)n, (int64_t)kBlock * kUnroll);
+        const int64_t ctas = ((int64_t)n + per_cta - 1) / per_cta;
+        bitcount_strided_kernel<<<(unsigned)ctas, kBlock, 0, st>>>(a1, (uint64_t)p1, (int64_t)s1, idx, (int64_t)n, per_cta, want_false, out);
     }
-    bitcount_fold_kernel<<<1, 32, 0, st>>>(partial, n_part, (unsigned long long)n, want_false, out);
-    cumo_cuda_runtime_free(reinterpret_cast<char*>(partial));
-    count_launch(2);
+    count_launch(1);
     cumo_cuda_runtime_check_kernel_launch();
 }
 

@@ -9,15 +9,17 @@
 //   * the host canonicalises the descriptor (drops extent-1 dims, merges dims
 //     that every operand walks with one stride) and classifies it;
 //   * ROW kernel: every operand's innermost step is the element size or 0
-//     (broadcast).  A CTA tile is 1024 "slots" of one 16-byte packet each,
-//     laid over (row, column-packet); outer dims are decomposed once per slot
-//     (one multiply when only one outer dim is left), never per element.
-//     Covers contiguous, (R,C)o(R,1), (R,C)o(1,C), (R,1)o(1,C), sliced views
-//     with a contiguous inner dim.  16-byte streaming loads/stores, 4 packets
-//     per operand in flight per thread;
+//     (broadcast).  One CTA = one tile of 512 "slots" of one 16-byte packet each,
+//     laid over (row, column-packet), two packets per operand in flight per
+//     thread, a grid of as many CTAs as there are tiles (measured on B200: many
+//     small CTAs stream ~10% faster than a persistent grid-stride loop).  Index
+//     arithmetic is 32-bit and per slot, never per element: one multiply per
+//     operand when at most one outer dim is left (contiguous, (R,C)o(R,1),
+//     (R,C)o(1,C), (R,1)o(1,C), row-sliced views), a short division chain when
+//     several outer dims survive canonicalisation;
 //   * GEN kernel: anything else (transposed operands, negative or non-unit
-//     inner steps).  One element per slot, consecutive threads on consecutive
-//     logical elements, index split in 32-bit arithmetic.
+//     inner steps, operands of different element sizes).  One element per slot,
+//     consecutive threads on consecutive logical elements.
 //   * comparisons write whole 32-bit words assembled with a warp OR-reduce /
 //     ballot when the Bit output is contiguous and word aligned; one atomic per
 //     element (the reference's CUMO_STORE_BIT, template_kernel.h:26-35) only
@@ -29,7 +31,9 @@
 
 namespace cb200 {
 
-constexpr int kSlots = kBlock * kUnroll;      // slots per CTA tile
+constexpr int kEwUnroll = 2;                     // packets per operand in flight per thread
+constexpr int kEwSlots = kBlock * kEwUnroll;     // slots per CTA tile
+constexpr int64_t kMaxGrid = 0x7fffffffLL;
 
 struct EwPlan {
     int nd;                                   // canonical dims, >= 1
@@ -41,11 +45,12 @@ struct EwPlan {
 struct RowGeom {
     int64_t L;                                // inner extent (elements)
     int64_t R;                                // rows = total / L
-    int64_t vpr;                              // slots per row = ceil(L / V)
     int64_t n_tiles;
-    int32_t rows_per_tile;                    // >1: several rows per tile; 1 and chunks>1: chunked rows
-    int32_t chunks_per_row;
-    int32_t inner[3];                         // inner step in elements: 1 or 0
+    int64_t rs[3];                            // row step (bytes) per operand when one outer dim is left
+    uint32_t vpr;                             // slots per row = ceil(L / V)
+    uint32_t rows_per_tile;                   // >1: several rows per tile
+    uint32_t chunks_per_row;                  // >1: several tiles per row
+    int32_t inner[2];                         // inner step of the inputs in elements: 1 or 0
 };
 
 // Canonical plan from up to two input descriptors and an output step array.
@@ -81,9 +86,9 @@ inline bool make_plan(EwPlan* p, const cumo_na_indexer_t* ix, const ssize_t* s1,
 }
 
 // ----------------------------------------------------------------------------
-// ROW kernel
+// ROW kernel.  ND: more than one outer dim (offsets from an index split).
 // ----------------------------------------------------------------------------
-template <typename Op, int V>
+template <typename Op, int V, bool ND>
 __global__ void __launch_bounds__(kBlock)
 ew_row_kernel(const EwPlan p, const RowGeom g, const char* __restrict__ a1, const char* __restrict__ a2,
               char* a3, typename Op::In1 sx, typename Op::In2 sy, int use_scalar, int* flag) {
@@ -92,97 +97,100 @@ ew_row_kernel(const EwPlan p, const RowGeom g, const char* __restrict__ a1, cons
     using TO = typename Op::Out;
     static_assert(sizeof(T1) == sizeof(TO) && sizeof(T2) == sizeof(TO), "row kernel needs equal element sizes");
     constexpr int ES = sizeof(TO);
+    constexpr int U = kEwUnroll;
     const bool have1 = use_scalar != 2;
     const bool have2 = Op::arity == 2 && use_scalar != 1;
-    const int nd_outer = p.nd - 1;
 
-    for (int64_t tile = blockIdx.x; tile < g.n_tiles; tile += gridDim.x) {
-        int64_t off[kUnroll][3];
-        int64_t col[kUnroll];
-        bool ok[kUnroll];
-        // where each of my slots lies
+    for (int64_t tile = blockIdx.x; tile < g.n_tiles; tile += gridDim.x) {   // one pass unless the grid was capped
+        int64_t row[U];
+        uint32_t col[U];                       // first element of my packet within the row
+        bool ok[U];
         if (g.rows_per_tile == 1) {
-            int64_t row = tile / g.chunks_per_row;
-            int64_t c0 = (tile - row * g.chunks_per_row) * kSlots;
-            int64_t ro[3];
-            offsets_of<3>(row, nd_outer, p.shape, p.step, ro);
+            int64_t r;
+            uint32_t ch;
+            if (tile <= 0xffffffffLL) {        // 32-bit division: this sits on every CTA's critical path
+                const uint32_t t = (uint32_t)tile, rr = t / g.chunks_per_row;
+                r = rr; ch = t - rr * g.chunks_per_row;
+            } else {
+                r = tile / g.chunks_per_row; ch = (uint32_t)(tile - r * g.chunks_per_row);
+            }
 #pragma unroll
-            for (int j = 0; j < kUnroll; ++j) {
-                int64_t c = c0 + j * kBlock + threadIdx.x;
-                col[j] = c * V;
-                ok[j] = col[j] < g.L;
-                off[j][0] = ro[0]; off[j][1] = ro[1]; off[j][2] = ro[2];
+            for (int j = 0; j < U; ++j) {
+                row[j] = r;
+                uint64_t c = ((uint64_t)ch * kEwSlots + j * kBlock + threadIdx.x) * V;
+                ok[j] = c < (uint64_t)g.L;
+                col[j] = (uint32_t)c;
             }
         } else {
-            const uint32_t vpr = (uint32_t)g.vpr;
-            const uint32_t live = vpr * (uint32_t)g.rows_per_tile;
+            const uint32_t live = g.vpr * g.rows_per_tile;
 #pragma unroll
-            for (int j = 0; j < kUnroll; ++j) {
-                uint32_t k = j * kBlock + threadIdx.x;
-                uint32_t r = k / vpr;
-                uint32_t c = k - r * vpr;
-                int64_t row = tile * g.rows_per_tile + r;
-                col[j] = (int64_t)c * V;
-                ok[j] = k < live && row < g.R;
-                if (ok[j]) offsets_of<3>(row, nd_outer, p.shape, p.step, off[j]);
+            for (int j = 0; j < U; ++j) {
+                const uint32_t k = j * kBlock + threadIdx.x;
+                const uint32_t r = k / g.vpr;
+                col[j] = (k - r * g.vpr) * V;
+                row[j] = tile * g.rows_per_tile + r;
+                ok[j] = k < live && row[j] < g.R;
+            }
+        }
+        int64_t off[U][3];
+#pragma unroll
+        for (int j = 0; j < U; ++j) {
+            if (ND) {
+                if (ok[j]) offsets_of<3>(row[j], p.nd - 1, p.shape, p.step, off[j]);
+            } else {
+                off[j][0] = row[j] * g.rs[0]; off[j][1] = row[j] * g.rs[1]; off[j][2] = row[j] * g.rs[2];
             }
         }
 
-        // issue every load of the tile before the first use
-        Pack<TO> x[kUnroll], y[kUnroll];
-        int nv[kUnroll];
+        // issue every load of the tile before the first use.  The host only picks V > 1 when
+        // the inner extent is a multiple of V, so a live slot always holds a whole packet.
+        Pack<T1> x[U];
+        Pack<T2> y[U];
 #pragma unroll
-        for (int j = 0; j < kUnroll; ++j) {
-            nv[j] = 0;
+        for (int j = 0; j < U; ++j) {
             if (!ok[j]) continue;
-            int64_t left = g.L - col[j];
-            nv[j] = left < V ? (int)left : V;
             if (have1) {
-                const char* q = a1 + off[j][0] + col[j] * g.inner[0] * ES;
+                const char* q = a1 + off[j][0] + (int64_t)col[j] * (g.inner[0] * ES);
                 if (g.inner[0] == 0) {
                     T1 s = ld_one<T1>(q);
 #pragma unroll
-                    for (int e = 0; e < V; ++e) reinterpret_cast<T1*>(&x[j])[e] = s;
-                } else if (V > 1 && nv[j] == V) {
-                    *reinterpret_cast<Pack<T1>*>(&x[j]) = ld_pack<T1>(q);
+                    for (int e = 0; e < V; ++e) x[j].v[e] = s;
                 } else {
-#pragma unroll
-                    for (int e = 0; e < V; ++e)
-                        if (e < nv[j]) reinterpret_cast<T1*>(&x[j])[e] = ld_one<T1>(q + e * ES);
+                    if (V > 1) x[j] = ld_pack<T1>(q); else x[j].v[0] = ld_one<T1>(q);
                 }
+            } else {
+#pragma unroll
+                for (int e = 0; e < V; ++e) x[j].v[e] = sx;
             }
             if (have2) {
-                const char* q = a2 + off[j][1] + col[j] * g.inner[1] * ES;
+                const char* q = a2 + off[j][1] + (int64_t)col[j] * (g.inner[1] * ES);
                 if (g.inner[1] == 0) {
                     T2 s = ld_one<T2>(q);
 #pragma unroll
-                    for (int e = 0; e < V; ++e) reinterpret_cast<T2*>(&y[j])[e] = s;
-                } else if (V > 1 && nv[j] == V) {
-                    *reinterpret_cast<Pack<T2>*>(&y[j]) = ld_pack<T2>(q);
+                    for (int e = 0; e < V; ++e) y[j].v[e] = s;
                 } else {
-#pragma unroll
-                    for (int e = 0; e < V; ++e)
-                        if (e < nv[j]) reinterpret_cast<T2*>(&y[j])[e] = ld_one<T2>(q + e * ES);
+                    if (V > 1) y[j] = ld_pack<T2>(q); else y[j].v[0] = ld_one<T2>(q);
                 }
+            } else {
+#pragma unroll
+                for (int e = 0; e < V; ++e) y[j].v[e] = sy;
             }
         }
 
 #pragma unroll
-        for (int j = 0; j < kUnroll; ++j) {
+        for (int j = 0; j < U; ++j) {
             if (!ok[j]) continue;
-            char* q = a3 + off[j][2] + col[j] * ES;
+            char* q = a3 + off[j][2] + (int64_t)col[j] * ES;
             Pack<TO> z;
-            unsigned keep = 0;
+            unsigned keep = 0;                 // folds to a constant for operations that never skip
 #pragma unroll
             for (int e = 0; e < V; ++e) {
-                T1 xv = have1 ? reinterpret_cast<T1*>(&x[j])[e] : sx;
-                T2 yv = have2 ? reinterpret_cast<T2*>(&y[j])[e] : sy;
                 TO zv = TO();
-                if (e < nv[j] && Op::apply(xv, yv, zv, flag)) keep |= 1u << e;
+                if (Op::apply(x[j].v[e], y[j].v[e], zv, flag)) keep |= 1u << e;
                 z.v[e] = zv;
             }
-            if (V > 1 && keep == (1u << V) - 1u) {
-                st_pack<TO>(q, z);
+            if (keep == (1u << V) - 1u) {
+                if (V > 1) st_pack<TO>(q, z); else st_one<TO>(q, z.v[0]);
             } else {
 #pragma unroll
                 for (int e = 0; e < V; ++e)
@@ -202,16 +210,17 @@ ew_gen_kernel(const EwPlan p, int64_t n_tiles, const char* __restrict__ a1, cons
     using T1 = typename Op::In1;
     using T2 = typename Op::In2;
     using TO = typename Op::Out;
+    constexpr int U = kEwUnroll;
     const bool have1 = use_scalar != 2;
     const bool have2 = Op::arity == 2 && use_scalar != 1;
     for (int64_t tile = blockIdx.x; tile < n_tiles; tile += gridDim.x) {
-        int64_t off[kUnroll][3];
-        bool ok[kUnroll];
-        T1 x[kUnroll];
-        T2 y[kUnroll];
+        int64_t off[U][3];
+        bool ok[U];
+        T1 x[U];
+        T2 y[U];
 #pragma unroll
-        for (int j = 0; j < kUnroll; ++j) {
-            int64_t i = tile * kSlots + j * kBlock + threadIdx.x;
+        for (int j = 0; j < U; ++j) {
+            int64_t i = tile * kEwSlots + j * kBlock + threadIdx.x;
             ok[j] = i < p.total;
             if (ok[j]) {
                 offsets_of<3>(i, p.nd, p.shape, p.step, off[j]);
@@ -220,13 +229,15 @@ ew_gen_kernel(const EwPlan p, int64_t n_tiles, const char* __restrict__ a1, cons
             }
         }
 #pragma unroll
-        for (int j = 0; j < kUnroll; ++j) {
+        for (int j = 0; j < U; ++j) {
             if (!ok[j]) continue;
             TO z;
             if (Op::apply(x[j], y[j], z, flag)) st_one<TO>(a3 + off[j][2], z);
         }
     }
 }
+
+inline unsigned grid_of(int64_t n_tiles) { return (unsigned)(n_tiles < 1 ? 1 : (n_tiles > kMaxGrid ? kMaxGrid : n_tiles)); }
 
 // host side ---------------------------------------------------------------
 template <typename Op>
@@ -251,8 +262,8 @@ void launch_elementwise(const cumo_na_iarray_t* a1, const cumo_na_iarray_t* a2, 
     bool row_ok = same_size && p.step[2][in] == ES &&
                   (!have1 || p.step[0][in] == ES || p.step[0][in] == 0) &&
                   (!have2 || p.step[1][in] == ES || p.step[1][in] == 0);
-    // a short inner dim under several outer dims pays the outer decomposition
-    // per packet; the generic kernel is the better plan there
+    // a short inner dim under several outer dims pays an index split per packet;
+    // the generic kernel is the better plan there
     if (row_ok && p.nd > 2 && p.shape[in] * ES < 64) row_ok = false;
 
     if constexpr (same_size) {
@@ -265,35 +276,57 @@ void launch_elementwise(const cumo_na_iarray_t* a1, const cumo_na_iarray_t* a2, 
                 if (have1 && p.step[0][in] != 0 && !mult16(p.step[0][d])) vec = false;
                 if (have2 && p.step[1][in] != 0 && !mult16(p.step[1][d])) vec = false;
             }
-            const int V = vec ? VMAX : 1;
-            RowGeom g;
-            g.L = p.shape[in];
-            g.R = p.total / g.L;
-            g.vpr = (g.L + V - 1) / V;
-            g.inner[0] = have1 && p.step[0][in] != 0;
-            g.inner[1] = have2 && p.step[1][in] != 0;
-            g.inner[2] = 1;
-            if (g.vpr >= kSlots) {
-                g.rows_per_tile = 1;
-                g.chunks_per_row = (int32_t)((g.vpr + kSlots - 1) / kSlots);
-                g.n_tiles = g.R * g.chunks_per_row;
-            } else {
-                g.rows_per_tile = (int32_t)(kSlots / g.vpr);
-                g.chunks_per_row = 1;
-                g.n_tiles = (g.R + g.rows_per_tile - 1) / g.rows_per_tile;
+            const int64_t L = p.shape[in];
+            // whole packets only: a ragged inner extent takes the scalar form, except for a flat
+            // array, whose few trailing elements get a launch of their own
+            int64_t tail = 0;
+            if (vec && L % VMAX != 0) {
+                if (p.nd == 1 && L > VMAX) tail = L % VMAX; else vec = false;
             }
-            unsigned grid = grid_for(g.n_tiles, 8);
-            if (vec)
-                ew_row_kernel<Op, VMAX><<<grid, kBlock, 0, st>>>(p, g, p1, p2, p3, sx, sy, use_scalar, flag);
-            else
-                ew_row_kernel<Op, 1><<<grid, kBlock, 0, st>>>(p, g, p1, p2, p3, sx, sy, use_scalar, flag);
-            count_launch();
-            cumo_cuda_runtime_check_kernel_launch();
-            return;
+            if (p.nd > 2 && !vec) row_ok = false;      // the split-index form exists for 16-byte packets only
+            int launches = 0;
+            auto run = [&](bool v16, int64_t len, const char* q1, const char* q2, char* q3) {
+                const int V = v16 ? VMAX : 1;
+                RowGeom g;
+                g.L = len;
+                g.R = p.total / L;
+                const int64_t vpr = (len + V - 1) / V;
+                g.inner[0] = have1 && p.step[0][in] != 0;
+                g.inner[1] = have2 && p.step[1][in] != 0;
+                for (int a = 0; a < 3; ++a) g.rs[a] = p.nd == 2 ? p.step[a][0] : 0;
+                if (vpr >= kEwSlots) {
+                    g.rows_per_tile = 1;
+                    const int64_t chunks = (vpr + kEwSlots - 1) / kEwSlots;
+                    if (chunks > 0xffffffffLL) return false;
+                    g.chunks_per_row = (uint32_t)chunks;
+                    g.vpr = kEwSlots;
+                    g.n_tiles = g.R * chunks;
+                } else {
+                    g.vpr = (uint32_t)vpr;
+                    g.rows_per_tile = (uint32_t)(kEwSlots / vpr);
+                    g.chunks_per_row = 1;
+                    g.n_tiles = (g.R + g.rows_per_tile - 1) / g.rows_per_tile;
+                }
+                const unsigned grid = grid_of(g.n_tiles);
+                if (p.nd > 2) ew_row_kernel<Op, VMAX, true><<<grid, kBlock, 0, st>>>(p, g, q1, q2, q3, sx, sy, use_scalar, flag);
+                else if (v16) ew_row_kernel<Op, VMAX, false><<<grid, kBlock, 0, st>>>(p, g, q1, q2, q3, sx, sy, use_scalar, flag);
+                else          ew_row_kernel<Op, 1, false><<<grid, kBlock, 0, st>>>(p, g, q1, q2, q3, sx, sy, use_scalar, flag);
+                ++launches;
+                return true;
+            };
+            if (row_ok && run(vec, L - tail, p1, p2, p3)) {
+                if (tail) {
+                    const int64_t done = L - tail;
+                    run(false, tail, p1 ? p1 + done * p.step[0][in] : p1, p2 ? p2 + done * p.step[1][in] : p2, p3 + done * ES);
+                }
+                count_launch(launches);
+                cumo_cuda_runtime_check_kernel_launch();
+                return;
+            }
         }
     }
-    int64_t n_tiles = (p.total + kSlots - 1) / kSlots;
-    ew_gen_kernel<Op><<<grid_for(n_tiles, 8), kBlock, 0, st>>>(p, n_tiles, p1, p2, p3, sx, sy, use_scalar, flag);
+    int64_t n_tiles = (p.total + kEwSlots - 1) / kEwSlots;
+    ew_gen_kernel<Op><<<grid_of(n_tiles), kBlock, 0, st>>>(p, n_tiles, p1, p2, p3, sx, sy, use_scalar, flag);
     count_launch();
     cumo_cuda_runtime_check_kernel_launch();
 }
@@ -312,57 +345,49 @@ cmp_flat_kernel(int64_t total, int64_t n_tiles, const char* __restrict__ a1, con
     using T2 = typename Op::In2;
     constexpr int ES = sizeof(T1);
     constexpr int LPW = 32 / V;               // lanes per output word
-    const bool have1 = use_scalar != 2;
-    const bool have2 = Op::arity == 2 && use_scalar != 1;
+    constexpr int U = kEwUnroll;
+    const bool have1 = use_scalar != 2 && st1 != 0;
+    const bool have2 = Op::arity == 2 && use_scalar != 1 && st2 != 0;
+    // a one-element (broadcast) array operand behaves like a scalar: read it once
+    if (use_scalar != 2 && st1 == 0) sx = ld_one<T1>(a1);
+    if (Op::arity == 2 && use_scalar != 1 && st2 == 0) sy = ld_one<T2>(a2);
     const int lane = threadIdx.x & 31;
-    const unsigned group_mask = (LPW == 32) ? 0xffffffffu : (((1u << LPW) - 1u) << (lane / LPW * LPW));
+    unsigned group_mask = 0xffffffffu;
+    if (LPW < 32) group_mask = ((1u << (LPW & 31)) - 1u) << (lane / LPW * LPW);
     for (int64_t tile = blockIdx.x; tile < n_tiles; tile += gridDim.x) {
-        Pack<T1> x[kUnroll];
-        Pack<T2> y[kUnroll];
-        int64_t e0[kUnroll];
+        Pack<T1> x[U];
+        Pack<T2> y[U];
+        int64_t e0[U];
 #pragma unroll
-        for (int j = 0; j < kUnroll; ++j) {
-            e0[j] = (tile * kSlots + j * kBlock + threadIdx.x) * (int64_t)V;
-            int64_t left = total - e0[j];
-            if (left <= 0) continue;
-            if (have1) {
-                if (st1 == 0) { T1 s = ld_one<T1>(a1);
+        for (int j = 0; j < U; ++j) {
+            e0[j] = (tile * kEwSlots + j * kBlock + threadIdx.x) * (int64_t)V;
+            const int64_t left = total - e0[j];
+            if (left >= V) {
+                if (have1) { if (V > 1) x[j] = ld_pack<T1>(a1 + e0[j] * ES); else x[j].v[0] = ld_one<T1>(a1 + e0[j] * ES); }
+                if (have2) { if (V > 1) y[j] = ld_pack<T2>(a2 + e0[j] * ES); else y[j].v[0] = ld_one<T2>(a2 + e0[j] * ES); }
+            } else {
 #pragma unroll
-                    for (int e = 0; e < V; ++e) x[j].v[e] = s; }
-                else if (V > 1 && left >= V) x[j] = ld_pack<T1>(a1 + e0[j] * ES);
-                else {
-#pragma unroll
-                    for (int e = 0; e < V; ++e) if (e < left) x[j].v[e] = ld_one<T1>(a1 + (e0[j] + e) * ES); }
-            }
-            if (have2) {
-                if (st2 == 0) { T2 s = ld_one<T2>(a2);
-#pragma unroll
-                    for (int e = 0; e < V; ++e) y[j].v[e] = s; }
-                else if (V > 1 && left >= V) y[j] = ld_pack<T2>(a2 + e0[j] * ES);
-                else {
-#pragma unroll
-                    for (int e = 0; e < V; ++e) if (e < left) y[j].v[e] = ld_one<T2>(a2 + (e0[j] + e) * ES); }
+                for (int e = 0; e < V; ++e) {
+                    if (have1) x[j].v[e] = e < left ? ld_one<T1>(a1 + (e0[j] + e) * ES) : T1();
+                    if (have2) y[j].v[e] = e < left ? ld_one<T2>(a2 + (e0[j] + e) * ES) : T2();
+                }
             }
         }
 #pragma unroll
-        for (int j = 0; j < kUnroll; ++j) {
-            int64_t left = total - e0[j];
+        for (int j = 0; j < U; ++j) {
+            const int64_t left = total - e0[j];
             uint32_t bits = 0;
 #pragma unroll
-            for (int e = 0; e < V; ++e) {
-                if (e < left) {
-                    T1 xv = have1 ? x[j].v[e] : sx;
-                    T2 yv = have2 ? y[j].v[e] : sy;
-                    bits |= (Op::test(xv, yv) ? 1u : 0u) << e;
-                }
-            }
+            for (int e = 0; e < V; ++e)
+                bits |= (Op::test(have1 ? x[j].v[e] : sx, have2 ? y[j].v[e] : sy) ? 1u : 0u) << e;
+            if (left < V) bits &= left > 0 ? (1u << left) - 1u : 0u;     // elements past the end
             bits <<= (lane % LPW) * V;
-            uint32_t word = __reduce_or_sync(group_mask, bits);
+            const uint32_t word = LPW == 32 ? __ballot_sync(0xffffffffu, bits != 0) : __reduce_or_sync(group_mask, bits);
             if (lane % LPW == 0 && left > 0) {
-                int64_t w = e0[j] >> 5;
+                const int64_t w = e0[j] >> 5;
                 if (left >= 32) out[w] = word;
                 else {                         // last, partial word: keep the bits past the end
-                    uint32_t m = (1u << left) - 1u;
+                    const uint32_t m = (1u << left) - 1u;
                     out[w] = (out[w] & ~m) | (word & m);
                 }
             }
@@ -384,8 +409,8 @@ cmp_gen_kernel(const EwPlan p, int64_t n_tiles, const char* __restrict__ a1, con
     const int lane = threadIdx.x & 31;
     for (int64_t tile = blockIdx.x; tile < n_tiles; tile += gridDim.x) {
 #pragma unroll
-        for (int j = 0; j < kUnroll; ++j) {
-            int64_t i = tile * kSlots + j * kBlock + threadIdx.x;
+        for (int j = 0; j < kEwUnroll; ++j) {
+            int64_t i = tile * kEwSlots + j * kBlock + threadIdx.x;
             bool ok = i < p.total;
             bool r = false;
             int64_t off[3] = {0, 0, 0};
@@ -437,11 +462,11 @@ void launch_compare(const cumo_na_iarray_t* a1, const cumo_na_iarray_t* a2, cumo
         constexpr int VMAX = 16 / ES;
         bool vec = (!st1 || aligned16(p1)) && (!st2 || aligned16(p2));
         if (vec) {
-            int64_t n_tiles = (p.total + (int64_t)kSlots * VMAX - 1) / ((int64_t)kSlots * VMAX);
-            cmp_flat_kernel<Op, VMAX><<<grid_for(n_tiles, 8), kBlock, 0, st>>>(p.total, n_tiles, p1, p2, out, st1, st2, sx, sy, use_scalar);
+            int64_t n_tiles = (p.total + (int64_t)kEwSlots * VMAX - 1) / ((int64_t)kEwSlots * VMAX);
+            cmp_flat_kernel<Op, VMAX><<<grid_of(n_tiles), kBlock, 0, st>>>(p.total, n_tiles, p1, p2, out, st1, st2, sx, sy, use_scalar);
         } else {
-            int64_t n_tiles = (p.total + kSlots - 1) / kSlots;
-            cmp_flat_kernel<Op, 1><<<grid_for(n_tiles, 8), kBlock, 0, st>>>(p.total, n_tiles, p1, p2, out, st1, st2, sx, sy, use_scalar);
+            int64_t n_tiles = (p.total + kEwSlots - 1) / kEwSlots;
+            cmp_flat_kernel<Op, 1><<<grid_of(n_tiles), kBlock, 0, st>>>(p.total, n_tiles, p1, p2, out, st1, st2, sx, sy, use_scalar);
         }
     } else {
         // is the output still one run of bits in logical order?
@@ -451,8 +476,8 @@ void launch_compare(const cumo_na_iarray_t* a1, const cumo_na_iarray_t* a2, cumo
             if (p.step[2][d] != run) word_store = false;
             run *= p.shape[d];
         }
-        int64_t n_tiles = (p.total + kSlots - 1) / kSlots;
-        cmp_gen_kernel<Op><<<grid_for(n_tiles, 8), kBlock, 0, st>>>(p, n_tiles, p1, p2, a3->ptr, (uint64_t)a3->pos, word_store ? 1 : 0, sx, sy, use_scalar);
+        int64_t n_tiles = (p.total + kEwSlots - 1) / kEwSlots;
+        cmp_gen_kernel<Op><<<grid_of(n_tiles), kBlock, 0, st>>>(p, n_tiles, p1, p2, a3->ptr, (uint64_t)a3->pos, word_store ? 1 : 0, sx, sy, use_scalar);
     }
     count_launch();
     cumo_cuda_runtime_check_kernel_launch();

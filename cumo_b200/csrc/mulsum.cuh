@@ -94,15 +94,10 @@ void launch_mulsum_reduce(char* p1, char* p2, char* p3, ssize_t s1, ssize_t s2, 
     constexpr int VMAX = 16 / ES;
     cudaStream_t st = current_stream();
     const bool vec = s1 == ES && s2 == ES && aligned16(p1) && aligned16(p2);
-    const int64_t min_seg = (int64_t)kBlock * VMAX * kUnroll * 2;
-    int64_t n_seg = (int64_t)n / min_seg;
-    const int64_t target = (int64_t)sm_count() * 8;
-    if (n_seg > target) n_seg = target;
-    if (n_seg < 1) n_seg = 1;
-    int64_t seg_len = ((int64_t)n + n_seg - 1) / n_seg;
-    seg_len = (seg_len + 31) / 32 * 32;
-    if (seg_len < 32) seg_len = 32;
-    n_seg = ((int64_t)n + seg_len - 1) / seg_len;
+    // fixed 32 KiB segments, one CTA each, doubled until one warp can fold the partials
+    int64_t seg_len = (32 << 10) / ES;
+    int64_t n_seg = ((int64_t)n + seg_len - 1) / seg_len;
+    while (n_seg > 4096) { seg_len *= 2; n_seg = ((int64_t)n + seg_len - 1) / seg_len; }
     if (n_seg < 1) n_seg = 1;
     T* partial = nullptr;
     if (n_seg > 1) partial = reinterpret_cast<T*>(cumo_cuda_runtime_malloc(sizeof(T) * n_seg));

@@ -8,17 +8,18 @@
 //   ROW  the reduce axes collapse to one contiguous run (step == element size).
 //        A "group" (a warp for short rows, a whole CTA for long ones) owns one
 //        (output, segment) item and streams it with 16-byte loads, 4 packets in
-//        flight per thread; long rows with few outputs are cut into segments so
-//        that every SM has several CTAs to run.
+//        flight per thread.  A long row is cut into fixed 32 KiB segments, one CTA
+//        each, consecutive CTAs on consecutive segments: B200 streams fastest with
+//        very many small CTAs marching through memory together.
 //   COL  the innermost OUTPUT axis is the contiguous one (a column / "transposed"
-//        reduction).  A CTA owns a strip of 32 lanes x 16 bytes of columns; its
-//        8 warps walk different rows with 16-byte loads and keep one accumulator
-//        per column in registers; rows are cut into segments across CTAs.
+//        reduction).  A CTA owns a strip of 32 lanes x 16 bytes of columns and a
+//        segment of 256 rows; its 8 warps walk different rows with 16-byte loads
+//        and keep one accumulator per column in registers.
 //   GEN  any other stride pattern: a group per (output, segment), offsets from a
 //        32-bit index split.
 //   Segmented plans write accumulators to scratch ([output][segment]) and a
 //   second launch folds the segments of each output in index order, so a result
-//   depends only on (shape, strides, SM count), never on scheduling.
+//   depends only on shape and strides, never on scheduling or on the device.
 //
 // Index reductions get, per element, either its position along the reduce axes
 // or its element offset from arg->in.ptr (reduce_kernel.h:219-239).
@@ -110,6 +111,37 @@ __device__ __forceinline__ typename R::Acc group_fold(const R& r, typename R::Ac
     return a;
 }
 
+// A thread's private accumulation over the elements it visits, addressed by a 32-bit
+// position inside the thread's segment; `idx_of(pos)` turns a position into the index
+// the functor wants and is only evaluated when it is needed.  Reducers with a private
+// scan (the index reductions) use it when positions are visited in increasing index
+// order; everything else folds combine(map()).
+template <typename R, bool SCAN>
+struct Runner;
+template <typename R>
+struct Runner<R, false> {
+    typename R::Acc a;
+    __device__ __forceinline__ void init(const R& r) { a = r.identity(); }
+    template <typename F>
+    __device__ __forceinline__ void step(const R& r, typename R::In v, int32_t pos, F idx_of) {
+        a = r.combine(a, r.map(v, R::kIndexed ? idx_of(pos) : (int64_t)0));
+    }
+    template <typename F>
+    __device__ __forceinline__ typename R::Acc finish(const R&, F) { return a; }
+};
+template <typename R>
+struct Runner<R, true> {
+    typename R::Local l;
+    __device__ __forceinline__ void init(const R& r) { l = r.local_identity(); }
+    template <typename F>
+    __device__ __forceinline__ void step(const R& r, typename R::In v, int32_t pos, F) { r.local_scan(l, v, pos); }
+    template <typename F>
+    __device__ __forceinline__ typename R::Acc finish(const R& r, F idx_of) {
+        if (l.pos < 0) return r.identity();
+        return typename R::Acc{l.value, idx_of(l.pos)};
+    }
+};
+
 template <typename R>
 __device__ __forceinline__ void emit(const R& r, const RedPlan& p, int64_t o, int n_split, int64_t s,
                                      typename R::Acc a, char* out, char* out2, typename R::Acc* partial) {
@@ -119,11 +151,59 @@ __device__ __forceinline__ void emit(const R& r, const RedPlan& p, int64_t o, in
     r.store(out + oo, out2 ? out2 + o2 : nullptr, a);
 }
 
+// what every first-pass kernel is told besides the plan
+struct RedLaunch {
+    int64_t seg_len;       // elements (ROW/GEN) or rows (COL) per segment
+    int64_t n_strips;      // COL only
+    int n_split;
+    int flat_index;        // 1: feed the element offset; 0: the position along the reduce axes
+    int ordered;           // indices grow with the position inside a segment
+};
+
 // ---- ROW ------------------------------------------------------------------------------
+// one (output, segment) item reduced by a group of G threads; returns the group's result in its thread 0
+template <typename R, int V, int G, bool SCAN>
+__device__ __forceinline__ typename R::Acc row_item(const R& r, const char* base, int64_t begin, int64_t end,
+                                                    int64_t idx_base, int gl, typename R::Acc* smem) {
+    using T = typename R::In;
+    constexpr int ES = sizeof(T);
+    constexpr int64_t SPAN = (int64_t)G * V * kUnroll;     // elements per group iteration
+    Runner<R, SCAN> run;
+    run.init(r);
+    auto idx_of = [&](int32_t pos) { return idx_base + begin + pos; };
+    int64_t eb = begin;
+    // whole iterations: every packet of every lane lies inside the segment, no tests per element
+    for (; eb + SPAN <= end; eb += SPAN) {
+        Pack<T> v[kUnroll];
+#pragma unroll
+        for (int j = 0; j < kUnroll; ++j) {
+            const char* q = base + (eb + (int64_t)(j * G + gl) * V) * ES;
+            if (V > 1) v[j] = ld_pack<T>(q); else v[j].v[0] = ld_one<T>(q);
+        }
+        const int32_t p0 = (int32_t)(eb - begin);
+#pragma unroll
+        for (int j = 0; j < kUnroll; ++j)
+#pragma unroll
+            for (int k = 0; k < V; ++k) run.step(r, v[j].v[k], p0 + (j * G + gl) * V + k, idx_of);
+    }
+    // the ragged end of the segment
+    if (eb < end) {
+        const int32_t p0 = (int32_t)(eb - begin);
+#pragma unroll
+        for (int j = 0; j < kUnroll; ++j) {
+            const int64_t e = eb + (int64_t)(j * G + gl) * V;
+#pragma unroll
+            for (int k = 0; k < V; ++k)
+                if (e + k < end) run.step(r, ld_one<T>(base + (e + k) * ES), p0 + (j * G + gl) * V + k, idx_of);
+        }
+    }
+    return group_fold<R, G>(r, run.finish(r, idx_of), smem);
+}
+
 template <typename R, int V, int G>
 __global__ void __launch_bounds__(kBlock)
-red_row_kernel(const RedPlan p, const R r, const char* __restrict__ in, char* out, char* out2,
-               typename R::Acc* partial, int64_t seg_len, int n_split, int flat_index) {
+red_row_kernel(const RedPlan p, const R r, const RedLaunch q, const char* __restrict__ in, char* out, char* out2,
+               typename R::Acc* partial) {
     using T = typename R::In;
     using Acc = typename R::Acc;
     constexpr int ES = sizeof(T);
@@ -131,53 +211,76 @@ red_row_kernel(const RedPlan p, const R r, const char* __restrict__ in, char* ou
     __shared__ Acc smem[kWarpsPerBlock];
     const int gid = threadIdx.x / G, gl = threadIdx.x % G;
     const int64_t L = p.n_red;
-    const int64_t items = p.n_out * n_split;
+    const int64_t items = p.n_out * q.n_split;
     for (int64_t item0 = (int64_t)blockIdx.x * GPB; item0 < items; item0 += (int64_t)gridDim.x * GPB) {
-        const int64_t item = item0 + gid;
+        int64_t item = item0 + gid;
         const bool live = item < items;      // whole groups go idle together; G==kBlock: always live
-        Acc acc = r.identity();
-        int64_t o = 0, s = 0;
-        if (live) {
-            o = item / n_split;
-            s = item - o * n_split;
-            const int64_t in_off = offset_of(o, p.n_od, p.oshape, p.in_ostep);
-            const int64_t begin = s * seg_len;
-            int64_t end = begin + seg_len; if (end > L) end = L;
-            const char* base = in + in_off;
-            const int64_t idx_base = flat_index ? in_off / ES : 0;
-            for (int64_t e0 = begin + (int64_t)gl * V; e0 < end; e0 += (int64_t)G * V * kUnroll) {
-                Pack<T> v[kUnroll];
-                int nv[kUnroll];
-#pragma unroll
-                for (int j = 0; j < kUnroll; ++j) {
-                    int64_t e = e0 + (int64_t)j * G * V;
-                    int64_t left = end - e;
-                    nv[j] = left >= V ? V : (left > 0 ? (int)left : 0);
-                    if (V > 1 && nv[j] == V) v[j] = ld_pack<T>(base + e * ES);
-                    else {
-#pragma unroll
-                        for (int k = 0; k < V; ++k) if (k < nv[j]) v[j].v[k] = ld_one<T>(base + (e + k) * ES);
-                    }
-                }
-#pragma unroll
-                for (int j = 0; j < kUnroll; ++j) {
-                    int64_t e = e0 + (int64_t)j * G * V;
-#pragma unroll
-                    for (int k = 0; k < V; ++k)
-                        if (k < nv[j]) acc = r.combine(acc, r.map(v[j].v[k], idx_base + e + k));
-                }
-            }
-        }
-        acc = group_fold<R, G>(r, acc, smem);
-        if (live && gl == 0) emit(r, p, o, n_split, s, acc, out, out2, partial);
+        if (!live) item = items - 1;         // idle groups of the last CTA redo the last item and drop it
+        int64_t o, s;
+        if (item <= 0xffffffffLL) { uint32_t oo = (uint32_t)item / (uint32_t)q.n_split; o = oo; s = (uint32_t)item - oo * (uint32_t)q.n_split; }
+        else { o = item / q.n_split; s = item - o * q.n_split; }
+        const int64_t in_off = offset_of(o, p.n_od, p.oshape, p.in_ostep);
+        const int64_t begin = s * q.seg_len;
+        int64_t end = begin + q.seg_len; if (end > L) end = L;
+        const int64_t idx_base = q.flat_index ? in_off / ES : 0;
+        Acc acc = row_item<R, V, G, R::kHasScan>(r, in + in_off, begin, end, idx_base, gl, smem);
+        if (live && gl == 0) emit(r, p, o, q.n_split, s, acc, out, out2, partial);
     }
 }
 
 // ---- COL ------------------------------------------------------------------------------
+template <typename R, int V, bool SCAN>
+__device__ __forceinline__ void col_item(const R& r, const RedPlan& p, const RedLaunch& q, const char* base, int64_t in_b,
+                                         int64_t col0, int nv, int64_t r_begin, int64_t r_end, int warp,
+                                         typename R::Acc* acc_out) {
+    using T = typename R::In;
+    constexpr int ES = sizeof(T);
+    Runner<R, SCAN> run[V];
+#pragma unroll
+    for (int k = 0; k < V; ++k) run[k].init(r);
+    auto row_off = [&](int64_t row) { return (p.n_rd == 1) ? row * p.in_rstep[0] : offset_of(row, p.n_rd, p.rshape, p.in_rstep); };
+    int64_t r0 = r_begin + warp;
+    if (nv == V) {
+        // whole iterations: four rows of this warp inside the segment, whole packets
+        for (; r0 + (kUnroll - 1) * kWarpsPerBlock < r_end; r0 += kWarpsPerBlock * kUnroll) {
+            Pack<T> v[kUnroll];
+#pragma unroll
+            for (int j = 0; j < kUnroll; ++j) {
+                const char* a = base + row_off(r0 + j * kWarpsPerBlock);
+                if (V > 1) v[j] = ld_pack<T>(a); else v[j].v[0] = ld_one<T>(a);
+            }
+#pragma unroll
+            for (int j = 0; j < kUnroll; ++j) {
+                const int32_t pos = (int32_t)(r0 + j * kWarpsPerBlock - r_begin);
+#pragma unroll
+                for (int k = 0; k < V; ++k)
+                    run[k].step(r, v[j].v[k], pos, [&](int32_t ps) {
+                        const int64_t row = r_begin + ps;
+                        return q.flat_index ? (in_b + row_off(row)) / ES + col0 + k : row; });
+            }
+        }
+    }
+    for (; r0 < r_end; r0 += kWarpsPerBlock) {
+        const char* a = base + row_off(r0);
+        const int32_t pos = (int32_t)(r0 - r_begin);
+#pragma unroll
+        for (int k = 0; k < V; ++k)
+            if (k < nv)
+                run[k].step(r, ld_one<T>(a + k * ES), pos, [&](int32_t ps) {
+                    const int64_t row = r_begin + ps;
+                    return q.flat_index ? (in_b + row_off(row)) / ES + col0 + k : row; });
+    }
+#pragma unroll
+    for (int k = 0; k < V; ++k)
+        acc_out[k] = run[k].finish(r, [&](int32_t ps) {
+            const int64_t row = r_begin + ps;
+            return q.flat_index ? (in_b + row_off(row)) / ES + col0 + k : row; });
+}
+
 template <typename R, int V>
 __global__ void __launch_bounds__(kBlock)
-red_col_kernel(const RedPlan p, const R r, const char* __restrict__ in, char* out, char* out2,
-               typename R::Acc* partial, int64_t rows_per_seg, int n_split, int64_t n_strips, int flat_index) {
+red_col_kernel(const RedPlan p, const R r, const RedLaunch q, const char* __restrict__ in, char* out, char* out2,
+               typename R::Acc* partial) {
     using T = typename R::In;
     using Acc = typename R::Acc;
     constexpr int ES = sizeof(T);
@@ -187,49 +290,34 @@ red_col_kernel(const RedPlan p, const R r, const char* __restrict__ in, char* ou
     const int od_in = p.n_od - 1;            // innermost out dim = the columns
     const int64_t C = p.oshape[od_in];
     const int64_t n_batch = p.n_out / C;
-    const int64_t items = n_batch * n_strips * n_split;
+    const int64_t items = n_batch * q.n_strips * q.n_split;
     for (int64_t item = blockIdx.x; item < items; item += gridDim.x) {
-        const int64_t s = item % n_split;
-        const int64_t t = item / n_split;
-        const int64_t strip = t % n_strips;
-        const int64_t b = t / n_strips;
+        // strips vary fastest: neighbouring CTAs read neighbouring columns of the same rows
+        int64_t strip, s, b;
+        if (item <= 0xffffffffLL) {
+            uint32_t it = (uint32_t)item, t = it / (uint32_t)q.n_strips;
+            strip = it - t * (uint32_t)q.n_strips;
+            uint32_t bb = t / (uint32_t)q.n_split;
+            s = t - bb * (uint32_t)q.n_split; b = bb;
+        } else {
+            strip = item % q.n_strips;
+            const int64_t t = item / q.n_strips;
+            s = t % q.n_split; b = t / q.n_split;
+        }
         const int64_t col0 = strip * W + (int64_t)lane * V;
         const int64_t cleft = C - col0;
         const int nv = cleft >= V ? V : (cleft > 0 ? (int)cleft : 0);
         const int64_t in_b = offset_of(b, od_in, p.oshape, p.in_ostep);
-        const int64_t r_begin = s * rows_per_seg;
-        int64_t r_end = r_begin + rows_per_seg; if (r_end > p.n_red) r_end = p.n_red;
+        const int64_t r_begin = s * q.seg_len;
+        int64_t r_end = r_begin + q.seg_len; if (r_end > p.n_red) r_end = p.n_red;
         Acc acc[V];
-#pragma unroll
-        for (int k = 0; k < V; ++k) acc[k] = r.identity();
         if (nv > 0) {
             const char* base = in + in_b + col0 * ES;
-            for (int64_t r0 = r_begin + warp; r0 < r_end; r0 += kWarpsPerBlock * kUnroll) {
-                Pack<T> v[kUnroll];
-                int64_t roff[kUnroll];
-                bool ok[kUnroll];
+            if (R::kHasScan && q.ordered) col_item<R, V, R::kHasScan>(r, p, q, base, in_b, col0, nv, r_begin, r_end, warp, acc);
+            else col_item<R, V, false>(r, p, q, base, in_b, col0, nv, r_begin, r_end, warp, acc);
+        } else {
 #pragma unroll
-                for (int j = 0; j < kUnroll; ++j) {
-                    int64_t row = r0 + j * kWarpsPerBlock;
-                    ok[j] = row < r_end;
-                    if (!ok[j]) continue;
-                    roff[j] = (p.n_rd == 1) ? row * p.in_rstep[0] : offset_of(row, p.n_rd, p.rshape, p.in_rstep);
-                    if (V > 1 && nv == V) v[j] = ld_pack<T>(base + roff[j]);
-                    else {
-#pragma unroll
-                        for (int k = 0; k < V; ++k) if (k < nv) v[j].v[k] = ld_one<T>(base + roff[j] + k * ES);
-                    }
-                }
-#pragma unroll
-                for (int j = 0; j < kUnroll; ++j) {
-                    if (!ok[j]) continue;
-                    int64_t row = r0 + j * kWarpsPerBlock;
-                    int64_t idx = flat_index ? (in_b + roff[j]) / ES + col0 : row;
-#pragma unroll
-                    for (int k = 0; k < V; ++k)
-                        if (k < nv) acc[k] = r.combine(acc[k], r.map(v[j].v[k], flat_index ? idx + k : idx));
-                }
-            }
+            for (int k = 0; k < V; ++k) acc[k] = r.identity();
         }
         __syncthreads();
 #pragma unroll
@@ -242,7 +330,7 @@ red_col_kernel(const RedPlan p, const R r, const char* __restrict__ in, char* ou
                 Acc a = smem[0][lane * V + k];
 #pragma unroll
                 for (int w = 1; w < kWarpsPerBlock; ++w) a = r.combine(a, smem[w][lane * V + k]);
-                emit(r, p, b * C + col0 + k, n_split, s, a, out, out2, partial);
+                emit(r, p, b * C + col0 + k, q.n_split, s, a, out, out2, partial);
             }
         }
     }
@@ -251,26 +339,26 @@ red_col_kernel(const RedPlan p, const R r, const char* __restrict__ in, char* ou
 // ---- GEN ------------------------------------------------------------------------------
 template <typename R, int G>
 __global__ void __launch_bounds__(kBlock)
-red_gen_kernel(const RedPlan p, const R r, const char* __restrict__ in, char* out, char* out2,
-               typename R::Acc* partial, int64_t seg_len, int n_split, int flat_index) {
+red_gen_kernel(const RedPlan p, const R r, const RedLaunch q, const char* __restrict__ in, char* out, char* out2,
+               typename R::Acc* partial) {
     using T = typename R::In;
     using Acc = typename R::Acc;
     constexpr int ES = sizeof(T);
     constexpr int GPB = kBlock / G;
     __shared__ Acc smem[kWarpsPerBlock];
     const int gid = threadIdx.x / G, gl = threadIdx.x % G;
-    const int64_t items = p.n_out * n_split;
+    const int64_t items = p.n_out * q.n_split;
     for (int64_t item0 = (int64_t)blockIdx.x * GPB; item0 < items; item0 += (int64_t)gridDim.x * GPB) {
         const int64_t item = item0 + gid;
         const bool live = item < items;
         Acc acc = r.identity();
         int64_t o = 0, s = 0;
         if (live) {
-            o = item / n_split;
-            s = item - o * n_split;
+            o = item / q.n_split;
+            s = item - o * q.n_split;
             const int64_t in_off = offset_of(o, p.n_od, p.oshape, p.in_ostep);
-            const int64_t begin = s * seg_len;
-            int64_t end = begin + seg_len; if (end > p.n_red) end = p.n_red;
+            const int64_t begin = s * q.seg_len;
+            int64_t end = begin + q.seg_len; if (end > p.n_red) end = p.n_red;
             for (int64_t e0 = begin + gl; e0 < end; e0 += (int64_t)G * kUnroll) {
                 T v[kUnroll];
                 int64_t off[kUnroll];
@@ -285,34 +373,54 @@ red_gen_kernel(const RedPlan p, const R r, const char* __restrict__ in, char* ou
 #pragma unroll
                 for (int j = 0; j < kUnroll; ++j) {
                     int64_t e = e0 + (int64_t)j * G;
-                    if (e < end) acc = r.combine(acc, r.map(v[j], flat_index ? off[j] / ES : e));
+                    if (e < end) acc = r.combine(acc, r.map(v[j], q.flat_index ? off[j] / ES : e));
                 }
             }
         }
         acc = group_fold<R, G>(r, acc, smem);
-        if (live && gl == 0) emit(r, p, o, n_split, s, acc, out, out2, partial);
+        if (live && gl == 0) emit(r, p, o, q.n_split, s, acc, out, out2, partial);
     }
 }
 
 // ---- second pass: fold the segments of each output, in segment order -------------------
-template <typename R>
+// G == 32: a warp per output; G == kBlock: a CTA per output (many segments, few outputs).
+template <typename R, int G>
 __global__ void __launch_bounds__(kBlock)
 red_fold_kernel(const RedPlan p, const R r, const typename R::Acc* __restrict__ partial, int n_split,
                 char* out, char* out2) {
     using Acc = typename R::Acc;
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    for (int64_t o = (int64_t)blockIdx.x * kWarpsPerBlock + warp; o < p.n_out; o += (int64_t)gridDim.x * kWarpsPerBlock) {
-        // lane l takes the contiguous run of segments [l*per, (l+1)*per): lane order == segment order
-        const int per = (n_split + 31) / 32;
+    constexpr int GPB = kBlock / G;
+    __shared__ Acc smem[kWarpsPerBlock];
+    const int gid = threadIdx.x / G, gl = threadIdx.x % G;
+    for (int64_t o0 = (int64_t)blockIdx.x * GPB; o0 < p.n_out; o0 += (int64_t)gridDim.x * GPB) {
+        const int64_t o = o0 + gid;
+        const bool live = o < p.n_out;
+        // thread t takes the contiguous run of segments [t*per, (t+1)*per): thread order == segment order
+        const int per = (n_split + G - 1) / G;
         Acc acc = r.identity();
-        for (int k = 0; k < per; ++k) {
-            int s = lane * per + k;
-            if (s < n_split) acc = r.combine(acc, partial[o * n_split + s]);
+        if (live) {
+            // eight independent loads at a time, folded in order
+            const Acc* run = partial + o * n_split;
+            for (int k = 0; k < per; k += 8) {
+                Acc buf[8];
+#pragma unroll
+                for (int i = 0; i < 8; ++i) {
+                    int s = gl * per + k + i;
+                    if (k + i < per && s < n_split) buf[i] = run[s];
+                }
+#pragma unroll
+                for (int i = 0; i < 8; ++i) {
+                    int s = gl * per + k + i;
+                    if (k + i < per && s < n_split) acc = r.combine(acc, buf[i]);
+                }
+            }
         }
-        acc = warp_fold(r, acc);
-        if (lane == 0) emit(r, p, o, 1, 0, acc, out, out2, (Acc*)nullptr);
+        acc = group_fold<R, G>(r, acc, smem);
+        if (live && gl == 0) emit(r, p, o, 1, 0, acc, out, out2, (Acc*)nullptr);
     }
 }
+
+inline unsigned red_grid(int64_t ctas) { return (unsigned)(ctas < 1 ? 1 : (ctas > 0x7fffffffLL ? 0x7fffffffLL : ctas)); }
 
 // ---- host ----------------------------------------------------------------------------------
 // flat_index: 0 = feed the position along the reduce axes, 1 = feed the element offset.
@@ -322,16 +430,23 @@ void launch_reduce(const cumo_na_reduction_arg_t* arg, const cumo_na_iarray_t* o
     using Acc = typename R::Acc;
     constexpr int ES = sizeof(T);
     constexpr int VMAX = 16 / ES;
+    constexpr int64_t kSegBytes = 32 << 10;           // one CTA's share of a long row
+    constexpr int64_t kColSegRows = 256;              // one CTA's share of a column strip
     RedPlan p;
     if (!make_red_plan(&p, arg, out2_arr)) return;
     const char* in = arg->in.ptr;
     char* out = arg->out.ptr;
     char* out2 = out2_arr ? out2_arr->ptr : nullptr;
     cudaStream_t st = current_stream();
-    const int64_t target = (int64_t)sm_count() * 8;   // CTAs wanted in flight
     Acc* partial = nullptr;
-    int n_split = 1;
-    int launches = 1;
+    RedLaunch q;
+    q.n_split = 1;
+    q.n_strips = 0;
+    q.flat_index = flat_index;
+    q.ordered = 1;
+    if (flat_index)                                   // element offsets grow along a run only with positive steps
+        for (int d = 0; d < p.n_rd; ++d) if (p.in_rstep[d] < 0) q.ordered = 0;
+    for (int d = 0; d + 1 < p.n_rd; ++d) if (flat_index && p.in_rstep[d] < p.in_rstep[d + 1] * p.rshape[d + 1]) q.ordered = 0;
 
     const bool row = p.n_rd == 1 && (p.in_rstep[0] == ES || p.n_red <= 1);
     const bool col = !row && p.in_ostep[p.n_od - 1] == ES && p.oshape[p.n_od - 1] >= 8;
@@ -340,30 +455,23 @@ void launch_reduce(const cumo_na_reduction_arg_t* arg, const cumo_na_iarray_t* o
         const int64_t L = p.n_red;
         bool vec = aligned16(in);
         for (int d = 0; d < p.n_od && vec; ++d) if (!mult16(p.in_ostep[d])) vec = false;
-        const int V = vec ? VMAX : 1;
-        const bool wide = L >= 4096;                    // a CTA per item, else a warp per item
-        int64_t seg_len = L > 0 ? L : 1;
-        if (wide && p.n_out < target) {
-            const int64_t min_seg = (int64_t)kBlock * VMAX * kUnroll * 2;
-            int64_t want = (target + p.n_out - 1) / p.n_out;
-            int64_t fits = L / min_seg;
-            int64_t ns = want < fits ? want : fits;
-            if (ns > 1) {
-                seg_len = (L + ns - 1) / ns;
-                seg_len = (seg_len + 31) / 32 * 32;     // keeps every segment start 16-byte aligned
-                n_split = (int)((L + seg_len - 1) / seg_len);
-            }
-        }
-        if (n_split > 1) partial = reinterpret_cast<Acc*>(cumo_cuda_runtime_malloc(sizeof(Acc) * p.n_out * n_split));
-        const int64_t items = p.n_out * n_split;
+        const bool wide = L >= 4096;                   // a CTA per item, else a warp per item
+        q.seg_len = L > 0 ? L : 1;
         if (wide) {
-            unsigned grid = grid_for(items, 8);
-            if (vec) red_row_kernel<R, VMAX, kBlock><<<grid, kBlock, 0, st>>>(p, r, in, out, out2, partial, seg_len, n_split, flat_index);
-            else     red_row_kernel<R, 1, kBlock><<<grid, kBlock, 0, st>>>(p, r, in, out, out2, partial, seg_len, n_split, flat_index);
+            int64_t seg = kSegBytes / ES;              // a multiple of 32 elements: segment starts stay 16-byte aligned
+            int64_t ns = (L + seg - 1) / seg;
+            while (ns > 8192) { seg *= 2; ns = (L + seg - 1) / seg; }
+            if (ns > 1) { q.seg_len = seg; q.n_split = (int)ns; }
+        }
+        if (q.n_split > 1) partial = reinterpret_cast<Acc*>(cumo_cuda_runtime_malloc(sizeof(Acc) * p.n_out * q.n_split));
+        const int64_t items = p.n_out * q.n_split;
+        if (wide) {
+            if (vec) red_row_kernel<R, VMAX, kBlock><<<red_grid(items), kBlock, 0, st>>>(p, r, q, in, out, out2, partial);
+            else     red_row_kernel<R, 1, kBlock><<<red_grid(items), kBlock, 0, st>>>(p, r, q, in, out, out2, partial);
         } else {
-            unsigned grid = grid_for((items + kWarpsPerBlock - 1) / kWarpsPerBlock, 8);
-            if (vec) red_row_kernel<R, VMAX, 32><<<grid, kBlock, 0, st>>>(p, r, in, out, out2, partial, seg_len, n_split, flat_index);
-            else     red_row_kernel<R, 1, 32><<<grid, kBlock, 0, st>>>(p, r, in, out, out2, partial, seg_len, n_split, flat_index);
+            const unsigned grid = red_grid((items + kWarpsPerBlock - 1) / kWarpsPerBlock);
+            if (vec) red_row_kernel<R, VMAX, 32><<<grid, kBlock, 0, st>>>(p, r, q, in, out, out2, partial);
+            else     red_row_kernel<R, 1, 32><<<grid, kBlock, 0, st>>>(p, r, q, in, out, out2, partial);
         }
     } else if (col) {
         const int od_in = p.n_od - 1;
@@ -371,45 +479,40 @@ void launch_reduce(const cumo_na_reduction_arg_t* arg, const cumo_na_iarray_t* o
         bool vec = aligned16(in);
         for (int d = 0; d < od_in && vec; ++d) if (!mult16(p.in_ostep[d])) vec = false;
         for (int d = 0; d < p.n_rd && vec; ++d) if (!mult16(p.in_rstep[d])) vec = false;
-        const int V = vec ? VMAX : 1;
-        const int64_t W = 32 * V;
-        const int64_t n_strips = (C + W - 1) / W;
-        const int64_t base_items = (p.n_out / C) * n_strips;
-        int64_t rows_per_seg = p.n_red > 0 ? p.n_red : 1;
-        if (base_items < target) {
-            const int64_t min_rows = kWarpsPerBlock * kUnroll * 2;
-            int64_t want = (target + base_items - 1) / base_items;
-            int64_t fits = p.n_red / min_rows;
-            int64_t ns = want < fits ? want : fits;
-            if (ns > 1) {
-                rows_per_seg = (p.n_red + ns - 1) / ns;
-                n_split = (int)((p.n_red + rows_per_seg - 1) / rows_per_seg);
-            }
+        const int64_t W = 32 * (vec ? VMAX : 1);
+        q.n_strips = (C + W - 1) / W;
+        q.seg_len = p.n_red > 0 ? p.n_red : 1;
+        if (p.n_red > kColSegRows + kColSegRows / 2) {
+            int64_t seg = kColSegRows;
+            int64_t ns = (p.n_red + seg - 1) / seg;
+            while (ns > 8192) { seg *= 2; ns = (p.n_red + seg - 1) / seg; }
+            q.seg_len = seg;
+            q.n_split = (int)ns;
         }
-        if (n_split > 1) partial = reinterpret_cast<Acc*>(cumo_cuda_runtime_malloc(sizeof(Acc) * p.n_out * n_split));
-        unsigned grid = grid_for(base_items * n_split, 8);
-        if (vec) red_col_kernel<R, VMAX><<<grid, kBlock, 0, st>>>(p, r, in, out, out2, partial, rows_per_seg, n_split, n_strips, flat_index);
-        else     red_col_kernel<R, 1><<<grid, kBlock, 0, st>>>(p, r, in, out, out2, partial, rows_per_seg, n_split, n_strips, flat_index);
+        if (q.n_split > 1) partial = reinterpret_cast<Acc*>(cumo_cuda_runtime_malloc(sizeof(Acc) * p.n_out * q.n_split));
+        const unsigned grid = red_grid((p.n_out / C) * q.n_strips * q.n_split);
+        if (vec) red_col_kernel<R, VMAX><<<grid, kBlock, 0, st>>>(p, r, q, in, out, out2, partial);
+        else     red_col_kernel<R, 1><<<grid, kBlock, 0, st>>>(p, r, q, in, out, out2, partial);
     } else {
         const bool wide = p.n_red >= 2048;
-        int64_t seg_len = p.n_red > 0 ? p.n_red : 1;
-        if (wide && p.n_out < target) {
-            const int64_t min_seg = (int64_t)kBlock * kUnroll * 2;
-            int64_t want = (target + p.n_out - 1) / p.n_out;
-            int64_t fits = p.n_red / min_seg;
-            int64_t ns = want < fits ? want : fits;
-            if (ns > 1) {
-                seg_len = (p.n_red + ns - 1) / ns;
-                n_split = (int)((p.n_red + seg_len - 1) / seg_len);
-            }
+        q.seg_len = p.n_red > 0 ? p.n_red : 1;
+        if (wide) {
+            int64_t seg = (int64_t)kBlock * kUnroll * 4;
+            int64_t ns = (p.n_red + seg - 1) / seg;
+            while (ns > 8192) { seg *= 2; ns = (p.n_red + seg - 1) / seg; }
+            if (ns > 1) { q.seg_len = seg; q.n_split = (int)ns; }
         }
-        if (n_split > 1) partial = reinterpret_cast<Acc*>(cumo_cuda_runtime_malloc(sizeof(Acc) * p.n_out * n_split));
-        const int64_t items = p.n_out * n_split;
-        if (wide) red_gen_kernel<R, kBlock><<<grid_for(items, 8), kBlock, 0, st>>>(p, r, in, out, out2, partial, seg_len, n_split, flat_index);
-        else      red_gen_kernel<R, 32><<<grid_for((items + kWarpsPerBlock - 1) / kWarpsPerBlock, 8), kBlock, 0, st>>>(p, r, in, out, out2, partial, seg_len, n_split, flat_index);
+        if (q.n_split > 1) partial = reinterpret_cast<Acc*>(cumo_cuda_runtime_malloc(sizeof(Acc) * p.n_out * q.n_split));
+        const int64_t items = p.n_out * q.n_split;
+        if (wide) red_gen_kernel<R, kBlock><<<red_grid(items), kBlock, 0, st>>>(p, r, q, in, out, out2, partial);
+        else      red_gen_kernel<R, 32><<<red_grid((items + kWarpsPerBlock - 1) / kWarpsPerBlock), kBlock, 0, st>>>(p, r, q, in, out, out2, partial);
     }
-    if (n_split > 1) {
-        red_fold_kernel<R><<<grid_for((p.n_out + kWarpsPerBlock - 1) / kWarpsPerBlock, 8), kBlock, 0, st>>>(p, r, partial, n_split, out, out2);
+    int launches = 1;
+    if (q.n_split > 1) {
+        if (q.n_split > 256 && p.n_out < 4096)
+            red_fold_kernel<R, kBlock><<<red_grid(p.n_out), kBlock, 0, st>>>(p, r, partial, q.n_split, out, out2);
+        else
+            red_fold_kernel<R, 32><<<red_grid((p.n_out + kWarpsPerBlock - 1) / kWarpsPerBlock), kBlock, 0, st>>>(p, r, partial, q.n_split, out, out2);
         ++launches;
         cumo_cuda_runtime_free(reinterpret_cast<char*>(partial));
     }

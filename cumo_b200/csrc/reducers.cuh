@@ -56,6 +56,7 @@ struct SumLike {
     using In = T;
     using Acc = typename WideOf<T>::type;
     static constexpr bool kIndexed = false;
+    static constexpr bool kHasScan = false;
     int mean;
     T n;
     __device__ __forceinline__ Acc identity() const { return PROD ? (Acc)1 : (Acc)0; }
@@ -76,6 +77,7 @@ struct MeanNan {
     using In = T;
     struct Acc { T sum; T n; };
     static constexpr bool kIndexed = false;
+    static constexpr bool kHasScan = false;
     __device__ __forceinline__ Acc identity() const { return {(T)0, (T)0}; }
     __device__ __forceinline__ Acc map(T v, int64_t) const { return is_nan(v) ? Acc{(T)0, (T)0} : Acc{v, (T)1}; }
     __device__ __forceinline__ Acc combine(Acc a, Acc b) const { return {a.sum + b.sum, a.n + b.n}; }
@@ -88,6 +90,7 @@ struct Rms {
     using In = T;
     struct Acc { T sum; T n; };
     static constexpr bool kIndexed = false;
+    static constexpr bool kHasScan = false;
     T n_all;
     __device__ __forceinline__ Acc identity() const { return {(T)0, (T)0}; }
     __device__ __forceinline__ Acc map(T v, int64_t) const {
@@ -107,6 +110,7 @@ struct Moments {
     using In = T;
     struct Acc { T n; T mean; T m2; };
     static constexpr bool kIndexed = false;
+    static constexpr bool kHasScan = false;
     int take_sqrt;
     __device__ __forceinline__ Acc identity() const { return {(T)0, (T)0, (T)0}; }
     __device__ __forceinline__ Acc map(T v, int64_t) const {
@@ -138,6 +142,7 @@ struct Kahan {
     using In = T;
     struct Acc { T sum; T comp; };
     static constexpr bool kIndexed = false;
+    static constexpr bool kHasScan = false;
     __device__ __forceinline__ Acc identity() const { return {(T)0, (T)0}; }
     __device__ __forceinline__ Acc map(T v, int64_t) const {
         if (NAN_SKIP && is_nan(v)) return {(T)0, (T)0};
@@ -160,6 +165,7 @@ struct MinMax {
     using In = T;
     using Acc = T;
     static constexpr bool kIndexed = false;
+    static constexpr bool kHasScan = false;
     __device__ __forceinline__ Acc identity() const {
         if constexpr (is_fp<T>::value && !NAN_WINS) return quiet_nan<T>();
         else return IS_MAX ? data_min<T>() : data_max<T>();
@@ -180,6 +186,7 @@ struct MinAndMax {
     using In = T;
     struct Acc { T mn; T mx; };
     static constexpr bool kIndexed = false;
+    static constexpr bool kHasScan = false;
     __device__ __forceinline__ Acc identity() const {
         if constexpr (TWO_OUT && is_fp<T>::value && !NAN_WINS) return {quiet_nan<T>(), quiet_nan<T>()};
         else return {data_max<T>(), data_min<T>()};
@@ -225,13 +232,28 @@ struct ArgMinMax {
     using In = T;
     struct Acc { T value; int64_t index; };
     static constexpr bool kIndexed = true;
+    static constexpr bool kHasScan = true;
     int idx64;
+    // A thread's private scan of a run visited in increasing index order.  A strict
+    // comparison keeps the earlier of two equal elements, so no index is ever compared,
+    // and the position is a 32-bit offset into the thread's segment (negative: nothing
+    // seen yet).  Same answers as folding combine(acc, map(v, idx)) over the run.
+    struct Local { T value; int32_t pos; };
+    __device__ __forceinline__ Local local_identity() const { return {identity().value, -1}; }
+    __device__ __forceinline__ void local_scan(Local& l, T v, int32_t pos) const {
+        bool take = l.pos < 0 || (IS_MAX ? (l.value < v) : (v < l.value));
+        if constexpr (is_fp<T>::value) {
+            if constexpr (NAN_WINS) take = !is_nan(l.value) && (take || is_nan(v));   // the first NaN sticks
+            else take = take || (is_nan(l.value) && !is_nan(v));                      // a number replaces a NaN
+        }
+        if (take) { l.value = v; l.pos = pos; }
+    }
     __device__ __forceinline__ Acc identity() const {
         T v;
         if constexpr (!is_fp<T>::value) v = IS_MAX ? data_min<T>() : data_max<T>();
         else if constexpr (NAN_WINS) v = IS_MAX ? (T)-INFINITY : (T)INFINITY;
         else v = quiet_nan<T>();
-        return {v, idx64 ? INT64_MAX : (int64_t)INT32_MAX};
+        return {v, INT64_MAX};   // loses every tie; no real index reaches it
     }
     __device__ __forceinline__ Acc map(T v, int64_t idx) const { return {v, idx}; }
     __device__ __forceinline__ Acc combine(Acc a, Acc b) const {

@@ -43,11 +43,7 @@ template <typename T> struct alignas(16) Pack { T v[16 / sizeof(T)]; };
 template <typename T>
 __device__ __forceinline__ Pack<T> ld_pack(const void* p) {
     Pack<T> r;
-#ifdef CB200_X_PLAIN_LD
-    int4 q = *reinterpret_cast<const int4*>(p);
-#else
     int4 q = __ldcs(reinterpret_cast<const int4*>(p));
-#endif
     *reinterpret_cast<int4*>(&r) = q;
     return r;
 }
@@ -56,13 +52,7 @@ __device__ __forceinline__ void st_pack(void* p, const Pack<T>& v) {
     __stcs(reinterpret_cast<int4*>(p), *reinterpret_cast<const int4*>(&v));
 }
 template <typename T>
-__device__ __forceinline__ T ld_one(const void* p) {
-#ifdef CB200_X_PLAIN_LD1
-    return *reinterpret_cast<const T*>(p);
-#else
-    return __ldcs(reinterpret_cast<const T*>(p));
-#endif
-}
+__device__ __forceinline__ T ld_one(const void* p) { return __ldcs(reinterpret_cast<const T*>(p)); }
 template <>
 __device__ __forceinline__ int64_t ld_one<int64_t>(const void* p) {
     return (int64_t)__ldcs(reinterpret_cast<const long long*>(p));

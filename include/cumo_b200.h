@@ -250,6 +250,27 @@ CB200_DECL_ACCUM(dfloat, double, kahan_sum_nan)
 CB200_DECL_BITCOUNT(count_true)
 CB200_DECL_BITCOUNT(count_false)
 
+/* float32 `sum` that allocates nothing (no counterpart in the reference, whose reductions
+ * always take scratch from cumo_cuda_runtime_malloc).  For callers that cannot reach an
+ * allocator when they need the sum: a finalizer or other context in which the Ruby
+ * extension's pool callback must not run the GC or raise, an embedder that handed out all
+ * device memory at start-up, a loop that must not take the allocator's lock.  Same kernels
+ * and same answers as cumo_sfloat_sum_kernel_launch; the [output][segment] partial sums
+ * live in a fixed 1 MiB array inside the library image instead.
+ *   - accepts only reductions whose reduced axes form one contiguous run (a full sum of a
+ *     contiguous array, sums along the last axes); needs outputs x segments <= 262144
+ *     (a row is cut into 32 KiB segments, at most 8192 per row);
+ *   - returns 0 on success; otherwise nothing was launched and `errbuf` (may be NULL)
+ *     holds the reason: 1 layout not supported, 2 scratch too small for this shape,
+ *     3 the scratch address could not be looked up, 4 the launch itself failed;
+ *   - calls no cudaMalloc/cudaFree and no allocating library routine; launches on the
+ *     stream cb200_set_stream chose and does not call cumo_cuda_runtime_check_kernel_launch;
+ *   - all calls on a device share the array: calls whose kernels may overlap on the GPU
+ *     race on it, so keep them on one stream; nothing in it needs clearing between calls;
+ *   - the first call on each device looks up the array's address with that device current
+ *     (cudaGetSymbolAddress): make that first call before any stream capture begins. */
+int cb200_sfloat_sum_noalloc_kernel_launch(cumo_na_reduction_arg_t* arg, char* errbuf, size_t errlen);
+
 #ifdef __cplusplus
 }
 #endif

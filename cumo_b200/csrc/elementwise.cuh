@@ -362,14 +362,16 @@ cmp_flat_kernel(int64_t total, int64_t n_tiles, const char* __restrict__ a1, con
         for (int j = 0; j < U; ++j) {
             e0[j] = (tile * kEwSlots + j * kBlock + threadIdx.x) * (int64_t)V;
             const int64_t left = total - e0[j];
+#pragma unroll
+            for (int e = 0; e < V; ++e) { x[j].v[e] = sx; y[j].v[e] = sy; }
             if (left >= V) {
                 if (have1) { if (V > 1) x[j] = ld_pack<T1>(a1 + e0[j] * ES); else x[j].v[0] = ld_one<T1>(a1 + e0[j] * ES); }
                 if (have2) { if (V > 1) y[j] = ld_pack<T2>(a2 + e0[j] * ES); else y[j].v[0] = ld_one<T2>(a2 + e0[j] * ES); }
             } else {
 #pragma unroll
                 for (int e = 0; e < V; ++e) {
-                    if (have1) x[j].v[e] = e < left ? ld_one<T1>(a1 + (e0[j] + e) * ES) : T1();
-                    if (have2) y[j].v[e] = e < left ? ld_one<T2>(a2 + (e0[j] + e) * ES) : T2();
+                    if (have1 && e < left) x[j].v[e] = ld_one<T1>(a1 + (e0[j] + e) * ES);
+                    if (have2 && e < left) y[j].v[e] = ld_one<T2>(a2 + (e0[j] + e) * ES);
                 }
             }
         }
@@ -379,7 +381,7 @@ cmp_flat_kernel(int64_t total, int64_t n_tiles, const char* __restrict__ a1, con
             uint32_t bits = 0;
 #pragma unroll
             for (int e = 0; e < V; ++e)
-                bits |= (Op::test(have1 ? x[j].v[e] : sx, have2 ? y[j].v[e] : sy) ? 1u : 0u) << e;
+                bits |= (Op::test(x[j].v[e], y[j].v[e]) ? 1u : 0u) << e;
             if (left < V) bits &= left > 0 ? (1u << left) - 1u : 0u;     // elements past the end
             bits <<= (lane % LPW) * V;
             const uint32_t word = LPW == 32 ? __ballot_sync(0xffffffffu, bits != 0) : __reduce_or_sync(group_mask, bits);

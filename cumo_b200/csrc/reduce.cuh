@@ -238,7 +238,7 @@ __device__ __forceinline__ void col_item(const R& r, const RedPlan& p, const Red
     Runner<R, SCAN> run[V];
 #pragma unroll
     for (int k = 0; k < V; ++k) run[k].init(r);
-    auto row_off = [&](int64_t row) { return (p.n_rd == 1) ? row * p.in_rstep[0] : offset_of(row, p.n_rd, p.rshape, p.in_rstep); };
+    auto row_off = [&](int64_t row) { return row * p.in_rstep[0]; };
     int64_t r0 = r_begin + warp;
     if (nv == V) {
         // whole iterations: four rows of this warp inside the segment, whole packets
@@ -313,8 +313,7 @@ red_col_kernel(const RedPlan p, const R r, const RedLaunch q, const char* __rest
         Acc acc[V];
         if (nv > 0) {
             const char* base = in + in_b + col0 * ES;
-            if (R::kHasScan && q.ordered) col_item<R, V, R::kHasScan>(r, p, q, base, in_b, col0, nv, r_begin, r_end, warp, acc);
-            else col_item<R, V, false>(r, p, q, base, in_b, col0, nv, r_begin, r_end, warp, acc);
+            col_item<R, V, R::kHasScan>(r, p, q, base, in_b, col0, nv, r_begin, r_end, warp, acc);
         } else {
 #pragma unroll
             for (int k = 0; k < V; ++k) acc[k] = r.identity();
@@ -449,13 +448,16 @@ void launch_reduce(const cumo_na_reduction_arg_t* arg, const cumo_na_iarray_t* o
     for (int d = 0; d + 1 < p.n_rd; ++d) if (flat_index && p.in_rstep[d] < p.in_rstep[d + 1] * p.rshape[d + 1]) q.ordered = 0;
 
     const bool row = p.n_rd == 1 && (p.in_rstep[0] == ES || p.n_red <= 1);
-    const bool col = !row && p.in_ostep[p.n_od - 1] == ES && p.oshape[p.n_od - 1] >= 8;
+    // the column plan takes one strided reduce dim and index-ordered runs; anything else is GEN's
+    const bool col = !row && p.n_rd == 1 && q.ordered && p.in_ostep[p.n_od - 1] == ES && p.oshape[p.n_od - 1] >= 8;
 
     if (row) {
         const int64_t L = p.n_red;
         bool vec = aligned16(in);
         for (int d = 0; d < p.n_od && vec; ++d) if (!mult16(p.in_ostep[d])) vec = false;
-        const bool wide = L >= 4096;                   // a CTA per item, else a warp per item
+        // a warp per row while there are rows enough to fill the device that way (no CTA-wide fold per
+        // 16 KiB of input); a CTA per (row, segment) for long or few rows
+        const bool wide = L >= 4096 && !(L <= 65536 && p.n_out >= (int64_t)sm_count() * 64);
         q.seg_len = L > 0 ? L : 1;
         if (wide) {
             int64_t seg = kSegBytes / ES;              // a multiple of 32 elements: segment starts stay 16-byte aligned

@@ -40,8 +40,8 @@ METRIC = "effective HBM GB/s, fp32 broadcast-elementwise chain x(8192,1)+y(1,163
 NOMINAL_HBM_GBS = 8000.0
 FALLBACK_HBM_GBS = 6650.0
 # dram__bytes_read.sum + dram__bytes_write.sum of one ew_row_kernel<Exp<float>,4> launch on this
-# workload, from the ncu capture summarised in profiles/; None until a capture exists.
-EXP_KERNEL_DRAM_TRAFFIC_BYTES = None
+# workload (profiles/kernel_counters_512MiB.md, row "exp": the same 512 MiB in / 512 MiB out launch).
+EXP_KERNEL_DRAM_TRAFFIC_BYTES = 536890624 + 485002240
 
 
 def measured_peak():

@@ -214,6 +214,15 @@ def kernel_table(torch, xp, peak):
     im = ia.reshape(32768, 4096)
     add("C4", "max_index(axis:1) (32768,4096)", s + 32768 * 4, lambda: im.max_index(axis=1))
     add("C4", "Int32 sum -> Int64", s + 8, lambda: ia.sum())
+    del ia, ib, mask, im
+    # C5 (BASELINE config 4): k-means assignment, 2^24 points x 64-D against 256 centres, fused
+    from cumo_b200 import kmeans
+    n, d, k = 1 << 24, 64, 256
+    cen = torch.randn(k, d, device="cuda", generator=g) * 4
+    pts = cen[torch.randint(0, k, (n,), device="cuda", generator=g)] + torch.randn(n, d, device="cuda", generator=g)
+    px, pc = xp.SFloat.from_torch(pts), xp.SFloat.from_torch(cen)
+    add("C5", "kmeans assign 2^24x64 vs 256 (fused, fp32 cores)", n * d * 4 + k * d * 4 + n * 4 + k * 8, lambda: kmeans.assign(px, pc))
+    rows[-1]["TFLOPs"] = round(2.0 * n * k * d / (rows[-1]["ms"] * 1e-3) / 1e12, 2)
     return rows
 
 

@@ -250,6 +250,18 @@ CB200_DECL_ACCUM(dfloat, double, kahan_sum_nan)
 CB200_DECL_BITCOUNT(count_true)
 CB200_DECL_BITCOUNT(count_false)
 
+/* Fused k-means assignment step (no counterpart in the reference, whose benchmark builds it from
+ * array operations and materialises the (N, K) distance matrix: bench/kmeans_bench.rb:108-126).
+ * x: n points of d float32 (row-major, 16-byte aligned), c: k centroids of d float32.
+ * labels[p] = argmin_k ( |c_k|^2 - 2 <x_p, c_k> ), lowest k on ties (the |x_p|^2 term is constant
+ * per point and left out, as in the reference's formulation); min_dist (may be NULL) gets that
+ * smallest value; counts (may be NULL) gets, ADDED to what it holds, the number of points per
+ * cluster (zero it first; integer atomics, exact in any order).  d must be a multiple of 4 and the
+ * centroid table must fit shared memory ((k rounded up to 128) * (d + 4) floats + 128 * (d + 4)
+ * floats <= 200 KiB).  Returns 0, or non-zero with the reason in errbuf (may be NULL). */
+int cb200_kmeans_assign_sfloat(const float* x, int64_t n, int d, const float* c, int k, int32_t* labels,
+                               float* min_dist, unsigned long long* counts, char* errbuf, size_t errlen);
+
 /* float32 `sum` that allocates nothing (no counterpart in the reference, whose reductions
  * always take scratch from cumo_cuda_runtime_malloc).  For callers that cannot reach an
  * allocator when they need the sum: a finalizer or other context in which the Ruby

@@ -189,6 +189,33 @@ double oracle_sum_f64ref(int dtype, const char* p, int64_t n) {
     return dtype == DT_SFLOAT ? pairwise_f32((const float*)p, n) : pairwise_f64((const double*)p, n);
 }
 
+/* k-means assignment (the step of bench/kmeans_bench.rb:108-126: d = |c|^2 - 2 x.c, then the index
+ * of the row minimum, lowest index on ties) evaluated in float64 from the float32 inputs, together
+ * with the winning value and the runner-up's, so that a caller can tell a genuine disagreement from
+ * a near-tie that float32 rounding may decide either way. */
+void oracle_kmeans_assign(const float* x, int64_t n, int d, const float* c, int k, int32_t* labels,
+                          double* best, double* second) {
+    #pragma omp parallel for schedule(static)
+    for (int64_t p = 0; p < n; ++p) {
+        double b = INFINITY, s = INFINITY;
+        int32_t bk = 0;
+        for (int kk = 0; kk < k; ++kk) {
+            double dot = 0, cn = 0;
+            for (int q = 0; q < d; ++q) {
+                double cv = c[(int64_t)kk * d + q];
+                dot += (double)x[p * d + q] * cv;
+                cn += cv * cv;
+            }
+            double dist = cn - 2 * dot;
+            if (dist < b) { s = b; b = dist; bk = kk; }
+            else if (dist < s) s = dist;
+        }
+        labels[p] = bk;
+        if (best) best[p] = b;
+        if (second) second[p] = s;
+    }
+}
+
 int oracle_threads(void) {
 #ifdef _OPENMP
     return omp_get_max_threads();

@@ -218,3 +218,19 @@ def sum_f64ref(a: np.ndarray) -> float:
     """Pairwise float64 sum of a contiguous float array: the yardstick of the stated tolerances."""
     a = np.ascontiguousarray(a)
     return float(lib().oracle_sum_f64ref(DT[a.dtype], a.ctypes.data, a.size))
+
+
+def kmeans_assign(x: np.ndarray, c: np.ndarray):
+    """(labels int32, best float64, second float64) of the assignment step in float64."""
+    x = np.ascontiguousarray(x, dtype=np.float32)
+    c = np.ascontiguousarray(c, dtype=np.float32)
+    n, d = x.shape
+    k = c.shape[0]
+    labels = np.empty(n, dtype=np.int32)
+    best = np.empty(n, dtype=np.float64)
+    second = np.empty(n, dtype=np.float64)
+    fn = lib().oracle_kmeans_assign
+    fn.restype = None
+    fn.argtypes = [c_void_p, c_int64, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p]
+    fn(x.ctypes.data, n, d, c.ctypes.data, k, labels.ctypes.data, best.ctypes.data, second.ctypes.data)
+    return labels, best, second

@@ -221,8 +221,12 @@ def kernel_table(torch, xp, peak):
     cen = torch.randn(k, d, device="cuda", generator=g) * 4
     pts = cen[torch.randint(0, k, (n,), device="cuda", generator=g)] + torch.randn(n, d, device="cuda", generator=g)
     px, pc = xp.SFloat.from_torch(pts), xp.SFloat.from_torch(cen)
-    add("C5", "kmeans assign 2^24x64 vs 256 (fused, fp32 cores)", n * d * 4 + k * d * 4 + n * 4 + k * 8, lambda: kmeans.assign(px, pc))
-    rows[-1]["TFLOPs"] = round(2.0 * n * k * d / (rows[-1]["ms"] * 1e-3) / 1e12, 2)
+    for algo, what in (("tensor", "fused, tcgen05 3xTF32"), ("cores", "fused, fp32 cores")):
+        add("C5", f"kmeans assign 2^24x64 vs 256 ({what})", n * d * 4 + k * d * 4 + n * 4 + k * 8, lambda algo=algo: kmeans.assign(px, pc, algo=algo))
+        # useful flops of the (N, K, D) contraction; the tensor form issues three TF32 MMAs per product
+        rows[-1]["TFLOPs"] = round(2.0 * n * k * d / (rows[-1]["ms"] * 1e-3) / 1e12, 2)
+        if algo == "tensor":
+            rows[-1]["TFLOPs_issued_tf32"] = round(3 * rows[-1]["TFLOPs"], 1)
     return rows
 
 

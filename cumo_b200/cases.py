@@ -46,6 +46,13 @@ def build_cases(xp, torch, mib: int):
         a = f32().reshape(rows32, cols)
         return a, a.sum(axis=1).reshape(rows32, 1)
 
+    def km():
+        from . import kmeans
+        n, d, k = n32 // 64, 64, 256
+        cen = torch.randn(k, d, device="cuda", generator=g) * 4
+        pts = cen[torch.randint(0, k, (n,), device="cuda", generator=g)] + torch.randn(n, d, device="cuda", generator=g)
+        return kmeans, xp.SFloat.from_torch(pts), xp.SFloat.from_torch(cen)
+
     cases = {
         # name: (setup -> callable, algorithmic bytes)
         "exp": (lambda: (lambda a=f32(): xp.NMath.exp(a)), 2 * n32 * 4),
@@ -64,6 +71,8 @@ def build_cases(xp, torch, mib: int):
         "gt_scalar_i32": (lambda: (lambda a=i32(): a > 0), n32 * 4 + n32 // 8),
         "count_true": (lambda: (lambda m=(i32() > 0): m.count_true()), n32 // 8),
         "mod_scalar_i32": (lambda: (lambda a=i32(): a % 7), 2 * n32 * 4),
+        "kmeans_tensor": (lambda: (lambda m=km(): m[0].assign(m[1], m[2], algo="tensor")), n32 * 4 + n32 // 16),
+        "kmeans_cores": (lambda: (lambda m=km(): m[0].assign(m[1], m[2], algo="cores")), n32 * 4 + n32 // 16),
         "sum_i32": (lambda: (lambda a=i32(): a.sum()), n32 * 4),
     }
     return cases

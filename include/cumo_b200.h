@@ -262,6 +262,15 @@ CB200_DECL_BITCOUNT(count_false)
 int cb200_kmeans_assign_sfloat(const float* x, int64_t n, int d, const float* c, int k, int32_t* labels,
                                float* min_dist, unsigned long long* counts, char* errbuf, size_t errlen);
 
+/* The same step with the contraction on the tcgen05 tensor cores (TF32 operands split into head and
+ * tail, three products accumulated in fp32 in tensor memory: fp32-grade accuracy).  Same arguments
+ * and results as cb200_kmeans_assign_sfloat; needs d a multiple of 32, k <= 256 and the centroid
+ * table (2 * d * roundup(k,16) * 4 bytes) plus 96 KiB of point slots within 227 KiB of shared memory
+ * (d = 64, k = 256 fits).  It reads back a status word, so it synchronises the stream; return 5 means
+ * a bounded wait inside the kernel ran out and the outputs are not valid. */
+int cb200_kmeans_assign_sfloat_tc(const float* x, int64_t n, int d, const float* c, int k, int32_t* labels,
+                                  float* min_dist, unsigned long long* counts, char* errbuf, size_t errlen);
+
 /* float32 `sum` that allocates nothing (no counterpart in the reference, whose reductions
  * always take scratch from cumo_cuda_runtime_malloc).  For callers that cannot reach an
  * allocator when they need the sum: a finalizer or other context in which the Ruby

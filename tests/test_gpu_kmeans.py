@@ -18,10 +18,10 @@ def mixture(rng, n, d, k):
     return (centres[which] + rng.standard_normal((n, d))).astype(np.float32), centres
 
 
-def check(xp_gpu, x, c):
+def check(xp_gpu, x, c, algo="auto"):
     from cumo_b200 import kmeans
 
-    labels, counts, dist = kmeans.assign(xp_gpu.SFloat.from_numpy(x), xp_gpu.SFloat.from_numpy(c), want_min_dist=True)
+    labels, counts, dist = kmeans.assign(xp_gpu.SFloat.from_numpy(x), xp_gpu.SFloat.from_numpy(c), want_min_dist=True, algo=algo)
     got = labels.to_numpy()
     want, best, second = orc.kmeans_assign(x, c)
     flips = np.nonzero(got != want)[0]
@@ -34,10 +34,33 @@ def check(xp_gpu, x, c):
 
 
 @pytest.mark.parametrize("n,d,k", [(1, 64, 256), (127, 64, 256), (1000, 64, 256), (100_003, 64, 256), (5000, 16, 7), (5000, 128, 120), (3000, 32, 600), (4096, 4, 1)])
-def test_kmeans_assign_matches_float64(xp_gpu, n, d, k):
+@pytest.mark.parametrize("algo", ["cores", "tensor"])
+def test_kmeans_assign_matches_float64(xp_gpu, n, d, k, algo):
+    from cumo_b200 import kmeans
+
+    if algo == "tensor" and not kmeans.tensor_core_form_fits(d, k):
+        pytest.skip("shape outside the tensor-core form")
     rng = np.random.default_rng(n + d + k)
     x, c = mixture(rng, n, d, k)
-    check(xp_gpu, x, c)
+    check(xp_gpu, x, c, algo)
+
+
+@pytest.mark.parametrize("n,d,k", [(128, 32, 16), (129, 32, 1), (70_000, 32, 250), (20_000, 96, 100), (40_000, 64, 33), (148 * 128 * 3 + 5, 64, 256)])
+def test_kmeans_tensor_core_form_shapes(xp_gpu, n, d, k):
+    """Shapes that exercise the tensor-core form's edges: one K-block, padded centroid counts,
+    a ragged last tile, more tiles than CTAs."""
+    rng = np.random.default_rng(7 * n + d + k)
+    x, c = mixture(rng, n, d, k)
+    check(xp_gpu, x, c, "tensor")
+
+
+def test_kmeans_tensor_core_form_refuses_other_shapes(xp_gpu):
+    from cumo_b200 import kmeans
+
+    with pytest.raises(xp_gpu.CumoError, match="multiple of 32"):
+        kmeans.assign(xp_gpu.SFloat.zeros(256, 48), xp_gpu.SFloat.zeros(8, 48), algo="tensor")
+    with pytest.raises(xp_gpu.CumoError, match="shared memory"):
+        kmeans.assign(xp_gpu.SFloat.zeros(256, 128), xp_gpu.SFloat.zeros(256, 128), algo="tensor")
 
 
 def test_kmeans_refuses_a_table_that_does_not_fit_shared_memory(xp_gpu):
@@ -49,7 +72,8 @@ def test_kmeans_refuses_a_table_that_does_not_fit_shared_memory(xp_gpu):
         kmeans.assign(x, c)
 
 
-def test_kmeans_ties_take_the_lowest_index(xp_gpu):
+@pytest.mark.parametrize("algo", ["cores", "tensor"])
+def test_kmeans_ties_take_the_lowest_index(xp_gpu, algo):
     from cumo_b200 import kmeans
 
     rng = np.random.default_rng(0)
@@ -57,12 +81,13 @@ def test_kmeans_ties_take_the_lowest_index(xp_gpu):
     c[200] = c[17]                       # two identical centroids: the earlier one must win
     c[130] = c[17]
     x = np.repeat(c[17][None, :], 300, axis=0) + (rng.standard_normal((300, 64)) * 1e-3).astype(np.float32)
-    labels, counts = kmeans.assign(xp_gpu.SFloat.from_numpy(x), xp_gpu.SFloat.from_numpy(c))
+    labels, counts = kmeans.assign(xp_gpu.SFloat.from_numpy(x), xp_gpu.SFloat.from_numpy(c), algo=algo)
     assert np.all(labels.to_numpy() == 17)
     assert counts.to_numpy()[17] == 300 and counts.to_numpy().sum() == 300
 
 
-def test_kmeans_baseline_config_sample(xp_gpu):
+@pytest.mark.parametrize("algo", ["cores", "tensor"])
+def test_kmeans_baseline_config_sample(xp_gpu, algo):
     """BASELINE config 4 at full size on the device (2^24 points, 64-D, 256 centres, a seeded mixture);
     the float64 check runs on every 97th point, the counts on all of them."""
     import torch
@@ -74,7 +99,7 @@ def test_kmeans_baseline_config_sample(xp_gpu):
     which = torch.randint(0, k, (n,), device="cuda", generator=g)
     x = centres[which] + torch.randn(n, d, device="cuda", generator=g)
     del which
-    labels, counts = kmeans.assign(xp_gpu.SFloat.from_torch(x), xp_gpu.SFloat.from_torch(centres))
+    labels, counts = kmeans.assign(xp_gpu.SFloat.from_torch(x), xp_gpu.SFloat.from_torch(centres), algo=algo)
     got = labels.to_numpy()
     assert np.array_equal(counts.to_numpy(), np.bincount(got, minlength=k).astype(np.uint64))
     sample = slice(0, n, 97)

@@ -144,12 +144,17 @@ def run_reference(args):
 
 
 def time_kernel(torch, fn, reps=10, warm=2):
-    """Median / min device time (ms) of fn() measured launch by launch with CUDA events on the launch stream."""
+    """Median / min device time (ms) of fn() measured launch by launch with CUDA events on the launch stream.
+    A short busy-wait kernel is queued ahead of the first event so that the host has the call enqueued before
+    the device reaches it: the interval is then the device time of the call, not the host's time to issue it."""
     for _ in range(warm):
         fn()
+    hold = getattr(torch.cuda, "_sleep", None)
     ts = []
     for _ in range(reps):
         a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        if hold is not None:
+            hold(400_000)                     # ~0.2 ms of device time on the same stream
         a.record()
         fn()
         b.record()

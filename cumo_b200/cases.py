@@ -60,6 +60,7 @@ def build_cases(xp, torch, mib: int):
         "mul": (lambda: (lambda a=f32(): a * a), 3 * n32 * 4),
         "outer_add": (lambda: (lambda xy=outer(): xy[0] + xy[1]), n32 * 4),
         "add_col": (lambda: (lambda ac=col(): ac[0] + ac[1]), 2 * n32 * 4),
+        "mul_row": (lambda: (lambda a=f32().reshape(rows32, cols), w=f32()[0:cols].reshape(1, cols): a * w), 2 * n32 * 4),
         "sum_f32": (lambda: (lambda a=f32(): a.sum()), n32 * 4),
         "sum_f64": (lambda: (lambda a=f64(): a.sum()), n64 * 8),
         "max_f64": (lambda: (lambda a=f64(): a.max()), n64 * 8),
@@ -99,8 +100,11 @@ def main():
     for _ in range(a.warm):
         fn()
     ts = []
+    hold = getattr(torch.cuda, "_sleep", None)
     for _ in range(a.reps):
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        if hold is not None:
+            hold(400_000)        # keeps the device busy ~0.2 ms so the call is enqueued before the first event fires
         e0.record()
         fn()
         e1.record()

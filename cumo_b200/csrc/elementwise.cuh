@@ -201,6 +201,114 @@ ew_row_kernel(const EwPlan p, const RowGeom g, const char* __restrict__ a1, cons
 }
 
 // ----------------------------------------------------------------------------
+// ROW-SHARE kernel.  Two canonical dims (rows x L) where an input is a row vector
+// repeated down the rows (row step 0, inner step one element) and the other input
+// is one element per row, another such vector or a scalar: x(R,1) + y(1,C).  The
+// output is the only real traffic, and the plain row kernel spends ~100 instructions
+// per 16-byte store on index arithmetic that is the same for every row; here a CTA
+// keeps its packets of the vector in registers and walks kShareRows rows with them.
+// ----------------------------------------------------------------------------
+constexpr int kShareRows = 16;                   // rows per CTA
+constexpr int kShareBatch = 4;                   // rows whose loads are issued together
+
+// How an input reaches a row of the tile.  The kernel is compiled per pair of modes so that
+// its inner loop carries no tests and no copies.
+enum : int { kHeld = 0,      // same packets for every row: the shared row vector, or a scalar argument
+             kRowScalar = 1, // one element per row (inner step 0)
+             kRowPack = 2 }; // a packet per row and slot
+
+template <typename Op, int V, int M1, int M2>
+__global__ void __launch_bounds__(kBlock)
+ew_rowshare_kernel(const RowGeom g, const char* __restrict__ a1, const char* __restrict__ a2, char* a3,
+                   typename Op::In1 sx, typename Op::In2 sy, int* flag) {
+    using T1 = typename Op::In1;
+    using T2 = typename Op::In2;
+    using TO = typename Op::Out;
+    constexpr int ES = sizeof(TO);
+    constexpr int U = kEwUnroll;
+    constexpr int B = kShareBatch;
+
+    for (int64_t tile = blockIdx.x; tile < g.n_tiles; tile += gridDim.x) {   // one pass unless the grid was capped
+        int64_t rg;
+        uint32_t ch;
+        if (tile <= 0xffffffffLL) {
+            const uint32_t t = (uint32_t)tile, q = t / g.chunks_per_row;
+            rg = q; ch = t - q * g.chunks_per_row;
+        } else {
+            rg = tile / g.chunks_per_row; ch = (uint32_t)(tile - rg * g.chunks_per_row);
+        }
+        uint32_t col[U];                       // byte offset of my packet within a row
+        bool ok[U];
+        Pack<T1> xs[U];
+        Pack<T2> ys[U];
+#pragma unroll
+        for (int j = 0; j < U; ++j) {
+            const uint64_t c = ((uint64_t)ch * kEwSlots + j * kBlock + threadIdx.x) * V;
+            ok[j] = c < (uint64_t)g.L;
+            col[j] = (uint32_t)c * ES;
+#pragma unroll
+            for (int e = 0; e < V; ++e) { xs[j].v[e] = sx; ys[j].v[e] = sy; }
+            if (ok[j]) {
+                if (M1 == kHeld && a1) xs[j] = ld_pack<T1>(a1 + col[j]);
+                if (M2 == kHeld && a2) ys[j] = ld_pack<T2>(a2 + col[j]);
+            }
+        }
+        const int64_t row0 = rg * kShareRows;
+        const int rows = (int)(g.R - row0 < kShareRows ? g.R - row0 : kShareRows);
+        const char* q1 = a1 + row0 * g.rs[0];
+        const char* q2 = a2 + row0 * g.rs[1];
+        char* q3 = a3 + row0 * g.rs[2];
+        for (int rb = 0; rb < rows; rb += B) {
+            T1 xr[B];
+            T2 yr[B];
+            Pack<T1> xp[B][U];
+            Pack<T2> yp[B][U];
+#pragma unroll
+            for (int r = 0; r < B; ++r) {
+                if (rb + r >= rows) continue;
+                if (M1 == kRowScalar) xr[r] = ld_one<T1>(q1 + r * g.rs[0]);
+                if (M2 == kRowScalar) yr[r] = ld_one<T2>(q2 + r * g.rs[1]);
+#pragma unroll
+                for (int j = 0; j < U; ++j) {
+                    if (!ok[j]) continue;
+                    if (M1 == kRowPack) xp[r][j] = ld_pack<T1>(q1 + r * g.rs[0] + col[j]);
+                    if (M2 == kRowPack) yp[r][j] = ld_pack<T2>(q2 + r * g.rs[1] + col[j]);
+                }
+            }
+#pragma unroll
+            for (int r = 0; r < B; ++r) {
+                if (rb + r >= rows) continue;
+#pragma unroll
+                for (int j = 0; j < U; ++j) {
+                    if (!ok[j]) continue;
+                    char* q = q3 + r * g.rs[2] + col[j];
+                    Pack<TO> z;
+                    unsigned keep = 0;
+#pragma unroll
+                    for (int e = 0; e < V; ++e) {
+                        const T1 xv = M1 == kHeld ? xs[j].v[e] : M1 == kRowScalar ? xr[r] : xp[r][j].v[e];
+                        const T2 yv = M2 == kHeld ? ys[j].v[e] : M2 == kRowScalar ? yr[r] : yp[r][j].v[e];
+                        TO zv = TO();
+                        if (Op::apply(xv, yv, zv, flag)) keep |= 1u << e;
+                        z.v[e] = zv;
+                    }
+                    if (keep == (1u << V) - 1u) {
+                        st_pack<TO>(q, z);
+                    } else {
+#pragma unroll
+                        for (int e = 0; e < V; ++e)
+                            if (keep & (1u << e)) st_one<TO>(q + e * ES, z.v[e]);
+                    }
+                }
+            }
+            q1 += B * g.rs[0];
+            q2 += B * g.rs[1];
+            q3 += B * g.rs[2];
+        }
+    }
+}
+
+// ----------------------------------------------------------------------------
 // GEN kernel: any strides, any element sizes
 // ----------------------------------------------------------------------------
 template <typename Op>
@@ -294,6 +402,28 @@ void launch_elementwise(const cumo_na_iarray_t* a1, const cumo_na_iarray_t* a2, 
                 g.inner[0] = have1 && p.step[0][in] != 0;
                 g.inner[1] = have2 && p.step[1][in] != 0;
                 for (int a = 0; a < 3; ++a) g.rs[a] = p.nd == 2 ? p.step[a][0] : 0;
+                // a row vector repeated down the rows is worth holding in registers
+                const bool shared_row = p.nd == 2 && ((g.inner[0] == 1 && g.rs[0] == 0) || (g.inner[1] == 1 && g.rs[1] == 0));
+                if constexpr (Op::arity == 2)
+                if (v16 && shared_row && vpr >= kBlock && g.R >= 2 * kShareRows && len * ES <= 0xffffffffLL) {
+                    const int64_t chunks = (vpr + kEwSlots - 1) / kEwSlots;
+                    g.rows_per_tile = 1;
+                    g.chunks_per_row = (uint32_t)chunks;
+                    g.vpr = kEwSlots;
+                    g.n_tiles = (g.R + kShareRows - 1) / kShareRows * chunks;
+                    // mode of each input: held (shared row vector, or the scalar argument: null pointer), one element per row, a packet per row
+                    const int m1 = !have1 || (g.inner[0] == 1 && g.rs[0] == 0) ? kHeld : g.inner[0] == 0 ? kRowScalar : kRowPack;
+                    const int m2 = !have2 || (g.inner[1] == 1 && g.rs[1] == 0) ? kHeld : g.inner[1] == 0 ? kRowScalar : kRowPack;
+                    const unsigned grid = grid_of(g.n_tiles);
+                    const char* h1 = have1 ? q1 : nullptr;
+                    const char* h2 = have2 ? q2 : nullptr;
+                    bool done = true;
+                    if (m1 == kHeld && m2 == kHeld)           ew_rowshare_kernel<Op, VMAX, kHeld, kHeld><<<grid, kBlock, 0, st>>>(g, h1, h2, q3, sx, sy, flag);
+                    else if (m1 == kHeld && m2 == kRowScalar) ew_rowshare_kernel<Op, VMAX, kHeld, kRowScalar><<<grid, kBlock, 0, st>>>(g, h1, h2, q3, sx, sy, flag);
+                    else if (m1 == kRowScalar && m2 == kHeld) ew_rowshare_kernel<Op, VMAX, kRowScalar, kHeld><<<grid, kBlock, 0, st>>>(g, h1, h2, q3, sx, sy, flag);
+                    else done = false;        // a full array against a row vector: the plain row kernel measures faster (fewer registers)
+                    if (done) { ++launches; return true; }
+                }
                 if (vpr >= kEwSlots) {
                     g.rows_per_tile = 1;
                     const int64_t chunks = (vpr + kEwSlots - 1) / kEwSlots;
@@ -337,6 +467,38 @@ void launch_elementwise(const cumo_na_iarray_t* a1, const cumo_na_iarray_t* a2, 
 // Flat kernel: inputs contiguous (or broadcast scalars), Bit output contiguous
 // and starting on a word boundary.  Each lane tests V consecutive elements;
 // the 32/V lanes that share an output word OR their bit groups together.
+// Whole-tile kernel for the flat case: each lane loads one element per step, so a warp's
+// ballot IS the output word (no bit assembly across lanes); lane j keeps the word of step j
+// and the first U lanes store the warp's U words together.  Array-or-scalar is a template
+// argument so the loop carries no tests.  Elements past the last whole tile go to
+// cmp_flat_kernel below.
+template <typename T> constexpr int cmp_steps() { return 64 / (int)sizeof(T); }     // 16 (4-byte) or 8 (8-byte) loads in flight per thread
+
+template <typename Op, bool A1, bool A2>
+__global__ void __launch_bounds__(kBlock)
+cmp_full_kernel(const typename Op::In1* __restrict__ a1, const typename Op::In2* __restrict__ a2, uint32_t* out,
+                typename Op::In1 sx, typename Op::In2 sy) {
+    using T1 = typename Op::In1;
+    using T2 = typename Op::In2;
+    constexpr int U = cmp_steps<T1>();
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const size_t first = ((size_t)blockIdx.x * (kBlock / 32) + warp) * (32 * U) + lane;
+    T1 x[U];
+    T2 y[U];
+#pragma unroll
+    for (int j = 0; j < U; ++j) {
+        x[j] = A1 ? ld_one<T1>(a1 + first + j * 32) : sx;
+        y[j] = A2 ? ld_one<T2>(a2 + first + j * 32) : sy;
+    }
+    uint32_t mine = 0;
+#pragma unroll
+    for (int j = 0; j < U; ++j) {
+        const uint32_t w = __ballot_sync(0xffffffffu, Op::test(x[j], y[j]));
+        if (lane == j) mine = w;
+    }
+    if (lane < U) out[((size_t)blockIdx.x * (kBlock / 32) + warp) * U + lane] = mine;
+}
+
 template <typename Op, int V>
 __global__ void __launch_bounds__(kBlock)
 cmp_flat_kernel(int64_t total, int64_t n_tiles, const char* __restrict__ a1, const char* __restrict__ a2,
@@ -462,14 +624,40 @@ void launch_compare(const cumo_na_iarray_t* a1, const cumo_na_iarray_t* a2, cumo
         uint32_t* out = a3->ptr + (a3->pos >> 5);
         int st1 = have1 && p.step[0][0] != 0, st2 = have2 && p.step[1][0] != 0;
         constexpr int VMAX = 16 / ES;
-        bool vec = (!st1 || aligned16(p1)) && (!st2 || aligned16(p2));
-        if (vec) {
-            int64_t n_tiles = (p.total + (int64_t)kEwSlots * VMAX - 1) / ((int64_t)kEwSlots * VMAX);
-            cmp_flat_kernel<Op, VMAX><<<grid_of(n_tiles), kBlock, 0, st>>>(p.total, n_tiles, p1, p2, out, st1, st2, sx, sy, use_scalar);
-        } else {
-            int64_t n_tiles = (p.total + kEwSlots - 1) / kEwSlots;
-            cmp_flat_kernel<Op, 1><<<grid_of(n_tiles), kBlock, 0, st>>>(p.total, n_tiles, p1, p2, out, st1, st2, sx, sy, use_scalar);
+        int launches = 0;
+        // whole tiles: every operand is an array that steps or a scalar argument (a one-element
+        // array that is broadcast has its value on the device and stays with the kernel below)
+        constexpr int64_t kTile = (int64_t)kBlock * cmp_steps<T1>();
+        const int64_t full = p.total / kTile;
+        int64_t done = 0;
+        if (full > 0 && full <= kMaxGrid && (st1 || st2) && (st1 || !have1) && (st2 || !have2)) {
+            using T2 = typename Op::In2;
+            const T1* q1 = reinterpret_cast<const T1*>(p1);
+            const T2* q2 = reinterpret_cast<const T2*>(p2);
+            if (st1 && st2)  cmp_full_kernel<Op, true, true><<<(unsigned)full, kBlock, 0, st>>>(q1, q2, out, sx, sy);
+            else if (st1)    cmp_full_kernel<Op, true, false><<<(unsigned)full, kBlock, 0, st>>>(q1, q2, out, sx, sy);
+            else             cmp_full_kernel<Op, false, true><<<(unsigned)full, kBlock, 0, st>>>(q1, q2, out, sx, sy);
+            ++launches;
+            done = full * kTile;
         }
+        if (done < p.total) {
+            const int64_t rest = p.total - done;
+            const char* r1 = st1 ? p1 + done * ES : p1;
+            const char* r2 = st2 ? p2 + done * ES : p2;
+            uint32_t* ro = out + (done >> 5);
+            bool vec = (!st1 || aligned16(r1)) && (!st2 || aligned16(r2));
+            if (vec) {
+                int64_t n_tiles = (rest + (int64_t)kEwSlots * VMAX - 1) / ((int64_t)kEwSlots * VMAX);
+                cmp_flat_kernel<Op, VMAX><<<grid_of(n_tiles), kBlock, 0, st>>>(rest, n_tiles, r1, r2, ro, st1, st2, sx, sy, use_scalar);
+            } else {
+                int64_t n_tiles = (rest + kEwSlots - 1) / kEwSlots;
+                cmp_flat_kernel<Op, 1><<<grid_of(n_tiles), kBlock, 0, st>>>(rest, n_tiles, r1, r2, ro, st1, st2, sx, sy, use_scalar);
+            }
+            ++launches;
+        }
+        count_launch(launches);
+        cumo_cuda_runtime_check_kernel_launch();
+        return;
     } else {
         // is the output still one run of bits in logical order?
         bool word_store = (a3->pos & 31) == 0;

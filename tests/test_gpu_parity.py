@@ -102,6 +102,7 @@ def test_binary_scalar_forms(xp_gpu, tname):
 
 @pytest.mark.parametrize("tname", list(NP))
 @pytest.mark.parametrize("shapes", [((4096, 1), (1, 512)), ((300, 784), (300, 1)), ((300, 784), (1, 784)), ((300, 784), (784,)),
+                                    ((70, 1), (1, 2052)), ((67, 2056), (1, 2056)), ((33, 1500), (1500,)), ((1, 4100), (40, 4100)),
                                     ((7, 1, 33), (1, 5, 33)), ((6, 5, 1, 3), (5, 4, 1)), ((2, 3, 4, 5, 6), (2, 3, 4, 5, 6)), ((5, 3), (1,))])
 def test_binary_broadcast(xp_gpu, tname, shapes):
     rng = np.random.default_rng(11)
@@ -230,7 +231,7 @@ def test_float_unary_and_math(xp_gpu, tname):
 
 
 @pytest.mark.parametrize("tname", list(NP))
-@pytest.mark.parametrize("n", [1, 31, 32, 33, 95, 96, 97, 1024, 4099, 100_000])
+@pytest.mark.parametrize("n", [1, 31, 32, 33, 95, 96, 97, 1024, 4099, 8192, 100_000])
 def test_compare_packs_bits_exactly(xp_gpu, tname, n):
     rng = np.random.default_rng(n + 1)
     ha, hb = rng_array(rng, tname, n, -3, 3), rng_array(rng, tname, n, -3, 3)

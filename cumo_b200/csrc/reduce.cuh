@@ -335,6 +335,84 @@ red_col_kernel(const RedPlan p, const R r, const RedLaunch q, const char* __rest
     }
 }
 
+// ---- COL, wide rows ---------------------------------------------------------------------
+// When a row of output columns is at least half a CTA's width of packets, every thread owns
+// V columns outright: the CTA reads kBlock contiguous packets of each row (4 KiB), walks the
+// rows of its segment with kColUnroll loads in flight per thread, and nothing is folded across
+// threads at all.
+constexpr int kColUnroll = 8;
+
+template <typename R, int V>
+__global__ void __launch_bounds__(kBlock, 4)
+red_colwide_kernel(const RedPlan p, const R r, const RedLaunch q, const char* __restrict__ in, char* out, char* out2,
+                   typename R::Acc* partial) {
+    using T = typename R::In;
+    constexpr int ES = sizeof(T);
+    constexpr int W = kBlock * V;            // columns per strip
+    constexpr int U = kColUnroll;
+    const int od_in = p.n_od - 1;            // innermost out dim = the columns
+    const int64_t C = p.oshape[od_in];
+    const int64_t n_batch = p.n_out / C;
+    const int64_t items = n_batch * q.n_strips * q.n_split;
+    const int64_t rstep = p.in_rstep[0];
+    for (int64_t item = blockIdx.x; item < items; item += gridDim.x) {
+        // strips vary fastest: neighbouring CTAs read neighbouring columns of the same rows
+        int64_t strip, s, b;
+        if (item <= 0xffffffffLL) {
+            uint32_t it = (uint32_t)item, t = it / (uint32_t)q.n_strips;
+            strip = it - t * (uint32_t)q.n_strips;
+            uint32_t bb = t / (uint32_t)q.n_split;
+            s = t - bb * (uint32_t)q.n_split; b = bb;
+        } else {
+            strip = item % q.n_strips;
+            const int64_t t = item / q.n_strips;
+            s = t % q.n_split; b = t / q.n_split;
+        }
+        const int64_t col0 = strip * W + (int64_t)threadIdx.x * V;
+        const int64_t cleft = C - col0;
+        const int nv = cleft >= V ? V : (cleft > 0 ? (int)cleft : 0);
+        if (nv == 0) continue;
+        const int64_t in_b = offset_of(b, od_in, p.oshape, p.in_ostep);
+        const int64_t r_begin = s * q.seg_len;
+        int64_t r_end = r_begin + q.seg_len; if (r_end > p.n_red) r_end = p.n_red;
+        const char* base = in + in_b + col0 * ES + r_begin * rstep;
+        const int32_t rows = (int32_t)(r_end - r_begin);
+        Runner<R, R::kHasScan> run[V];
+#pragma unroll
+        for (int k = 0; k < V; ++k) run[k].init(r);
+        auto idx_of = [&](int32_t ps, int k) {
+            const int64_t row = r_begin + ps;
+            return q.flat_index ? (in_b + row * rstep) / ES + col0 + k : row;
+        };
+        int32_t r0 = 0;
+        if (nv == V) {
+            for (; r0 + U <= rows; r0 += U) {
+                Pack<T> v[U];
+#pragma unroll
+                for (int j = 0; j < U; ++j) {
+                    const char* a = base + (int64_t)(r0 + j) * rstep;
+                    if (V > 1) v[j] = ld_pack<T>(a); else v[j].v[0] = ld_one<T>(a);
+                }
+#pragma unroll
+                for (int j = 0; j < U; ++j)
+#pragma unroll
+                    for (int k = 0; k < V; ++k)
+                        run[k].step(r, v[j].v[k], r0 + j, [&](int32_t ps) { return idx_of(ps, k); });
+            }
+        }
+        for (; r0 < rows; ++r0) {
+            const char* a = base + (int64_t)r0 * rstep;
+#pragma unroll
+            for (int k = 0; k < V; ++k)
+                if (k < nv) run[k].step(r, ld_one<T>(a + k * ES), r0, [&](int32_t ps) { return idx_of(ps, k); });
+        }
+#pragma unroll
+        for (int k = 0; k < V; ++k)
+            if (k < nv)
+                emit(r, p, b * C + col0 + k, q.n_split, s, run[k].finish(r, [&](int32_t ps) { return idx_of(ps, k); }), out, out2, partial);
+    }
+}
+
 // ---- GEN ------------------------------------------------------------------------------
 template <typename R, int G>
 __global__ void __launch_bounds__(kBlock)
@@ -431,6 +509,9 @@ void launch_reduce(const cumo_na_reduction_arg_t* arg, const cumo_na_iarray_t* o
     constexpr int VMAX = 16 / ES;
     constexpr int64_t kSegBytes = 32 << 10;           // one CTA's share of a long row
     constexpr int64_t kColSegRows = 256;              // one CTA's share of a column strip
+    constexpr int64_t kColWideSegRows = 128;          // the same when the strip is a CTA wide (4 KiB per row)
+    constexpr int64_t kColWideRound = 148 * 4;        // CTAs of that plan resident at once on a B200: 148 SMs x 4
+    constexpr size_t kColWideSmem = 48 << 10;
     RedPlan p;
     if (!make_red_plan(&p, arg, out2_arr)) return;
     const char* in = arg->in.ptr;
@@ -481,20 +562,42 @@ void launch_reduce(const cumo_na_reduction_arg_t* arg, const cumo_na_iarray_t* o
         bool vec = aligned16(in);
         for (int d = 0; d < od_in && vec; ++d) if (!mult16(p.in_ostep[d])) vec = false;
         for (int d = 0; d < p.n_rd && vec; ++d) if (!mult16(p.in_rstep[d])) vec = false;
-        const int64_t W = 32 * (vec ? VMAX : 1);
+        // thread-owned columns when a row of columns fills at least half a CTA; else a warp-wide strip with rows spread over warps
+        const bool wide_cols = C >= (int64_t)kBlock * (vec ? VMAX : 1) / 2;
+        const int64_t W = (wide_cols ? kBlock : 32) * (vec ? VMAX : 1);
+        const int64_t seg_rows = wide_cols ? kColWideSegRows : kColSegRows;
         q.n_strips = (C + W - 1) / W;
         q.seg_len = p.n_red > 0 ? p.n_red : 1;
-        if (p.n_red > kColSegRows + kColSegRows / 2) {
-            int64_t seg = kColSegRows;
+        if (p.n_red > seg_rows + seg_rows / 2) {
+            int64_t seg = seg_rows;
             int64_t ns = (p.n_red + seg - 1) / seg;
             while (ns > 8192) { seg *= 2; ns = (p.n_red + seg - 1) / seg; }
+            if (wide_cols) {
+                // These CTAs are large (half a MiB of input) and all alike, so they run in rounds of
+                // kColWideRound; a last round that is mostly empty costs as much as a full one.  Cut the
+                // rows so that the CTA count is just under a whole number of rounds.  The round size is a
+                // constant of the plan, not a property read from the device, so results stay the same anywhere.
+                const int64_t lanes = (p.n_out / C) * q.n_strips;           // CTAs per segment index
+                const int64_t rounds = (lanes * ns + kColWideRound - 1) / kColWideRound;
+                const int64_t want = rounds * kColWideRound / lanes;
+                if (want >= 2 && want <= 8192) {
+                    seg = (p.n_red + want - 1) / want;
+                    ns = (p.n_red + seg - 1) / seg;
+                }
+            }
             q.seg_len = seg;
             q.n_split = (int)ns;
         }
         if (q.n_split > 1) partial = reinterpret_cast<Acc*>(cumo_cuda_runtime_malloc(sizeof(Acc) * p.n_out * q.n_split));
         const unsigned grid = red_grid((p.n_out / C) * q.n_strips * q.n_split);
-        if (vec) red_col_kernel<R, VMAX><<<grid, kBlock, 0, st>>>(p, r, q, in, out, out2, partial);
-        else     red_col_kernel<R, 1><<<grid, kBlock, 0, st>>>(p, r, q, in, out, out2, partial);
+        if (wide_cols) {
+            // 48 KiB of (unused) dynamic shared memory per CTA holds residency at 4 CTAs per SM for every functor
+            if (vec) red_colwide_kernel<R, VMAX><<<grid, kBlock, kColWideSmem, st>>>(p, r, q, in, out, out2, partial);
+            else     red_colwide_kernel<R, 1><<<grid, kBlock, kColWideSmem, st>>>(p, r, q, in, out, out2, partial);
+        } else {
+            if (vec) red_col_kernel<R, VMAX><<<grid, kBlock, 0, st>>>(p, r, q, in, out, out2, partial);
+            else     red_col_kernel<R, 1><<<grid, kBlock, 0, st>>>(p, r, q, in, out, out2, partial);
+        }
     } else {
         const bool wide = p.n_red >= 2048;
         q.seg_len = p.n_red > 0 ? p.n_red : 1;

@@ -342,7 +342,7 @@ def test_full_reductions_1d(xp_gpu, tname, n):
 
 
 @pytest.mark.parametrize("tname", list(NP))
-@pytest.mark.parametrize("shape", [(96, 130), (3000, 33), (33, 3000), (4, 70_000), (70_000, 4), (1, 257), (257, 1), (513, 512)])
+@pytest.mark.parametrize("shape", [(96, 130), (3000, 33), (33, 3000), (4, 70_000), (70_000, 4), (1, 257), (257, 1), (513, 512), (700, 1030), (261, 2048)])
 def test_axis_reductions_2d(xp_gpu, tname, shape):
     rng = np.random.default_rng(shape[0] * 7 + shape[1])
     g, o = both(xp_gpu, tname, planted(rng, tname, shape))

@@ -126,6 +126,8 @@ struct Runner<R, false> {
     __device__ __forceinline__ void step(const R& r, typename R::In v, int32_t pos, F idx_of) {
         a = r.combine(a, r.map(v, R::kIndexed ? idx_of(pos) : (int64_t)0));
     }
+    __device__ __forceinline__ void merge(const R& r, const Runner& o) { a = r.combine(a, o.a); }
+    __device__ __forceinline__ void settle(int32_t) {}
     template <typename F>
     __device__ __forceinline__ typename R::Acc finish(const R&, F) { return a; }
 };
@@ -135,6 +137,9 @@ struct Runner<R, true> {
     __device__ __forceinline__ void init(const R& r) { l = r.local_identity(); }
     template <typename F>
     __device__ __forceinline__ void step(const R& r, typename R::In v, int32_t pos, F) { r.local_scan(l, v, pos); }
+    __device__ __forceinline__ void merge(const R& r, const Runner& o) { r.local_merge(l, o.l); }
+    // first: the first position this scan visited, negative if it visited nothing
+    __device__ __forceinline__ void settle(int32_t first) { if (l.pos < 0 && first >= 0) l.pos = first; }
     template <typename F>
     __device__ __forceinline__ typename R::Acc finish(const R& r, F idx_of) {
         if (l.pos < 0) return r.identity();
@@ -167,37 +172,46 @@ __device__ __forceinline__ typename R::Acc row_item(const R& r, const char* base
                                                     int64_t idx_base, int gl, typename R::Acc* smem) {
     using T = typename R::In;
     constexpr int ES = sizeof(T);
-    constexpr int64_t SPAN = (int64_t)G * V * kUnroll;     // elements per group iteration
-    Runner<R, SCAN> run;
-    run.init(r);
+    // a scan spends longer on each packet than a sum does, so it keeps twice as many loads in flight
+    constexpr int UN = SCAN ? 2 * kUnroll : kUnroll;
+    constexpr int64_t SPAN = (int64_t)G * V * UN;          // elements per group iteration
+    // a private scan is a chain of dependent compares: one chain per packet lane keeps V of them in flight
+    constexpr int NR = SCAN ? V : 1;
+    Runner<R, SCAN> run[NR];
+#pragma unroll
+    for (int k = 0; k < NR; ++k) run[k].init(r);
     auto idx_of = [&](int32_t pos) { return idx_base + begin + pos; };
     int64_t eb = begin;
     // whole iterations: every packet of every lane lies inside the segment, no tests per element
     for (; eb + SPAN <= end; eb += SPAN) {
-        Pack<T> v[kUnroll];
+        Pack<T> v[UN];
 #pragma unroll
-        for (int j = 0; j < kUnroll; ++j) {
+        for (int j = 0; j < UN; ++j) {
             const char* q = base + (eb + (int64_t)(j * G + gl) * V) * ES;
             if (V > 1) v[j] = ld_pack<T>(q); else v[j].v[0] = ld_one<T>(q);
         }
         const int32_t p0 = (int32_t)(eb - begin);
 #pragma unroll
-        for (int j = 0; j < kUnroll; ++j)
+        for (int j = 0; j < UN; ++j)
 #pragma unroll
-            for (int k = 0; k < V; ++k) run.step(r, v[j].v[k], p0 + (j * G + gl) * V + k, idx_of);
+            for (int k = 0; k < V; ++k) run[SCAN ? k : 0].step(r, v[j].v[k], p0 + (j * G + gl) * V + k, idx_of);
     }
     // the ragged end of the segment
     if (eb < end) {
         const int32_t p0 = (int32_t)(eb - begin);
 #pragma unroll
-        for (int j = 0; j < kUnroll; ++j) {
+        for (int j = 0; j < UN; ++j) {
             const int64_t e = eb + (int64_t)(j * G + gl) * V;
 #pragma unroll
             for (int k = 0; k < V; ++k)
-                if (e + k < end) run.step(r, ld_one<T>(base + (e + k) * ES), p0 + (j * G + gl) * V + k, idx_of);
+                if (e + k < end) run[SCAN ? k : 0].step(r, ld_one<T>(base + (e + k) * ES), p0 + (j * G + gl) * V + k, idx_of);
         }
     }
-    return group_fold<R, G>(r, run.finish(r, idx_of), smem);
+#pragma unroll
+    for (int k = 0; k < NR; ++k) run[k].settle(begin + gl * V + k < end ? gl * V + k : -1);
+#pragma unroll
+    for (int k = 1; k < NR; ++k) run[0].merge(r, run[k]);
+    return group_fold<R, G>(r, run[0].finish(r, idx_of), smem);
 }
 
 template <typename R, int V, int G>
@@ -270,6 +284,8 @@ __device__ __forceinline__ void col_item(const R& r, const RedPlan& p, const Red
                     const int64_t row = r_begin + ps;
                     return q.flat_index ? (in_b + row_off(row)) / ES + col0 + k : row; });
     }
+#pragma unroll
+    for (int k = 0; k < V; ++k) run[k].settle(k < nv && r_begin + warp < r_end ? warp : -1);
 #pragma unroll
     for (int k = 0; k < V; ++k)
         acc_out[k] = run[k].finish(r, [&](int32_t ps) {
@@ -407,6 +423,8 @@ red_colwide_kernel(const RedPlan p, const R r, const RedLaunch q, const char* __
                 if (k < nv) run[k].step(r, ld_one<T>(a + k * ES), r0, [&](int32_t ps) { return idx_of(ps, k); });
         }
 #pragma unroll
+        for (int k = 0; k < V; ++k) run[k].settle(k < nv && rows > 0 ? 0 : -1);
+#pragma unroll
         for (int k = 0; k < V; ++k)
             if (k < nv)
                 emit(r, p, b * C + col0 + k, q.n_split, s, run[k].finish(r, [&](int32_t ps) { return idx_of(ps, k); }), out, out2, partial);
@@ -497,6 +515,43 @@ red_fold_kernel(const RedPlan p, const R r, const typename R::Acc* __restrict__ 
     }
 }
 
+// Many segments, few outputs: a CTA of 1024 threads per output, so that even 8192 segments are
+// one batch of eight independent loads per thread.  Thread order == segment order throughout.
+template <typename R>
+__global__ void __launch_bounds__(1024)
+red_fold_big_kernel(const RedPlan p, const R r, const typename R::Acc* __restrict__ partial, int n_split,
+                    char* out, char* out2) {
+    using Acc = typename R::Acc;
+    __shared__ Acc smem[32];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int per = (n_split + 1023) / 1024;
+    for (int64_t o = blockIdx.x; o < p.n_out; o += gridDim.x) {
+        const Acc* run = partial + o * n_split;
+        Acc acc = r.identity();
+        for (int k = 0; k < per; k += 8) {
+            Acc buf[8];
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+                const int s = (int)threadIdx.x * per + k + i;
+                if (k + i < per && s < n_split) buf[i] = run[s];
+            }
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+                const int s = (int)threadIdx.x * per + k + i;
+                if (k + i < per && s < n_split) acc = r.combine(acc, buf[i]);
+            }
+        }
+        acc = warp_fold(r, acc);
+        __syncthreads();                     // smem may still be read from the previous output
+        if (lane == 0) smem[warp] = acc;
+        __syncthreads();
+        if (warp == 0) {
+            acc = warp_fold(r, smem[lane]);
+            if (lane == 0) emit(r, p, o, 1, 0, acc, out, out2, (Acc*)nullptr);
+        }
+    }
+}
+
 inline unsigned red_grid(int64_t ctas) { return (unsigned)(ctas < 1 ? 1 : (ctas > 0x7fffffffLL ? 0x7fffffffLL : ctas)); }
 
 // ---- host ----------------------------------------------------------------------------------
@@ -509,7 +564,7 @@ void launch_reduce(const cumo_na_reduction_arg_t* arg, const cumo_na_iarray_t* o
     constexpr int VMAX = 16 / ES;
     constexpr int64_t kSegBytes = 32 << 10;           // one CTA's share of a long row
     constexpr int64_t kColSegRows = 256;              // one CTA's share of a column strip
-    constexpr int64_t kColWideSegRows = 128;          // the same when the strip is a CTA wide (4 KiB per row)
+    constexpr int64_t kColWideSegRows = 256;          // the same when the strip is a CTA wide (4 KiB per row)
     constexpr int64_t kColWideRound = 148 * 4;        // CTAs of that plan resident at once on a B200: 148 SMs x 4
     constexpr size_t kColWideSmem = 48 << 10;
     RedPlan p;
@@ -614,7 +669,9 @@ void launch_reduce(const cumo_na_reduction_arg_t* arg, const cumo_na_iarray_t* o
     }
     int launches = 1;
     if (q.n_split > 1) {
-        if (q.n_split > 256 && p.n_out < 4096)
+        if (q.n_split > 1024 && p.n_out <= 64)
+            red_fold_big_kernel<R><<<red_grid(p.n_out), 1024, 0, st>>>(p, r, partial, q.n_split, out, out2);
+        else if (q.n_split > 256 && p.n_out < 4096)
             red_fold_kernel<R, kBlock><<<red_grid(p.n_out), kBlock, 0, st>>>(p, r, partial, q.n_split, out, out2);
         else
             red_fold_kernel<R, 32><<<red_grid((p.n_out + kWarpsPerBlock - 1) / kWarpsPerBlock), kBlock, 0, st>>>(p, r, partial, q.n_split, out, out2);

@@ -236,17 +236,31 @@ struct ArgMinMax {
     int idx64;
     // A thread's private scan of a run visited in increasing index order.  A strict
     // comparison keeps the earlier of two equal elements, so no index is ever compared,
-    // and the position is a 32-bit offset into the thread's segment (negative: nothing
-    // seen yet).  Same answers as folding combine(acc, map(v, idx)) over the run.
+    // and the position is a 32-bit offset into the thread's segment.  The scan starts from
+    // the identity value with position -1 and costs two compares and two selects per element;
+    // if it ends with the position still negative, every element it saw ranks equal to the
+    // identity (all NaN, all -inf, all INT_MIN ...), and the caller settles it on the first
+    // position visited.  Same answers as folding combine(acc, map(v, idx)) over the run.
     struct Local { T value; int32_t pos; };
     __device__ __forceinline__ Local local_identity() const { return {identity().value, -1}; }
     __device__ __forceinline__ void local_scan(Local& l, T v, int32_t pos) const {
-        bool take = l.pos < 0 || (IS_MAX ? (l.value < v) : (v < l.value));
-        if constexpr (is_fp<T>::value) {
-            if constexpr (NAN_WINS) take = !is_nan(l.value) && (take || is_nan(v));   // the first NaN sticks
-            else take = take || (is_nan(l.value) && !is_nan(v));                      // a number replaces a NaN
+        bool take;
+        if constexpr (!is_fp<T>::value) take = IS_MAX ? (l.value < v) : (v < l.value);
+        else {
+            // "not >=" is also true when either side is NaN
+            const bool beats = IS_MAX ? !(l.value >= v) : !(l.value <= v);
+            if constexpr (NAN_WINS) take = beats && (l.value == l.value);     // a NaN, once held, sticks
+            else take = beats && (v == v);                                    // a NaN never replaces anything
         }
         if (take) { l.value = v; l.pos = pos; }
+    }
+    // two scans over disjoint sets of positions: the same total order as combine()
+    __device__ __forceinline__ void local_merge(Local& a, const Local& b) const {
+        if (b.pos < 0) return;
+        if (a.pos < 0) { a = b; return; }
+        const Acc m = combine(Acc{a.value, (int64_t)a.pos}, Acc{b.value, (int64_t)b.pos});
+        a.value = m.value;
+        a.pos = (int32_t)m.index;
     }
     __device__ __forceinline__ Acc identity() const {
         T v;

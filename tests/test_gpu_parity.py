@@ -341,6 +341,40 @@ def test_full_reductions_1d(xp_gpu, tname, n):
         check_reductions(xp_gpu, tname, g[::-1], o[::-1], None)      # reversed
 
 
+def extreme_fills(tname):
+    if tname in FLOATS:
+        return {"all_nan": np.nan, "all_neg_inf": -np.inf, "all_pos_inf": np.inf, "all_zero": 0.0}
+    info = np.iinfo(NP[tname])
+    return {"all_min": info.min, "all_max": info.max, "all_zero": 0}
+
+
+@pytest.mark.parametrize("tname", list(NP))
+@pytest.mark.parametrize("shape", [(5,), (70_001,), (300_000,), (40, 600), (600, 40), (300, 1030), (9, 40_000)])
+def test_index_reductions_on_extreme_values(xp_gpu, tname, shape):
+    """Arrays where every element ranks equal to the identity of the scan (all NaN, all -inf, all INT_MIN ...),
+    then the same with a few ordinary values and NaNs sprinkled in: the first index must win everywhere."""
+    rng = np.random.default_rng(len(shape) * 1000 + shape[0])
+    axes = [None] if len(shape) == 1 else [None, 0, 1]
+    for name, fill in extreme_fills(tname).items():
+        for sprinkle in (False, True):
+            host = np.full(shape, fill, dtype=NP[tname])
+            if sprinkle:
+                flat = host.reshape(-1)
+                pick = rng.choice(flat.size, size=min(7, flat.size), replace=False)
+                flat[pick] = rng_array(rng, tname, len(pick))
+                if tname in FLOATS:
+                    flat[rng.integers(0, flat.size)] = np.nan
+                    flat[rng.integers(0, flat.size)] = -0.0
+            g, o = both(xp_gpu, tname, host)
+            for axis in axes:
+                for op in INDEX_REDS:
+                    same(getattr(g, op)(axis=axis), getattr(o, op)(axis=axis))
+                    if tname in FLOATS:
+                        same(getattr(g, op)(axis=axis, nan=True), getattr(o, op)(axis=axis, nan=True))
+                for op in ("min", "max"):
+                    same(getattr(g, op)(axis=axis), getattr(o, op)(axis=axis))
+
+
 @pytest.mark.parametrize("tname", list(NP))
 @pytest.mark.parametrize("shape", [(96, 130), (3000, 33), (33, 3000), (4, 70_000), (70_000, 4), (1, 257), (257, 1), (513, 512), (700, 1030), (261, 2048)])
 def test_axis_reductions_2d(xp_gpu, tname, shape):

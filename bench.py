@@ -163,75 +163,144 @@ def time_kernel(torch, fn, reps=10, warm=2):
     return float(np.median(ts)), float(np.min(ts))
 
 
-def kernel_table(torch, xp, peak):
-    """Per-kernel effective GB/s at the BASELINE sizes (1 GPU, inputs resident, arrays >= 256 MB except C1)."""
-    rows = []
+FULL_SIZES = {"c1": (16384, 4096), "c2": (R, C), "c3_n": 1 << 28, "c3_m": (65536, 4096), "c4_n": 1 << 27, "c4_m": (32768, 4096), "c5": (1 << 24, 64, 256)}
+# what the single-threaded CPU leg runs: the same kernels on arrays of a few MiB (the oracle streams at a few GB/s at best)
+CPU_SAMPLE_SIZES = {"c1": (1024, 512), "c2": (256, C), "c3_n": 1 << 22, "c3_m": (1024, 4096), "c4_n": 1 << 22, "c4_m": (1024, 4096), "c5": (4096, 64, 256)}
 
-    def add(config, name, nbytes, fn):
-        med, best = time_kernel(torch, fn)
-        gbs = nbytes / (med * 1e-3) / 1e9
-        rows.append({"config": config, "kernel": name, "bytes": int(nbytes), "ms": round(med, 4), "ms_min": round(best, 4),
-                     "GBps": round(gbs, 1), "frac_of_measured": round(gbs / peak, 3), "frac_of_nominal": round(gbs / NOMINAL_HBM_GBS, 3)})
 
-    g = torch.Generator(device="cuda").manual_seed(0)
-    MiB = 1 << 20
-    # C1 scaled to 16384^2 (1 GiB) and at its own 4096^2 (64 MiB, below the 256 MB bar: reported only)
-    for n, tag in ((16384, "C1x16"), (4096, "C1")):
-        a = xp.SFloat.from_torch(torch.rand(n, n, device="cuda", generator=g) * 2 - 1)
-        b = xp.SFloat.from_torch(torch.rand(n, n, device="cuda", generator=g) * 2 - 1)
+def kernel_rows(X, arr, S, copies=1):
+    """Yield (config, kernel, algorithmic bytes, callable) for every per-kernel line of BASELINE's configs.
+    X is the array module (device library or CPU oracle facade), arr(kind, shape) makes a seeded input in it,
+    S the sizes.  `copies` > 1 rotates the small C1 operands among that many distinct buffers."""
+    def rot(items):
+        state = {"i": 0}
+
+        def nxt():
+            state["i"] = (state["i"] + 1) % len(items)
+            return items[state["i"]]
+        return nxt
+
+    # C1 scaled (1 GiB at full size) and at its own 4096^2 (64 MiB: below the 256 MB bar, reported only)
+    for n, tag in ((S["c1"][0], "C1x16"), (S["c1"][1], "C1")):
+        k = copies if tag == "C1" else 1
+        a = rot([arr("f32_pm1", (n, n)) for _ in range(k)])
+        b = rot([arr("f32_pm1", (n, n)) for _ in range(k)])
+        col = rot([arr("f32_pm1", (n, 1)) for _ in range(k)])
         s = n * n * 4
-        add(tag, "a*b", 3 * s, lambda: a * b)
-        add(tag, "a.sum(axis:1)", s + n * 4, lambda: a.sum(axis=1))
-        col = a.sum(axis=1).reshape(n, 1)
-        add(tag, "a + col(n,1)", 2 * s + n * 4, lambda: a + col)
-        add(tag, "c.sum(axis:0)", s + n * 4, lambda: a.sum(axis=0))
-        add(tag, "c.max_index(axis:1)", s + n * 4, lambda: a.max_index(axis=1))
+        yield tag, "a*b", 3 * s, lambda a=a, b=b: a() * b()
+        yield tag, "a.sum(axis:1)", s + n * 4, lambda a=a: a().sum(axis=1)
+        yield tag, "a + col(n,1)", 2 * s + n * 4, lambda a=a, col=col: a() + col()
+        yield tag, "c.sum(axis:0)", s + n * 4, lambda a=a: a().sum(axis=0)
+        yield tag, "c.max_index(axis:1)", s + n * 4, lambda a=a: a().max_index(axis=1)
         del a, b, col
     # C2
-    x = xp.SFloat.from_torch(torch.randn(R, 1, device="cuda", generator=g))
-    y = xp.SFloat.from_torch(torch.randn(1, C, device="cuda", generator=g))
+    r2, c2 = S["c2"]
+    x, y = arr("f32_normal", (r2, 1)), arr("f32_normal", (1, c2))
     t = x + y
-    add("C2", "x(8192,1)+y(1,16384)", BYTES_ADD, lambda: x + y)
-    add("C2", "exp", BYTES_EXP, lambda: xp.NMath.exp(t))
-    add("C2", "*0.5", BYTES_MUL, lambda: t * 0.5)
+    yield "C2", "x(R,1)+y(1,C)", r2 * c2 * 4 + (r2 + c2) * 4, lambda: x + y
+    yield "C2", "exp", 2 * r2 * c2 * 4, lambda: X.NMath.exp(t)
+    yield "C2", "*0.5", 2 * r2 * c2 * 4, lambda: t * 0.5
     del t
     # C3
-    for T, tt, es, tag in ((xp.SFloat, torch.float32, 4, "f32"), (xp.DFloat, torch.float64, 8, "f64")):
-        v = T.from_torch(torch.rand(1 << 28, device="cuda", dtype=tt, generator=g))
-        s = (1 << 28) * es
+    n3, (mr, mc) = S["c3_n"], S["c3_m"]
+    for kind, es, tag in (("f32_01", 4, "f32"), ("f64_01", 8, "f64")):
+        v = arr(kind, (n3,))
         for op in ("sum", "mean", "max", "min", "argmax"):
-            add("C3", f"{tag} 2^28 {op}", s + (4 if op == "argmax" else es), lambda op=op: getattr(v, op)())
-        m = v.reshape(65536, 4096)
-        for ax, n_out in ((0, 4096), (1, 65536)):
+            yield "C3", f"{tag} 1-D {op}", n3 * es + (4 if op == "argmax" else es), lambda op=op, v=v: getattr(v, op)()
+        m = arr(kind, (mr, mc))
+        for ax, n_out in ((0, mc), (1, mr)):
             for op in ("sum", "mean", "max", "min", "argmax"):
-                add("C3", f"{tag} (65536,4096) {op}(axis:{ax})", s + n_out * (4 if op == "argmax" else es), lambda op=op, ax=ax: getattr(m, op)(axis=ax))
+                yield "C3", f"{tag} 2-D {op}(axis:{ax})", mr * mc * es + n_out * (4 if op == "argmax" else es), lambda op=op, ax=ax, m=m: getattr(m, op)(axis=ax)
         del v, m
     # C4
-    ia = xp.Int32.from_torch(torch.randint(-(1 << 20), 1 << 20, (1 << 27,), device="cuda", dtype=torch.int32, generator=g))
-    ib = xp.Int32.from_torch(torch.randint(-(1 << 20), 1 << 20, (1 << 27,), device="cuda", dtype=torch.int32, generator=g))
-    s = (1 << 27) * 4
-    add("C4", "a*3", 2 * s, lambda: ia * 3)
-    add("C4", "+b", 3 * s, lambda: ia + ib)
-    add("C4", "%7 (incl. the flag sync)", 2 * s, lambda: ia % 7)
-    add("C4", "a>0 -> Bit", s + s // 32, lambda: ia > 0)
+    n4, (ir, ic) = S["c4_n"], S["c4_m"]
+    ia, ib = arr("i32", (n4,)), arr("i32", (n4,))
+    s = n4 * 4
+    yield "C4", "a*3", 2 * s, lambda: ia * 3
+    yield "C4", "+b", 3 * s, lambda: ia + ib
+    yield "C4", "%7 (incl. the flag sync)", 2 * s, lambda: ia % 7
+    yield "C4", "a>0 -> Bit", s + s // 32, lambda: ia > 0
     mask = ia > 0
-    add("C4", "count_true", s // 32 + 8, lambda: mask.count_true())
-    im = ia.reshape(32768, 4096)
-    add("C4", "max_index(axis:1) (32768,4096)", s + 32768 * 4, lambda: im.max_index(axis=1))
-    add("C4", "Int32 sum -> Int64", s + 8, lambda: ia.sum())
-    del ia, ib, mask, im
+    yield "C4", "count_true", s // 32 + 8, lambda: mask.count_true()
+    im = arr("i32", (ir, ic))
+    yield "C4", "max_index(axis:1)", ir * ic * 4 + ir * 4, lambda: im.max_index(axis=1)
+    yield "C4", "Int32 sum -> Int64", s + 8, lambda: ia.sum()
+
+
+def kernel_table(torch, xp, peak):
+    """Per-kernel effective GB/s at the BASELINE sizes (1 GPU, inputs resident, arrays >= 256 MB except C1), each beside
+    the single-threaded CPU oracle running the same kernel on a sample of a few MiB."""
+    g = torch.Generator(device="cuda").manual_seed(0)
+
+    def dev_arr(kind, shape):
+        if kind == "f32_pm1":
+            return xp.SFloat.from_torch(torch.rand(*shape, device="cuda", generator=g) * 2 - 1)
+        if kind == "f32_normal":
+            return xp.SFloat.from_torch(torch.randn(*shape, device="cuda", generator=g))
+        if kind == "f32_01":
+            return xp.SFloat.from_torch(torch.rand(*shape, device="cuda", generator=g))
+        if kind == "f64_01":
+            return xp.DFloat.from_torch(torch.rand(*shape, device="cuda", dtype=torch.float64, generator=g))
+        return xp.Int32.from_torch(torch.randint(-(1 << 20), 1 << 20, shape, device="cuda", dtype=torch.int32, generator=g))
+
+    sys.path.insert(0, str(ROOT / "tests"))
+    from oracle_narray import OracleXP as ox
+    from oracle import cumo_oracle as orc
+    orc.set_threads(1)
+    rng = np.random.default_rng(0)
+
+    def cpu_arr(kind, shape):
+        if kind == "f32_pm1":
+            return ox.SFloat.cast(rng.uniform(-1, 1, shape).astype(np.float32))
+        if kind == "f32_normal":
+            return ox.SFloat.cast(rng.standard_normal(shape).astype(np.float32))
+        if kind == "f32_01":
+            return ox.SFloat.cast(rng.random(shape, dtype=np.float32))
+        if kind == "f64_01":
+            return ox.DFloat.cast(rng.random(shape))
+        return ox.Int32.cast(rng.integers(-(1 << 20), 1 << 20, shape, dtype=np.int32))
+
+    cpu = {}
+    for config, name, nbytes, fn in kernel_rows(ox, cpu_arr, CPU_SAMPLE_SIZES):
+        fn()
+        best = float("inf")
+        for _ in range(2):
+            t0 = time.perf_counter()
+            fn()
+            best = min(best, time.perf_counter() - t0)
+        cpu[(config, name)] = round(nbytes / best / 1e9, 3)
+
+    rows = []
+    for config, name, nbytes, fn in kernel_rows(xp, dev_arr, FULL_SIZES, copies=8):
+        med, best = time_kernel(torch, fn, reps=20)
+        gbs = nbytes / (med * 1e-3) / 1e9
+        rows.append({"config": config, "kernel": name, "bytes": int(nbytes), "ms": round(med, 4), "ms_min": round(best, 4),
+                     "GBps": round(gbs, 1), "frac_of_measured": round(gbs / peak, 3), "frac_of_nominal": round(gbs / NOMINAL_HBM_GBS, 3),
+                     "cpu_GBps_1thread_sample": cpu.get((config, name))})
+
     # C5 (BASELINE config 4): k-means assignment, 2^24 points x 64-D against 256 centres, fused
     from cumo_b200 import kmeans
-    n, d, k = 1 << 24, 64, 256
+    n, d, k = FULL_SIZES["c5"]
     cen = torch.randn(k, d, device="cuda", generator=g) * 4
     pts = cen[torch.randint(0, k, (n,), device="cuda", generator=g)] + torch.randn(n, d, device="cuda", generator=g)
     px, pc = xp.SFloat.from_torch(pts), xp.SFloat.from_torch(cen)
+    ns = CPU_SAMPLE_SIZES["c5"][0]
+    hx, hc = pts[:ns].cpu().numpy(), cen.cpu().numpy()
+    t0 = time.perf_counter()
+    orc.kmeans_assign(hx, hc)
+    cpu_sec = time.perf_counter() - t0
     for algo, what in (("tensor", "fused, tcgen05 3xTF32"), ("cores", "fused, fp32 cores")):
-        add("C5", f"kmeans assign 2^24x64 vs 256 ({what})", n * d * 4 + k * d * 4 + n * 4 + k * 8, lambda algo=algo: kmeans.assign(px, pc, algo=algo))
-        # useful flops of the (N, K, D) contraction; the tensor form issues three TF32 MMAs per product
-        rows[-1]["TFLOPs"] = round(2.0 * n * k * d / (rows[-1]["ms"] * 1e-3) / 1e12, 2)
+        nbytes = n * d * 4 + k * d * 4 + n * 4 + k * 8
+        med, best = time_kernel(torch, lambda algo=algo: kmeans.assign(px, pc, algo=algo), reps=20)
+        gbs = nbytes / (med * 1e-3) / 1e9
+        row = {"config": "C5", "kernel": f"kmeans assign 2^24x64 vs 256 ({what})", "bytes": int(nbytes), "ms": round(med, 4), "ms_min": round(best, 4),
+               "GBps": round(gbs, 1), "frac_of_measured": round(gbs / peak, 3), "frac_of_nominal": round(gbs / NOMINAL_HBM_GBS, 3),
+               "cpu_GBps_1thread_sample": round((ns * d * 4 + k * d * 4 + ns * 4 + k * 8) / cpu_sec / 1e9, 4),
+               # useful flops of the (N, K, D) contraction; the tensor form issues three TF32 MMAs per product
+               "TFLOPs": round(2.0 * n * k * d / (med * 1e-3) / 1e12, 2)}
         if algo == "tensor":
-            rows[-1]["TFLOPs_issued_tf32"] = round(3 * rows[-1]["TFLOPs"], 1)
+            row["TFLOPs_issued_tf32"] = round(3 * row["TFLOPs"], 1)
+        rows.append(row)
     return rows
 
 

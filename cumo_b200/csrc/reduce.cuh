@@ -196,15 +196,37 @@ __device__ __forceinline__ typename R::Acc row_item(const R& r, const char* base
 #pragma unroll
             for (int k = 0; k < V; ++k) run[SCAN ? k : 0].step(r, v[j].v[k], p0 + (j * G + gl) * V + k, idx_of);
     }
-    // the ragged end of the segment
+    // the ragged end of the segment: its whole packets, strided over the group (four loads issued
+    // before the first use while four remain), then the few elements past the last whole packet
     if (eb < end) {
+        const char* rb = base + eb * ES;
         const int32_t p0 = (int32_t)(eb - begin);
+        const int32_t n_pk = (int32_t)((end - eb) / V);            // < UN * G
+        int32_t pk = gl;
+        for (; pk + 3 * G < n_pk; pk += 4 * G) {
+            Pack<T> v[4];
 #pragma unroll
-        for (int j = 0; j < UN; ++j) {
-            const int64_t e = eb + (int64_t)(j * G + gl) * V;
+            for (int j = 0; j < 4; ++j) {
+                const char* q = rb + (int64_t)(pk + j * G) * (V * ES);
+                if (V > 1) v[j] = ld_pack<T>(q); else v[j].v[0] = ld_one<T>(q);
+            }
+#pragma unroll
+            for (int j = 0; j < 4; ++j)
+#pragma unroll
+                for (int k = 0; k < V; ++k) run[SCAN ? k : 0].step(r, v[j].v[k], p0 + (pk + j * G) * V + k, idx_of);
+        }
+        for (; pk < n_pk; pk += G) {
+            Pack<T> v;
+            const char* q = rb + (int64_t)pk * (V * ES);
+            if (V > 1) v = ld_pack<T>(q); else v.v[0] = ld_one<T>(q);
+#pragma unroll
+            for (int k = 0; k < V; ++k) run[SCAN ? k : 0].step(r, v.v[k], p0 + pk * V + k, idx_of);
+        }
+        if (V > 1 && gl == 0) {                                    // thread 0's positions stay in rising order
+            const int32_t rest = (int32_t)(end - eb) - n_pk * V;
 #pragma unroll
             for (int k = 0; k < V; ++k)
-                if (e + k < end) run[SCAN ? k : 0].step(r, ld_one<T>(base + (e + k) * ES), p0 + (j * G + gl) * V + k, idx_of);
+                if (k < rest) run[SCAN ? k : 0].step(r, ld_one<T>(rb + (int64_t)(n_pk * V + k) * ES), p0 + n_pk * V + k, idx_of);
         }
     }
 #pragma unroll

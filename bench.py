@@ -430,9 +430,16 @@ def sharded_section(torch, dist, xp, rank, world):
     sv = ShardedArray(comm, v, n * world, n * rank)
     m = v.reshape(65536, 4096)
     sm = ShardedArray(comm, m, 65536 * world, 65536 * rank)
+    from cumo_b200 import kmeans
+    kn, kd, kk = 1 << 24, 64, 256                    # BASELINE config 4 per GPU: points sharded, centroids replicated, counts all-reduced
+    gc = torch.Generator(device="cuda").manual_seed(4)
+    cen = torch.randn(kk, kd, device="cuda", generator=gc) * 4
+    pts = cen[torch.randint(0, kk, (kn,), device="cuda", generator=g)] + torch.randn(kn, kd, device="cuda", generator=g)
+    px, pc = xp.SFloat.from_torch(pts), xp.SFloat.from_torch(cen)
     out = []
     for name, fn, nbytes in (("sum 1-D 2^28/GPU", lambda: sv.sum(), n * 4), ("argmax 1-D 2^28/GPU", lambda: sv.argmax(), n * 4),
-                             ("sum(axis:0) (65536,4096)/GPU", lambda: sm.sum(axis=0), n * 4), ("max(axis:0) (65536,4096)/GPU", lambda: sm.max(axis=0), n * 4)):
+                             ("sum(axis:0) (65536,4096)/GPU", lambda: sm.sum(axis=0), n * 4), ("max(axis:0) (65536,4096)/GPU", lambda: sm.max(axis=0), n * 4),
+                             ("kmeans assign 2^24x64 vs 256 /GPU (tcgen05) + counts all_reduce", lambda: kmeans.assign_sharded(comm, px, pc), kn * kd * 4 + kn * 4)):
         for _ in range(2):
             fn()
         dist.barrier(); torch.cuda.synchronize()

@@ -33,6 +33,24 @@ static inline CB_C reduce_length(const cumo_na_reduction_arg_t* arg) {
     extern "C" void CB_RED(name##_int64)(cumo_na_reduction_arg_t* arg) {                \
         launch_reduce(arg, nullptr, red::ArgMinMax<CB_C, IS_MAX, NANW>{1}, 0); }
 
+// Index and value from one pass (no reference counterpart: the reference has no multi-GPU
+// reductions, whose per-rank partial is exactly this pair).  Indices are int64_t.
+#define CB_VSYM_(t, name) cb200_##t##_##name##_with_value_kernel_launch
+#define CB_VSYM(t, name) CB_VSYM_(t, name)
+#define DEF_WITH_VALUE(name, IS_MAX, NANW, FLAT)                                                           \
+    extern "C" void CB_VSYM(CB_T, name)(cumo_na_reduction_arg_t* arg, cumo_na_iarray_t* values) {           \
+        launch_reduce(arg, values, red::ArgMinMax<CB_C, IS_MAX, NANW>{1}, FLAT); }
+DEF_WITH_VALUE(max_index, true, false, 1)
+DEF_WITH_VALUE(min_index, false, false, 1)
+DEF_WITH_VALUE(argmax, true, false, 0)
+DEF_WITH_VALUE(argmin, false, false, 0)
+#if CB_FLOAT
+DEF_WITH_VALUE(max_index_nan, true, true, 1)
+DEF_WITH_VALUE(min_index_nan, false, true, 1)
+DEF_WITH_VALUE(argmax_nan, true, true, 0)
+DEF_WITH_VALUE(argmin_nan, false, true, 0)
+#endif
+
 DEF_ACCUM(sum, red::SumLike<CB_C, false, false>{0, CB_C(0)})
 DEF_ACCUM(prod, red::SumLike<CB_C, false, true>{0, CB_C(0)})
 DEF_ACCUM(min, red::MinMax<CB_C, false, false>{})

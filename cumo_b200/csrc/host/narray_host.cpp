@@ -842,6 +842,41 @@ int cb200_na_minmax(cb200_na_t* a, uint32_t axis_mask, int keepdims, int nan, cb
     return 0;
 }
 
+// index (Int64) and winning value from one pass: the per-GPU partial of a sharded arg reduction
+int cb200_na_arg_with_value(const char* op_c, cb200_na_t* a, uint32_t axis_mask, int nan, cb200_na_t** out_index, cb200_na_t** out_value) {
+    std::string op = op_c;
+    if (!is_value_type(a->dtype)) { fail("TypeError", "%s is not defined for %s", op_c, kTypeName[a->dtype]); return 1; }
+    const bool index_op = op == "max_index" || op == "min_index";
+    if (!index_op && op != "argmax" && op != "argmin") { fail("NoMethodError", "undefined method %s", op_c); return 1; }
+    if (size_of(a) == 0) { fail("ShapeError", "cannot reduce an empty array with %s", op_c); return 1; }
+    ReducePlan rp;
+    if (!plan_reduce(a, axis_mask, &rp)) return 1;
+    cb200_na* copy = nullptr;
+    if (index_op && !is_contiguous(a)) { copy = cast_to(a, a->dtype); if (!copy) return 1; }
+    const cb200_na* in = copy ? copy : a;
+    cb200_na* oi = make(CB200_INT64, rp.n_keep, rp.out_shape, false);
+    cb200_na* ov = oi ? make(a->dtype, rp.n_keep, rp.out_shape, false) : nullptr;
+    if (!ov) { cb200_na_release(oi); cb200_na_release(copy); return 1; }
+    using Fn = void (*)(cumo_na_reduction_arg_t*, cumo_na_iarray_t*);
+    Fn f = (Fn)sym(std::string("cb200_") + kTypeName[a->dtype] + "_" + op + ((nan && is_float_type(a->dtype)) ? "_nan" : "") + "_with_value_kernel_launch");
+    bool ok = f != nullptr;
+    if (ok) {
+        cumo_na_reduction_arg_t arg;
+        fill_reduction_arg(&arg, in, rp, oi);
+        cumo_na_iarray_t values;
+        memset(&values, 0, sizeof values);
+        values.ptr = data_ptr(ov);
+        for (int i = 0; i < rp.n_keep; ++i) values.step[i] = (ssize_t)ov->step[i];
+        f(&arg, &values);
+        ok = launch_ok();
+    }
+    cb200_na_release(copy);
+    if (!ok) { cb200_na_release(oi); cb200_na_release(ov); return 1; }
+    *out_index = oi;
+    *out_value = ov;
+    return 0;
+}
+
 cb200_na_t* cb200_na_count(cb200_na_t* a, uint32_t axis_mask, int keepdims, int want_false) {
     if (a->dtype != CB200_BIT) return (cb200_na*)fail("TypeError", "count_true needs a Bit array");
     ReducePlan rp;

@@ -281,9 +281,11 @@ struct ArgMinMax {
         bool better = IS_MAX ? (a.value < b.value) : (a.value > b.value);
         return (better || (a.value == b.value && b.index < a.index)) ? b : a;
     }
-    __device__ __forceinline__ void store(char* out, char*, Acc a) const {
+    // out2, when given, receives the winning value beside its index
+    __device__ __forceinline__ void store(char* out, char* out2, Acc a) const {
         if (idx64) *reinterpret_cast<int64_t*>(out) = a.index;
         else *reinterpret_cast<int32_t*>(out) = (int32_t)a.index;
+        if (out2) *reinterpret_cast<T*>(out2) = a.value;
     }
 };
 

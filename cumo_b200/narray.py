@@ -503,6 +503,13 @@ class NArray:
             _raise_last()
         return NArray._from_handle(lo.value), NArray._from_handle(hi.value)
 
+    def arg_with_value(self, op, axis=None, nan=False):
+        """(index Int64, value) of max_index / min_index / argmax / argmin from one pass over the data."""
+        idx, val = c_void_p(), c_void_p()
+        if _lib.load().cb200_na_arg_with_value(op.encode(), self._h, _axis_mask(axis, self.ndim), int(nan), byref(idx), byref(val)):
+            _raise_last()
+        return NArray._from_handle(idx.value), NArray._from_handle(val.value)
+
     def mulsum(self, other, axis=None, keepdims=False, nan=False):
         other = other if isinstance(other, NArray) else type(self).cast(other)
         nd = max(self.ndim, other.ndim)

@@ -174,8 +174,7 @@ class ShardedArray:
             if flat:
                 idx = xp.Int64.cast(idx) + self.row_start * self._row_elems()
             return self._like(idx)
-        val = getattr(self.local, "max" if want_max else "min")(axis=axis, **kw)
-        idx = xp.Int64.cast(getattr(self.local, name_local)(axis=axis, **kw))
+        idx, val = self.local.arg_with_value(name_local, axis=axis, **kw)     # one pass: Int64 index and its value
         # local -> global index
         if axis is None or flat:
             idx = idx + self.row_start * self._row_elems()

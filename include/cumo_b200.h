@@ -169,6 +169,13 @@ const char* cb200_version(void);
     void cumo_##T##_##op##_int32_kernel_launch(cumo_na_reduction_arg_t* arg); \
     void cumo_##T##_##op##_int64_kernel_launch(cumo_na_reduction_arg_t* arg);
 
+/* Index reductions that also write the winning value (same descriptor as the entry above,
+ * indices as int64_t; `values` has the layout of arg->out with the element type of the input).
+ * NOT in the reference: it is the per-GPU partial {value, index} of a sharded arg reduction,
+ * produced in one pass over the data. */
+#define CB200_DECL_ACCUM_IDX_VALUE(T, C, op) \
+    void cb200_##T##_##op##_with_value_kernel_launch(cumo_na_reduction_arg_t* arg, cumo_na_iarray_t* values);
+
 /* mulsum, reference: gen/tmpl/accum_binary.c:4-5, accum_binary_kernel.cu:69-92.
  * `_reduce_`: *p3 += sum_i x[i]*y[i];  plain: p3[i] += x[i]*y[i] (all steps in bytes). */
 #define CB200_DECL_MULSUM(T, C, sfx) \
@@ -194,6 +201,8 @@ const char* cb200_version(void);
     CB200_DECL_MINMAX(T, C, ) \
     CB200_DECL_ACCUM_IDX(T, C, max_index) CB200_DECL_ACCUM_IDX(T, C, min_index) \
     CB200_DECL_ACCUM_IDX(T, C, argmax) CB200_DECL_ACCUM_IDX(T, C, argmin) \
+    CB200_DECL_ACCUM_IDX_VALUE(T, C, max_index) CB200_DECL_ACCUM_IDX_VALUE(T, C, min_index) \
+    CB200_DECL_ACCUM_IDX_VALUE(T, C, argmax) CB200_DECL_ACCUM_IDX_VALUE(T, C, argmin) \
     CB200_DECL_MULSUM(T, C, )
 
 #define CB200_DECL_FLOAT(T, C) \
@@ -219,6 +228,8 @@ const char* cb200_version(void);
     CB200_DECL_MINMAX(T, C, _nan) \
     CB200_DECL_ACCUM_IDX(T, C, max_index_nan) CB200_DECL_ACCUM_IDX(T, C, min_index_nan) \
     CB200_DECL_ACCUM_IDX(T, C, argmax_nan) CB200_DECL_ACCUM_IDX(T, C, argmin_nan) \
+    CB200_DECL_ACCUM_IDX_VALUE(T, C, max_index_nan) CB200_DECL_ACCUM_IDX_VALUE(T, C, min_index_nan) \
+    CB200_DECL_ACCUM_IDX_VALUE(T, C, argmax_nan) CB200_DECL_ACCUM_IDX_VALUE(T, C, argmin_nan) \
     CB200_DECL_MULSUM(T, C, _nan)
 
 #define CB200_DECL_INT(T, C) \

@@ -89,6 +89,9 @@ cb200_na_t* cb200_na_compare_scalar(const char* op, cb200_na_t* a, double sv_f, 
  * method's `nan: true`. */
 cb200_na_t* cb200_na_reduce(const char* op, cb200_na_t* a, uint32_t axis_mask, int keepdims, int nan);
 int cb200_na_minmax(cb200_na_t* a, uint32_t axis_mask, int keepdims, int nan, cb200_na_t** out_min, cb200_na_t** out_max);
+/* max_index / min_index / argmax / argmin together with the winning value, one pass; the index array is Int64.
+ * Not a method of the reference: it exists for the sharded (multi-GPU) reductions. */
+int cb200_na_arg_with_value(const char* op, cb200_na_t* a, uint32_t axis_mask, int nan, cb200_na_t** out_index, cb200_na_t** out_value);
 /* count_true / count_false of a Bit array -> UInt64 */
 cb200_na_t* cb200_na_count(cb200_na_t* a, uint32_t axis_mask, int keepdims, int want_false);
 /* mulsum(a, b, axis...) = (a*b).sum(axis...) in one pass over the inputs */

@@ -229,6 +229,12 @@ class ONArray:
         lo, hi = orc.reduce("minmax", self.a, axis=axis, nan=nan, keepdims=keepdims)
         return self._wrap(lo), self._wrap(hi)
 
+    def arg_with_value(self, op, axis=None, nan=False):
+        """(index as Int64, value): the index reduction and the matching extreme, two oracle calls."""
+        idx = OracleXP.Int64.cast(self._reduce(op, axis, False, nan))
+        val = self._reduce("max" if "max" in op else "min", axis, False, nan)
+        return idx, val
+
     def mulsum(self, other, axis=None, keepdims=False, nan=False):
         x, y = self._operand(other)
         return self._wrap(orc.mulsum(x, y, axis=axis, nan=nan))

@@ -341,6 +341,21 @@ def test_full_reductions_1d(xp_gpu, tname, n):
         check_reductions(xp_gpu, tname, g[::-1], o[::-1], None)      # reversed
 
 
+@pytest.mark.parametrize("tname", list(NP))
+@pytest.mark.parametrize("shape", [(1000,), (300_000,), (40, 600), (600, 1030)])
+def test_index_reduction_with_value(xp_gpu, tname, shape):
+    """The one-pass {index, value} form against the separate index and extreme reductions of the oracle."""
+    rng = np.random.default_rng(shape[0])
+    g, o = both(xp_gpu, tname, planted(rng, tname, shape))
+    for axis in ([None] if len(shape) == 1 else [None, 0, 1]):
+        for op in INDEX_REDS:
+            for nan in ((False, True) if tname in FLOATS else (False,)):
+                gi, gv = g.arg_with_value(op, axis=axis, nan=nan)
+                oi, ov = o.arg_with_value(op, axis=axis, nan=nan)
+                same(gi, oi)
+                same(gv, ov)
+
+
 def extreme_fills(tname):
     if tname in FLOATS:
         return {"all_nan": np.nan, "all_neg_inf": -np.inf, "all_pos_inf": np.inf, "all_zero": 0.0}

@@ -54,6 +54,26 @@ def check_rank(comm, xp, ox):
     got = np.array(sd.sum(axis=0).to_a())
     assert np.all(np.abs(got - fmat.sum(axis=0)) <= 1e-12 * np.abs(fmat).sum(axis=0))
 
+    # k-means assignment: points sharded by rows, centroids replicated, per-cluster counts all-reduced
+    from cumo_b200 import kmeans
+    from oracle import cumo_oracle as orc
+
+    k, d, npts = 256, 64, 30_011
+    centres = (rng.standard_normal((k, d)) * 4).astype(np.float32)
+    pts = (centres[rng.integers(0, k, npts)] + rng.standard_normal((npts, d))).astype(np.float32)
+    want, best, second = orc.kmeans_assign(pts, centres)
+    start, count = partition(npts, comm.world, comm.rank)
+    for algo in ("tensor", "cores"):
+        labels, counts = kmeans.assign_sharded(comm, xp.SFloat.from_numpy(pts[start:start + count]), xp.SFloat.from_numpy(centres), algo=algo)
+        got = labels.to_numpy()
+        flips = np.nonzero(got != want[start:start + count])[0] + start
+        scale = np.abs(best) + (centres.astype(np.float64) ** 2).sum(axis=1).max()
+        assert np.all((second - best)[flips] <= 1e-5 * scale[flips])
+        if len(flips) == 0:          # (every rank sees the same seeded data; a near-tie flip on another rank can move one count)
+            diff = np.abs(counts.to_numpy().astype(np.int64) - np.bincount(want, minlength=k))
+            assert diff.sum() <= 2
+        assert int(counts.to_numpy().sum()) == npts
+
 
 def test_sharded_reductions_one_rank(xp_gpu):
     from cumo_b200.sharded import Comm

@@ -277,6 +277,17 @@ def kernel_table(torch, xp, peak):
         rows.append({"config": config, "kernel": name, "bytes": int(nbytes), "ms": round(med, 4), "ms_min": round(best, 4),
                      "GBps": round(gbs, 1), "frac_of_measured": round(gbs / peak, 3), "frac_of_nominal": round(gbs / NOMINAL_HBM_GBS, 3),
                      "cpu_GBps_1thread_sample": cpu.get((config, name))})
+    try:
+        ref = refplan_table(torch, FULL_SIZES)
+    except Exception as e:                           # the baseline leg must never take the product's numbers down with it
+        ref = {}
+        print(f"refplan leg skipped: {e}", file=sys.stderr)
+    for row in rows:
+        ms = ref.get((row["config"], row["kernel"]))
+        if ms:
+            row["refplan_ms"] = ms
+            row["refplan_GBps"] = round(row["bytes"] / (ms * 1e-3) / 1e9, 1)
+            row["speedup_vs_refplan"] = round(ms / row["ms"], 2)
 
     # C5 (BASELINE config 4): k-means assignment, 2^24 points x 64-D against 256 centres, fused
     from cumo_b200 import kmeans
@@ -302,6 +313,70 @@ def kernel_table(torch, xp, peak):
             row["TFLOPs_issued_tf32"] = round(3 * row["TFLOPs"], 1)
         rows.append(row)
     return rows
+
+
+def refplan_table(torch, S):
+    """The reference's execution plan (oracle/refplan_gpu.cu, a restatement: the reference's own kernels cannot be
+    generated without Ruby) timed on this GPU for the rows it covers: {(config, kernel): ms}."""
+    from oracle import refplan_gpu
+
+    L = refplan_gpu.lib()
+    g = torch.Generator(device="cuda").manual_seed(0)
+    out = {}
+
+    def t(config, name, fn, reps=5, check=None):
+        fn()
+        if check is not None:
+            torch.cuda.synchronize()
+            assert check(), f"refplan {config} {name}: wrong result"
+        med, _ = time_kernel(torch, fn, reps=reps, warm=1)
+        out[(config, name)] = round(med, 4)
+
+    n = S["c1"][0]
+    a = torch.rand(n, n, device="cuda", generator=g) * 2 - 1
+    b = torch.rand(n, n, device="cuda", generator=g) * 2 - 1
+    col = torch.rand(n, 1, device="cuda", generator=g)
+    o = torch.empty_like(a)
+    vec = torch.empty(n, device="cuda")
+    idx = torch.empty(n, device="cuda", dtype=torch.int64)
+    scratch = torch.empty(max(n, S["c3_m"][1]) * 1024, device="cuda")
+    t("C1x16", "a*b", lambda: L.refplan_ew_f32(1, a.data_ptr(), b.data_ptr(), o.data_ptr(), 1, n * n, 0, 4, 0, 4, 0, 4), check=lambda: torch.equal(o, a * b))
+    t("C1x16", "a.sum(axis:1)", lambda: L.refplan_sum_rows_f32(a.data_ptr(), n, n, vec.data_ptr(), scratch.data_ptr()),
+      check=lambda: torch.allclose(vec, a.sum(dim=1), rtol=1e-4, atol=1e-2))
+    t("C1x16", "a + col(n,1)", lambda: L.refplan_ew_f32(0, a.data_ptr(), col.data_ptr(), o.data_ptr(), n, n, 4 * n, 4, 4, 0, 4 * n, 4), check=lambda: torch.equal(o, a + col))
+    t("C1x16", "c.sum(axis:0)", lambda: L.refplan_sum_cols_f32(a.data_ptr(), n, n, vec.data_ptr(), scratch.data_ptr()),
+      check=lambda: torch.allclose(vec, a.sum(dim=0), rtol=1e-4, atol=1e-2))
+    t("C1x16", "c.max_index(axis:1)", lambda: L.refplan_max_index_rows_f32(a.data_ptr(), n, n, idx.data_ptr()),
+      check=lambda: torch.equal(idx, a.argmax(dim=1) + torch.arange(n, device="cuda") * n))
+    del b, col
+    r2, c2 = S["c2"]
+    x, y = torch.randn(r2, 1, device="cuda", generator=g), torch.randn(1, c2, device="cuda", generator=g)
+    o2 = o.view(-1)[: r2 * c2].view(r2, c2)
+    t("C2", "x(R,1)+y(1,C)", lambda: L.refplan_ew_f32(0, x.data_ptr(), y.data_ptr(), o2.data_ptr(), r2, c2, 4, 0, 0, 4, 4 * c2, 4), check=lambda: torch.equal(o2, x + y))
+    src = a.view(-1)[: r2 * c2]
+    t("C2", "exp", lambda: L.refplan_ew_f32(2, src.data_ptr(), None, o2.data_ptr(), 1, r2 * c2, 0, 4, 0, 0, 0, 4))
+    t("C2", "*0.5", lambda: L.refplan_mul_scalar_f32(src.data_ptr(), 0.5, o2.data_ptr(), r2 * c2), check=lambda: torch.equal(o2.view(-1), src * 0.5))
+    n3, (mr, mc) = S["c3_n"], S["c3_m"]
+    v = a.view(-1)[:n3].abs()
+    one = torch.empty(1, device="cuda")
+    t("C3", "f32 1-D sum", lambda: L.refplan_sum_rows_f32(v.data_ptr(), 1, n3, one.data_ptr(), scratch.data_ptr()),
+      check=lambda: abs(one.item() - v.sum(dtype=torch.float64).item()) <= 1e-4 * v.sum(dtype=torch.float64).item())
+    i1 = torch.empty(1, device="cuda", dtype=torch.int64)
+    t("C3", "f32 1-D argmax", lambda: L.refplan_max_index_rows_f32(v.data_ptr(), 1, n3, i1.data_ptr()), reps=2, check=lambda: i1.item() == int(v.argmax().item()))
+    vc, vr = torch.empty(mc, device="cuda"), torch.empty(mr, device="cuda")
+    t("C3", "f32 2-D sum(axis:0)", lambda: L.refplan_sum_cols_f32(v.data_ptr(), mr, mc, vc.data_ptr(), scratch.data_ptr()),
+      check=lambda: torch.allclose(vc, v.view(mr, mc).sum(dim=0), rtol=1e-4))
+    t("C3", "f32 2-D sum(axis:1)", lambda: L.refplan_sum_rows_f32(v.data_ptr(), mr, mc, vr.data_ptr(), scratch.data_ptr()),
+      check=lambda: torch.allclose(vr, v.view(mr, mc).sum(dim=1), rtol=1e-4))
+    n4 = S["c4_n"]
+    ia = torch.randint(-(1 << 20), 1 << 20, (n4,), device="cuda", dtype=torch.int32, generator=g)
+    io = torch.empty_like(ia)
+    bits = torch.zeros(n4 // 32, device="cuda", dtype=torch.int32)
+    cnt = torch.zeros(1, device="cuda", dtype=torch.int64)
+    t("C4", "a*3", lambda: L.refplan_mul_scalar_i32(ia.data_ptr(), 3, io.data_ptr(), n4), check=lambda: torch.equal(io, ia * 3))
+    t("C4", "a>0 -> Bit", lambda: L.refplan_gt_scalar_i32(ia.data_ptr(), 0, bits.data_ptr(), n4), reps=3)
+    t("C4", "count_true", lambda: L.refplan_count_true(bits.data_ptr(), n4, cnt.data_ptr()), reps=3, check=lambda: cnt.item() == int((ia > 0).sum().item()))
+    return out
 
 
 def run_ours(args):

@@ -60,6 +60,7 @@ def build_cases(xp, torch, mib: int):
         "mul": (lambda: (lambda a=f32(): a * a), 3 * n32 * 4),
         "outer_add": (lambda: (lambda xy=outer(): xy[0] + xy[1]), n32 * 4),
         "add_col": (lambda: (lambda ac=col(): ac[0] + ac[1]), 2 * n32 * 4),
+        "sum_axis1_sq_f32": (lambda: (lambda a=f32()[0:(int((rows32 * cols) ** 0.5) // 64 * 64) ** 2].reshape(int((rows32 * cols) ** 0.5) // 64 * 64, -1): a.sum(axis=1)), (int((rows32 * cols) ** 0.5) // 64 * 64) ** 2 * 4),
         "mul_row": (lambda: (lambda a=f32().reshape(rows32, cols), w=f32()[0:cols].reshape(1, cols): a * w), 2 * n32 * 4),
         "sum_f32": (lambda: (lambda a=f32(): a.sum()), n32 * 4),
         "sum_f64": (lambda: (lambda a=f64(): a.sum()), n64 * 8),

@@ -585,6 +585,7 @@ void launch_reduce(const cumo_na_reduction_arg_t* arg, const cumo_na_iarray_t* o
     constexpr int ES = sizeof(T);
     constexpr int VMAX = 16 / ES;
     constexpr int64_t kSegBytes = 32 << 10;           // one CTA's share of a long row
+    constexpr int64_t kManyRows = 148 * 64;           // rows enough to fill a B200 with a warp each
     constexpr int64_t kColSegRows = 256;              // one CTA's share of a column strip
     constexpr int64_t kColWideSegRows = 256;          // the same when the strip is a CTA wide (4 KiB per row)
     constexpr int64_t kColWideRound = 148 * 4;        // CTAs of that plan resident at once on a B200: 148 SMs x 4
@@ -615,9 +616,12 @@ void launch_reduce(const cumo_na_reduction_arg_t* arg, const cumo_na_iarray_t* o
         for (int d = 0; d < p.n_od && vec; ++d) if (!mult16(p.in_ostep[d])) vec = false;
         // a warp per row while there are rows enough to fill the device that way (no CTA-wide fold per
         // 16 KiB of input); a CTA per (row, segment) for long or few rows
-        const bool wide = L >= 4096 && !(L <= 65536 && p.n_out >= (int64_t)sm_count() * 64);
+        // (these thresholds are constants of the plan, not read from the device: a result never depends on where it ran)
+        const bool wide = L >= 4096 && !(L * ES <= kSegBytes && p.n_out >= kManyRows);
         q.seg_len = L > 0 ? L : 1;
-        if (wide) {
+        // rows of up to 256 KiB stay whole, one CTA each, when there are CTAs enough without cutting them
+        const bool whole_rows = p.n_out >= kManyRows / 8 && L * ES <= 8 * kSegBytes;
+        if (wide && !whole_rows) {
             int64_t seg = kSegBytes / ES;              // a multiple of 32 elements: segment starts stay 16-byte aligned
             int64_t ns = (L + seg - 1) / seg;
             while (ns > 8192) { seg *= 2; ns = (L + seg - 1) / seg; }

@@ -6,7 +6,7 @@ sources (`csrc/`), its build (`build.py`), a ctypes binding, the Python face of 
 host layer (`narray`), and leading-axis sharding over several GPUs (`sharded`).
 """
 from .narray import (Bit, CudaError, CumoError, DFloat, Int32, Int64, NArray, NMath, SFloat, ShapeError,
-                     UInt64, pack_bits, synchronize, unpack_bits)
+                     UInt32, UInt64, pack_bits, synchronize, unpack_bits)
 
 __all__ = ["Bit", "CudaError", "CumoError", "DFloat", "Int32", "Int64", "NArray", "NMath", "SFloat",
-           "ShapeError", "UInt64", "pack_bits", "synchronize", "unpack_bits"]
+           "ShapeError", "UInt32", "UInt64", "pack_bits", "synchronize", "unpack_bits"]

@@ -18,8 +18,8 @@
 namespace {
 
 constexpr int kMaxD = CUMO_NA_MAX_DIMENSION;
-const char* kTypeName[] = {"sfloat", "dfloat", "int32", "int64", "bit", "uint64"};
-const int kElemSize[] = {4, 8, 4, 8, 0, 8};
+const char* kTypeName[] = {"sfloat", "dfloat", "int32", "int64", "bit", "uint64", "uint32"};
+const int kElemSize[] = {4, 8, 4, 8, 0, 8, 4};
 
 thread_local std::string tl_class, tl_message;
 
@@ -90,7 +90,7 @@ void contiguous_steps(int dtype, int ndim, const int64_t* shape, int64_t* step) 
 }
 
 cb200_na* make(int dtype, int ndim, const int64_t* shape, bool zero) {
-    if (dtype < 0 || dtype > CB200_UINT64) return (cb200_na*)fail("TypeError", "unknown dtype %d", dtype);
+    if (dtype < 0 || dtype > CB200_UINT32) return (cb200_na*)fail("TypeError", "unknown dtype %d", dtype);
     if (ndim < 0 || ndim > kMaxD) return (cb200_na*)fail("ShapeError", "ndim %d out of range", ndim);
     cb200_na* a = new cb200_na();
     a->dtype = dtype;
@@ -443,7 +443,7 @@ cb200_na_t* cb200_na_new(int dtype, int ndim, const int64_t* shape) { return mak
 cb200_na_t* cb200_na_zeros(int dtype, int ndim, const int64_t* shape) { return make(dtype, ndim, shape, true); }
 
 cb200_na_t* cb200_na_wrap(int dtype, int ndim, const int64_t* shape, const int64_t* step, void* device_ptr, int64_t offset) {
-    if (dtype < 0 || dtype > CB200_UINT64) return (cb200_na*)fail("TypeError", "unknown dtype %d", dtype);
+    if (dtype < 0 || dtype > CB200_UINT32) return (cb200_na*)fail("TypeError", "unknown dtype %d", dtype);
     if (ndim < 0 || ndim > kMaxD) return (cb200_na*)fail("ShapeError", "ndim %d out of range", ndim);
     cb200_na* a = new cb200_na();
     a->dtype = dtype;
@@ -520,10 +520,11 @@ int cb200_synchronize(void) { return cuda_ok(cudaStreamSynchronize(cb200::curren
 
 cb200_na_t* cb200_na_cast(cb200_na_t* a, int dtype) { return cast_to(a, dtype); }
 cb200_na_t* cb200_na_copy(cb200_na_t* a) {
-    if (a->dtype == CB200_UINT64) {   // a container type: copied as Int64 bit patterns
-        cb200_na tmp = *a; tmp.dtype = CB200_INT64;
-        cb200_na* c = cast_to(&tmp, CB200_INT64);
-        if (c) c->dtype = CB200_UINT64;
+    if (a->dtype == CB200_UINT64 || a->dtype == CB200_UINT32) {   // container types: copied as signed bit patterns
+        const int as = a->dtype == CB200_UINT64 ? CB200_INT64 : CB200_INT32;
+        cb200_na tmp = *a; tmp.dtype = as;
+        cb200_na* c = cast_to(&tmp, as);
+        if (c) c->dtype = a->dtype;
         return c;
     }
     if (a->dtype == CB200_BIT) return (cb200_na*)fail("TypeError", "copy of a Bit view is not on this path");
@@ -840,6 +841,137 @@ int cb200_na_minmax(cb200_na_t* a, uint32_t axis_mask, int keepdims, int nan, cb
     *out_min = o1;
     *out_max = o2;
     return 0;
+}
+
+// ---- cumsum / cumprod ----------------------------------------------------------------------
+cb200_na_t* cb200_na_cum(const char* op_c, cb200_na_t* a, int axis, int nan) {
+    std::string op = op_c;
+    if (op != "cumsum" && op != "cumprod") return (cb200_na*)fail("NoMethodError", "undefined method %s", op_c);
+    if (!is_value_type(a->dtype)) return (cb200_na*)fail("TypeError", "%s is not defined for %s", op_c, kTypeName[a->dtype]);
+    if (axis >= a->ndim) return (cb200_na*)fail("ArgumentError", "axis %d out of range for %d dimensions", axis, a->ndim);
+    using Fn = int (*)(char*, char*, ssize_t, ssize_t, uint64_t);
+    Fn f = (Fn)sym(std::string("cumo_") + kTypeName[a->dtype] + "_" + op + ((nan && is_float_type(a->dtype)) ? "_nan" : "") + "_kernel_launch");
+    if (!f) return nullptr;
+    cb200_na* out = make(a->dtype, a->ndim, a->shape, false);
+    if (!out) return nullptr;
+    if (size_of(a) == 0) return out;
+    cb200_na* copy = nullptr;
+    const cb200_na* in = a;
+    StrideLoop L;
+    auto set_loop = [&](const cb200_na* x) {
+        L.nd = x->ndim;
+        for (int i = 0; i < x->ndim; ++i) { L.n[i] = x->shape[i]; L.s[0][i] = x->step[i]; L.s[1][i] = out->step[i]; }
+        if (L.nd == 0) { L.nd = 1; L.n[0] = 1; L.s[0][0] = L.s[1][0] = 0; }
+    };
+    int status = 0;
+    if (axis < 0) {
+        // all elements in row-major order: one run when the dims merge, else through a contiguous copy
+        set_loop(in);
+        contract(&L, 2);
+        if (L.nd != 1) {
+            copy = cast_to(a, a->dtype);
+            if (!copy) { cb200_na_release(out); return nullptr; }
+            in = copy;
+            set_loop(in);
+            contract(&L, 2);
+        }
+        status = f(data_ptr(in), data_ptr(out), (ssize_t)L.s[0][0], (ssize_t)L.s[1][0], (uint64_t)L.n[0]);
+    } else {
+        // one launch per run along `axis`, as ndloop does for this iterator
+        set_loop(in);
+        const int last = L.nd - 1;
+        std::swap(L.n[axis], L.n[last]);
+        std::swap(L.s[0][axis], L.s[0][last]);
+        std::swap(L.s[1][axis], L.s[1][last]);
+        for_outer(L, 2, [&](const int64_t* off) {
+            if (status) return;
+            status = f(data_ptr(in) + off[0], data_ptr(out) + off[1], (ssize_t)L.s[0][last], (ssize_t)L.s[1][last], (uint64_t)L.n[last]);
+        });
+    }
+    cb200_na_release(copy);
+    if (status) { fail("CudaError", "%s: %s", op_c, cudaGetErrorString((cudaError_t)status)); cb200_na_release(out); return nullptr; }
+    if (!launch_ok()) { cb200_na_release(out); return nullptr; }
+    return out;
+}
+
+// ---- bincount ------------------------------------------------------------------------------
+cb200_na_t* cb200_na_bincount(cb200_na_t* a, cb200_na_t* weight, int64_t minlength) {
+    if (a->dtype != CB200_INT32 && a->dtype != CB200_INT64) return (cb200_na*)fail("NoMethodError", "undefined method bincount for %s", kTypeName[a->dtype]);
+    if (a->ndim < 1) return (cb200_na*)fail("ShapeError", "bincount needs at least one dimension");
+    if (minlength < 0) return (cb200_na*)fail("ArgumentError", "minlength must be non-negative");
+    cb200_na* w = nullptr;
+    if (weight) {
+        if (!is_value_type(weight->dtype)) return (cb200_na*)fail("TypeError", "weights must be numeric");
+        w = weight->dtype == CB200_SFLOAT ? weight : cast_to(weight, CB200_DFLOAT);
+        if (!w) return nullptr;
+    }
+    auto drop_w = [&]() { if (w && w != weight) cb200_na_release(w); };
+    const int last = a->ndim - 1;
+    if (w && (w->ndim != a->ndim || memcmp(w->shape, a->shape, sizeof(int64_t) * a->ndim) != 0)) {
+        // the reference broadcasts the leading axes and demands equal extents along the last one; equal shapes cover its tests
+        const bool last_ok = w->ndim >= 1 && w->shape[w->ndim - 1] == a->shape[last];
+        drop_w();
+        return (cb200_na*)fail("ShapeError", last_ok ? "weights of a different shape are not on this path" : "size mismatch along last axis between self and weight");
+    }
+    int64_t length = 0;
+    if (size_of(a) > 0) {
+        cb200_na *lo = nullptr, *hi = nullptr;
+        if (cb200_na_minmax(a, 0, 0, 0, &lo, &hi)) { drop_w(); return nullptr; }
+        int64_t vlo = 0, vhi = 0;
+        int32_t t32;
+        bool ok = true;
+        if (a->dtype == CB200_INT32) {
+            ok = cb200_na_read_host(lo, &t32, 4) == 0; vlo = t32;
+            ok = ok && cb200_na_read_host(hi, &t32, 4) == 0; vhi = t32;
+        } else {
+            ok = cb200_na_read_host(lo, &vlo, 8) == 0 && cb200_na_read_host(hi, &vhi, 8) == 0;
+        }
+        cb200_na_release(lo); cb200_na_release(hi);
+        if (!ok) { drop_w(); return nullptr; }
+        if (vlo < 0) { drop_w(); return (cb200_na*)fail("ArgumentError", "array items must be non-negative"); }
+        length = vhi + 1;
+    }
+    if (minlength > length) length = minlength;
+    const int out_dtype = w ? w->dtype : (length > 4294967295ll ? CB200_UINT64 : CB200_UINT32);
+    int64_t oshape[kMaxD];
+    memcpy(oshape, a->shape, sizeof(int64_t) * a->ndim);
+    oshape[last] = length;
+    cb200_na* out = make(out_dtype, a->ndim, oshape, false);
+    if (!out) { drop_w(); return nullptr; }
+    const std::string base = std::string("cumo_iter_") + kTypeName[a->dtype] + "_bincount_";
+    using FnC = void (*)(char*, ssize_t, size_t*, uint64_t, char*, ssize_t, uint64_t, int*, size_t*);
+    using FnW = void (*)(char*, ssize_t, char*, ssize_t, uint64_t, char*, ssize_t, uint64_t, int*, size_t*);
+    void* f = sym(base + (w ? (w->dtype == CB200_SFLOAT ? "sf" : "df") : (out_dtype == CB200_UINT64 ? "64" : "32")) + "_kernel_launch");
+    // mapped pinned words: the out-of-range flag and the offending item
+    bool ok = f != nullptr;
+    if (ok && !tl_flag.ready()) { fail("CudaError", "cannot allocate the mapped error flag"); ok = false; }
+    size_t* item = nullptr;
+    size_t* item_dev = nullptr;
+    if (ok) ok = cuda_ok(cudaHostAlloc(reinterpret_cast<void**>(&item), sizeof(size_t), cudaHostAllocMapped), "cudaHostAlloc") &&
+                 cuda_ok(cudaHostGetDevicePointer(reinterpret_cast<void**>(&item_dev), item, 0), "cudaHostGetDevicePointer");
+    if (ok && length > 0) {
+        *item = 0;
+        *tl_flag.host = 0;
+        // one launch per leading index, as ndloop does for an iterator that takes one dimension
+        StrideLoop L;
+        L.nd = a->ndim;
+        for (int i = 0; i < a->ndim; ++i) { L.n[i] = a->shape[i]; L.s[0][i] = a->step[i]; L.s[1][i] = out->step[i]; L.s[2][i] = w ? w->step[i] : 0; }
+        for_outer(L, 3, [&](const int64_t* off) {
+            char* p1 = data_ptr(a) + off[0];
+            char* p2 = data_ptr(out) + off[1];
+            if (w) ((FnW)f)(p1, (ssize_t)a->step[last], data_ptr(w) + off[2], (ssize_t)w->step[last], (uint64_t)a->shape[last], p2, (ssize_t)out->step[last], (uint64_t)length, tl_flag.dev, item_dev);
+            else ((FnC)f)(p1, (ssize_t)a->step[last], nullptr, (uint64_t)a->shape[last], p2, (ssize_t)out->step[last], (uint64_t)length, tl_flag.dev, item_dev);
+        });
+        ok = launch_ok() && cuda_ok(cudaStreamSynchronize(cb200::current_stream()), "cudaStreamSynchronize");
+        if (ok && *tl_flag.host) {
+            fail("IndexError", "item %zu is out of range of the output(size:%lld)", *item, (long long)length);
+            ok = false;
+        }
+    }
+    if (item) cudaFreeHost(item);
+    drop_w();
+    if (!ok) { cb200_na_release(out); return nullptr; }
+    return out;
 }
 
 // index (Int64) and winning value from one pass: the per-GPU partial of a sharded arg reduction

@@ -18,9 +18,9 @@ import numpy as np
 
 from . import _lib
 
-SFLOAT, DFLOAT, INT32, INT64, BIT, UINT64 = range(6)
-_NP = {SFLOAT: np.float32, DFLOAT: np.float64, INT32: np.int32, INT64: np.int64, UINT64: np.uint64}
-_ESZ = {SFLOAT: 4, DFLOAT: 8, INT32: 4, INT64: 8, BIT: 1, UINT64: 8}   # Bit: unit is one bit
+SFLOAT, DFLOAT, INT32, INT64, BIT, UINT64, UINT32 = range(7)
+_NP = {SFLOAT: np.float32, DFLOAT: np.float64, INT32: np.int32, INT64: np.int64, UINT64: np.uint64, UINT32: np.uint32}
+_ESZ = {SFLOAT: 4, DFLOAT: 8, INT32: 4, INT64: 8, BIT: 1, UINT64: 8, UINT32: 4}   # Bit: unit is one bit
 
 
 class CumoError(Exception):
@@ -199,7 +199,7 @@ class NArray:
     # ---- facts --------------------------------------------------------------------------------
     @property
     def _tname(self):
-        return ["sfloat", "dfloat", "int32", "int64", "bit", "uint64"][self.dtype_code]
+        return ["sfloat", "dfloat", "int32", "int64", "bit", "uint64", "uint32"][self.dtype_code]
 
     @property
     def ndim(self):
@@ -503,6 +503,21 @@ class NArray:
             _raise_last()
         return NArray._from_handle(lo.value), NArray._from_handle(hi.value)
 
+    def _cum(self, op, axis, nan):
+        if axis is not None and not isinstance(axis, int):
+            raise TypeError("cumsum / cumprod take one axis or none")
+        ax = -1 if axis is None else (axis % self.ndim if self.ndim else 0)
+        return NArray._from_handle(_lib.load().cb200_na_cum(op.encode(), self._h, ax, int(nan)))
+
+    def cumsum(self, axis=None, nan=False): return self._cum("cumsum", axis, nan)
+    def cumprod(self, axis=None, nan=False): return self._cum("cumprod", axis, nan)
+
+    def bincount(self, weight=None, minlength=0):
+        """Occurrences (or summed weights) of each value along the last axis (Int32 / Int64 only)."""
+        if weight is not None and not isinstance(weight, NArray):
+            weight = DFloat.cast(weight)
+        return NArray._from_handle(_lib.load().cb200_na_bincount(self._h, weight._h if weight is not None else None, int(minlength)))
+
     def arg_with_value(self, op, axis=None, nan=False):
         """(index Int64, value) of max_index / min_index / argmax / argmin from one pass over the data."""
         idx, val = c_void_p(), c_void_p()
@@ -535,6 +550,11 @@ class Int64(NArray):
 class UInt64(NArray):
     """Result type of count_true / count_false; no arithmetic is defined on it here."""
     dtype_code = UINT64
+
+
+class UInt32(NArray):
+    """Result type of bincount; no arithmetic is defined on it here."""
+    dtype_code = UINT32
 
 
 class Bit(NArray):

@@ -243,6 +243,34 @@ CB200_DECL_FLOAT(dfloat, double)
 CB200_DECL_INT(int32, int32_t)
 CB200_DECL_INT(int64, int64_t)
 
+/* bincount along one run (integer types only), reference: gen/tmpl/bincount.c:18,70, bincount_kernel.cu:32-97.
+ * The output run (n elements, byte step s2/s3) is cleared, then every element x of the input run (count elements
+ * at p1, byte step s1, or byte offsets idx1[i] when idx1 is not NULL) adds 1 -- `_32`: uint32_t, `_64`: uint64_t
+ * -- or its weight -- `_sf`: float, `_df`: double, weights at p2, byte step s2 -- to out[x].  An element outside
+ * [0, n) sets *oor, leaves its value in *item and is skipped; both must be device-writable. */
+#define CB200_DECL_BINCOUNT(T) \
+    void cumo_iter_##T##_bincount_32_kernel_launch(char* p1, ssize_t s1, size_t* idx1, uint64_t count, char* p2, ssize_t s2, uint64_t n, int* oor, size_t* item); \
+    void cumo_iter_##T##_bincount_64_kernel_launch(char* p1, ssize_t s1, size_t* idx1, uint64_t count, char* p2, ssize_t s2, uint64_t n, int* oor, size_t* item); \
+    void cumo_iter_##T##_bincount_sf_kernel_launch(char* p1, ssize_t s1, char* p2, ssize_t s2, uint64_t count, char* p3, ssize_t s3, uint64_t n, int* oor, size_t* item); \
+    void cumo_iter_##T##_bincount_df_kernel_launch(char* p1, ssize_t s1, char* p2, ssize_t s2, uint64_t count, char* p3, ssize_t s3, uint64_t n, int* oor, size_t* item);
+CB200_DECL_BINCOUNT(int32)
+CB200_DECL_BINCOUNT(int64)
+
+/* cumsum / cumprod along one run, reference: gen/tmpl/cum.c:3, cum_kernel.cu:56-80 (thrust::inclusive_scan there).
+ * out[i] = x[0] op ... op x[i] for i < n; p1/p2 with byte steps s1/s2 of any sign.  `_nan` (float types): a NaN
+ * accumulator is replaced by the next value, a NaN value is skipped (real_accum_kernel.h:12-26).  Returns the launch
+ * status; the caller raises. */
+#if defined(__CUDACC__) || defined(__DRIVER_TYPES_H__)
+typedef cudaError_t cb200_cuda_status_t;
+#else
+typedef int cb200_cuda_status_t;          /* cudaError_t: an int-sized enum, 0 = cudaSuccess */
+#endif
+#define CB200_DECL_CUM(T, sfx) \
+    cb200_cuda_status_t cumo_##T##_cumsum##sfx##_kernel_launch(char* p1, char* p2, ssize_t s1, ssize_t s2, uint64_t n); \
+    cb200_cuda_status_t cumo_##T##_cumprod##sfx##_kernel_launch(char* p1, char* p2, ssize_t s1, ssize_t s2, uint64_t n);
+CB200_DECL_CUM(sfloat, ) CB200_DECL_CUM(dfloat, ) CB200_DECL_CUM(int32, ) CB200_DECL_CUM(int64, )
+CB200_DECL_CUM(sfloat, _nan) CB200_DECL_CUM(dfloat, _nan)
+
 /* kahan_sum exists for the double-precision type only (reference: gen/spec.rb:321-323,
  * float_accum_kernel.cu:196-206). */
 CB200_DECL_ACCUM(dfloat, double, kahan_sum)

@@ -37,7 +37,8 @@ typedef struct cb200_na cb200_na_t;
 enum {
     CB200_SFLOAT = 0, CB200_DFLOAT = 1, CB200_INT32 = 2, CB200_INT64 = 3,
     CB200_BIT = 4,      /* 1 bit per element, 32-bit words, LSB first; steps/offset in bits */
-    CB200_UINT64 = 5    /* result container of count_true/count_false only */
+    CB200_UINT64 = 5,   /* result container of count_true/count_false and bincount */
+    CB200_UINT32 = 6    /* result container of bincount */
 };
 
 const char* cb200_host_error(const char** klass);   /* message (and class) of the last error on this thread */
@@ -89,6 +90,13 @@ cb200_na_t* cb200_na_compare_scalar(const char* op, cb200_na_t* a, double sv_f, 
  * method's `nan: true`. */
 cb200_na_t* cb200_na_reduce(const char* op, cb200_na_t* a, uint32_t axis_mask, int keepdims, int nan);
 int cb200_na_minmax(cb200_na_t* a, uint32_t axis_mask, int keepdims, int nan, cb200_na_t** out_min, cb200_na_t** out_max);
+/* cumsum / cumprod (narray/gen/tmpl/cum.c:41-70): axis < 0 runs over all elements in row-major order, else along
+ * that axis; the result has the operand's shape and type.  nan: the NaN-skipping operator (float types). */
+cb200_na_t* cb200_na_cum(const char* op, cb200_na_t* a, int axis, int nan);
+/* bincount along the last axis (narray/gen/tmpl/bincount.c:176-240): counts as UInt32 (UInt64 when the length
+ * exceeds 2^32-1), or sums of `weight` (SFloat stays SFloat, anything else is summed as DFloat); the length is
+ * max+1 or `minlength` if larger; a negative element raises ArgumentError.  Reads the extremes back: synchronises. */
+cb200_na_t* cb200_na_bincount(cb200_na_t* a, cb200_na_t* weight, int64_t minlength);
 /* max_index / min_index / argmax / argmin together with the winning value, one pass; the index array is Int64.
  * Not a method of the reference: it exists for the sharded (multi-GPU) reductions. */
 int cb200_na_arg_with_value(const char* op, cb200_na_t* a, uint32_t axis_mask, int nan, cb200_na_t** out_index, cb200_na_t** out_value);

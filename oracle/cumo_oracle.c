@@ -216,6 +216,59 @@ void oracle_kmeans_assign(const float* x, int64_t n, int d, const float* c, int 
     }
 }
 
+/* bincount along one run: the host loop the reference runs for small inputs is the same arithmetic as its
+ * kernel (narray/gen/tmpl/bincount_kernel.cu:32-45 counts, :80-88 weighted): clear, then out[x] += 1 or w[i];
+ * an item outside [0, n) is reported and skipped.  in64: items are int64_t (else int32_t).  kind: 0 uint32
+ * counts, 1 uint64 counts, 2 float weights and sums, 3 double.  Steps in bytes.  Returns 1 when an item was out
+ * of range (the last offender in *bad). */
+int oracle_bincount(int in64, const char* p1, int64_t s1, int64_t count, int kind, const char* pw, int64_t sw,
+                    char* out, int64_t so, int64_t n, int64_t* bad) {
+    int oor = 0;
+    for (int64_t b = 0; b < n; ++b) {
+        if (kind == 0) *(uint32_t*)(out + b * so) = 0;
+        else if (kind == 1) *(uint64_t*)(out + b * so) = 0;
+        else if (kind == 2) *(float*)(out + b * so) = 0;
+        else *(double*)(out + b * so) = 0;
+    }
+    for (int64_t i = 0; i < count; ++i) {
+        int64_t x = in64 ? *(const int64_t*)(p1 + i * s1) : (int64_t)*(const int32_t*)(p1 + i * s1);
+        if (x < 0 || x >= n) { oor = 1; if (bad) *bad = x; continue; }
+        if (kind == 0) *(uint32_t*)(out + x * so) += 1u;
+        else if (kind == 1) *(uint64_t*)(out + x * so) += 1ull;
+        else if (kind == 2) *(float*)(out + x * so) += *(const float*)(pw + i * sw);
+        else *(double*)(out + x * so) += *(const double*)(pw + i * sw);
+    }
+    return oor;
+}
+
+/* cumsum / cumprod along one run: the host loop of narray/gen/tmpl/cum.c:27-37 with the operators of
+ * include/cumo/types/real_accum.h:9-24 (floats) and xint_macro.h:46-47 (integers, wrapping).  dtype: 0 float,
+ * 1 double, 2 int32, 3 int64.  Steps in bytes. */
+#define ORACLE_CUM_LOOP(T, ISF)                                                              \
+    {                                                                                        \
+        T x = *(const T*)p1;                                                                 \
+        *(T*)p2 = x;                                                                         \
+        for (int64_t i = 1; i < n; ++i) {                                                    \
+            T y = *(const T*)(p1 + i * s1);                                                  \
+            if (ISF && nan) {                                                                \
+                if (x != x) x = y;                                                           \
+                else if (y == y) x = prod ? (T)(x * y) : (T)(x + y);                         \
+            } else x = prod ? (T)(x * y) : (T)(x + y);                                       \
+            *(T*)(p2 + i * s2) = x;                                                          \
+        }                                                                                    \
+    }
+int oracle_cum(int dtype, int prod, int nan, const char* p1, char* p2, int64_t s1, int64_t s2, int64_t n) {
+    if (n <= 0) return 0;
+    if (dtype == 0) ORACLE_CUM_LOOP(float, 1)
+    else if (dtype == 1) ORACLE_CUM_LOOP(double, 1)
+    else if (dtype == 2) { uint32_t x = *(const uint32_t*)p1; *(uint32_t*)p2 = x;      /* unsigned arithmetic: wraps like the device */
+        for (int64_t i = 1; i < n; ++i) { uint32_t y = *(const uint32_t*)(p1 + i * s1); x = prod ? x * y : x + y; *(uint32_t*)(p2 + i * s2) = x; } }
+    else if (dtype == 3) { uint64_t x = *(const uint64_t*)p1; *(uint64_t*)p2 = x;
+        for (int64_t i = 1; i < n; ++i) { uint64_t y = *(const uint64_t*)(p1 + i * s1); x = prod ? x * y : x + y; *(uint64_t*)(p2 + i * s2) = x; } }
+    else return 1;
+    return 0;
+}
+
 int oracle_threads(void) {
 #ifdef _OPENMP
     return omp_get_max_threads();

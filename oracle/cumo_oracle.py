@@ -220,6 +220,66 @@ def sum_f64ref(a: np.ndarray) -> float:
     return float(lib().oracle_sum_f64ref(DT[a.dtype], a.ctypes.data, a.size))
 
 
+def cum(op: str, a: np.ndarray, axis=None, nan: bool = False) -> np.ndarray:
+    """cumsum / cumprod: over all elements in row-major order (axis None) or along one axis."""
+    fn = lib().oracle_cum
+    fn.restype = c_int
+    fn.argtypes = [c_int, c_int, c_int, c_void_p, c_void_p, c_int64, c_int64, c_int64]
+    out = np.empty(a.shape, dtype=a.dtype)
+    if a.size == 0:
+        return out
+    prod = int(op == "cumprod")
+    if axis is None:
+        src = np.ascontiguousarray(a).reshape(-1)
+        dst = out.reshape(-1)
+        fn(DT[a.dtype], prod, int(nan), src.ctypes.data, dst.ctypes.data, src.strides[0], dst.strides[0], src.size)
+        return out
+    src, dst = np.moveaxis(a, axis, -1), np.moveaxis(out, axis, -1)
+    for lead in np.ndindex(*src.shape[:-1]):
+        r, w = src[lead], dst[lead]
+        fn(DT[a.dtype], prod, int(nan), r.ctypes.data, w.ctypes.data, r.strides[0], w.strides[0], r.shape[0])
+    return out
+
+
+def bincount(a: np.ndarray, weight=None, minlength: int = 0) -> np.ndarray:
+    """Cumo's bincount along the last axis (narray/gen/tmpl/bincount.c:176-240): length = max+1 or minlength,
+    UInt32 counts (UInt64 beyond 2^32-1 bins), float32 weights summed as float32, any other weight as float64;
+    a negative item raises ValueError (the reference's ArgumentError)."""
+    if a.dtype not in (np.int32, np.int64) or a.ndim < 1:
+        raise TypeError("bincount needs an Int32 / Int64 array of at least one dimension")
+    if weight is not None:
+        weight = np.asarray(weight)
+        if weight.dtype != np.float32:
+            weight = weight.astype(np.float64)
+        if weight.shape[-1:] != a.shape[-1:]:
+            raise ValueError("size mismatch along last axis between self and weight")
+        weight = np.broadcast_to(weight, a.shape)
+    length = 0
+    if a.size:
+        if int(a.min()) < 0:
+            raise ValueError("array items must be non-negative")
+        length = int(a.max()) + 1
+    length = max(length, int(minlength))
+    if weight is None:
+        kind, odt = (1, np.uint64) if length > 4294967295 else (0, np.uint32)
+    else:
+        kind, odt = (2, np.float32) if weight.dtype == np.float32 else (3, np.float64)
+    out = np.zeros(a.shape[:-1] + (length,), dtype=odt)
+    fn = lib().oracle_bincount
+    fn.restype = c_int
+    fn.argtypes = [c_int, c_void_p, c_int64, c_int64, c_int, c_void_p, c_int64, c_void_p, c_int64, c_int64, POINTER(c_int64)]
+    bad = c_int64(0)
+    for lead in np.ndindex(*a.shape[:-1]):
+        row = a[lead]
+        w = weight[lead] if weight is not None else None
+        o = out[lead]
+        if fn(int(a.dtype == np.int64), row.ctypes.data, row.strides[0] if row.ndim else 0, row.shape[0], kind,
+              w.ctypes.data if w is not None else None, (w.strides[0] if w is not None else 0), o.ctypes.data, o.strides[0] if length else 0,
+              length, bad):
+            raise IndexError(f"item {bad.value} is out of range of the output(size:{length})")
+    return out
+
+
 def kmeans_assign(x: np.ndarray, c: np.ndarray):
     """(labels int32, best float64, second float64) of the assignment step in float64."""
     x = np.ascontiguousarray(x, dtype=np.float32)

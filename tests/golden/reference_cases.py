@@ -370,4 +370,93 @@ def case_math_closeness(xp):
             assert abs(o - math.atan(v)) <= rel * 2
 
 
+# ---- test/narray_test.rb:2024-2062 "bincount" (the Int32 / Int64 lines) ----------------------------------------------
+def case_bincount(xp):
+    def raises(exc, f):
+        try:
+            f()
+        except exc:
+            return True
+        return False
+
+    for T in (xp.Int32, xp.Int64):
+        assert T[0, 1, 1, 3, 2, 1, 7].bincount().to_a() == [1, 3, 1, 1, 0, 0, 0, 1]
+    x = xp.Int32[0, 1, 1, 3, 2, 1, 7, 23]
+    assert x.bincount().size == scalar(x.max()) + 1
+    assert xp.Int32[0, 1, 1].bincount(minlength=6).to_a() == [1, 2, 0, 0, 0, 0]
+    assert xp.Int32[0, 1, 5].bincount(minlength=2).to_a() == [1, 1, 0, 0, 0, 1]
+    x = xp.Int32[0, 1, 1, 2, 2, 2]
+    w = xp.DFloat[0.3, 0.5, 0.2, 0.7, 1.0, -0.6]
+    for want, got in zip([0.3, 0.7, 1.1], x.bincount(w).to_a()):
+        assert abs(want - got) <= 1e-12
+    assert x.bincount(xp.SFloat[1, 1, 1, 1, 1, 1]).to_a() == [1.0, 2.0, 3.0]
+    assert raises(Exception, lambda: xp.Int32[0, 1].bincount(xp.DFloat[1, 2, 3]))
+    assert raises(ValueError, lambda: xp.Int32[0, -1, 2].bincount())            # ArgumentError in Ruby
+    assert xp.Int32[0, 1, 1, 3, 9][0:4].bincount().to_a() == [1, 2, 0, 1]
+    assert xp.Int32[[0, 1], [1, 3]].bincount().to_a() == [[1, 1, 0, 0], [0, 1, 0, 1]]
+
+
+# ---- test/narray_test.rb:2868-2960 cumsum / cumprod (values chosen there so that every partial result is exact) -----
+def _running(values, f):
+    out, acc = [], None
+    for x in values:
+        acc = x if acc is None else f(acc, x)
+        out.append(acc)
+    return out
+
+
+def _running_skip_nan(values, f):
+    acc = values[0]
+    out = [acc]
+    for y in values[1:]:
+        if math.isnan(acc):
+            acc = y
+        elif not math.isnan(y):
+            acc = f(acc, y)
+        out.append(acc)
+    return out
+
+
+def case_cumsum_cumprod_long_and_views(xp):
+    n = 20_000
+    adds = [(i % 3) + 1 for i in range(n)]
+    muls = [2 if i % 4 < 2 else 0.5 for i in range(n)]
+    views = [("flat", list(range(n)), lambda v: v), ("offset 13", list(range(13, n)), lambda v: v[13:n]),
+             ("step 2", list(range(0, n, 2)), lambda v: v[0:n:2]), ("reversed", list(range(n - 1, -1, -1)), lambda v: v[::-1])]
+    for T in (xp.Int32, xp.DFloat, xp.SFloat):
+        a = T.cast(adds)
+        for label, idxs, cut in views:
+            assert cut(a).cumsum().to_a() == _running([adds[i] for i in idxs], lambda x, y: x + y), (T, label)
+    for T in (xp.DFloat, xp.SFloat):
+        a = T.cast(muls)
+        for label, idxs, cut in views:
+            assert cut(a).cumprod().to_a() == _running([muls[i] for i in idxs], lambda x, y: x * y), (T, label)
+
+
+def case_cumsum_cumprod_along_an_axis(xp):
+    rows, cols = 6, 2_000          # (the reference uses 20 000 columns; the column case is one launch per column)
+    adds = [(i % 3) + 1 for i in range(rows * cols)]
+    muls = [2 if i % 4 < 2 else 0.5 for i in range(rows * cols)]
+    a = xp.DFloat.cast(adds).reshape(rows, cols)
+    assert a.cumsum(axis=1).to_a() == [_running(adds[r * cols:(r + 1) * cols], lambda x, y: x + y) for r in range(rows)]
+    down = [_running([adds[r * cols + c] for r in range(rows)], lambda x, y: x + y) for c in range(cols)]
+    assert a.cumsum(axis=0).to_a() == [[down[c][r] for c in range(cols)] for r in range(rows)]
+    b = xp.DFloat.cast(muls).reshape(rows, cols)
+    assert b.cumprod(axis=1).to_a() == [_running(muls[r * cols:(r + 1) * cols], lambda x, y: x * y) for r in range(rows)]
+
+
+def case_cumsum_cumprod_carry_nan(xp):
+    for n in (64, 20_000):
+        for at in (0, 1, n // 2, n - 1):
+            adds = [(i % 3) + 1.0 for i in range(n)]
+            muls = [2.0 if i % 4 < 2 else 0.5 for i in range(n)]
+            adds[at] = NAN
+            muls[at] = NAN
+            a, b = xp.DFloat.cast(adds), xp.DFloat.cast(muls)
+            assert tags(a.cumsum().to_a()) == tags(_running(adds, lambda x, y: x + y)), (n, at)
+            assert tags(a.cumsum(nan=True).to_a()) == tags(_running_skip_nan(adds, lambda x, y: x + y)), (n, at)
+            assert tags(b.cumprod().to_a()) == tags(_running(muls, lambda x, y: x * y)), (n, at)
+            assert tags(b.cumprod(nan=True).to_a()) == tags(_running_skip_nan(muls, lambda x, y: x * y)), (n, at)
+
+
 ALL_CASES = [v for k, v in sorted(globals().items()) if k.startswith("case_")]

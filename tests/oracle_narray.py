@@ -229,6 +229,13 @@ class ONArray:
         lo, hi = orc.reduce("minmax", self.a, axis=axis, nan=nan, keepdims=keepdims)
         return self._wrap(lo), self._wrap(hi)
 
+    def cumsum(self, axis=None, nan=False): return self._wrap(orc.cum("cumsum", self.a, axis, nan))
+    def cumprod(self, axis=None, nan=False): return self._wrap(orc.cum("cumprod", self.a, axis, nan))
+
+    def bincount(self, weight=None, minlength=0):
+        w = weight.a if isinstance(weight, ONArray) else weight
+        return self._wrap(orc.bincount(self.a, w, minlength))
+
     def arg_with_value(self, op, axis=None, nan=False):
         """(index as Int64, value): the index reduction and the matching extreme, two oracle calls."""
         idx = OracleXP.Int64.cast(self._reduce(op, axis, False, nan))
@@ -262,6 +269,10 @@ class OInt64(ONArray):
 
 class OUInt64(ONArray):
     np_dtype = np.uint64
+
+
+class OUInt32(ONArray):
+    np_dtype = np.uint32
 
 
 class OBit:
@@ -316,7 +327,7 @@ class OBit:
 
 
 _BY_DTYPE = {np.dtype(np.float32): OSFloat, np.dtype(np.float64): ODFloat, np.dtype(np.int32): OInt32,
-             np.dtype(np.int64): OInt64, np.dtype(np.uint64): OUInt64}
+             np.dtype(np.int64): OInt64, np.dtype(np.uint64): OUInt64, np.dtype(np.uint32): OUInt32}
 
 
 def _upcast(ta, tb):
@@ -349,7 +360,7 @@ class _ONMath:
 
 class OracleXP:
     """Namespace with the same names as the cumo_b200 package."""
-    SFloat, DFloat, Int32, Int64, UInt64, Bit = OSFloat, ODFloat, OInt32, OInt64, OUInt64, OBit
+    SFloat, DFloat, Int32, Int64, UInt64, UInt32, Bit = OSFloat, ODFloat, OInt32, OInt64, OUInt64, OUInt32, OBit
     NMath = _ONMath()
     ShapeError = ShapeErrorO
     name = "oracle"

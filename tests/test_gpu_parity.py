@@ -356,6 +356,83 @@ def test_index_reduction_with_value(xp_gpu, tname, shape):
                 same(gv, ov)
 
 
+@pytest.mark.parametrize("tname", list(NP))
+@pytest.mark.parametrize("n", [1, 15, 16, 17, 4095, 4096, 4097, 100_003, (1 << 24) + 5])
+def test_cumsum_cumprod_1d(xp_gpu, tname, n):
+    rng = np.random.default_rng(n)
+    if tname in FLOATS:
+        host = rng.integers(-3, 4, n).astype(NP[tname])            # small integers: float sums stay exact in any association
+        hostp = np.where(rng.integers(0, 2, n) == 0, 2.0, 0.5).astype(NP[tname])
+    else:
+        host = rng.integers(-(1 << 30), 1 << 30, n).astype(NP[tname])    # sums and products wrap: must wrap identically
+        hostp = rng.integers(-3, 4, n).astype(NP[tname])
+    g, o = both(xp_gpu, tname, host)
+    same(g.cumsum(), o.cumsum())
+    gp, op_ = both(xp_gpu, tname, hostp)
+    same(gp.cumprod(), op_.cumprod())
+    if n > 64 and n < (1 << 22):
+        same(g[3:-5].cumsum(), o[3:-5].cumsum())
+        same(g[::3].cumsum(), o[::3].cumsum())
+        same(g[::-1].cumsum(), o[::-1].cumsum())
+    if tname in FLOATS and n > 16:
+        hn = host.copy()
+        hn[[0, n // 2, n - 1]] = np.nan
+        hn[5] = -0.0
+        gn, on = both(xp_gpu, tname, hn)
+        same(gn.cumsum(), on.cumsum())
+        same(gn.cumsum(nan=True), on.cumsum(nan=True))
+        same(gn.cumprod(nan=True), on.cumprod(nan=True))
+        hz = np.full(min(n, 5000), -0.0, dtype=NP[tname])
+        gz, oz = both(xp_gpu, tname, hz)
+        assert np.array_equal(np.signbit(gz.cumsum().to_numpy()), np.signbit(oz.cumsum().to_numpy()))   # -0.0 stays -0.0
+
+
+@pytest.mark.parametrize("tname", ["SFloat", "Int64"])
+def test_cumsum_along_axes_and_random_floats(xp_gpu, tname):
+    rng = np.random.default_rng(2)
+    host = rng.integers(-5, 6, (37, 5000)).astype(NP[tname])
+    g, o = both(xp_gpu, tname, host)
+    same(g.cumsum(axis=1), o.cumsum(axis=1))
+    same(g[:, :300].cumsum(axis=0), o[:, :300].cumsum(axis=0))
+    same(g.cumsum(), o.cumsum())
+    same(g.transpose().cumsum(), o.transpose().cumsum())            # not one strided run: goes through a copy
+    if tname == "SFloat":
+        hf = rng.uniform(0, 1, 1 << 20).astype(np.float32)
+        got = xp_gpu.SFloat.from_numpy(hf).cumsum().to_numpy().astype(np.float64)
+        want = np.cumsum(hf.astype(np.float64))
+        assert np.all(np.abs(got - want) <= 1e-5 * want)
+
+
+@pytest.mark.parametrize("tname", INTS)
+@pytest.mark.parametrize("n,bins", [(1, 1), (1000, 7), (100_003, 256), (300_000, 8192), (300_000, 8193), (50_000, 100_000)])
+def test_bincount_counts_and_weights(xp_gpu, tname, n, bins):
+    rng = np.random.default_rng(n + bins)
+    host = rng.integers(0, bins, n).astype(NP[tname])
+    host[rng.integers(0, n)] = bins - 1
+    g, o = both(xp_gpu, tname, host)
+    same(g.bincount(), o.bincount())
+    same(g.bincount(minlength=bins + 5), o.bincount(minlength=bins + 5))
+    same(g[::3].bincount(), o[::3].bincount())                                   # a strided run
+    for wt, tol in (("SFloat", 1e-5), ("DFloat", 1e-12)):
+        hw = rng.uniform(0, 1, n).astype(NP[wt])
+        gw, ow = both(xp_gpu, wt, hw)
+        got, want = g.bincount(gw).to_numpy(), o.bincount(ow).to_numpy()
+        assert got.dtype == want.dtype and got.shape == want.shape
+        exact = np.bincount(host.astype(np.int64), weights=hw.astype(np.float64), minlength=bins)
+        assert np.all(np.abs(got - exact) <= tol * np.maximum(1.0, np.bincount(host.astype(np.int64), minlength=bins)))
+    if n > 10:
+        rows = host[: n // 4 * 4].reshape(4, -1)
+        g2, o2 = both(xp_gpu, tname, rows)
+        same(g2.bincount(), o2.bincount())                                          # one launch per leading index
+
+
+def test_bincount_rejects_negative_items(xp_gpu):
+    with pytest.raises(ValueError):
+        xp_gpu.Int32.from_numpy(np.array([0, 5, -1, 2], dtype=np.int32)).bincount()
+    with pytest.raises(AttributeError):
+        xp_gpu.SFloat.from_numpy(np.array([0, 1], dtype=np.float32)).bincount()
+
+
 def extreme_fills(tname):
     if tname in FLOATS:
         return {"all_nan": np.nan, "all_neg_inf": -np.inf, "all_pos_inf": np.inf, "all_zero": 0.0}

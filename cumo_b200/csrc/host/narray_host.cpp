@@ -843,6 +843,49 @@ int cb200_na_minmax(cb200_na_t* a, uint32_t axis_mask, int keepdims, int nan, cb
     return 0;
 }
 
+// ---- Bit#where -----------------------------------------------------------------------------
+cb200_na_t* cb200_na_where(cb200_na_t* a, int want_zeros) {
+    if (a->dtype != CB200_BIT) return (cb200_na*)fail("TypeError", "where needs a Bit array");
+    const int64_t size = size_of(a);
+    // the number of hits sizes the result: one read-back
+    int64_t hits = 0;
+    if (size > 0) {
+        cb200_na* c = cb200_na_count(a, 0, 0, want_zeros);
+        if (!c) return nullptr;
+        uint64_t v = 0;
+        const bool ok = cb200_na_read_host(c, &v, 8) == 0;
+        cb200_na_release(c);
+        if (!ok) return nullptr;
+        hits = (int64_t)v;
+    }
+    const int out_dtype = (uint64_t)size > 4294967295ull ? CB200_INT64 : CB200_INT32;
+    cb200_na* out = make(out_dtype, 1, &hits, false);
+    if (!out || hits == 0) return out;
+    using FnNew = char* (*)();
+    using FnRun = void (*)(CUMO_BIT_DIGIT*, size_t, ssize_t, size_t*, uint64_t, int, char*, size_t, uint64_t, char*);
+    FnNew fnew = (FnNew)sym("cumo_bit_where_scratch_new");
+    FnRun frun = (FnRun)sym("cumo_bit_where_kernel_launch");
+    char* scratch = fnew && frun ? fnew() : nullptr;
+    if (!scratch) { cb200_na_release(out); if (fnew && frun) fail("CudaError", "no memory for the where scratch"); return nullptr; }
+    // FULL_LOOP: merge what merges, then one launch per run of the innermost dim left
+    StrideLoop L;
+    L.nd = a->ndim;
+    for (int i = 0; i < a->ndim; ++i) { L.n[i] = a->shape[i]; L.s[0][i] = a->step[i]; }
+    if (L.nd == 0) { L.nd = 1; L.n[0] = 1; L.s[0][0] = 0; }
+    contract(&L, 1);
+    const int in = L.nd - 1;
+    uint64_t count = 0;
+    CUMO_BIT_DIGIT* words = reinterpret_cast<CUMO_BIT_DIGIT*>(a->st->ptr);
+    for_outer(L, 1, [&](const int64_t* off) {
+        frun(words, (size_t)(a->offset + off[0]), (ssize_t)L.s[0][in], nullptr, (uint64_t)L.n[in], want_zeros, data_ptr(out),
+             out_dtype == CB200_INT64 ? 8 : 4, count, scratch);
+        count += (uint64_t)L.n[in];
+    });
+    cumo_cuda_runtime_free(scratch);
+    if (!launch_ok()) { cb200_na_release(out); return nullptr; }
+    return out;
+}
+
 // ---- cumsum / cumprod ----------------------------------------------------------------------
 cb200_na_t* cb200_na_cum(const char* op_c, cb200_na_t* a, int axis, int nan) {
     std::string op = op_c;

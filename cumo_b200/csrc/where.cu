@@ -1,0 +1,206 @@
+// Bit#where / where2: the positions of the one (or, inverted, zero) bits of a run, ascending.
+//
+// Entry points and protocol are the reference's (narray/gen/tmpl_bit/where.c:11-12 declares
+// them, where_kernel.cu:83-110 defines them): the host allocates `scratch` once per call with
+// cumo_bit_where_scratch_new(), then launches once per run of the array; a cursor inside the
+// scratch (one for ones, one for zeros) carries the output position from one launch to the next
+// on the device, so nothing is read back.  Position i of a run is reported as `count + i`.
+//
+// Plan: a "chunk" is 32 consecutive elements of the run gathered into one word (two loads and a
+// funnel shift when the run is contiguous, 32 single-bit loads otherwise).  A tile is 256 threads
+// x 4 consecutive chunks.  (1) every CTA counts the hits of its tiles, (2) one CTA turns the
+// counts into output positions and advances the cursor, (3) every CTA gathers its chunks again,
+// scans its threads' counts and writes the positions.  The reference caps the grid at 1024
+// blocks; here it grows with the run up to 65536 CTAs.
+#include "common.cuh"
+
+namespace cb200 {
+
+constexpr int kWhereChunksPerThread = 4;
+constexpr int kWhereTileChunks = kBlock * kWhereChunksPerThread;        // 1024 chunks = 32768 elements
+constexpr int kWhereMaxCtas = 65536;
+
+struct WhereRun {
+    const uint32_t* words;
+    uint64_t p;            // bit position of element 0
+    int64_t s;             // bit step
+    const size_t* idx;     // or bit offsets
+    uint64_t n;            // elements
+    uint64_t n_chunks;
+    int contiguous;
+    int invert;
+};
+
+// elements [32c, 32c+32) of the run as a word, zero past the end
+__device__ __forceinline__ uint32_t where_chunk(const WhereRun& r, uint64_t c) {
+    const uint64_t e0 = c * 32;
+    if (e0 >= r.n) return 0;
+    uint32_t z;
+    if (r.contiguous) {
+        const uint64_t b = r.p + e0;
+        const uint64_t w = b >> 5;
+        const uint32_t sh = (uint32_t)(b & 31);
+        const uint32_t lo = r.words[w];
+        // the second word exists only if the chunk really reaches into it
+        const uint64_t last_bit = r.p + (e0 + 32 <= r.n ? e0 + 31 : r.n - 1);
+        const uint32_t hi = (sh != 0 && (last_bit >> 5) > w) ? r.words[w + 1] : 0u;
+        z = __funnelshift_r(lo, hi, sh);
+    } else {
+        z = 0;
+        const uint32_t m = r.n - e0 < 32 ? (uint32_t)(r.n - e0) : 32u;
+        for (uint32_t k = 0; k < m; ++k) {
+            const uint64_t b = r.idx ? r.p + r.idx[e0 + k] : r.p + (uint64_t)((int64_t)(e0 + k) * r.s);
+            z |= ((r.words[b >> 5] >> (b & 31)) & 1u) << k;
+        }
+    }
+    if (r.invert) z = ~z;
+    if (r.n - e0 < 32) z &= (1u << (uint32_t)(r.n - e0)) - 1u;
+    return z;
+}
+
+// exclusive scan of one count per thread over the CTA, thread order; *total = the CTA's sum
+__device__ __forceinline__ uint32_t block_exscan(uint32_t v, uint32_t* total, uint32_t* smem /* [warps + 1] */) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    uint32_t inc = v;
+#pragma unroll
+    for (int d = 1; d < 32; d <<= 1) {
+        const uint32_t o = __shfl_up_sync(0xffffffffu, inc, d);
+        if (lane >= d) inc += o;
+    }
+    if (lane == 31) smem[warp] = inc;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        uint32_t acc = 0;
+        for (int w = 0; w < kWarpsPerBlock; ++w) { const uint32_t t = smem[w]; smem[w] = acc; acc += t; }
+        smem[kWarpsPerBlock] = acc;
+    }
+    __syncthreads();
+    const uint32_t pre = smem[warp] + inc - v;
+    *total = smem[kWarpsPerBlock];
+    __syncthreads();
+    return pre;
+}
+
+__global__ void __launch_bounds__(kBlock)
+where_count_kernel(const WhereRun r, uint64_t tiles_per_cta, uint64_t n_tiles, unsigned long long* cta_sums) {
+    const uint64_t t_begin = blockIdx.x * tiles_per_cta;
+    uint64_t t_end = t_begin + tiles_per_cta; if (t_end > n_tiles) t_end = n_tiles;
+    uint32_t cnt = 0;                          // per thread at most tiles_per_cta * 128: the host keeps that below 2^32
+    for (uint64_t t = t_begin; t < t_end; ++t) {
+        const uint64_t c0 = t * kWhereTileChunks + (uint64_t)threadIdx.x * kWhereChunksPerThread;
+#pragma unroll
+        for (int j = 0; j < kWhereChunksPerThread; ++j) cnt += __popc(where_chunk(r, c0 + j));
+    }
+    // 64-bit CTA total
+    unsigned long long v = cnt;
+#pragma unroll
+    for (int d = 16; d > 0; d >>= 1) v += __shfl_down_sync(0xffffffffu, v, d);
+    __shared__ unsigned long long wsum[kWarpsPerBlock];
+    if ((threadIdx.x & 31) == 0) wsum[threadIdx.x >> 5] = v;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        unsigned long long acc = 0;
+        for (int w = 0; w < kWarpsPerBlock; ++w) acc += wsum[w];
+        cta_sums[blockIdx.x] = acc;
+    }
+}
+
+// cta_sums -> exclusive output positions (cursor included); cursor += everything
+__global__ void __launch_bounds__(1024)
+where_scan_kernel(unsigned long long* cta_sums, uint32_t n_ctas, unsigned long long* running) {
+    __shared__ unsigned long long wsum[33];
+    __shared__ unsigned long long carry_s;
+    if (threadIdx.x == 0) carry_s = *running;
+    __syncthreads();
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    for (uint32_t base = 0; base < n_ctas; base += 1024) {
+        const uint32_t i = base + threadIdx.x;
+        const unsigned long long v = i < n_ctas ? cta_sums[i] : 0ull;
+        unsigned long long inc = v;
+#pragma unroll
+        for (int d = 1; d < 32; d <<= 1) {
+            const unsigned long long o = __shfl_up_sync(0xffffffffu, inc, d);
+            if (lane >= d) inc += o;
+        }
+        if (lane == 31) wsum[warp] = inc;
+        __syncthreads();
+        if (threadIdx.x == 0) {
+            unsigned long long acc = 0;
+            for (int w = 0; w < 32; ++w) { const unsigned long long t = wsum[w]; wsum[w] = acc; acc += t; }
+            wsum[32] = acc;
+        }
+        __syncthreads();
+        const unsigned long long carry = carry_s;
+        if (i < n_ctas) cta_sums[i] = carry + wsum[warp] + inc - v;
+        __syncthreads();
+        if (threadIdx.x == 0) carry_s = carry + wsum[32];
+        __syncthreads();
+    }
+    if (threadIdx.x == 0) *running = carry_s;
+}
+
+template <typename TI>
+__global__ void __launch_bounds__(kBlock)
+where_scatter_kernel(const WhereRun r, uint64_t tiles_per_cta, uint64_t n_tiles, const unsigned long long* __restrict__ cta_pos,
+                     TI* out, uint64_t count) {
+    __shared__ uint32_t smem[kWarpsPerBlock + 1];
+    const uint64_t t_begin = blockIdx.x * tiles_per_cta;
+    uint64_t t_end = t_begin + tiles_per_cta; if (t_end > n_tiles) t_end = n_tiles;
+    unsigned long long off = cta_pos[blockIdx.x];
+    for (uint64_t t = t_begin; t < t_end; ++t) {
+        const uint64_t c0 = t * kWhereTileChunks + (uint64_t)threadIdx.x * kWhereChunksPerThread;
+        uint32_t z[kWhereChunksPerThread];
+        uint32_t mine = 0;
+#pragma unroll
+        for (int j = 0; j < kWhereChunksPerThread; ++j) { z[j] = where_chunk(r, c0 + j); mine += __popc(z[j]); }
+        uint32_t total;
+        const uint32_t pre = block_exscan(mine, &total, smem);
+        unsigned long long o = off + pre;
+#pragma unroll
+        for (int j = 0; j < kWhereChunksPerThread; ++j) {
+            uint32_t w = z[j];
+            const uint64_t e0 = count + (c0 + j) * 32;
+            while (w) {
+                const int k = __ffs(w) - 1;
+                out[o++] = (TI)(e0 + k);
+                w &= w - 1;
+            }
+        }
+        off += total;
+    }
+}
+
+}  // namespace cb200
+
+using namespace cb200;
+
+// scratch: [cursor for ones][cursor for zeros][per-CTA sums x kWhereMaxCtas], cursors cleared
+extern "C" char* cumo_bit_where_scratch_new(void) {
+    char* scratch = cumo_cuda_runtime_malloc((2 + (size_t)kWhereMaxCtas) * sizeof(unsigned long long));
+    if (scratch) cudaMemsetAsync(scratch, 0, 2 * sizeof(unsigned long long), current_stream());
+    cumo_cuda_runtime_check_kernel_launch();
+    return scratch;
+}
+
+extern "C" void cumo_bit_where_kernel_launch(CUMO_BIT_DIGIT* a, size_t p, ssize_t s, size_t* idx, uint64_t n, int invert, char* out,
+                                             size_t elmsz, uint64_t count, char* scratch) {
+    if (n == 0 || !scratch) return;
+    WhereRun r;
+    r.words = a; r.p = p; r.s = s; r.idx = idx; r.n = n;
+    r.n_chunks = (n + 31) / 32;
+    r.contiguous = idx == nullptr && s == 1;
+    r.invert = invert;
+    const uint64_t n_tiles = (r.n_chunks + kWhereTileChunks - 1) / kWhereTileChunks;
+    uint64_t tiles_per_cta = (n_tiles + kWhereMaxCtas - 1) / kWhereMaxCtas;
+    if (tiles_per_cta < 1) tiles_per_cta = 1;
+    const uint32_t n_ctas = (uint32_t)((n_tiles + tiles_per_cta - 1) / tiles_per_cta);
+    unsigned long long* running = reinterpret_cast<unsigned long long*>(scratch) + (invert ? 1 : 0);
+    unsigned long long* cta_sums = reinterpret_cast<unsigned long long*>(scratch) + 2;
+    cudaStream_t st = current_stream();
+    where_count_kernel<<<n_ctas, kBlock, 0, st>>>(r, tiles_per_cta, n_tiles, cta_sums);
+    where_scan_kernel<<<1, 1024, 0, st>>>(cta_sums, n_ctas, running);
+    if (elmsz == 8) where_scatter_kernel<int64_t><<<n_ctas, kBlock, 0, st>>>(r, tiles_per_cta, n_tiles, cta_sums, reinterpret_cast<int64_t*>(out), count);
+    else            where_scatter_kernel<int32_t><<<n_ctas, kBlock, 0, st>>>(r, tiles_per_cta, n_tiles, cta_sums, reinterpret_cast<int32_t*>(out), count);
+    count_launch(3);
+    cumo_cuda_runtime_check_kernel_launch();
+}

@@ -574,6 +574,15 @@ class Bit(NArray):
     def to_a(self):
         return self.to_numpy().astype(np.int64).tolist()
 
+    def where(self):
+        """Ascending row-major positions of the one bits (Int32; Int64 for arrays beyond 2^32-1 elements)."""
+        return NArray._from_handle(_lib.load().cb200_na_where(self._h, 0))
+
+    def where2(self):
+        """(positions of the ones, positions of the zeros)."""
+        lib = _lib.load()
+        return NArray._from_handle(lib.cb200_na_where(self._h, 0)), NArray._from_handle(lib.cb200_na_where(self._h, 1))
+
     def count_true(self, axis=None, keepdims=False):
         return NArray._from_handle(_lib.load().cb200_na_count(self._h, _axis_mask(axis, self.ndim), int(keepdims), 0))
 

@@ -271,6 +271,15 @@ typedef int cb200_cuda_status_t;          /* cudaError_t: an int-sized enum, 0 =
 CB200_DECL_CUM(sfloat, ) CB200_DECL_CUM(dfloat, ) CB200_DECL_CUM(int32, ) CB200_DECL_CUM(int64, )
 CB200_DECL_CUM(sfloat, _nan) CB200_DECL_CUM(dfloat, _nan)
 
+/* Bit#where / where2, reference: gen/tmpl_bit/where.c:11-12, where_kernel.cu:83-110.  One call of
+ * cumo_bit_where_scratch_new() per result (device memory from cumo_cuda_runtime_malloc, freed by the caller with
+ * cumo_cuda_runtime_free), then one launch per run of the Bit array: element i of the run (bit p + i*s of `a`, or
+ * p + idx[i]) that is one (invert: zero) appends `count + i` to `out` (elmsz 4: int32_t, 8: int64_t) at a cursor kept
+ * in the scratch, so successive launches continue where the last one stopped. */
+char* cumo_bit_where_scratch_new(void);
+void cumo_bit_where_kernel_launch(CUMO_BIT_DIGIT* a, size_t p, ssize_t s, size_t* idx, uint64_t n, int invert, char* out,
+                                  size_t elmsz, uint64_t count, char* scratch);
+
 /* kahan_sum exists for the double-precision type only (reference: gen/spec.rb:321-323,
  * float_accum_kernel.cu:196-206). */
 CB200_DECL_ACCUM(dfloat, double, kahan_sum)

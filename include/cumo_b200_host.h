@@ -90,6 +90,10 @@ cb200_na_t* cb200_na_compare_scalar(const char* op, cb200_na_t* a, double sv_f, 
  * method's `nan: true`. */
 cb200_na_t* cb200_na_reduce(const char* op, cb200_na_t* a, uint32_t axis_mask, int keepdims, int nan);
 int cb200_na_minmax(cb200_na_t* a, uint32_t axis_mask, int keepdims, int nan, cb200_na_t** out_min, cb200_na_t** out_max);
+/* Bit#where (want_zeros 0) and the second half of where2 (want_zeros 1): ascending row-major positions of the
+ * one / zero bits as Int32, or Int64 when the array has more than 2^32-1 elements (gen/tmpl_bit/where.c:97-130).
+ * Reads the count back to size the result: synchronises. */
+cb200_na_t* cb200_na_where(cb200_na_t* bits, int want_zeros);
 /* cumsum / cumprod (narray/gen/tmpl/cum.c:41-70): axis < 0 runs over all elements in row-major order, else along
  * that axis; the result has the operand's shape and type.  nan: the NaN-skipping operator (float types). */
 cb200_na_t* cb200_na_cum(const char* op, cb200_na_t* a, int axis, int nan);

@@ -269,6 +269,18 @@ int oracle_cum(int dtype, int prod, int nan, const char* p1, char* p2, int64_t s
     return 0;
 }
 
+/* Bit#where: the host loop of narray/gen/tmpl_bit/where.c:64-86 over elements given one per byte (0 / non-0),
+ * in row-major order: the running element number of every one (invert: zero) bit.  Returns the hit count. */
+int64_t oracle_where(const uint8_t* bits, int64_t n, int invert, int64_t* out) {
+    int64_t hits = 0;
+    for (int64_t count = 0; count < n; ++count) {
+        int x = bits[count] != 0;
+        if (invert) x = !x;
+        if (x) out[hits++] = count;
+    }
+    return hits;
+}
+
 int oracle_threads(void) {
 #ifdef _OPENMP
     return omp_get_max_threads();

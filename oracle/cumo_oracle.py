@@ -220,6 +220,17 @@ def sum_f64ref(a: np.ndarray) -> float:
     return float(lib().oracle_sum_f64ref(DT[a.dtype], a.ctypes.data, a.size))
 
 
+def where(bits: np.ndarray, invert: bool = False) -> np.ndarray:
+    """Row-major positions of the one (invert: zero) elements of a boolean array: int32, int64 beyond 2^32-1 elements."""
+    flat = np.ascontiguousarray(bits, dtype=bool).reshape(-1).view(np.uint8)
+    out = np.empty(flat.size, dtype=np.int64)
+    fn = lib().oracle_where
+    fn.restype = c_int64
+    fn.argtypes = [c_void_p, c_int64, c_int, c_void_p]
+    hits = fn(flat.ctypes.data, flat.size, int(invert), out.ctypes.data)
+    return out[:hits].astype(np.int64 if flat.size > 4294967295 else np.int32)
+
+
 def cum(op: str, a: np.ndarray, axis=None, nan: bool = False) -> np.ndarray:
     """cumsum / cumprod: over all elements in row-major order (axis None) or along one axis."""
     fn = lib().oracle_cum

@@ -352,6 +352,20 @@ def case_bit_counts(xp):
     assert scalar(a.count_false()) == 4
 
 
+# ---- test/bit_test.rb:35-36, 67-68, 161-162 (where / where2 of the 8-bit literal, flat, 2-D and empty) ---------------
+def case_bit_where(xp):
+    src = [0, 1, 1, 0, 1, 0, 0, 1]
+    a = xp.Bit.cast(src)
+    assert a.where().to_a() == [1, 2, 4, 7]
+    assert [x.to_a() for x in a.where2()] == [[1, 2, 4, 7], [0, 3, 5, 6]]
+    b = xp.Bit.cast([[0, 1, 1, 0], [1, 0, 0, 1]])
+    assert b.where().to_a() == [1, 2, 4, 7]
+    assert [x.to_a() for x in b.where2()] == [[1, 2, 4, 7], [0, 3, 5, 6]]
+    e = xp.Bit.cast([])
+    assert e.where().to_a() == []
+    assert [x.to_a() for x in e.where2()] == [[], []]
+
+
 # ---- test/math_test.rb (closeness of NMath functions on small literals) --------------------------------------------
 def case_math_closeness(xp):
     vals = [0.25, 0.5, 1.0, 2.0, 3.5]

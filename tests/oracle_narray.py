@@ -299,6 +299,15 @@ class OBit:
     def to_a(self):
         return self.b.astype(np.int64).tolist()
 
+    def where(self):
+        return ONArray._wrap(orc.where(self.b))
+
+    def where2(self):
+        return ONArray._wrap(orc.where(self.b)), ONArray._wrap(orc.where(self.b, invert=True))
+
+    def __getitem__(self, key):
+        return OBit(self.b[key])
+
     def _count(self, axis, keepdims, want_false):
         nd = self.b.ndim
         axes = tuple(range(nd)) if axis is None else ((axis,) if isinstance(axis, int) else tuple(axis))

@@ -356,6 +356,26 @@ def test_index_reduction_with_value(xp_gpu, tname, shape):
                 same(gv, ov)
 
 
+@pytest.mark.parametrize("n", [1, 31, 32, 33, 1000, 32767, 32768, 32769, 1_000_003, (1 << 25) + 77])
+@pytest.mark.parametrize("density", [0.0, 0.03, 0.5, 1.0])
+def test_bit_where(xp_gpu, n, density):
+    rng = np.random.default_rng(n)
+    host = rng.random(n) < density
+    g, o = xp_gpu.Bit.from_numpy(host), OracleXP.Bit.cast(host)
+    same(g.where(), o.where())
+    ones, zeros = g.where2()
+    o1, o0 = o.where2()
+    same(ones, o1)
+    same(zeros, o0)
+
+
+def test_bit_where_of_a_comparison_and_2d(xp_gpu):
+    rng = np.random.default_rng(1)
+    host = rng.integers(-50, 50, (300, 1000)).astype(np.int32)
+    g = xp_gpu.Int32.from_numpy(host) > 10
+    assert np.array_equal(g.where().to_numpy(), np.flatnonzero(host > 10).astype(np.int32))
+
+
 @pytest.mark.parametrize("tname", list(NP))
 @pytest.mark.parametrize("n", [1, 15, 16, 17, 4095, 4096, 4097, 100_003, (1 << 24) + 5])
 def test_cumsum_cumprod_1d(xp_gpu, tname, n):

@@ -280,6 +280,15 @@ char* cumo_bit_where_scratch_new(void);
 void cumo_bit_where_kernel_launch(CUMO_BIT_DIGIT* a, size_t p, ssize_t s, size_t* idx, uint64_t n, int invert, char* out,
                                   size_t elmsz, uint64_t count, char* scratch);
 
+/* Single-precision matrix product on the tensor cores: C[M,N] = A[M,K] . Bt[N,K]^T, all row-major, leading
+ * dimensions in elements.  Stands where the reference calls cublasSgemm for `a.dot(b)` on 2-D SFloat operands
+ * (ext/cumo/narray/gen/tmpl/gemm.c:252-297); the reference has no kernel-launch entry of its own for it.
+ * TF32 instructions with every operand split in two, fp32 accumulation: fp32-grade results.  K, lda, ldb must be
+ * multiples of 4 and A, Bt 16-byte aligned.  Returns 0, or an error code with the reason in errbuf (1: shape or
+ * alignment, nothing launched; 3/4: launch; 5: an in-kernel bounded wait ran out).  Synchronises the stream. */
+int cb200_sgemm_nt_tc(int64_t M, int64_t N, int64_t K, const float* A, int64_t lda, const float* Bt, int64_t ldb,
+                      float* C, int64_t ldc, char* errbuf, size_t errlen);
+
 /* kahan_sum exists for the double-precision type only (reference: gen/spec.rb:321-323,
  * float_accum_kernel.cu:196-206). */
 CB200_DECL_ACCUM(dfloat, double, kahan_sum)

@@ -281,6 +281,24 @@ int64_t oracle_where(const uint8_t* bits, int64_t n, int invert, int64_t* out) {
     return hits;
 }
 
+/* Reference value for the single-precision matrix product (the reference delegates it to cuBLAS,
+ * narray/gen/tmpl/gemm.c:252-297, so there is no host loop to restate): C = A . Bt^T accumulated in double, plus
+ * the sum of |a||b| per element, which bounds the rounding error of any fp32 summation order. */
+void oracle_gemm_nt_f64(int64_t M, int64_t N, int64_t K, const float* A, const float* Bt, double* C, double* Cabs) {
+#pragma omp parallel for schedule(static)
+    for (int64_t i = 0; i < M; ++i)
+        for (int64_t j = 0; j < N; ++j) {
+            double s = 0, sa = 0;
+            for (int64_t k = 0; k < K; ++k) {
+                double p = (double)A[i * K + k] * (double)Bt[j * K + k];
+                s += p;
+                sa += p < 0 ? -p : p;
+            }
+            C[i * N + j] = s;
+            if (Cabs) Cabs[i * N + j] = sa;
+        }
+}
+
 int oracle_threads(void) {
 #ifdef _OPENMP
     return omp_get_max_threads();

@@ -220,6 +220,21 @@ def sum_f64ref(a: np.ndarray) -> float:
     return float(lib().oracle_sum_f64ref(DT[a.dtype], a.ctypes.data, a.size))
 
 
+def gemm_nt_f64(a: np.ndarray, bt: np.ndarray):
+    """(a . bt^T in float64, sum of |a||b| per element) for float32 a (M, K) and bt (N, K)."""
+    a = np.ascontiguousarray(a, dtype=np.float32)
+    bt = np.ascontiguousarray(bt, dtype=np.float32)
+    m, k = a.shape
+    n = bt.shape[0]
+    c = np.empty((m, n), dtype=np.float64)
+    cabs = np.empty((m, n), dtype=np.float64)
+    fn = lib().oracle_gemm_nt_f64
+    fn.restype = None
+    fn.argtypes = [c_int64, c_int64, c_int64, c_void_p, c_void_p, c_void_p, c_void_p]
+    fn(m, n, k, a.ctypes.data, bt.ctypes.data, c.ctypes.data, cabs.ctypes.data)
+    return c, cabs
+
+
 def where(bits: np.ndarray, invert: bool = False) -> np.ndarray:
     """Row-major positions of the one (invert: zero) elements of a boolean array: int32, int64 beyond 2^32-1 elements."""
     flat = np.ascontiguousarray(bits, dtype=bool).reshape(-1).view(np.uint8)

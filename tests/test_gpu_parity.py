@@ -382,7 +382,7 @@ def test_cumsum_cumprod_1d(xp_gpu, tname, n):
     rng = np.random.default_rng(n)
     if tname in FLOATS:
         host = rng.integers(-3, 4, n).astype(NP[tname])            # small integers: float sums stay exact in any association
-        hostp = np.where(rng.integers(0, 2, n) == 0, 2.0, 0.5).astype(NP[tname])
+        hostp = np.where(np.arange(n) % 4 < 2, 2.0, 0.5).astype(NP[tname])      # products stay within [0.5, 4]: nothing overflows
     else:
         host = rng.integers(-(1 << 30), 1 << 30, n).astype(NP[tname])    # sums and products wrap: must wrap identically
         hostp = rng.integers(-3, 4, n).astype(NP[tname])
@@ -401,7 +401,11 @@ def test_cumsum_cumprod_1d(xp_gpu, tname, n):
         gn, on = both(xp_gpu, tname, hn)
         same(gn.cumsum(), on.cumsum())
         same(gn.cumsum(nan=True), on.cumsum(nan=True))
-        same(gn.cumprod(nan=True), on.cumprod(nan=True))
+        hpn = hostp.copy()
+        hpn[[0, n // 2, n - 1]] = np.nan
+        gpn, opn = both(xp_gpu, tname, hpn)
+        same(gpn.cumprod(), opn.cumprod())
+        same(gpn.cumprod(nan=True), opn.cumprod(nan=True))
         hz = np.full(min(n, 5000), -0.0, dtype=NP[tname])
         gz, oz = both(xp_gpu, tname, hz)
         assert np.array_equal(np.signbit(gz.cumsum().to_numpy()), np.signbit(oz.cumsum().to_numpy()))   # -0.0 stays -0.0

@@ -225,6 +225,13 @@ def kernel_rows(X, arr, S, copies=1):
     im = arr("i32", (ir, ic))
     yield "C4", "max_index(axis:1)", ir * ic * 4 + ir * 4, lambda: im.max_index(axis=1)
     yield "C4", "Int32 sum -> Int64", s + 8, lambda: ia.sum()
+    # F: the rows after the hot path (scan, histogram, compaction), same sizes
+    v32 = arr("f32_01", (n3,))
+    yield "F", "f32 1-D cumsum", 2 * n3 * 4, lambda: v32.cumsum()
+    del v32
+    lab = arr("labels256", (n4,))
+    yield "F", "Int32 bincount (256 bins)", n4 * 4 + 256 * 4, lambda: lab.bincount()
+    yield "F", "Bit where (half set)", n4 // 8 + (n4 // 2) * 4, lambda: mask.where()
 
 
 def kernel_table(torch, xp, peak):
@@ -241,6 +248,8 @@ def kernel_table(torch, xp, peak):
             return xp.SFloat.from_torch(torch.rand(*shape, device="cuda", generator=g))
         if kind == "f64_01":
             return xp.DFloat.from_torch(torch.rand(*shape, device="cuda", dtype=torch.float64, generator=g))
+        if kind == "labels256":
+            return xp.Int32.from_torch(torch.randint(0, 256, shape, device="cuda", dtype=torch.int32, generator=g))
         return xp.Int32.from_torch(torch.randint(-(1 << 20), 1 << 20, shape, device="cuda", dtype=torch.int32, generator=g))
 
     sys.path.insert(0, str(ROOT / "tests"))
@@ -258,6 +267,8 @@ def kernel_table(torch, xp, peak):
             return ox.SFloat.cast(rng.random(shape, dtype=np.float32))
         if kind == "f64_01":
             return ox.DFloat.cast(rng.random(shape))
+        if kind == "labels256":
+            return ox.Int32.cast(rng.integers(0, 256, shape, dtype=np.int32))
         return ox.Int32.cast(rng.integers(-(1 << 20), 1 << 20, shape, dtype=np.int32))
 
     cpu = {}
@@ -312,6 +323,21 @@ def kernel_table(torch, xp, peak):
         if algo == "tensor":
             row["TFLOPs_issued_tf32"] = round(3 * row["TFLOPs"], 1)
         rows.append(row)
+    # single-precision matrix product on the tensor cores (`dot`): TFLOP/s, beside torch's fp32 (non-TF32) cuBLAS product
+    from cumo_b200 import linalg
+    del px, pc, pts
+    gm = 8192
+    ga = torch.randn(gm, gm, device="cuda", generator=g)
+    gb = torch.randn(gm, gm, device="cuda", generator=g)
+    xa, xb = xp.SFloat.from_torch(ga), xp.SFloat.from_torch(gb)
+    med, best = time_kernel(torch, lambda: linalg.gemm_nt(xa, xb), reps=10)
+    torch.backends.cuda.matmul.allow_tf32 = False
+    med_lib, _ = time_kernel(torch, lambda: ga @ gb.T, reps=5)
+    nbytes = 3 * gm * gm * 4
+    rows.append({"config": "F", "kernel": "SFloat dot 8192^3 (tcgen05 3xTF32, K-chunked)", "bytes": nbytes, "ms": round(med, 4), "ms_min": round(best, 4),
+                 "GBps": round(nbytes / (med * 1e-3) / 1e9, 1), "TFLOPs": round(2.0 * gm ** 3 / (med * 1e-3) / 1e12, 1),
+                 "TFLOPs_issued_tf32": round(6.0 * gm ** 3 / (med * 1e-3) / 1e12, 1),
+                 "cublas_fp32_ms": round(med_lib, 4), "cublas_fp32_TFLOPs": round(2.0 * gm ** 3 / (med_lib * 1e-3) / 1e12, 1)})
     return rows
 
 

@@ -53,6 +53,13 @@ def build_cases(xp, torch, mib: int):
         pts = cen[torch.randint(0, k, (n,), device="cuda", generator=g)] + torch.randn(n, d, device="cuda", generator=g)
         return kmeans, xp.SFloat.from_torch(pts), xp.SFloat.from_torch(cen)
 
+    def gemm():
+        from . import linalg
+        m, k, n = max(128, n32 // 4096), 4096, 4096
+        a = xp.SFloat.from_torch(torch.randn(m, k, device="cuda", generator=g))
+        bt = xp.SFloat.from_torch(torch.randn(n, k, device="cuda", generator=g))
+        return linalg, a, bt
+
     cases = {
         # name: (setup -> callable, algorithmic bytes)
         "exp": (lambda: (lambda a=f32(): xp.NMath.exp(a)), 2 * n32 * 4),
@@ -73,6 +80,7 @@ def build_cases(xp, torch, mib: int):
         "gt_scalar_i32": (lambda: (lambda a=i32(): a > 0), n32 * 4 + n32 // 8),
         "count_true": (lambda: (lambda m=(i32() > 0): m.count_true()), n32 // 8),
         "mod_scalar_i32": (lambda: (lambda a=i32(): a % 7), 2 * n32 * 4),
+        "gemm_tc": (lambda: (lambda m=gemm(): m[0].gemm_nt(m[1], m[2])), n32 * 4 + 4096 * 4096 * 4 + n32 * 4),
         "kmeans_tensor": (lambda: (lambda m=km(): m[0].assign(m[1], m[2], algo="tensor")), n32 * 4 + n32 // 16),
         "kmeans_cores": (lambda: (lambda m=km(): m[0].assign(m[1], m[2], algo="cores")), n32 * 4 + n32 // 16),
         "sum_i32": (lambda: (lambda a=i32(): a.sum()), n32 * 4),

@@ -5,7 +5,11 @@
 // (ext/cumo/narray/gen/tmpl/gemm.c:252-297).  It is computed with TF32 tensor-core instructions at
 // fp32-grade accuracy by splitting every operand into a TF32 head and tail and accumulating three
 // products per term (see kmeans_tc.cu, which uses the same scheme); accumulators are fp32 in tensor
-// memory.  Bt is the second operand with its axes swapped: the caller passes `b` itself when it is
+// memory, for at most 512 elements of K at a time: the tensor cores add into the accumulator with
+// truncation, a bias that grows with the length of the chain (measured: 1e-2 absolute on sums of
+// magnitude 300 at K = 4096), so after every 16 K-blocks the epilogue takes the partial product over
+// into C with ordinary rounded fp32 additions and the MMAs start a fresh accumulator.
+// Bt is the second operand with its axes swapped: the caller passes `b` itself when it is
 // already laid out that way (a weight matrix stored [out, in]) or a transposed copy otherwise.
 //
 // One persistent CTA per SM owns 128 x 256 tiles of C, 13 warps:
@@ -27,6 +31,7 @@ namespace cb200 {
 
 constexpr int kGemmM = 128, kGemmN = 256, kGemmKB = 32;
 constexpr int kGemmStages = 2;
+constexpr int kGemmChunkBlocks = 16;                             // K-blocks accumulated in tensor memory before C takes them over
 constexpr int kGemmStageBytes = 2 * (kGemmM + kGemmN) * 128;     // hi + lo of A and Bt rows: 96 KiB
 constexpr int kGemmProducers = 256;                              // threads
 constexpr int kGemmLoads = (kGemmM + kGemmN) * 8 / kGemmProducers;   // 16-byte chunks per producer thread per K-block: 12
@@ -86,38 +91,42 @@ sgemm_nt_tc_kernel(const float* __restrict__ A, int64_t lda, const float* __rest
             // M = 128, N = 256, TF32 x TF32 -> F32, both operands K-major
             const uint32_t idesc = (1u << 4) | (2u << 7) | (2u << 10) | ((uint32_t)(kGemmN >> 3) << 17) | ((uint32_t)(kGemmM >> 4) << 24);
             uint32_t it = 0;                      // K-blocks consumed so far
-            for (int64_t t = 0; t < my_tiles; ++t) {
-                const uint32_t acc = (uint32_t)(t & 1);
-                if (!mbar_wait(acc_empty + acc, ((uint32_t)(t >> 1) & 1u) ^ 1u, abort_flag)) break;
-                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                const uint32_t d_tmem = tmem_base + acc * 256u;
-                bool ok = true;
-                for (uint32_t kb = 0; kb < KB; ++kb, ++it) {
-                    const uint32_t slot = it % kGemmStages;
-                    if (!mbar_wait(slot_full + slot, (it / kGemmStages) & 1u, abort_flag)) { ok = false; break; }
+            uint32_t item = 0;                    // (tile, K-chunk) pairs issued so far: each gets an accumulator of its own
+            bool ok = true;
+            for (int64_t t = 0; t < my_tiles && ok; ++t) {
+                for (uint32_t kb0 = 0; kb0 < KB && ok; kb0 += kGemmChunkBlocks, ++item) {
+                    const uint32_t acc = item & 1u;
+                    if (!mbar_wait(acc_empty + acc, ((item >> 1) & 1u) ^ 1u, abort_flag)) { ok = false; break; }
                     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                    const uint32_t a_hi = smem_u32(base + slot * kGemmStageBytes);
-                    const uint32_t a_lo = a_hi + kGemmM * 128u;
-                    const uint32_t b_hi = a_lo + kGemmM * 128u;
-                    const uint32_t b_lo = b_hi + kGemmN * 128u;
+                    const uint32_t d_tmem = tmem_base + acc * 256u;
+                    const uint32_t kb1 = kb0 + kGemmChunkBlocks < KB ? kb0 + kGemmChunkBlocks : KB;
+                    for (uint32_t kb = kb0; kb < kb1; ++kb, ++it) {
+                        const uint32_t slot = it % kGemmStages;
+                        if (!mbar_wait(slot_full + slot, (it / kGemmStages) & 1u, abort_flag)) { ok = false; break; }
+                        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                        const uint32_t a_hi = smem_u32(base + slot * kGemmStageBytes);
+                        const uint32_t a_lo = a_hi + kGemmM * 128u;
+                        const uint32_t b_hi = a_lo + kGemmM * 128u;
+                        const uint32_t b_lo = b_hi + kGemmN * 128u;
 #pragma unroll
-                    for (int term = 0; term < 3; ++term) {
-                        const uint32_t a_addr = term == 1 ? a_lo : a_hi;
-                        const uint32_t b_addr = term == 2 ? b_lo : b_hi;
+                        for (int term = 0; term < 3; ++term) {
+                            const uint32_t a_addr = term == 1 ? a_lo : a_hi;
+                            const uint32_t b_addr = term == 2 ? b_lo : b_hi;
 #pragma unroll
-                        for (int ks = 0; ks < 4; ++ks) {          // 8 TF32 (32 bytes) of K per instruction
-                            const uint64_t da = umma_desc(a_addr + ks * 32u), db = umma_desc(b_addr + ks * 32u);
-                            const uint32_t accumulate = (kb | (uint32_t)term | (uint32_t)ks) != 0;
-                            asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
-                                         "tcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, p;\n\t}"
-                                         ::"r"(d_tmem), "l"(da), "l"(db), "r"(idesc), "r"(accumulate) : "memory");
+                            for (int ks = 0; ks < 4; ++ks) {          // 8 TF32 (32 bytes) of K per instruction
+                                const uint64_t da = umma_desc(a_addr + ks * 32u), db = umma_desc(b_addr + ks * 32u);
+                                const uint32_t accumulate = ((kb - kb0) | (uint32_t)term | (uint32_t)ks) != 0;
+                                asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+                                             "tcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, p;\n\t}"
+                                             ::"r"(d_tmem), "l"(da), "l"(db), "r"(idesc), "r"(accumulate) : "memory");
+                            }
                         }
+                        // the stage is free again once these MMAs have read it
+                        asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(slot_empty + slot)) : "memory");
                     }
-                    // the stage is free again once these MMAs have read it
-                    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(slot_empty + slot)) : "memory");
+                    if (!ok) break;
+                    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(acc_full + acc)) : "memory");
                 }
-                if (!ok) break;
-                asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(acc_full + acc)) : "memory");
             }
             // whatever happened above, let the MMAs already issued finish before tensor memory is freed (bounded, like every wait)
             asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(drain)) : "memory");
@@ -171,46 +180,54 @@ sgemm_nt_tc_kernel(const float* __restrict__ A, int64_t lda, const float* __rest
         // ---- epilogue: one row of C (one tensor-memory lane) per thread ------------------------
         const uint32_t quarter = (uint32_t)(warp & 3);             // the lanes this warp may read
         const int row = (int)quarter * 32 + lane;
-        for (int64_t t = 0; t < my_tiles; ++t) {
-            const uint32_t acc = (uint32_t)(t & 1);
-            // tcgen05.ld is warp-collective: the warp leaves together or not at all
-            if (!__all_sync(0xffffffffu, mbar_wait(acc_full + acc, (uint32_t)(t >> 1) & 1u, abort_flag))) break;
-            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        uint32_t item = 0;
+        bool ok = true;
+        for (int64_t t = 0; t < my_tiles && ok; ++t) {
             int64_t m0, n0;
             tile_of(t, &m0, &n0);
-            const uint32_t taddr = tmem_base + acc * 256u + ((quarter * 32u) << 16);
             float* crow = C + (m0 + row) * ldc + n0;
             const bool row_ok = m0 + row < M;
             const bool vec_ok = ((reinterpret_cast<uintptr_t>(crow) & 15) == 0);
-            uint32_t ra[16], rb[16];
-            auto put16 = [&](int c0, const uint32_t (&r)[16]) {
-                if (!row_ok) return;
-                if (vec_ok && n0 + c0 + 16 <= N) {
+            for (uint32_t kb0 = 0; kb0 < KB; kb0 += kGemmChunkBlocks, ++item) {
+                const uint32_t acc = item & 1u;
+                // tcgen05.ld is warp-collective: the warp leaves together or not at all
+                if (!__all_sync(0xffffffffu, mbar_wait(acc_full + acc, (item >> 1) & 1u, abort_flag))) { ok = false; break; }
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                const uint32_t taddr = tmem_base + acc * 256u + ((quarter * 32u) << 16);
+                const bool add = kb0 > 0;             // later K-chunks are added to what C already holds, rounded to nearest
+                uint32_t ra[16], rb[16];
+                auto put16 = [&](int c0, const uint32_t (&r)[16]) {
+                    if (!row_ok) return;
+                    if (vec_ok && n0 + c0 + 16 <= N) {
 #pragma unroll
-                    for (int q = 0; q < 4; ++q)
-                        __stcs(reinterpret_cast<float4*>(crow + c0) + q,
-                               make_float4(__uint_as_float(r[4 * q]), __uint_as_float(r[4 * q + 1]), __uint_as_float(r[4 * q + 2]), __uint_as_float(r[4 * q + 3])));
-                } else {
+                        for (int q = 0; q < 4; ++q) {
+                            float4 v = make_float4(__uint_as_float(r[4 * q]), __uint_as_float(r[4 * q + 1]), __uint_as_float(r[4 * q + 2]), __uint_as_float(r[4 * q + 3]));
+                            float4* dst = reinterpret_cast<float4*>(crow + c0) + q;
+                            if (add) { const float4 o = *dst; v.x += o.x; v.y += o.y; v.z += o.z; v.w += o.w; }
+                            *dst = v;
+                        }
+                    } else {
 #pragma unroll
-                    for (int j = 0; j < 16; ++j)
-                        if (n0 + c0 + j < N) crow[c0 + j] = __uint_as_float(r[j]);
-                }
-            };
-            constexpr int n_chunks = kGemmN / 16;
-            tmem_ld16(taddr, ra);
-            tmem_ld_wait(ra);
+                        for (int j = 0; j < 16; ++j)
+                            if (n0 + c0 + j < N) crow[c0 + j] = add ? crow[c0 + j] + __uint_as_float(r[j]) : __uint_as_float(r[j]);
+                    }
+                };
+                constexpr int n_chunks = kGemmN / 16;
+                tmem_ld16(taddr, ra);
+                tmem_ld_wait(ra);
 #pragma unroll 1
-            for (int chn = 0; chn < n_chunks; chn += 2) {
-                tmem_ld16(taddr + (uint32_t)(chn + 1) * 16u, rb);
-                put16(chn * 16, ra);
-                tmem_ld_wait(rb);
-                if (chn + 2 < n_chunks) tmem_ld16(taddr + (uint32_t)(chn + 2) * 16u, ra);
-                put16((chn + 1) * 16, rb);
-                if (chn + 2 < n_chunks) tmem_ld_wait(ra);
+                for (int chn = 0; chn < n_chunks; chn += 2) {
+                    tmem_ld16(taddr + (uint32_t)(chn + 1) * 16u, rb);
+                    put16(chn * 16, ra);
+                    tmem_ld_wait(rb);
+                    if (chn + 2 < n_chunks) tmem_ld16(taddr + (uint32_t)(chn + 2) * 16u, ra);
+                    put16((chn + 1) * 16, rb);
+                    if (chn + 2 < n_chunks) tmem_ld_wait(ra);
+                }
+                // the accumulator may be overwritten now
+                asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+                mbar_arrive(acc_empty + acc);
             }
-            // the accumulator may be overwritten now
-            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-            mbar_arrive(acc_empty + acc);
         }
     }
 

@@ -15,7 +15,7 @@ TOL = 2e-6
 
 
 @pytest.mark.parametrize("m,n,k", [(1, 1, 4), (128, 256, 32), (127, 255, 36), (129, 257, 64), (300, 520, 100), (1000, 700, 512),
-                                   (64, 3000, 256), (4096, 256, 64), (150 * 128, 256, 32)])
+                                   (64, 3000, 256), (4096, 256, 64), (150 * 128, 256, 32), (256, 512, 4096), (100, 300, 8200)])
 def test_gemm_nt_matches_float64(xp_gpu, m, n, k):
     from cumo_b200 import linalg
 

@@ -80,6 +80,9 @@ def build_cases(xp, torch, mib: int):
         "gt_scalar_i32": (lambda: (lambda a=i32(): a > 0), n32 * 4 + n32 // 8),
         "count_true": (lambda: (lambda m=(i32() > 0): m.count_true()), n32 // 8),
         "mod_scalar_i32": (lambda: (lambda a=i32(): a % 7), 2 * n32 * 4),
+        "cumsum_f32": (lambda: (lambda a=f32(): a.cumsum()), 2 * n32 * 4),
+        "bincount_i32": (lambda: (lambda a=xp.Int32.from_torch(torch.randint(0, 256, (rows32 * cols,), device="cuda", dtype=torch.int32, generator=g)): a.bincount()), n32 * 4 + 1024),
+        "where_bits": (lambda: (lambda m=(i32() > 0): m.where()), n32 // 8 + (n32 // 2) * 4),
         "gemm_tc": (lambda: (lambda m=gemm(): m[0].gemm_nt(m[1], m[2])), n32 * 4 + 4096 * 4096 * 4 + n32 * 4),
         "kmeans_tensor": (lambda: (lambda m=km(): m[0].assign(m[1], m[2], algo="tensor")), n32 * 4 + n32 // 16),
         "kmeans_cores": (lambda: (lambda m=km(): m[0].assign(m[1], m[2], algo="cores")), n32 * 4 + n32 // 16),

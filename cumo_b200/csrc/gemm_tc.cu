@@ -26,6 +26,7 @@
 #include "tc_common.cuh"
 
 #include <cstdio>
+#include <mutex>
 
 namespace cb200 {
 
@@ -196,15 +197,21 @@ sgemm_nt_tc_kernel(const float* __restrict__ A, int64_t lda, const float* __rest
                 const uint32_t taddr = tmem_base + acc * 256u + ((quarter * 32u) << 16);
                 const bool add = kb0 > 0;             // later K-chunks are added to what C already holds, rounded to nearest
                 uint32_t ra[16], rb[16];
-                auto put16 = [&](int c0, const uint32_t (&r)[16]) {
+                // what C holds so far for 16 columns, requested a step ahead so that the round trip overlaps the step before
+                float4 oa[4], ob[4];
+                auto fetch16 = [&](int c0, float4 (&o)[4]) {
+                    if (!(add && row_ok && vec_ok && n0 + c0 + 16 <= N)) return;
+#pragma unroll
+                    for (int q = 0; q < 4; ++q) o[q] = *(reinterpret_cast<const float4*>(crow + c0) + q);
+                };
+                auto put16 = [&](int c0, const uint32_t (&r)[16], const float4 (&o)[4]) {
                     if (!row_ok) return;
                     if (vec_ok && n0 + c0 + 16 <= N) {
 #pragma unroll
                         for (int q = 0; q < 4; ++q) {
                             float4 v = make_float4(__uint_as_float(r[4 * q]), __uint_as_float(r[4 * q + 1]), __uint_as_float(r[4 * q + 2]), __uint_as_float(r[4 * q + 3]));
-                            float4* dst = reinterpret_cast<float4*>(crow + c0) + q;
-                            if (add) { const float4 o = *dst; v.x += o.x; v.y += o.y; v.z += o.z; v.w += o.w; }
-                            *dst = v;
+                            if (add) { v.x += o[q].x; v.y += o[q].y; v.z += o[q].z; v.w += o[q].w; }
+                            *(reinterpret_cast<float4*>(crow + c0) + q) = v;
                         }
                     } else {
 #pragma unroll
@@ -213,15 +220,17 @@ sgemm_nt_tc_kernel(const float* __restrict__ A, int64_t lda, const float* __rest
                     }
                 };
                 constexpr int n_chunks = kGemmN / 16;
+                fetch16(0, oa);
                 tmem_ld16(taddr, ra);
                 tmem_ld_wait(ra);
 #pragma unroll 1
                 for (int chn = 0; chn < n_chunks; chn += 2) {
                     tmem_ld16(taddr + (uint32_t)(chn + 1) * 16u, rb);
-                    put16(chn * 16, ra);
+                    fetch16((chn + 1) * 16, ob);
+                    put16(chn * 16, ra, oa);
                     tmem_ld_wait(rb);
-                    if (chn + 2 < n_chunks) tmem_ld16(taddr + (uint32_t)(chn + 2) * 16u, ra);
-                    put16((chn + 1) * 16, rb);
+                    if (chn + 2 < n_chunks) { tmem_ld16(taddr + (uint32_t)(chn + 2) * 16u, ra); fetch16((chn + 2) * 16, oa); }
+                    put16((chn + 1) * 16, rb, ob);
                     if (chn + 2 < n_chunks) tmem_ld_wait(ra);
                 }
                 // the accumulator may be overwritten now
@@ -261,6 +270,9 @@ extern "C" int cb200_sgemm_nt_tc(int64_t M, int64_t N, int64_t K, const float* A
         return 1;
     }
     const size_t smem = (size_t)kGemmStages * kGemmStageBytes + 9 * 8 + 16;
+    // one call at a time per process: the error word is per device, and the call ends with a read-back anyway
+    static std::mutex call_mutex;
+    std::lock_guard<std::mutex> lock(call_mutex);
     struct PerDevice { bool ready; int* error_word; };
     static PerDevice dev_state[64] = {};
     int dev = 0;

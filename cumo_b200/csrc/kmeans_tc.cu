@@ -27,6 +27,7 @@
 #include "tc_common.cuh"
 
 #include <cstdio>
+#include <mutex>
 
 namespace cb200 {
 
@@ -272,6 +273,9 @@ extern "C" int cb200_kmeans_assign_sfloat_tc(const float* x, int64_t n, int d, c
         snprintf(errbuf, errlen, "kmeans_assign_tc: K=%d x D=%d needs %zu bytes of shared memory (limit %d)", k, d, smem, 227 * 1024);
         return 2;
     }
+    // one call at a time per process: the error word is per device, and the call ends with a read-back anyway
+    static std::mutex call_mutex;
+    std::lock_guard<std::mutex> lock(call_mutex);
     struct PerDevice { bool ready; int* error_word; };
     static PerDevice dev_state[64] = {};
     int dev = 0;

@@ -4,7 +4,8 @@
 // them, bincount_kernel.cu:32-97 defines them): the output is cleared, then every element x of
 // the run adds 1 (or its weight) to out[x]; an element outside [0, n) raises `*oor`, leaves its
 // value in `*item` and is skipped.  The reference does one global atomicAdd per element.  Here a
-// CTA counts into a private histogram in shared memory (up to kSmemBins bins), reading the run
+// CTA counts into private histograms in shared memory (up to kSmemBins bins; several copies picked
+// by lane when the bins are few, so that equal values within a warp collide less), reading the run
 // with 16-byte loads when it is contiguous, and adds each non-empty bin to the output once, so
 // global atomics drop from one per element to one per (CTA, occupied bin).  Integer counts are
 // exact in any order; weighted sums use floating-point atomics, as in the reference, so their
@@ -34,22 +35,24 @@ __device__ __forceinline__ TI load_item(const char* p1, int64_t s1, const size_t
 template <typename TI, typename TC, typename TW, bool SMEM>
 __global__ void __launch_bounds__(kBlock)
 bincount_kernel(const char* __restrict__ p1, int64_t s1, const size_t* __restrict__ idx1, uint64_t count,
-                const char* __restrict__ pw, int64_t sw, char* out, int64_t so, uint64_t n, int* oor, size_t* item) {
+                const char* __restrict__ pw, int64_t sw, char* out, int64_t so, uint64_t n, int copies, int* oor, size_t* item) {
     constexpr bool WEIGHTED = !std::is_same<TW, void>::value;
     using TS = typename std::conditional<WEIGHTED, TC, uint32_t>::type;
     extern __shared__ __align__(16) char smem_raw[];
     TS* hist = reinterpret_cast<TS*>(smem_raw);
+    // `copies` private histograms, picked by lane: threads of a warp that meet the same value collide less often
+    TS* my_hist = hist + (size_t)(threadIdx.x % copies) * n;
     if (SMEM) {
-        for (uint32_t b = threadIdx.x; b < n; b += kBlock) hist[b] = TS(0);
+        for (uint32_t b = threadIdx.x; b < n * copies; b += kBlock) hist[b] = TS(0);
         __syncthreads();
     }
     auto add = [&](TI x, uint64_t i) {
         if (x < 0 || (uint64_t)x >= n) { *item = (size_t)x; *oor = 1; return; }     // any offender will do: the stores race harmlessly
         if constexpr (WEIGHTED) {
             const TC w = (TC)*reinterpret_cast<const typename std::conditional<WEIGHTED, TW, float>::type*>(pw + (int64_t)i * sw);
-            if (SMEM) atomicAdd(hist + x, w); else atomicAdd(reinterpret_cast<TC*>(out + (int64_t)x * so), w);
+            if (SMEM) atomicAdd(my_hist + x, w); else atomicAdd(reinterpret_cast<TC*>(out + (int64_t)x * so), w);
         } else {
-            if (SMEM) atomicAdd(hist + x, 1u);
+            if (SMEM) atomicAdd(my_hist + x, 1u);
             else atomicAdd(reinterpret_cast<typename std::conditional<sizeof(TC) == 8, unsigned long long, unsigned>::type*>(out + (int64_t)x * so), 1);
         }
     };
@@ -77,7 +80,8 @@ bincount_kernel(const char* __restrict__ p1, int64_t s1, const size_t* __restric
     if (SMEM) {
         __syncthreads();
         for (uint32_t b = threadIdx.x; b < n; b += kBlock) {
-            const TS c = hist[b];
+            TS c = hist[b];
+            for (int r = 1; r < copies; ++r) c += hist[(size_t)r * n + b];
             if (c != TS(0)) {
                 if constexpr (WEIGHTED) atomicAdd(reinterpret_cast<TC*>(out + (int64_t)b * so), c);
                 else atomicAdd(reinterpret_cast<typename std::conditional<sizeof(TC) == 8, unsigned long long, unsigned>::type*>(out + (int64_t)b * so), c);
@@ -101,12 +105,15 @@ void launch_bincount(char* p1, ssize_t s1, size_t* idx1, uint64_t count, char* p
         const unsigned grid = grid_for((int64_t)((count + per_cta - 1) / per_cta), 8);
         const size_t ts = WEIGHTED ? sizeof(TC) : sizeof(uint32_t);
         if (n <= (uint64_t)kSmemBins) {
-            const size_t smem = (size_t)n * ts;
+            int copies = (int)(kSmemBins / n);           // as many private histograms as fit the budget, at most 8
+            if (copies > 8) copies = 8;
+            if (copies < 1) copies = 1;
+            const size_t smem = (size_t)n * copies * ts;
             if (smem > 48 * 1024)
                 cudaFuncSetAttribute(bincount_kernel<TI, TC, TW, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)(kSmemBins * sizeof(double)));
-            bincount_kernel<TI, TC, TW, true><<<grid, kBlock, smem, st>>>(p1, s1, idx1, count, pw, sw, out, so, n, oor, item);
+            bincount_kernel<TI, TC, TW, true><<<grid, kBlock, smem, st>>>(p1, s1, idx1, count, pw, sw, out, so, n, copies, oor, item);
         } else {
-            bincount_kernel<TI, TC, TW, false><<<grid, kBlock, 0, st>>>(p1, s1, idx1, count, pw, sw, out, so, n, oor, item);
+            bincount_kernel<TI, TC, TW, false><<<grid, kBlock, 0, st>>>(p1, s1, idx1, count, pw, sw, out, so, n, 1, oor, item);
         }
         ++launches;
     }

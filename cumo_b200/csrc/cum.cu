@@ -7,10 +7,11 @@
 // a NaN accumulator is replaced by the next value and a NaN value is skipped, i.e. NaN means
 // "nothing yet" -- which makes it associative, so it can be scanned in parallel as it stands.
 //
-// Plan: tiles of 4096 elements, 16 consecutive elements per thread (four 16-byte loads when the
-// run is contiguous).  Short runs are one CTA.  Longer runs take three launches with no waiting
-// between CTAs: (1) every CTA folds its tile into one value, (2) one CTA scans those values,
-// (3) every CTA scans its tile again starting from the value before it.  No identity element is
+// Plan: tiles of 4096 elements, 16 consecutive elements per thread (staged through shared memory so
+// that global memory sees coalesced 16-byte accesses when the run is contiguous).  Short runs are one
+// CTA.  Longer runs take three launches with no waiting between CTAs: (1) every CTA folds its run of
+// consecutive tiles into one value, (2) one CTA scans those (at most 4096) values, (3) every CTA scans
+// its tiles again starting from the value before it.  No identity element is
 // ever combined in, so out[0] is x[0] bit for bit (a -0.0 stays -0.0) and integer overflow wraps
 // exactly as in the sequential loop; floating-point results differ from it only by association.
 #include "common.cuh"
@@ -78,25 +79,87 @@ __device__ __forceinline__ void load_items(const char* p, int64_t s, int64_t fir
     }
 }
 
-// pass 1: the fold of every tile, in element order
+// Whole, contiguous, 16-byte-aligned tiles go through shared memory so that global memory sees a warp's
+// 32 packets side by side (512 bytes per instruction) while each thread still ends up with its 16 consecutive
+// elements.  A thread's chunk is followed by 16 bytes of padding: with that stride the 16-byte accesses of a
+// quarter-warp fall on disjoint banks.
+template <typename T>
+struct ScanStage {
+    static constexpr int kChunk = kScanItems * (int)sizeof(T);
+    static constexpr int kStride = kChunk + 16;
+    static constexpr int kBytes = kBlock * kStride;
+    static constexpr int kPacksPerThread = kChunk / 16;
+};
+
+template <typename T>
+__device__ __forceinline__ void load_tile_staged(const char* tile_ptr, char* stage, T (&x)[kScanItems]) {
+    constexpr int PPT = ScanStage<T>::kPacksPerThread;
+    constexpr int V = 16 / sizeof(T);
+#pragma unroll
+    for (int j = 0; j < PPT; ++j) {
+        const int q = j * kBlock + threadIdx.x;                              // packet of the tile
+        const int4 v = __ldcs(reinterpret_cast<const int4*>(tile_ptr) + q);
+        *reinterpret_cast<int4*>(stage + (q / PPT) * ScanStage<T>::kStride + (q % PPT) * 16) = v;
+    }
+    __syncthreads();
+#pragma unroll
+    for (int j = 0; j < PPT; ++j) {
+        Pack<T> v;
+        *reinterpret_cast<int4*>(&v) = *reinterpret_cast<const int4*>(stage + threadIdx.x * ScanStage<T>::kStride + j * 16);
+#pragma unroll
+        for (int e = 0; e < V; ++e) x[j * V + e] = v.v[e];
+    }
+    __syncthreads();                                                          // the stage is reused for the way out
+}
+
+template <typename T>
+__device__ __forceinline__ void store_tile_staged(char* tile_ptr, char* stage, const T (&x)[kScanItems]) {
+    constexpr int PPT = ScanStage<T>::kPacksPerThread;
+    constexpr int V = 16 / sizeof(T);
+#pragma unroll
+    for (int j = 0; j < PPT; ++j) {
+        Pack<T> v;
+#pragma unroll
+        for (int e = 0; e < V; ++e) v.v[e] = x[j * V + e];
+        *reinterpret_cast<int4*>(stage + threadIdx.x * ScanStage<T>::kStride + j * 16) = *reinterpret_cast<const int4*>(&v);
+    }
+    __syncthreads();
+#pragma unroll
+    for (int j = 0; j < PPT; ++j) {
+        const int q = j * kBlock + threadIdx.x;
+        __stcs(reinterpret_cast<int4*>(tile_ptr) + q,
+               *reinterpret_cast<const int4*>(stage + (q / PPT) * ScanStage<T>::kStride + (q % PPT) * 16));
+    }
+}
+
+// pass 1: the fold of every CTA's run of `tiles_per_cta` consecutive tiles, in element order
 template <typename T, typename Op>
 __global__ void __launch_bounds__(kBlock)
-scan_fold_kernel(const char* __restrict__ p1, int64_t s1, int64_t n, bool packed, T* tile_sums) {
+scan_fold_kernel(const char* __restrict__ p1, int64_t s1, int64_t n, bool packed, int64_t tiles_per_cta, int64_t n_tiles, T* cta_sums) {
     __shared__ T smem[2 * kWarpsPerBlock];
-    const int64_t tile = blockIdx.x;
-    const int64_t first = tile * kScanTile + (int64_t)threadIdx.x * kScanItems;
-    T x[kScanItems];
-    load_items<T>(p1, s1, first, n, packed, x);
-    T acc = x[0];                               // threads past the end carry garbage that never flows backwards
+    __shared__ T tile_fold_s;
+    T running = T();                            // thread 0's: the fold of the tiles so far
+    const int64_t t_begin = (int64_t)blockIdx.x * tiles_per_cta;
+    int64_t t_end = t_begin + tiles_per_cta; if (t_end > n_tiles) t_end = n_tiles;
+    for (int64_t tile = t_begin; tile < t_end; ++tile) {
+        const int64_t first = tile * kScanTile + (int64_t)threadIdx.x * kScanItems;
+        T x[kScanItems];
+        load_items<T>(p1, s1, first, n, packed, x);           // (staging through shared memory measured slower for this read-only pass)
+        T acc = x[0];                           // threads past the end hold zeros that never flow backwards
 #pragma unroll
-    for (int j = 1; j < kScanItems; ++j)
-        if (first + j < n) acc = Op::combine(acc, x[j]);
-    T before, total;
-    block_scan<T, Op>(acc, &before, &total, smem);
-    // the tile's fold is the inclusive value at the last thread that holds an element
-    const int64_t last_elem = (tile + 1) * kScanTile <= n ? (tile + 1) * kScanTile - 1 : n - 1;
-    const int last_thread = (int)((last_elem - tile * kScanTile) / kScanItems);
-    if ((int)threadIdx.x == last_thread) tile_sums[tile] = threadIdx.x > 0 ? Op::combine(before, acc) : acc;
+        for (int j = 1; j < kScanItems; ++j)
+            if (first + j < n) acc = Op::combine(acc, x[j]);
+        T before, total;
+        block_scan<T, Op>(acc, &before, &total, smem);
+        // the tile's fold is the inclusive value at the last thread that holds an element
+        const int64_t last_elem = (tile + 1) * kScanTile <= n ? (tile + 1) * kScanTile - 1 : n - 1;
+        const int last_thread = (int)((last_elem - tile * kScanTile) / kScanItems);
+        if ((int)threadIdx.x == last_thread) tile_fold_s = threadIdx.x > 0 ? Op::combine(before, acc) : acc;
+        __syncthreads();
+        if (threadIdx.x == 0) running = tile == t_begin ? tile_fold_s : Op::combine(running, tile_fold_s);
+        __syncthreads();
+    }
+    if (threadIdx.x == 0) cta_sums[blockIdx.x] = running;
 }
 
 // pass 2: inclusive scan of the tile folds, one CTA, kScanTile values per round
@@ -135,44 +198,56 @@ scan_tiles_kernel(T* tile_sums, int64_t n_tiles) {
     }
 }
 
-// pass 3 (or the only pass of a short run): the scan itself
+// pass 3 (or the only pass of a short run): the scan itself, a CTA walking its tiles with the fold so far
 template <typename T, typename Op>
 __global__ void __launch_bounds__(kBlock)
 scan_write_kernel(const char* __restrict__ p1, int64_t s1, char* p2, int64_t s2, int64_t n, bool packed_in, bool packed_out,
-                  const T* __restrict__ tile_sums) {
+                  int64_t tiles_per_cta, int64_t n_tiles, const T* __restrict__ cta_sums) {
     __shared__ T smem[2 * kWarpsPerBlock];
-    const int64_t tile = blockIdx.x;
-    const int64_t first = tile * kScanTile + (int64_t)threadIdx.x * kScanItems;
-    T x[kScanItems];
-    load_items<T>(p1, s1, first, n, packed_in, x);
-    T acc[kScanItems];
-    acc[0] = x[0];
+    __shared__ __align__(16) char stage[ScanStage<T>::kBytes];
+    const int64_t t_begin = (int64_t)blockIdx.x * tiles_per_cta;
+    int64_t t_end = t_begin + tiles_per_cta; if (t_end > n_tiles) t_end = n_tiles;
+    bool have_carry = blockIdx.x > 0;            // everything before this CTA's first tile
+    T carry = have_carry ? cta_sums[blockIdx.x - 1] : T();
+    for (int64_t tile = t_begin; tile < t_end; ++tile) {
+        const int64_t first = tile * kScanTile + (int64_t)threadIdx.x * kScanItems;
+        const bool whole = (tile + 1) * kScanTile <= n;       // the same for every thread of the CTA
+        T acc[kScanItems];                           // the elements, then their running fold in place
+        if (packed_in && whole) load_tile_staged<T>(p1 + tile * kScanTile * (int64_t)sizeof(T), stage, acc);
+        else load_items<T>(p1, s1, first, n, packed_in, acc);
 #pragma unroll
-    for (int j = 1; j < kScanItems; ++j) acc[j] = first + j < n ? Op::combine(acc[j - 1], x[j]) : acc[j - 1];
-    T before, total;
-    block_scan<T, Op>(acc[kScanItems - 1], &before, &total, smem);
-    const bool have_tile = tile > 0;
-    T prefix = T();
-    bool have_prefix = false;
-    if (threadIdx.x > 0) { prefix = before; have_prefix = true; }
-    if (have_tile) {
-        const T t = tile_sums[tile - 1];
-        prefix = have_prefix ? Op::combine(t, prefix) : t;
-        have_prefix = true;
-    }
-    constexpr int V = 16 / sizeof(T);
-    if (packed_out && first + kScanItems <= n) {
-#pragma unroll
-        for (int j = 0; j < kScanItems / V; ++j) {
-            Pack<T> o;
-#pragma unroll
-            for (int e = 0; e < V; ++e) o.v[e] = have_prefix ? Op::combine(prefix, acc[j * V + e]) : acc[j * V + e];
-            st_pack<T>(p2 + (first + j * V) * (int64_t)sizeof(T), o);
+        for (int j = 1; j < kScanItems; ++j) acc[j] = first + j < n ? Op::combine(acc[j - 1], acc[j]) : acc[j - 1];
+        T before, total;
+        block_scan<T, Op>(acc[kScanItems - 1], &before, &total, smem);
+        T prefix = T();
+        bool have_prefix = false;
+        if (threadIdx.x > 0) { prefix = before; have_prefix = true; }
+        if (have_carry) {
+            prefix = have_prefix ? Op::combine(carry, prefix) : carry;
+            have_prefix = true;
         }
-    } else {
+        constexpr int V = 16 / sizeof(T);
+        if (packed_out && whole) {
 #pragma unroll
-        for (int j = 0; j < kScanItems; ++j)
-            if (first + j < n) *reinterpret_cast<T*>(p2 + (first + j) * s2) = have_prefix ? Op::combine(prefix, acc[j]) : acc[j];
+            for (int j = 0; j < kScanItems; ++j) acc[j] = have_prefix ? Op::combine(prefix, acc[j]) : acc[j];
+            store_tile_staged<T>(p2 + tile * kScanTile * (int64_t)sizeof(T), stage, acc);
+            __syncthreads();                             // the stage is loaded again for the next tile
+        } else if (packed_out && first + kScanItems <= n) {
+#pragma unroll
+            for (int j = 0; j < kScanItems / V; ++j) {
+                Pack<T> o;
+#pragma unroll
+                for (int e = 0; e < V; ++e) o.v[e] = have_prefix ? Op::combine(prefix, acc[j * V + e]) : acc[j * V + e];
+                st_pack<T>(p2 + (first + j * V) * (int64_t)sizeof(T), o);
+            }
+        } else {
+#pragma unroll
+            for (int j = 0; j < kScanItems; ++j)
+                if (first + j < n) *reinterpret_cast<T*>(p2 + (first + j) * s2) = have_prefix ? Op::combine(prefix, acc[j]) : acc[j];
+        }
+        // a whole tile's total is the inclusive value of its last thread (only the run's last tile can be partial)
+        carry = have_carry ? Op::combine(carry, total) : total;
+        have_carry = true;
     }
 }
 
@@ -185,20 +260,22 @@ cudaError_t launch_scan(char* p1, char* p2, ssize_t s1, ssize_t s2, uint64_t n64
     const bool packed_in = s1 == (ssize_t)sizeof(T) && aligned16(p1);
     const bool packed_out = s2 == (ssize_t)sizeof(T) && aligned16(p2);
     const int64_t n_tiles = (n + kScanTile - 1) / kScanTile;
-    if (n_tiles > 0x7fffffffLL) return cudaErrorInvalidValue;
     if (n_tiles == 1) {
-        scan_write_kernel<T, Op><<<1, kBlock, 0, st>>>(p1, s1, p2, s2, n, packed_in, packed_out, nullptr);
+        scan_write_kernel<T, Op><<<1, kBlock, 0, st>>>(p1, s1, p2, s2, n, packed_in, packed_out, 1, 1, nullptr);
         count_launch();
         return cudaGetLastError();
     }
-    T* tile_sums = reinterpret_cast<T*>(cumo_cuda_runtime_malloc(sizeof(T) * (size_t)n_tiles));
-    if (!tile_sums) return cudaErrorMemoryAllocation;
-    scan_fold_kernel<T, Op><<<(unsigned)n_tiles, kBlock, 0, st>>>(p1, s1, n, packed_in, tile_sums);
-    scan_tiles_kernel<T, Op><<<1, kBlock, 0, st>>>(tile_sums, n_tiles);
-    scan_write_kernel<T, Op><<<(unsigned)n_tiles, kBlock, 0, st>>>(p1, s1, p2, s2, n, packed_in, packed_out, tile_sums);
+    // at most kScanTile CTAs, so that the middle pass is a single round of one CTA
+    const int64_t tiles_per_cta = (n_tiles + kScanTile - 1) / kScanTile;
+    const int64_t n_ctas = (n_tiles + tiles_per_cta - 1) / tiles_per_cta;
+    T* cta_sums = reinterpret_cast<T*>(cumo_cuda_runtime_malloc(sizeof(T) * (size_t)n_ctas));
+    if (!cta_sums) return cudaErrorMemoryAllocation;
+    scan_fold_kernel<T, Op><<<(unsigned)n_ctas, kBlock, 0, st>>>(p1, s1, n, packed_in, tiles_per_cta, n_tiles, cta_sums);
+    scan_tiles_kernel<T, Op><<<1, kBlock, 0, st>>>(cta_sums, n_ctas);
+    scan_write_kernel<T, Op><<<(unsigned)n_ctas, kBlock, 0, st>>>(p1, s1, p2, s2, n, packed_in, packed_out, tiles_per_cta, n_tiles, cta_sums);
     count_launch(3);
     const cudaError_t e = cudaGetLastError();
-    cumo_cuda_runtime_free(reinterpret_cast<char*>(tile_sums));      // stream-ordered reuse: later kernels queue behind these
+    cumo_cuda_runtime_free(reinterpret_cast<char*>(cta_sums));      // stream-ordered reuse: later kernels queue behind these
     return e;
 }
 

@@ -78,7 +78,9 @@ sgemm_nt_tc_kernel(const float* __restrict__ A, int64_t lda, const float* __rest
     const uint32_t KB = (uint32_t)((K + kGemmKB - 1) / kGemmKB);
     const int64_t my_tiles = n_tiles > blockIdx.x ? (n_tiles - blockIdx.x + gridDim.x - 1) / gridDim.x : 0;
     // tile t of this CTA -> (row block, column block); row blocks vary fastest so that CTAs running
-    // together share the same 256 rows of Bt
+    // together share the same 256 rows of Bt.  (Numbering the tiles in bands of 16 row blocks, which cuts the
+    // DRAM reads of A from once per column block to about once, measured 12 % slower at 8192^3: the kernel is
+    // bound by shared-memory traffic, not by DRAM.)
     auto tile_of = [&](int64_t t, int64_t* m0, int64_t* n0) {
         const int64_t g = (int64_t)blockIdx.x + t * gridDim.x;
         const int64_t tn = g / tiles_m;

@@ -155,15 +155,23 @@ where_scatter_kernel(const WhereRun r, uint64_t tiles_per_cta, uint64_t n_tiles,
         for (int j = 0; j < kWhereChunksPerThread; ++j) { z[j] = where_chunk(r, c0 + j); mine += __popc(z[j]); }
         uint32_t total;
         const uint32_t pre = block_exscan(mine, &total, smem);
-        unsigned long long o = off + pre;
+        // Expansion, a warp at a time over its 128 chunks: the word of chunk (lane s, j) is broadcast and every
+        // lane k writes position k if it is set, at the word's output offset plus the number of set bits below k.
+        // A word's positions leave in one coalesced store instead of up to 32 stores from one thread.
+        const int lane = threadIdx.x & 31;
+        const uint32_t below = (1u << lane) - 1u;
+        uint32_t o_local = pre;                              // my chunk j starts at off + o_local
 #pragma unroll
         for (int j = 0; j < kWhereChunksPerThread; ++j) {
-            uint32_t w = z[j];
-            const uint64_t e0 = count + (c0 + j) * 32;
-            while (w) {
-                const int k = __ffs(w) - 1;
-                out[o++] = (TI)(e0 + k);
-                w &= w - 1;
+            const uint32_t my_word = z[j];
+            const uint32_t my_off = o_local;
+            o_local += __popc(my_word);
+            for (int src = 0; src < 32; ++src) {
+                const uint32_t w = __shfl_sync(0xffffffffu, my_word, src);
+                if (w == 0) continue;                        // warp-uniform
+                const uint32_t wo = __shfl_sync(0xffffffffu, my_off, src);
+                const uint64_t c_src = c0 - (uint64_t)lane * kWhereChunksPerThread + (uint64_t)src * kWhereChunksPerThread + j;
+                if ((w >> lane) & 1u) out[off + wo + __popc(w & below)] = (TI)(count + c_src * 32 + lane);
             }
         }
         off += total;

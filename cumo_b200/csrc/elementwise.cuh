@@ -444,7 +444,17 @@ void launch_elementwise(const cumo_na_iarray_t* a1, const cumo_na_iarray_t* a2, 
                 ++launches;
                 return true;
             };
-            if (row_ok && run(vec, L - tail, p1, p2, p3)) {
+            // the row kernels address a slot's column with 32 bits: an inner extent beyond that goes in slices
+            // (a multiple of every packet size, so each slice keeps the alignment of the whole)
+            constexpr int64_t kMaxInner = 1LL << 31;
+            auto run_sliced = [&](bool v16, int64_t len, const char* q1, const char* q2, char* q3) {
+                for (int64_t done = 0; done < len; done += kMaxInner) {
+                    const int64_t part = len - done < kMaxInner ? len - done : kMaxInner;
+                    if (!run(v16, part, q1 ? q1 + done * p.step[0][in] : q1, q2 ? q2 + done * p.step[1][in] : q2, q3 + done * ES)) return false;
+                }
+                return true;
+            };
+            if (row_ok && run_sliced(vec, L - tail, p1, p2, p3)) {
                 if (tail) {
                     const int64_t done = L - tail;
                     run(false, tail, p1 ? p1 + done * p.step[0][in] : p1, p2 ? p2 + done * p.step[1][in] : p2, p3 + done * ES);

@@ -450,6 +450,17 @@ def test_bincount_counts_and_weights(xp_gpu, tname, n, bins):
         same(g2.bincount(), o2.bincount())                                          # one launch per leading index
 
 
+def test_new_ops_on_empty_arrays(xp_gpu):
+    for xp in (xp_gpu, OracleXP):
+        e = xp.Int32.cast(np.array([], dtype=np.int32))
+        assert e.bincount().to_a() == []
+        assert e.bincount(minlength=3).to_a() == [0, 0, 0]
+        assert e.cumsum().to_a() == []
+        f = xp.SFloat.cast(np.zeros((0, 5), dtype=np.float32))
+        assert f.cumsum(axis=1).shape == (0, 5)
+        assert xp.Bit.cast(np.zeros(0, dtype=bool)).where().to_a() == []
+
+
 def test_bincount_rejects_negative_items(xp_gpu):
     with pytest.raises(ValueError):
         xp_gpu.Int32.from_numpy(np.array([0, 5, -1, 2], dtype=np.int32)).bincount()

@@ -73,7 +73,7 @@ using namespace cb200;
         launch_elementwise<op::OP<CB_C>>(a1, a2, a3, ix, CB_C(), CB_C(), 0, nullptr);                   \
     }
 
-// store from each of the four element types; a1 is the destination
+// store from another element type; a1 is the destination
 #define DEF_STORE(from, FC)                                                                            \
     extern "C" void CB_ITER(store_##from, _kernel_launch)(cumo_na_iarray_t* a1, cumo_na_iarray_t* a2,   \
             cumo_na_indexer_t* ix) {                                                                    \
@@ -83,6 +83,14 @@ DEF_STORE(sfloat, float)
 DEF_STORE(dfloat, double)
 DEF_STORE(int32, int32_t)
 DEF_STORE(int64, int64_t)
+// the reference instantiates the store template once per source class in every destination type
+// (gen/spec.rb:121-140), so the narrow and unsigned integers are sources here too
+DEF_STORE(int16, int16_t)
+DEF_STORE(int8, int8_t)
+DEF_STORE(uint64, uint64_t)
+DEF_STORE(uint32, uint32_t)
+DEF_STORE(uint16, uint16_t)
+DEF_STORE(uint8, uint8_t)
 
 DEF_BINARY_S(add, Add)
 DEF_BINARY_S(sub, Sub)

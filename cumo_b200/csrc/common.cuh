@@ -65,6 +65,10 @@ __device__ __forceinline__ void st_one<int64_t>(void* p, int64_t v) {
 }
 
 // ---- index decomposition ------------------------------------------------------
+// An extent as the 32-bit divisor of an index below 2^31: anything of 2^32 or more divides such an index to
+// zero and leaves it as the remainder, and so does 2^32 - 1, so huge extents are clamped instead of truncated.
+__device__ __forceinline__ uint32_t extent32(int64_t n) { return n > 0xffffffffLL ? 0xffffffffu : (uint32_t)n; }
+
 // Row-major split of a flat index over `nd` extents into a byte offset, 32-bit
 // arithmetic when the index fits (integer division on 64-bit operands is an
 // order of magnitude more instructions).
@@ -73,7 +77,7 @@ __device__ __forceinline__ int64_t offset_of(int64_t flat, int nd, const int64_t
     if (flat < 0x7fffffffLL) {
         uint32_t i = (uint32_t)flat;
         for (int d = nd - 1; d > 0; --d) {
-            uint32_t n = (uint32_t)shape[d];
+            uint32_t n = extent32(shape[d]);
             uint32_t q = i / n;
             off += (int64_t)(i - q * n) * step[d];
             i = q;
@@ -101,7 +105,7 @@ __device__ __forceinline__ void offsets_of(int64_t flat, int nd, const int64_t* 
     if (flat < 0x7fffffffLL) {
         uint32_t i = (uint32_t)flat;
         for (int d = nd - 1; d > 0; --d) {
-            uint32_t n = (uint32_t)shape[d];
+            uint32_t n = extent32(shape[d]);
             uint32_t q = i / n;
             int64_t r = (int64_t)(i - q * n);
 #pragma unroll

@@ -252,6 +252,9 @@ sgemm_nt_tc_kernel(const float* __restrict__ A, int64_t lda, const float* __rest
     if ((abort_flag[0] | abort_flag[1]) && tid == 0) atomicExch(error_word, 1);
 }
 
+// status word of the kernel's bounded waits, one per device that loads the library (host code sees only a handle)
+static __device__ int g_sgemm_nt_tc_error_word;
+
 }  // namespace cb200
 
 // C[M, N] = A[M, K] . Bt[N, K]^T, float32, row-major with leading dimensions in elements.
@@ -283,8 +286,10 @@ extern "C" int cb200_sgemm_nt_tc(int64_t M, int64_t N, int64_t K, const float* A
     if (!dev_state[dev].ready) {
         cudaError_t e = cudaFuncSetAttribute(sgemm_nt_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
         if (e != cudaSuccess) { snprintf(errbuf, errlen, "cudaFuncSetAttribute: %s", cudaGetErrorString(e)); return 3; }
-        dev_state[dev].error_word = reinterpret_cast<int*>(cumo_cuda_runtime_malloc(sizeof(int)));
-        if (!dev_state[dev].error_word) { snprintf(errbuf, errlen, "sgemm_nt_tc: no memory for the error word"); return 3; }
+        // the word lives in the library image: no allocator callback (which, inside the Ruby extension, may
+        // raise with a longjmp) is ever called while call_mutex is held
+        e = cudaGetSymbolAddress(reinterpret_cast<void**>(&dev_state[dev].error_word), g_sgemm_nt_tc_error_word);
+        if (e != cudaSuccess || !dev_state[dev].error_word) { snprintf(errbuf, errlen, "sgemm_nt_tc: cudaGetSymbolAddress: %s", cudaGetErrorString(e)); return 3; }
         dev_state[dev].ready = true;
     }
     cudaStream_t st = current_stream();

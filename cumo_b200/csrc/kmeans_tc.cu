@@ -249,6 +249,9 @@ static size_t tc_smem_bytes(int d, int n_pad) {
     return 2 * KB * (size_t)n_pad * 128 + (size_t)kTcSlots * kTcSlotBytes + 2 * (size_t)n_pad * 4 + 11 * 8 + 16;
 }
 
+// status word of the kernel's bounded waits, one per device that loads the library (host code sees only a handle)
+static __device__ int g_kmeans_assign_tc_error_word;
+
 }  // namespace cb200
 
 // The tensor-core form.  Shapes: d a multiple of 32, k <= 256, and the table must fit shared memory
@@ -284,8 +287,10 @@ extern "C" int cb200_kmeans_assign_sfloat_tc(const float* x, int64_t n, int d, c
     if (!dev_state[dev].ready) {
         cudaError_t e = cudaFuncSetAttribute(kmeans_assign_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
         if (e != cudaSuccess) { snprintf(errbuf, errlen, "cudaFuncSetAttribute: %s", cudaGetErrorString(e)); return 3; }
-        dev_state[dev].error_word = reinterpret_cast<int*>(cumo_cuda_runtime_malloc(sizeof(int)));
-        if (!dev_state[dev].error_word) { snprintf(errbuf, errlen, "kmeans_assign_tc: no memory for the error word"); return 3; }
+        // the word lives in the library image: no allocator callback (which, inside the Ruby extension, may
+        // raise with a longjmp) is ever called while call_mutex is held
+        e = cudaGetSymbolAddress(reinterpret_cast<void**>(&dev_state[dev].error_word), g_kmeans_assign_tc_error_word);
+        if (e != cudaSuccess || !dev_state[dev].error_word) { snprintf(errbuf, errlen, "kmeans_assign_tc: cudaGetSymbolAddress: %s", cudaGetErrorString(e)); return 3; }
         dev_state[dev].ready = true;
     }
     cudaStream_t st = current_stream();

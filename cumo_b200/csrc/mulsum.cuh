@@ -100,7 +100,10 @@ void launch_mulsum_reduce(char* p1, char* p2, char* p3, ssize_t s1, ssize_t s2, 
     while (n_seg > 4096) { seg_len *= 2; n_seg = ((int64_t)n + seg_len - 1) / seg_len; }
     if (n_seg < 1) n_seg = 1;
     T* partial = nullptr;
-    if (n_seg > 1) partial = reinterpret_cast<T*>(cumo_cuda_runtime_malloc(sizeof(T) * n_seg));
+    if (n_seg > 1) {
+        partial = reinterpret_cast<T*>(cumo_cuda_runtime_malloc(sizeof(T) * n_seg));
+        if (!partial) return;          // the allocator reported it; several CTAs adding into *p3 without partials would be wrong
+    }
     if (vec) mulsum_partial_kernel<T, NAN_SKIP, VMAX><<<(unsigned)n_seg, kBlock, 0, st>>>(p1, p2, s1, s2, (int64_t)n, seg_len, partial, reinterpret_cast<T*>(p3));
     else     mulsum_partial_kernel<T, NAN_SKIP, 1><<<(unsigned)n_seg, kBlock, 0, st>>>(p1, p2, s1, s2, (int64_t)n, seg_len, partial, reinterpret_cast<T*>(p3));
     int launches = 1;

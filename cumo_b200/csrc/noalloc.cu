@@ -14,7 +14,10 @@
 //     cudaMalloc/cudaFree fallback of an empty pool.
 // This variant runs the same two kernels (red_row_kernel, then red_fold_kernel) but keeps
 // the scratch in a fixed array that is part of the library image, so it never allocates or
-// frees anything, on the device or through any library.
+// frees anything, on the device or through any library.  It always cuts long rows into
+// 32 KiB segments, where the regular entry point keeps rows of up to 256 KiB whole when there
+// are many of them, so the two agree to rounding (the additions are grouped differently), not
+// bit for bit.
 //
 // Limits and rules, all of them consequences of the fixed array:
 //   * the array holds kNoAllocScratchFloats partial sums (1 MiB); a reduction that needs
@@ -83,6 +86,10 @@ extern "C" int cb200_sfloat_sum_noalloc_kernel_launch(cumo_na_reduction_arg_t* a
                  (long long)p.in_rstep[p.n_rd - 1], p.n_rd);
         return 1;
     }
+    // The array's address is looked up on the first call on each device, whatever that call's shape, so that a
+    // small warm-up call made before a stream capture covers the segmented calls that follow.
+    float* const scratch = noalloc_scratch_address(errbuf, errlen);
+    if (!scratch) return 3;
     const R r{0, 0.0f};
     RedLaunch q;
     q.n_split = 1;
@@ -110,8 +117,7 @@ extern "C" int cb200_sfloat_sum_noalloc_kernel_launch(cumo_na_reduction_arg_t* a
                      (long long)need, (long long)p.n_out, q.n_split, (long long)kNoAllocScratchFloats);
             return 2;
         }
-        partial = noalloc_scratch_address(errbuf, errlen);
-        if (!partial) return 3;
+        partial = scratch;
     }
     cudaStream_t st = current_stream();
     const int64_t items = p.n_out * q.n_split;

@@ -574,6 +574,14 @@ red_fold_big_kernel(const RedPlan p, const R r, const typename R::Acc* __restric
     }
 }
 
+// Scratch for the [output][segment] partials from the host program's allocator.  A null answer means the
+// allocator has already reported the failure its own way (an exception in the extension, the error latch in the
+// library's default): the caller launches nothing, because a first pass would write through the null pointer.
+template <typename Acc>
+inline Acc* take_partials(int64_t count) {
+    return reinterpret_cast<Acc*>(cumo_cuda_runtime_malloc(sizeof(Acc) * (size_t)count));
+}
+
 inline unsigned red_grid(int64_t ctas) { return (unsigned)(ctas < 1 ? 1 : (ctas > 0x7fffffffLL ? 0x7fffffffLL : ctas)); }
 
 // ---- host ----------------------------------------------------------------------------------
@@ -627,7 +635,7 @@ void launch_reduce(const cumo_na_reduction_arg_t* arg, const cumo_na_iarray_t* o
             while (ns > 8192) { seg *= 2; ns = (L + seg - 1) / seg; }
             if (ns > 1) { q.seg_len = seg; q.n_split = (int)ns; }
         }
-        if (q.n_split > 1) partial = reinterpret_cast<Acc*>(cumo_cuda_runtime_malloc(sizeof(Acc) * p.n_out * q.n_split));
+        if (q.n_split > 1 && !(partial = take_partials<Acc>(p.n_out * q.n_split))) return;
         const int64_t items = p.n_out * q.n_split;
         if (wide) {
             if (vec) red_row_kernel<R, VMAX, kBlock><<<red_grid(items), kBlock, 0, st>>>(p, r, q, in, out, out2, partial);
@@ -669,7 +677,7 @@ void launch_reduce(const cumo_na_reduction_arg_t* arg, const cumo_na_iarray_t* o
             q.seg_len = seg;
             q.n_split = (int)ns;
         }
-        if (q.n_split > 1) partial = reinterpret_cast<Acc*>(cumo_cuda_runtime_malloc(sizeof(Acc) * p.n_out * q.n_split));
+        if (q.n_split > 1 && !(partial = take_partials<Acc>(p.n_out * q.n_split))) return;
         const unsigned grid = red_grid((p.n_out / C) * q.n_strips * q.n_split);
         if (wide_cols) {
             // 48 KiB of (unused) dynamic shared memory per CTA holds residency at 4 CTAs per SM for every functor
@@ -688,7 +696,7 @@ void launch_reduce(const cumo_na_reduction_arg_t* arg, const cumo_na_iarray_t* o
             while (ns > 8192) { seg *= 2; ns = (p.n_red + seg - 1) / seg; }
             if (ns > 1) { q.seg_len = seg; q.n_split = (int)ns; }
         }
-        if (q.n_split > 1) partial = reinterpret_cast<Acc*>(cumo_cuda_runtime_malloc(sizeof(Acc) * p.n_out * q.n_split));
+        if (q.n_split > 1 && !(partial = take_partials<Acc>(p.n_out * q.n_split))) return;
         const int64_t items = p.n_out * q.n_split;
         if (wide) red_gen_kernel<R, kBlock><<<red_grid(items), kBlock, 0, st>>>(p, r, q, in, out, out2, partial);
         else      red_gen_kernel<R, 32><<<red_grid((items + kWarpsPerBlock - 1) / kWarpsPerBlock), kBlock, 0, st>>>(p, r, q, in, out, out2, partial);

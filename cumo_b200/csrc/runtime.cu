@@ -5,8 +5,8 @@
 //
 // The default scratch pool follows the shape of the reference's pool
 // (ext/cumo/cuda/memory_pool_impl.hpp:23,160-288): sizes rounded up to 512
-// bytes, freed blocks cached per device and handed out best-fit, everything
-// released and the allocation retried once when the device is out of memory.
+// bytes, freed blocks cached per device AND per stream and handed out best-fit,
+// everything released and the allocation retried once when the device is out of memory.
 // It backs only reduction scratch here, so it is small; it hands out plain
 // device memory (cudaMalloc), not managed memory.
 #include "common.cuh"
@@ -49,59 +49,75 @@ static void latch(cudaError_t e, const char* what) {
 }
 
 // ---- scratch pool --------------------------------------------------------------------
+// One pool per device, one arena of cached blocks per (device, stream), like the reference's
+// per-stream arenas (ext/cumo/cuda/memory_pool_impl.hpp:222-244): a block goes back to the arena of
+// the stream that was current when it was taken, so the next taker queues behind the kernels that
+// may still be reading it.  A block remembers its device, so it finds its way home even when
+// another device is current at the time it is freed.
 struct Pool {
-    std::mutex mu;
-    std::multimap<size_t, char*> free_blocks;           // size -> block
-    std::unordered_map<char*, size_t> live;             // handed out
+    struct Block { size_t size; int dev; cudaStream_t stream; };
+    std::map<cudaStream_t, std::multimap<size_t, char*>> arenas;   // stream -> (size -> block)
     size_t total = 0, used = 0;
-
-    char* take(size_t size) {
-        size_t need = (size + 511) / 512 * 512;
-        if (need == 0) need = 512;
-        std::lock_guard<std::mutex> lk(mu);
-        auto it = free_blocks.lower_bound(need);
-        // reuse a cached block unless it wastes more than half of itself
-        if (it != free_blocks.end() && it->first <= need * 2) {
-            char* p = it->second;
-            size_t sz = it->first;
-            free_blocks.erase(it);
-            live[p] = sz;
-            used += sz;
-            return p;
-        }
-        void* p = nullptr;
-        cudaError_t e = cudaMalloc(&p, need);
-        if (e != cudaSuccess) {
-            (void)cudaGetLastError();
-            release_locked();
-            e = cudaMalloc(&p, need);
-        }
-        if (e != cudaSuccess) { (void)cudaGetLastError(); latch(e, "cumo_cuda_runtime_malloc"); return nullptr; }
-        live[(char*)p] = need;
-        total += need;
-        used += need;
-        return (char*)p;
-    }
-    void give(char* p) {
-        if (!p) return;
-        std::lock_guard<std::mutex> lk(mu);
-        auto it = live.find(p);
-        if (it == live.end()) return;
-        used -= it->second;
-        free_blocks.emplace(it->second, p);
-        live.erase(it);
-    }
-    void release_locked() {
-        for (auto& kv : free_blocks) { cudaFree(kv.second); total -= kv.first; }
-        free_blocks.clear();
-    }
 };
 
-static Pool& pool_of_current_device() {
-    static Pool pools[64];
+static std::mutex g_pool_mu;                                        // guards every pool and the table of live blocks
+static Pool g_pools[64];
+static std::unordered_map<char*, Pool::Block> g_live;               // handed out, any device
+
+static int current_device() {
     int dev = 0;
     if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) dev = 0;
-    return pools[dev];
+    return dev;
+}
+
+static void release_locked(Pool& p) {
+    for (auto& arena : p.arenas)
+        for (auto& kv : arena.second) { cudaFree(kv.second); p.total -= kv.first; }
+    p.arenas.clear();
+}
+
+static char* pool_take(size_t size) {
+    size_t need = (size + 511) / 512 * 512;
+    if (need == 0) need = 512;
+    const int dev = current_device();
+    const cudaStream_t st = tl_stream;
+    std::lock_guard<std::mutex> lk(g_pool_mu);
+    Pool& p = g_pools[dev];
+    auto& arena = p.arenas[st];
+    auto it = arena.lower_bound(need);
+    // reuse a cached block unless it wastes more than half of itself
+    if (it != arena.end() && it->first <= need * 2) {
+        char* b = it->second;
+        const size_t sz = it->first;
+        arena.erase(it);
+        g_live[b] = {sz, dev, st};
+        p.used += sz;
+        return b;
+    }
+    void* b = nullptr;
+    cudaError_t e = cudaMalloc(&b, need);
+    if (e != cudaSuccess) {
+        (void)cudaGetLastError();
+        release_locked(p);                                          // cudaFree synchronises the device: nothing still reads the blocks
+        e = cudaMalloc(&b, need);
+    }
+    if (e != cudaSuccess) { (void)cudaGetLastError(); latch(e, "cumo_cuda_runtime_malloc"); return nullptr; }
+    g_live[(char*)b] = {need, dev, st};
+    p.total += need;
+    p.used += need;
+    return (char*)b;
+}
+
+static void pool_give(char* b) {
+    if (!b) return;
+    std::lock_guard<std::mutex> lk(g_pool_mu);
+    auto it = g_live.find(b);
+    if (it == g_live.end()) return;
+    const Pool::Block blk = it->second;
+    g_live.erase(it);
+    Pool& p = g_pools[blk.dev];
+    p.used -= blk.size;
+    p.arenas[blk.stream].emplace(blk.size, b);
 }
 
 }  // namespace cb200
@@ -113,13 +129,14 @@ __attribute__((weak)) void cumo_cuda_runtime_check_kernel_launch(void) {
 }
 
 __attribute__((weak)) char* cumo_cuda_runtime_malloc(size_t size) {
-    return cb200::pool_of_current_device().take(size);
+    return cb200::pool_take(size);
 }
 
 __attribute__((weak)) void cumo_cuda_runtime_free(char* ptr) {
-    // Stream-ordered reuse: the block goes back while kernels that read it may
-    // still be queued; whoever takes it next queues behind them on the same stream.
-    cb200::pool_of_current_device().give(ptr);
+    // Stream-ordered reuse: the block goes back while kernels that read it may still be
+    // queued; it returns to the arena of the stream it was taken on, so whoever takes it
+    // next queues behind them on that same stream.
+    cb200::pool_give(ptr);
 }
 
 void cb200_set_stream(void* s) { cb200::tl_stream = (cudaStream_t)s; }
@@ -134,9 +151,9 @@ int cb200_last_error(const char** message) {
 
 uint64_t cb200_launch_count(void) { return cb200::g_launches.load(std::memory_order_relaxed); }
 
-size_t cb200_pool_total_bytes(void) { auto& p = cb200::pool_of_current_device(); std::lock_guard<std::mutex> lk(p.mu); return p.total; }
-size_t cb200_pool_used_bytes(void) { auto& p = cb200::pool_of_current_device(); std::lock_guard<std::mutex> lk(p.mu); return p.used; }
-void cb200_pool_free_all_blocks(void) { auto& p = cb200::pool_of_current_device(); std::lock_guard<std::mutex> lk(p.mu); p.release_locked(); }
+size_t cb200_pool_total_bytes(void) { std::lock_guard<std::mutex> lk(cb200::g_pool_mu); return cb200::g_pools[cb200::current_device()].total; }
+size_t cb200_pool_used_bytes(void) { std::lock_guard<std::mutex> lk(cb200::g_pool_mu); return cb200::g_pools[cb200::current_device()].used; }
+void cb200_pool_free_all_blocks(void) { std::lock_guard<std::mutex> lk(cb200::g_pool_mu); cb200::release_locked(cb200::g_pools[cb200::current_device()]); }
 
 const char* cb200_version(void) { return "cumo_b200 0.1 (sm_100a)"; }
 

@@ -1,4 +1,4 @@
-// Bit#where / where2: the positions of the one (or, inverted, zero) bits of a run, ascending.
+// Bit#where / where2 / mask: the positions of the one (or, inverted, zero) bits of a run, ascending.
 //
 // Entry points and protocol are the reference's (narray/gen/tmpl_bit/where.c:11-12 declares
 // them, where_kernel.cu:83-110 defines them): the host allocates `scratch` once per call with
@@ -139,10 +139,25 @@ where_scan_kernel(unsigned long long* cta_sums, uint32_t n_ctas, unsigned long l
     if (threadIdx.x == 0) *running = carry_s;
 }
 
-template <typename TI>
+// What a hit at element e of the run appends: where -- its position `count + e`; mask -- the byte position
+// of element e of the masked array, p2 + e * s2 or p2 + idx2[e] (mask_kernel.cu:6-36 of the reference).
+struct WhereEmit {
+    uint64_t count;
+    __device__ __forceinline__ uint64_t operator()(uint64_t e) const { return count + e; }
+};
+struct MaskEmit {
+    uint64_t p2;
+    int64_t s2;
+    const size_t* idx2;
+    __device__ __forceinline__ uint64_t operator()(uint64_t e) const {
+        return idx2 ? p2 + idx2[e] : (uint64_t)((int64_t)p2 + (int64_t)e * s2);
+    }
+};
+
+template <typename TI, typename Emit>
 __global__ void __launch_bounds__(kBlock)
 where_scatter_kernel(const WhereRun r, uint64_t tiles_per_cta, uint64_t n_tiles, const unsigned long long* __restrict__ cta_pos,
-                     TI* out, uint64_t count) {
+                     TI* out, const Emit emit) {
     __shared__ uint32_t smem[kWarpsPerBlock + 1];
     const uint64_t t_begin = blockIdx.x * tiles_per_cta;
     uint64_t t_end = t_begin + tiles_per_cta; if (t_end > n_tiles) t_end = n_tiles;
@@ -171,7 +186,7 @@ where_scatter_kernel(const WhereRun r, uint64_t tiles_per_cta, uint64_t n_tiles,
                 if (w == 0) continue;                        // warp-uniform
                 const uint32_t wo = __shfl_sync(0xffffffffu, my_off, src);
                 const uint64_t c_src = c0 - (uint64_t)lane * kWhereChunksPerThread + (uint64_t)src * kWhereChunksPerThread + j;
-                if ((w >> lane) & 1u) out[off + wo + __popc(w & below)] = (TI)(count + c_src * 32 + lane);
+                if ((w >> lane) & 1u) out[off + wo + __popc(w & below)] = (TI)emit(c_src * 32 + lane);
             }
         }
         off += total;
@@ -207,8 +222,36 @@ extern "C" void cumo_bit_where_kernel_launch(CUMO_BIT_DIGIT* a, size_t p, ssize_
     cudaStream_t st = current_stream();
     where_count_kernel<<<n_ctas, kBlock, 0, st>>>(r, tiles_per_cta, n_tiles, cta_sums);
     where_scan_kernel<<<1, 1024, 0, st>>>(cta_sums, n_ctas, running);
-    if (elmsz == 8) where_scatter_kernel<int64_t><<<n_ctas, kBlock, 0, st>>>(r, tiles_per_cta, n_tiles, cta_sums, reinterpret_cast<int64_t*>(out), count);
-    else            where_scatter_kernel<int32_t><<<n_ctas, kBlock, 0, st>>>(r, tiles_per_cta, n_tiles, cta_sums, reinterpret_cast<int32_t*>(out), count);
+    const WhereEmit emit{count};
+    if (elmsz == 8) where_scatter_kernel<int64_t><<<n_ctas, kBlock, 0, st>>>(r, tiles_per_cta, n_tiles, cta_sums, reinterpret_cast<int64_t*>(out), emit);
+    else            where_scatter_kernel<int32_t><<<n_ctas, kBlock, 0, st>>>(r, tiles_per_cta, n_tiles, cta_sums, reinterpret_cast<int32_t*>(out), emit);
+    count_launch(3);
+    cumo_cuda_runtime_check_kernel_launch();
+}
+
+// Bit#mask (narray/gen/tmpl_bit/mask.c:1 declares it, mask_kernel.cu:38-53 defines it): the same compaction, but a
+// set bit at element i of the run appends the BYTE position of element i of the masked array -- p2 + i * s2, or
+// p2 + idx2[i] when that array is itself addressed through an index array -- as a size_t.  The host then wraps
+// `out` as the index array of a 1-D view of the masked array.  Same scratch and cursor protocol as where.
+extern "C" void cumo_bit_mask_kernel_launch(CUMO_BIT_DIGIT* a, size_t p, ssize_t s, size_t* idx, uint64_t n, size_t* out, size_t p2,
+                                            ssize_t s2, size_t* idx2, char* scratch) {
+    if (n == 0 || !scratch) return;
+    WhereRun r;
+    r.words = a; r.p = p; r.s = s; r.idx = idx; r.n = n;
+    r.n_chunks = (n + 31) / 32;
+    r.contiguous = idx == nullptr && s == 1;
+    r.invert = 0;
+    const uint64_t n_tiles = (r.n_chunks + kWhereTileChunks - 1) / kWhereTileChunks;
+    uint64_t tiles_per_cta = (n_tiles + kWhereMaxCtas - 1) / kWhereMaxCtas;
+    if (tiles_per_cta < 1) tiles_per_cta = 1;
+    const uint32_t n_ctas = (uint32_t)((n_tiles + tiles_per_cta - 1) / tiles_per_cta);
+    unsigned long long* running = reinterpret_cast<unsigned long long*>(scratch);
+    unsigned long long* cta_sums = reinterpret_cast<unsigned long long*>(scratch) + 2;
+    cudaStream_t st = current_stream();
+    where_count_kernel<<<n_ctas, kBlock, 0, st>>>(r, tiles_per_cta, n_tiles, cta_sums);
+    where_scan_kernel<<<1, 1024, 0, st>>>(cta_sums, n_ctas, running);
+    const MaskEmit emit{(uint64_t)p2, (int64_t)s2, idx2};
+    where_scatter_kernel<unsigned long long><<<n_ctas, kBlock, 0, st>>>(r, tiles_per_cta, n_tiles, cta_sums, reinterpret_cast<unsigned long long*>(out), emit);
     count_launch(3);
     cumo_cuda_runtime_check_kernel_launch();
 }

@@ -65,6 +65,19 @@ typedef struct {
     ssize_t step[CUMO_NA_MAX_DIMENSION];     /* BIT step per dimension             */
 } cumo_na_bit_iarray_t;
 
+/* A byte step or, when the low bit of the word is clear, a device array of byte offsets, one per position
+ * along the dimension (reference: ext/cumo/include/cumo/narray_kernel.h:168-176, narray.h:329-330:
+ * a step s is stored as (s << 1) | 1, an index array as its address). */
+typedef union {
+    ssize_t stride;
+    size_t* index;
+} cumo_stridx_t;
+
+typedef struct {
+    char* ptr;                               /* first element (view offset applied) */
+    cumo_stridx_t stridx[CUMO_NA_MAX_DIMENSION];
+} cumo_na_iarray_stridx_t;
+
 typedef struct {
     cumo_na_iarray_t in;                     /* reduce dimensions are the LAST dims of `in` */
     cumo_na_iarray_t out;                    /* steps for the leading out_indexer.ndim dims */
@@ -188,8 +201,16 @@ const char* cb200_version(void);
 #define CB200_DECL_STORE(T, F) \
     void cumo_iter_##T##_store_##F##_kernel_launch(cumo_na_iarray_t* a1, cumo_na_iarray_t* a2, cumo_na_indexer_t* indexer);
 
+/* The same-type store for operands that may be addressed through index arrays (a view made by
+ * `x[index_array, true]` or by Bit#mask), reference: gen/tmpl/store_from.c:5, store_from_kernel.cu:21-36. */
+#define CB200_DECL_STORE_STRIDX(T) \
+    void cumo_iter_##T##_store_##T##_stridx_kernel_launch(cumo_na_iarray_stridx_t* a1, cumo_na_iarray_stridx_t* a2, cumo_na_indexer_t* indexer);
+
+/* one store per source class, as the reference instantiates them (gen/spec.rb:121-140) */
 #define CB200_DECL_COMMON(T, C) \
     CB200_DECL_STORE(T, sfloat) CB200_DECL_STORE(T, dfloat) CB200_DECL_STORE(T, int32) CB200_DECL_STORE(T, int64) \
+    CB200_DECL_STORE(T, int16) CB200_DECL_STORE(T, int8) CB200_DECL_STORE(T, uint64) CB200_DECL_STORE(T, uint32) \
+    CB200_DECL_STORE(T, uint16) CB200_DECL_STORE(T, uint8) CB200_DECL_STORE_STRIDX(T) \
     CB200_DECL_BINARY_S(T, C, add) CB200_DECL_BINARY_S(T, C, sub) CB200_DECL_BINARY_S(T, C, mul) \
     CB200_DECL_BINARY_S(T, C, div) CB200_DECL_BINARY_S(T, C, mod) \
     CB200_DECL_UNARY(T, C, minus) CB200_DECL_UNARY(T, C, reciprocal) CB200_DECL_UNARY(T, C, sign) CB200_DECL_UNARY(T, C, square) \
@@ -280,6 +301,13 @@ char* cumo_bit_where_scratch_new(void);
 void cumo_bit_where_kernel_launch(CUMO_BIT_DIGIT* a, size_t p, ssize_t s, size_t* idx, uint64_t n, int invert, char* out,
                                   size_t elmsz, uint64_t count, char* scratch);
 
+/* Bit#mask, reference: gen/tmpl_bit/mask.c:1, mask_kernel.cu:38-53.  The compaction of where, but a one at element
+ * i of the run (bit p + i*s of `a`, or p + idx[i]) appends to `out` the BYTE position of element i of the masked
+ * array: p2 + i*s2, or p2 + idx2[i].  `scratch` is a cumo_bit_where_scratch_new() block whose first cursor carries
+ * the output position from one launch to the next. */
+void cumo_bit_mask_kernel_launch(CUMO_BIT_DIGIT* a, size_t p, ssize_t s, size_t* idx, uint64_t n, size_t* out, size_t p2,
+                                 ssize_t s2, size_t* idx2, char* scratch);
+
 /* Single-precision matrix product on the tensor cores: C[M,N] = A[M,K] . Bt[N,K]^T, all row-major, leading
  * dimensions in elements.  Stands where the reference calls cublasSgemm for `a.dot(b)` on 2-D SFloat operands
  * (ext/cumo/narray/gen/tmpl/gemm.c:252-297); the reference has no kernel-launch entry of its own for it.
@@ -333,8 +361,10 @@ int cb200_kmeans_assign_sfloat_tc(const float* x, int64_t n, int d, const float*
  * allocator when they need the sum: a finalizer or other context in which the Ruby
  * extension's pool callback must not run the GC or raise, an embedder that handed out all
  * device memory at start-up, a loop that must not take the allocator's lock.  Same kernels
- * and same answers as cumo_sfloat_sum_kernel_launch; the [output][segment] partial sums
- * live in a fixed 1 MiB array inside the library image instead.
+ * as cumo_sfloat_sum_kernel_launch, with the [output][segment] partial sums in a fixed 1 MiB
+ * array inside the library image instead.  Its plan always cuts long rows into 32 KiB
+ * segments, so its sums agree with the regular entry point's to fp32 rounding (<= 1e-5
+ * relative to a float64 sum), not bit for bit.
  *   - accepts only reductions whose reduced axes form one contiguous run (a full sum of a
  *     contiguous array, sums along the last axes); needs outputs x segments <= 262144
  *     (a row is cut into 32 KiB segments, at most 8192 per row);
@@ -345,8 +375,9 @@ int cb200_kmeans_assign_sfloat_tc(const float* x, int64_t n, int d, const float*
  *     stream cb200_set_stream chose and does not call cumo_cuda_runtime_check_kernel_launch;
  *   - all calls on a device share the array: calls whose kernels may overlap on the GPU
  *     race on it, so keep them on one stream; nothing in it needs clearing between calls;
- *   - the first call on each device looks up the array's address with that device current
- *     (cudaGetSymbolAddress): make that first call before any stream capture begins. */
+ *   - the first call on each device, whatever its shape, looks up the array's address with
+ *     that device current (cudaGetSymbolAddress): make that first call before any stream
+ *     capture begins. */
 int cb200_sfloat_sum_noalloc_kernel_launch(cumo_na_reduction_arg_t* arg, char* errbuf, size_t errlen);
 
 #ifdef __cplusplus

@@ -91,3 +91,24 @@ def test_noalloc_sum_refuses_what_it_cannot_hold():
     arg = reduction_arg(_lib, m.t(), torch.empty((256,), device="cuda"), 1)
     rc = fn(byref(arg), err, len(err))
     assert rc == 1 and b"contiguous" in err.value
+
+
+def test_noalloc_sum_small_call_first_then_a_segmented_one():
+    """A short, unsegmented call followed by a long one that needs the shared array: the first call on a device,
+    whatever its shape, is the one that looks the array up, so a caller can warm up with any shape."""
+    import torch
+    from cumo_b200 import _lib
+
+    lib = _lib.load()
+    fn = lib.cb200_sfloat_sum_noalloc_kernel_launch
+    fn.restype = ctypes.c_int
+    fn.argtypes = [ctypes.POINTER(_lib.NaReductionArg), c_char_p, c_size_t]
+    err = create_string_buffer(256)
+    g = torch.Generator(device="cuda").manual_seed(11)
+    for n in (64, (1 << 21) + 5):
+        src = torch.rand((n,), device="cuda", generator=g)
+        got = torch.full((), float("nan"), device="cuda")
+        assert fn(byref(reduction_arg(_lib, src, got, 0)), err, len(err)) == 0, err.value.decode()
+        torch.cuda.synchronize()
+        ref = src.double().sum()
+        assert abs(got.double() - ref) <= FP32_SUM_TOL * ref

@@ -289,16 +289,16 @@ def kernel_table(torch, xp, peak):
                      "GBps": round(gbs, 1), "frac_of_measured": round(gbs / peak, 3), "frac_of_nominal": round(gbs / NOMINAL_HBM_GBS, 3),
                      "cpu_GBps_1thread_sample": cpu.get((config, name))})
     try:
-        ref = refplan_table(torch, FULL_SIZES)
+        ref = ref_gpu_table(torch, FULL_SIZES)
     except Exception as e:                           # the baseline leg must never take the product's numbers down with it
         ref = {}
-        print(f"refplan leg skipped: {e}", file=sys.stderr)
+        print(f"reference-kernel leg skipped: {e}", file=sys.stderr)
     for row in rows:
         ms = ref.get((row["config"], row["kernel"]))
         if ms:
-            row["refplan_ms"] = ms
-            row["refplan_GBps"] = round(row["bytes"] / (ms * 1e-3) / 1e9, 1)
-            row["speedup_vs_refplan"] = round(ms / row["ms"], 2)
+            row["ref_gpu_ms"] = ms
+            row["ref_gpu_GBps"] = round(row["bytes"] / (ms * 1e-3) / 1e9, 1)
+            row["speedup_vs_ref_gpu"] = round(ms / row["ms"], 2)
 
     # C5 (BASELINE config 4): k-means assignment, 2^24 points x 64-D against 256 centres, fused
     from cumo_b200 import kmeans
@@ -342,67 +342,109 @@ def kernel_table(torch, xp, peak):
     return rows
 
 
-def refplan_table(torch, S):
-    """The reference's execution plan (oracle/refplan_gpu.cu, a restatement: the reference's own kernels cannot be
-    generated without Ruby) timed on this GPU for the rows it covers: {(config, kernel): ms}."""
-    from oracle import refplan_gpu
+def ref_gpu_table(torch, S):
+    """The reference's OWN kernels (oracle/_ref/libcumo_ref_kernels.so: its templates expanded and compiled with the
+    same nvcc by oracle/build_ref_kernels.py) timed on this GPU with the descriptors its host code would build for the
+    same rows: {(config, kernel): ms}.  Empty when that library was never built."""
+    from oracle import ref_kernels
 
-    L = refplan_gpu.lib()
+    L = ref_kernels.lib()
+    if L is None:
+        return {}
+    sys.path.insert(0, str(ROOT / "tests"))
+    import abi_call as ac
+    from ctypes import byref, c_float, c_int, c_int32, c_size_t, c_ssize_t, c_uint64, c_void_p
+
     g = torch.Generator(device="cuda").manual_seed(0)
     out = {}
 
-    def t(config, name, fn, reps=5, check=None):
-        fn()
-        if check is not None:
-            torch.cuda.synchronize()
-            assert check(), f"refplan {config} {name}: wrong result"
+    def t(config, name, fn, reps=5):
         med, _ = time_kernel(torch, fn, reps=reps, warm=1)
+        if L.refk_last_error():
+            raise RuntimeError(f"reference kernel failed to launch: {config} {name}")
         out[(config, name)] = round(med, 4)
 
-    n = S["c1"][0]
-    a = torch.rand(n, n, device="cuda", generator=g) * 2 - 1
-    b = torch.rand(n, n, device="cuda", generator=g) * 2 - 1
-    col = torch.rand(n, 1, device="cuda", generator=g)
-    o = torch.empty_like(a)
-    vec = torch.empty(n, device="cuda")
-    idx = torch.empty(n, device="cuda", dtype=torch.int64)
-    scratch = torch.empty(max(n, S["c3_m"][1]) * 1024, device="cuda")
-    t("C1x16", "a*b", lambda: L.refplan_ew_f32(1, a.data_ptr(), b.data_ptr(), o.data_ptr(), 1, n * n, 0, 4, 0, 4, 0, 4), check=lambda: torch.equal(o, a * b))
-    t("C1x16", "a.sum(axis:1)", lambda: L.refplan_sum_rows_f32(a.data_ptr(), n, n, vec.data_ptr(), scratch.data_ptr()),
-      check=lambda: torch.allclose(vec, a.sum(dim=1), rtol=1e-4, atol=1e-2))
-    t("C1x16", "a + col(n,1)", lambda: L.refplan_ew_f32(0, a.data_ptr(), col.data_ptr(), o.data_ptr(), n, n, 4 * n, 4, 4, 0, 4 * n, 4), check=lambda: torch.equal(o, a + col))
-    t("C1x16", "c.sum(axis:0)", lambda: L.refplan_sum_cols_f32(a.data_ptr(), n, n, vec.data_ptr(), scratch.data_ptr()),
-      check=lambda: torch.allclose(vec, a.sum(dim=0), rtol=1e-4, atol=1e-2))
-    t("C1x16", "c.max_index(axis:1)", lambda: L.refplan_max_index_rows_f32(a.data_ptr(), n, n, idx.data_ptr()),
-      check=lambda: torch.equal(idx, a.argmax(dim=1) + torch.arange(n, device="cuda") * n))
-    del b, col
+    def ew(sym, x, y, o, shape):
+        ac.fn(L, sym)(byref(ac.iarray(x, shape)), byref(ac.iarray(y, shape)), byref(ac.iarray(o)), byref(ac.indexer(shape)), None)
+
+    def red(sym, src, dst, axes):
+        ac.fn(L, sym)(byref(ac.reduction_arg(src, dst, axes)))
+
+    for n, tag in ((S["c1"][0], "C1x16"), (S["c1"][1], "C1")):
+        a = torch.rand(n, n, device="cuda", generator=g) * 2 - 1
+        b = torch.rand(n, n, device="cuda", generator=g) * 2 - 1
+        col = torch.rand(n, 1, device="cuda", generator=g)
+        o = torch.empty_like(a)
+        vec = torch.empty(n, device="cuda")
+        idx = torch.empty(n, device="cuda", dtype=torch.int32)
+        t(tag, "a*b", lambda: ew("cumo_iter_sfloat_mul_kernel_launch", a.view(-1), b.view(-1), o.view(-1), (n * n,)))
+        t(tag, "a.sum(axis:1)", lambda: red("cumo_sfloat_sum_kernel_launch", a, vec, (1,)))
+        t(tag, "a + col(n,1)", lambda: ew("cumo_iter_sfloat_add_kernel_launch", a, col, o, (n, n)))
+        t(tag, "c.sum(axis:0)", lambda: red("cumo_sfloat_sum_kernel_launch", a, vec, (0,)))
+        t(tag, "c.max_index(axis:1)", lambda: red("cumo_sfloat_max_index_int32_kernel_launch", a, idx, (1,)))
+        del a, b, col, o
     r2, c2 = S["c2"]
     x, y = torch.randn(r2, 1, device="cuda", generator=g), torch.randn(1, c2, device="cuda", generator=g)
-    o2 = o.view(-1)[: r2 * c2].view(r2, c2)
-    t("C2", "x(R,1)+y(1,C)", lambda: L.refplan_ew_f32(0, x.data_ptr(), y.data_ptr(), o2.data_ptr(), r2, c2, 4, 0, 0, 4, 4 * c2, 4), check=lambda: torch.equal(o2, x + y))
-    src = a.view(-1)[: r2 * c2]
-    t("C2", "exp", lambda: L.refplan_ew_f32(2, src.data_ptr(), None, o2.data_ptr(), 1, r2 * c2, 0, 4, 0, 0, 0, 4))
-    t("C2", "*0.5", lambda: L.refplan_mul_scalar_f32(src.data_ptr(), 0.5, o2.data_ptr(), r2 * c2), check=lambda: torch.equal(o2.view(-1), src * 0.5))
+    tt = x + y
+    o2 = torch.empty_like(tt)
+    t("C2", "x(R,1)+y(1,C)", lambda: ew("cumo_iter_sfloat_add_kernel_launch", x, y, o2, (r2, c2)))
+    t("C2", "exp", lambda: ac.fn(L, "cumo_iter_sfloat_math_s_exp_kernel_launch")(byref(ac.iarray(tt.view(-1))), byref(ac.iarray(o2.view(-1))), byref(ac.indexer((r2 * c2,)))))
+    t("C2", "*0.5", lambda: ac.fn(L, "cumo_iter_sfloat_mul_s_kernel_launch")(byref(ac.iarray(tt.view(-1))), c_float(0.5), byref(ac.iarray(o2.view(-1))), byref(ac.indexer((r2 * c2,))), None, c_int(0)))
+    del tt, o2
     n3, (mr, mc) = S["c3_n"], S["c3_m"]
-    v = a.view(-1)[:n3].abs()
-    one = torch.empty(1, device="cuda")
-    t("C3", "f32 1-D sum", lambda: L.refplan_sum_rows_f32(v.data_ptr(), 1, n3, one.data_ptr(), scratch.data_ptr()),
-      check=lambda: abs(one.item() - v.sum(dtype=torch.float64).item()) <= 1e-4 * v.sum(dtype=torch.float64).item())
-    i1 = torch.empty(1, device="cuda", dtype=torch.int64)
-    t("C3", "f32 1-D argmax", lambda: L.refplan_max_index_rows_f32(v.data_ptr(), 1, n3, i1.data_ptr()), reps=2, check=lambda: i1.item() == int(v.argmax().item()))
-    vc, vr = torch.empty(mc, device="cuda"), torch.empty(mr, device="cuda")
-    t("C3", "f32 2-D sum(axis:0)", lambda: L.refplan_sum_cols_f32(v.data_ptr(), mr, mc, vc.data_ptr(), scratch.data_ptr()),
-      check=lambda: torch.allclose(vc, v.view(mr, mc).sum(dim=0), rtol=1e-4))
-    t("C3", "f32 2-D sum(axis:1)", lambda: L.refplan_sum_rows_f32(v.data_ptr(), mr, mc, vr.data_ptr(), scratch.data_ptr()),
-      check=lambda: torch.allclose(vr, v.view(mr, mc).sum(dim=1), rtol=1e-4))
-    n4 = S["c4_n"]
+    for dt, tname, tag in ((torch.float32, "sfloat", "f32"), (torch.float64, "dfloat", "f64")):
+        v = torch.rand(n3, device="cuda", generator=g, dtype=dt)
+        m = v.view(mr, mc)
+        for op in ("sum", "mean", "max", "min", "argmax"):
+            sym = f"cumo_{tname}_{op}_int32_kernel_launch" if op == "argmax" else f"cumo_{tname}_{op}_kernel_launch"
+            odt = torch.int32 if op == "argmax" else dt
+            one = torch.empty((), device="cuda", dtype=odt)
+            t("C3", f"{tag} 1-D {op}", lambda: red(sym, v, one, (0,)), reps=3)
+            for ax, n_out in ((0, mc), (1, mr)):
+                dst = torch.empty(n_out, device="cuda", dtype=odt)
+                t("C3", f"{tag} 2-D {op}(axis:{ax})", lambda: red(sym, m, dst, (ax,)), reps=3)
+        del v, m
+    n4, (ir, ic) = S["c4_n"], S["c4_m"]
     ia = torch.randint(-(1 << 20), 1 << 20, (n4,), device="cuda", dtype=torch.int32, generator=g)
+    ib = torch.randint(-(1 << 20), 1 << 20, (n4,), device="cuda", dtype=torch.int32, generator=g)
     io = torch.empty_like(ia)
-    bits = torch.zeros(n4 // 32, device="cuda", dtype=torch.int32)
+    flag = torch.zeros(1, device="cuda", dtype=torch.int32)
+    ix = ac.indexer((n4,))
+    t("C4", "a*3", lambda: ac.fn(L, "cumo_iter_int32_mul_s_kernel_launch")(byref(ac.iarray(ia)), c_int32(3), byref(ac.iarray(io)), byref(ix), None, c_int(0)))
+    t("C4", "+b", lambda: ew("cumo_iter_int32_add_kernel_launch", ia, ib, io, (n4,)))
+
+    def mod7():                                       # the reference's host reads the division-by-zero flag back after the launch
+        ac.fn(L, "cumo_iter_int32_mod_s_kernel_launch")(byref(ac.iarray(ia)), c_int32(7), byref(ac.iarray(io)), byref(ix), c_void_p(flag.data_ptr()), c_int(0))
+        torch.cuda.synchronize()
+    t("C4", "%7 (incl. the flag sync)", mod7)
+    words = torch.zeros(n4 // 32, device="cuda", dtype=torch.int32)
+    t("C4", "a>0 -> Bit", lambda: ac.fn(L, "cumo_iter_int32_gt_s_kernel_launch")(byref(ac.iarray(ia)), c_int32(0), byref(ac.bit_iarray(words)), byref(ix), c_int(0)), reps=3)
     cnt = torch.zeros(1, device="cuda", dtype=torch.int64)
-    t("C4", "a*3", lambda: L.refplan_mul_scalar_i32(ia.data_ptr(), 3, io.data_ptr(), n4), check=lambda: torch.equal(io, ia * 3))
-    t("C4", "a>0 -> Bit", lambda: L.refplan_gt_scalar_i32(ia.data_ptr(), 0, bits.data_ptr(), n4), reps=3)
-    t("C4", "count_true", lambda: L.refplan_count_true(bits.data_ptr(), n4, cnt.data_ptr()), reps=3, check=lambda: cnt.item() == int((ia > 0).sum().item()))
+    t("C4", "count_true", lambda: ac.fn(L, "cumo_iter_bit_count_true_stride_kernel_launch")(c_size_t(0), c_void_p(cnt.data_ptr()), c_void_p(words.data_ptr()), c_ssize_t(1), c_uint64(n4)), reps=3)
+    im = ia.view(ir, ic)
+    idx = torch.empty(ir, device="cuda", dtype=torch.int32)
+    t("C4", "max_index(axis:1)", lambda: red("cumo_int32_max_index_int32_kernel_launch", im, idx, (1,)))
+    s64 = torch.empty((), device="cuda", dtype=torch.int64)
+    t("C4", "Int32 sum -> Int64", lambda: red("cumo_int32_sum_kernel_launch", ia, s64, (0,)))
+    # the rows after the hot path: thrust scan, global-atomic histogram, compaction
+    v32 = torch.rand(n3, device="cuda", generator=g)
+    o32 = torch.empty_like(v32)
+    t("F", "f32 1-D cumsum", lambda: ac.fn(L, "cumo_sfloat_cumsum_kernel_launch", c_int)(c_void_p(v32.data_ptr()), c_void_p(o32.data_ptr()), c_ssize_t(4), c_ssize_t(4), c_uint64(n3)), reps=3)
+    del v32, o32
+    lab = torch.randint(0, 256, (n4,), device="cuda", dtype=torch.int32, generator=g)
+    counts = torch.empty(256, device="cuda", dtype=torch.int32)
+    oor, item = torch.zeros(1, device="cuda", dtype=torch.int32), torch.zeros(1, device="cuda", dtype=torch.int64)
+    t("F", "Int32 bincount (256 bins)", lambda: ac.fn(L, "cumo_iter_int32_bincount_32_kernel_launch")(c_void_p(lab.data_ptr()), c_ssize_t(4), None, c_uint64(n4), c_void_p(counts.data_ptr()), c_ssize_t(4),
+                                                                                                     c_uint64(256), c_void_p(oor.data_ptr()), c_void_p(item.data_ptr())), reps=3)
+    ac.fn(L, "cumo_iter_int32_gt_s_kernel_launch")(byref(ac.iarray(ia)), c_int32(0), byref(ac.bit_iarray(words)), byref(ix), c_int(0))
+    pos = torch.empty(n4, device="cuda", dtype=torch.int32)
+    new, free = ac.fn(L, "cumo_bit_where_scratch_new", c_void_p), ac.fn(L, "cumo_cuda_runtime_free")
+
+    def where():
+        scratch = new()
+        ac.fn(L, "cumo_bit_where_kernel_launch")(c_void_p(words.data_ptr()), c_size_t(0), c_ssize_t(1), None, c_uint64(n4), c_int(0), c_void_p(pos.data_ptr()), c_size_t(4), c_uint64(0), c_void_p(scratch))
+        free(c_void_p(scratch))
+    t("F", "Bit where (half set)", where, reps=3)
     return out
 
 

@@ -87,6 +87,8 @@ def _declare(lib: ctypes.CDLL) -> None:
         "cb200_na_cum": (H, [c_char_p, H, c_int, c_int]),
         "cb200_na_where": (H, [H, c_int]),
         "cb200_na_arg_with_value": (c_int, [c_char_p, H, c_uint32, c_int, POINTER(H), POINTER(H)]),
+        "cb200_na_take": (H, [H, c_int, H]),
+        "cb200_na_mask": (H, [H, H]),
         "cb200_na_count": (H, [H, c_uint32, c_int, c_int]),
         "cb200_na_mulsum": (H, [H, H, c_uint32, c_int, c_int]),
         "cb200_na_cast": (H, [H, c_int]),

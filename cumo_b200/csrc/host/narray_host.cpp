@@ -1140,4 +1140,99 @@ cb200_na_t* cb200_na_mulsum(cb200_na_t* a, cb200_na_t* b, uint32_t axis_mask, in
     return out;
 }
 
+// ---- index-array gather and Bit#mask --------------------------------------------------------------
+// Both end in the same-type store through an index array (cumo_iter_T_store_T_stridx_kernel_launch), which is how the
+// reference materialises a view that carries an index array (gen/tmpl/store_from.c:82-89).  The result here is the
+// contiguous copy; the reference hands back the view and copies when the view is next used.
+static bool stridx_copy(const cb200_na* dst, char* src_ptr, int dtype, int ndim, const int64_t* shape, const int64_t* src_step,
+                        int indexed_dim, size_t* index) {
+    using Fn = void (*)(cumo_na_iarray_stridx_t*, cumo_na_iarray_stridx_t*, cumo_na_indexer_t*);
+    Fn f = (Fn)sym(std::string("cumo_iter_") + kTypeName[dtype] + "_store_" + kTypeName[dtype] + "_stridx_kernel_launch");
+    if (!f) return false;
+    cumo_na_iarray_stridx_t d, s2;
+    cumo_na_indexer_t ix;
+    memset(&d, 0, sizeof d); memset(&s2, 0, sizeof s2); memset(&ix, 0, sizeof ix);
+    d.ptr = data_ptr(dst);
+    s2.ptr = src_ptr;
+    ix.ndim = (unsigned char)ndim;
+    ix.total_size = 1;
+    for (int i = 0; i < ndim; ++i) {
+        ix.shape[i] = (size_t)shape[i];
+        ix.total_size *= (size_t)shape[i];
+        d.stridx[i].stride = (ssize_t)((dst->step[i] << 1) | 1);
+        if (i == indexed_dim) s2.stridx[i].index = index;
+        else s2.stridx[i].stride = (ssize_t)((src_step[i] << 1) | 1);
+    }
+    f(&d, &s2, &ix);
+    return launch_ok();
+}
+
+cb200_na_t* cb200_na_take(cb200_na_t* a, int axis, cb200_na_t* idx) {
+    if (!is_value_type(a->dtype)) return (cb200_na*)fail("TypeError", "take needs a numeric array");
+    if (idx->dtype != CB200_INT32 && idx->dtype != CB200_INT64) return (cb200_na*)fail("TypeError", "the index array must be Int32 or Int64");
+    if (axis < 0) axis += a->ndim;
+    if (axis < 0 || axis >= a->ndim || idx->ndim != 1) return (cb200_na*)fail("IndexError", "take: axis %d of a %d-d array, %d-d index", axis, a->ndim, idx->ndim);
+    // byte offsets = positions * step of the axis, computed by the library's own kernels
+    cb200_na* wide = cast_to(idx, CB200_INT64);
+    if (!wide) return nullptr;
+    cb200_na* off = cb200_na_binary_scalar("mul", wide, 0.0, a->step[axis], 0);
+    cb200_na_release(wide);
+    if (!off) return nullptr;
+    int64_t shape[kMaxD];
+    for (int i = 0; i < a->ndim; ++i) shape[i] = a->shape[i];
+    shape[axis] = idx->shape[0];
+    cb200_na* out = make(a->dtype, a->ndim, shape, false);
+    bool ok = out != nullptr;
+    if (ok && size_of(out) > 0) ok = stridx_copy(out, data_ptr(a), a->dtype, a->ndim, shape, a->step, axis, reinterpret_cast<size_t*>(data_ptr(off)));
+    cb200_na_release(off);
+    if (!ok) { cb200_na_release(out); return nullptr; }
+    return out;
+}
+
+cb200_na_t* cb200_na_mask(cb200_na_t* bits, cb200_na_t* a) {
+    if (bits->dtype != CB200_BIT) return (cb200_na*)fail("TypeError", "mask needs a Bit array");
+    if (!is_value_type(a->dtype)) return (cb200_na*)fail("TypeError", "mask needs a numeric array to select from");
+    if (bits->ndim != a->ndim) return (cb200_na*)fail("ShapeError", "mask and masked arrays must have the same shape");
+    for (int i = 0; i < a->ndim; ++i)
+        if (bits->shape[i] != a->shape[i]) return (cb200_na*)fail("ShapeError", "mask and masked arrays must have the same shape");
+    int64_t hits = 0;
+    if (size_of(bits) > 0) {                       // the count sizes the result: one read-back, as in the reference (mask.c:122)
+        cb200_na* c = cb200_na_count(bits, 0, 0, 0);
+        if (!c) return nullptr;
+        uint64_t v = 0;
+        const bool ok = cb200_na_read_host(c, &v, 8) == 0;
+        cb200_na_release(c);
+        if (!ok) return nullptr;
+        hits = (int64_t)v;
+    }
+    cb200_na* out = make(a->dtype, 1, &hits, false);
+    if (!out || hits == 0) return out;
+    cb200_na* pos = make(CB200_INT64, 1, &hits, false);           // byte positions of the kept elements (size_t)
+    if (!pos) { cb200_na_release(out); return nullptr; }
+    using FnNew = char* (*)();
+    using FnRun = void (*)(CUMO_BIT_DIGIT*, size_t, ssize_t, size_t*, uint64_t, size_t*, size_t, ssize_t, size_t*, char*);
+    FnNew fnew = (FnNew)sym("cumo_bit_where_scratch_new");
+    FnRun frun = (FnRun)sym("cumo_bit_mask_kernel_launch");
+    char* scratch = fnew && frun ? fnew() : nullptr;
+    if (!scratch) { cb200_na_release(out); cb200_na_release(pos); if (fnew && frun) fail("CudaError", "no memory for the mask scratch"); return nullptr; }
+    StrideLoop L;
+    L.nd = a->ndim;
+    for (int i = 0; i < a->ndim; ++i) { L.n[i] = a->shape[i]; L.s[0][i] = bits->step[i]; L.s[1][i] = a->step[i]; }
+    if (L.nd == 0) { L.nd = 1; L.n[0] = 1; L.s[0][0] = L.s[1][0] = 0; }
+    contract(&L, 2);
+    const int in = L.nd - 1;
+    CUMO_BIT_DIGIT* words = reinterpret_cast<CUMO_BIT_DIGIT*>(bits->st->ptr);
+    for_outer(L, 2, [&](const int64_t* off) {
+        frun(words, (size_t)(bits->offset + off[0]), (ssize_t)L.s[0][in], nullptr, (uint64_t)L.n[in], reinterpret_cast<size_t*>(data_ptr(pos)),
+             (size_t)(a->offset + off[1]), (ssize_t)L.s[1][in], nullptr, scratch);
+    });
+    cumo_cuda_runtime_free(scratch);
+    bool ok = launch_ok();
+    const int64_t no_step = 0;
+    if (ok) ok = stridx_copy(out, a->st->ptr, a->dtype, 1, &hits, &no_step, 0, reinterpret_cast<size_t*>(data_ptr(pos)));
+    cb200_na_release(pos);
+    if (!ok) { cb200_na_release(out); return nullptr; }
+    return out;
+}
+
 }  // extern "C"

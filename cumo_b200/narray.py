@@ -291,9 +291,22 @@ class NArray:
         return NArray._from_handle(h, keep=self._keep)
 
     def __getitem__(self, key):
-        """Integers, slices (any step), None (new axis) and Ellipsis; `True` means `:` as in Ruby."""
+        """Integers, slices (any step), None (new axis) and Ellipsis; `True` means `:` as in Ruby.  One list or
+        integer array among the keys picks positions along that axis (`a[[5, 0, 3], true]`), and a Bit array of
+        the same shape selects where it is one (`a[mask]`); both return the copy that the reference makes when
+        such a view is next used (gen/tmpl/store_from.c:82-89, gen/tmpl_bit/mask.c:95-140)."""
+        if isinstance(key, Bit):
+            return key.mask(self)
         if not isinstance(key, tuple):
             key = (key,)
+        picks = [i for i, k in enumerate(key) if isinstance(k, (list, np.ndarray, NArray))]
+        if picks:
+            if len(picks) > 1:
+                raise IndexError("one index array per expression on this path")
+            at = picks[0]
+            axis = sum(1 for k in key[:at] if k is not None and k is not Ellipsis and (k is True or not isinstance(k, int)))
+            rest = tuple(True if i == at else k for i, k in enumerate(key))
+            return self[rest].take(key[at], axis)
         shp, stp = self.shape, self.steps
         n_real = sum(1 for k in key if k is not None and k is not Ellipsis)
         if n_real > len(shp):
@@ -321,6 +334,17 @@ class NArray:
         while d < len(shp):
             out_shape.append(shp[d]); out_steps.append(stp[d]); d += 1
         return self._view(out_shape, out_steps, off)
+
+    def take(self, index, axis=0):
+        """The elements at `index` (a list or an Int32/Int64 array of positions, negative ones counting from the end)
+        along `axis`, as a new array."""
+        if not isinstance(index, NArray):
+            pos = np.asarray(index, dtype=np.int64)
+            n = self.shape[axis]
+            if pos.size and (pos.min() < -n or pos.max() >= n):
+                raise IndexError(f"index out of range for extent {n}")
+            index = Int64.from_numpy(np.where(pos < 0, pos + n, pos))
+        return NArray._from_handle(_lib.load().cb200_na_take(self._h, int(axis), index._h))
 
     def transpose(self, *perm):
         shp, stp = self.shape, self.steps
@@ -582,6 +606,10 @@ class Bit(NArray):
         """(positions of the ones, positions of the zeros)."""
         lib = _lib.load()
         return NArray._from_handle(lib.cb200_na_where(self._h, 0)), NArray._from_handle(lib.cb200_na_where(self._h, 1))
+
+    def mask(self, array):
+        """The elements of `array` (same shape) where this mask is one, in row-major order, as a 1-D array."""
+        return NArray._from_handle(_lib.load().cb200_na_mask(self._h, array._h))
 
     def count_true(self, axis=None, keepdims=False):
         return NArray._from_handle(_lib.load().cb200_na_count(self._h, _axis_mask(axis, self.ndim), int(keepdims), 0))

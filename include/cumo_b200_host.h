@@ -104,6 +104,12 @@ cb200_na_t* cb200_na_bincount(cb200_na_t* a, cb200_na_t* weight, int64_t minleng
 /* max_index / min_index / argmax / argmin together with the winning value, one pass; the index array is Int64.
  * Not a method of the reference: it exists for the sharded (multi-GPU) reductions. */
 int cb200_na_arg_with_value(const char* op, cb200_na_t* a, uint32_t axis_mask, int nan, cb200_na_t** out_index, cb200_na_t** out_value);
+/* `a[idx, true]`-style selection along one axis (narray/index.c index arrays + the store through an index array,
+ * gen/tmpl/store_from.c:82-89): positions from a 1-D Int32/Int64 device array, not range-checked; returns the copy. */
+cb200_na_t* cb200_na_take(cb200_na_t* a, int axis, cb200_na_t* idx);
+/* Bit#mask (gen/tmpl_bit/mask.c:95-140): the elements of `a` where `bits` (same shape) is one, row-major order, as a
+ * 1-D array of a's type.  Reads the count back to size the result: synchronises. */
+cb200_na_t* cb200_na_mask(cb200_na_t* bits, cb200_na_t* a);
 /* count_true / count_false of a Bit array -> UInt64 */
 cb200_na_t* cb200_na_count(cb200_na_t* a, uint32_t axis_mask, int keepdims, int want_false);
 /* mulsum(a, b, axis...) = (a*b).sum(axis...) in one pass over the inputs */

@@ -36,7 +36,10 @@ BIT_TEMPLATES = {"bit_count", "where", "mask"}
 TYPES = ("sfloat", "dfloat", "int32", "int64", "bit")
 
 NVCC_FLAGS = ["-gencode", "arch=compute_100,code=sm_100", "-O3", "-std=c++17", "-Xcompiler", "-fPIC",
-              "-DHAVE_STDINT_H", "-DHAVE_STDBOOL_H", "-DHAVE_TYPE_BOOL", "-DHAVE_SYS_TYPES_H", "-w"]
+              "-DHAVE_STDINT_H", "-DHAVE_STDBOOL_H", "-DHAVE_TYPE_BOOL", "-DHAVE_SYS_TYPES_H",
+              # what the extension's own configure step finds on Linux/glibc (ext/cumo/extconf.rb:140 have_func("exp10")):
+              # with it m_exp10 is exp10(x), without it pow(10, x) (types/float_macro_kernel.h:96-100)
+              "-DHAVE_EXP10", "-w"]
 
 
 def _nvcc() -> str:

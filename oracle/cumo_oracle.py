@@ -147,6 +147,25 @@ def pow_int(a, exponent: int):
     return out
 
 
+def pow_int32(base, exponent):
+    """x ** e with an Int32 exponent by repeated multiplication; either side may be an array (the exponent an int32
+    array) or a host numeric: the array forms of gen/tmpl/pow_kernel.cu:22-32 and its `_s` / `_s_left` forms."""
+    arr = base if _is_array(base) else None
+    exp = np.ascontiguousarray(exponent, dtype=np.int32) if _is_array(exponent) else None
+    like = arr if arr is not None else exp
+    dtype = arr.dtype if arr is not None else np.dtype(type(base)) if isinstance(base, np.generic) else None
+    if dtype is None:
+        raise TypeError("a scalar base must be a numpy scalar of the element type")
+    shape = like.shape
+    out = np.zeros(shape, dtype=dtype)
+    sv_f, sv_i = _scalar_args(base if arr is None else 0, dtype)
+    lib().oracle_pow_int32(DT[np.dtype(dtype)], len(shape), _i64(shape), arr.ctypes.data if arr is not None else None,
+                           _i64(arr.strides) if arr is not None else _i64([]), exp.ctypes.data if exp is not None else None,
+                           _i64(exp.strides) if exp is not None else _i64([]), out.ctypes.data, _i64(out.strides), sv_f, sv_i,
+                           0 if exp is not None else int(exponent))
+    return out
+
+
 def reduce(op, a, axis=None, nan=False, keepdims=False, idx64=None):
     """Reduction of `a` (any strides) over `axis` (None: all).  For max_index/min_index the
     answer is the element offset from a's first element in units of elements, which for a

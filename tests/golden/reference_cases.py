@@ -473,4 +473,218 @@ def case_cumsum_cumprod_carry_nan(xp):
             assert tags(b.cumprod(nan=True).to_a()) == tags(_running_skip_nan(muls, lambda x, y: x * y)), (n, at)
 
 
+# ---- test/narray_test.rb:3449-3486 (assert_reductions) and :4329-4363 ------------------------------------
+# "reductions reach every element of an axis that is not the innermost".  The reference folds its expectations in
+# Ruby from the view's own nested list, so that a wrong address cannot cancel out between the two sides; the same
+# fold is done here in plain Python.  Its inputs are Ruby shuffles of 1..n (Random.new(4649), Random.new(57)); a
+# fixed permutation of the same numbers stands in, since any permutation exercises the same addresses.
+def _fold_axes(nested, shape, axes, f):
+    """Fold the nested list over `axes` with f, keeping the other axes (row-major), as a flat list."""
+    import itertools
+
+    nd = len(shape)
+    keep = [d for d in range(nd) if d not in axes]
+
+    def at(idx):
+        v = nested
+        for i in idx:
+            v = v[i]
+        return v
+    out = []
+    for ko in itertools.product(*[range(shape[d]) for d in keep]):
+        acc = None
+        for ro in itertools.product(*[range(shape[d]) for d in axes]):
+            idx = [0] * nd
+            for d, i in zip(keep, ko):
+                idx[d] = i
+            for d, i in zip(axes, ro):
+                idx[d] = i
+            v = at(idx)
+            acc = v if acc is None else f(acc, v)
+        out.append(acc)
+    return out
+
+
+def _flat(x):
+    return [y for v in x for y in _flat(v)] if isinstance(x, list) else [x]
+
+
+def _assert_reductions(view, what, axes=None):
+    nested = view.to_a()
+    shape = list(view.shape)
+    nd = len(shape)
+    flat = _flat(nested)
+    strides = [1] * nd
+    for i in range(nd - 2, -1, -1):
+        strides[i] = strides[i + 1] * shape[i + 1]
+    # position of every element in the row-major flattening of the VIEW: what max_index / min_index answer with
+    counter = iter(range(len(flat)))
+
+    def number(x):
+        return [number(v) for v in x] if isinstance(x, list) else next(counter)
+    positions = number(nested)
+    if axes is None:
+        axes = [[i] for i in range(nd)] + [list(range(nd))]
+    for ax in axes:
+        tag = f"{what} axis {ax}"
+        lo = _fold_axes(nested, shape, ax, lambda x, y: x if x < y else y)
+        hi = _fold_axes(nested, shape, ax, lambda x, y: y if x < y else x)
+        kw = {"axis": ax}
+        assert _flat(view.sum(**kw).to_a()) == _fold_axes(nested, shape, ax, lambda x, y: x + y), "sum of " + tag
+        assert _flat(view.min(**kw).to_a()) == lo, "min of " + tag
+        assert _flat(view.max(**kw).to_a()) == hi, "max of " + tag
+        assert _flat(view.ptp(**kw).to_a()) == [h - l for h, l in zip(hi, lo)], "ptp of " + tag
+        got_lo, got_hi = view.minmax(**kw)
+        assert _flat(got_lo.to_a()) == lo and _flat(got_hi.to_a()) == hi, "minmax of " + tag
+        at_hi = _fold_axes(positions, shape, ax, lambda p, q: q if flat[p] < flat[q] else p)
+        at_lo = _fold_axes(positions, shape, ax, lambda p, q: q if flat[q] < flat[p] else p)
+        assert _flat(view.max_index(**kw).to_a()) == at_hi, "max_index of " + tag
+        assert _flat(view.min_index(**kw).to_a()) == at_lo, "min_index of " + tag
+        if len(ax) == 1:
+            along = lambda p: (p // strides[ax[0]]) % shape[ax[0]]
+            assert _flat(view.argmax(axis=ax[0]).to_a()) == [along(p) for p in at_hi], "argmax of " + tag
+            assert _flat(view.argmin(axis=ax[0]).to_a()) == [along(p) for p in at_lo], "argmin of " + tag
+
+
+def _permutation(n, seed):
+    """A fixed permutation of 1..n: the numbers ordered by a multiplicative hash of themselves."""
+    return sorted(range(1, n + 1), key=lambda i: ((i + seed) * 2654435761) % 4294967291)
+
+
+def case_reductions_over_view_kinds(xp):
+    rows, cols = 9, 7
+    src = xp.Int32.cast(_permutation(rows * cols, 4649)).reshape(rows, cols)
+    idx = [5, 0, 3, 8, 1]
+    views = {
+        "contiguous": lambda a: a,
+        "column slice": lambda a: a[True, 1:cols - 1],
+        "reversed": lambda a: a[True, ::-1],
+        "row stride": lambda a: a[0:rows:2, True],
+        "index view": lambda a: a[idx, True],
+        "transpose": lambda a: a.transpose(),
+    }
+    for what, take in views.items():
+        _assert_reductions(take(src), what)
+    # a 5-d shape runs past the dimension-specialised accessors
+    deep = [2, 3, 2, 2, 3]
+    n = 72
+    a = xp.Int32.cast(_permutation(n, 57)).reshape(*deep)
+    _assert_reductions(a, "5-d")
+    _assert_reductions(a.transpose(), "5-d transpose")
+    _assert_reductions(a[True, [2, 0], True, True, True], "5-d index view")
+    # long enough for the reduce axis to be split across a second launch
+    big = xp.Int32(3000, 33).seq()
+    _assert_reductions(big, "3000x33", axes=[[0], [1]])
+    _assert_reductions(big[True, 0:33:2], "3000x33 column slice", axes=[[0], [1]])
+    _assert_reductions(big.transpose(), "3000x33 transpose", axes=[[0], [1]])
+
+
+# ---- test/narray_test.rb:5088-5161 "the nan-aware reductions skip NaN, and min and max answer NaN" ----------------
+def _close(got, want, label):
+    g, w = _flat(got.to_a()) if hasattr(got, "to_a") else [got], _flat(want.to_a()) if hasattr(want, "to_a") else [want]
+    assert len(g) == len(w), label
+    for i, (x, y) in enumerate(zip(g, w)):
+        if isinstance(y, float) and math.isnan(y):
+            assert isinstance(x, float) and math.isnan(x), f"{label}[{i}]: expected NaN, got {x!r}"
+        else:
+            assert abs(x - y) <= abs(y) * 1e-5 + 1e-5, f"{label}[{i}]: {x!r} vs {y!r}"
+
+
+def case_nan_aware_reductions(xp):
+    for T in float_types(xp):
+        with_nan = T.cast([3.0, -1.0, NAN, 1.0, 5.0])
+        kept = T.cast([3.0, -1.0, 1.0, 5.0])
+        for op in ("sum", "prod", "mean", "var", "stddev", "rms"):
+            _close(getattr(with_nan, op)(nan=True), getattr(kept, op)(), f"{T.__name__} {op}")
+        for op in ("min", "max", "ptp"):
+            _close(getattr(with_nan, op)(nan=True), NAN, f"{T.__name__} {op}")
+        lo, hi = with_nan.minmax(nan=True)
+        _close(lo, NAN, "minmax min")
+        _close(hi, NAN, "minmax max")
+        none = T.cast([NAN] * 4)
+        _close(none.sum(nan=True), 0, "sum of all NaN")
+        _close(none.prod(nan=True), 1, "prod of all NaN")
+        _close(none.var(nan=True), 0, "var of all NaN")
+        _close(none.stddev(nan=True), 0, "stddev of all NaN")
+        for op in ("mean", "rms", "min", "max", "ptp"):
+            _close(getattr(none, op)(nan=True), NAN, f"{op} of all NaN")
+    # whole rows are NaN, so the answer is the plain reduction over the rows that are left
+    T = xp.DFloat
+    base_rows = [[float(r * 40 + c + 1) for c in range(40)] for r in range(6)]
+    nan_rows = [1, 4]
+    kept_rows = [r for r in range(6) if r not in nan_rows]
+    a = T.cast([[NAN] * 40 if r in nan_rows else base_rows[r] for r in range(6)])
+    kept = T.cast([base_rows[r] for r in kept_rows])
+    for op in ("sum", "mean", "var", "stddev", "rms"):
+        _close(getattr(a, op)(axis=0, nan=True), getattr(kept, op)(axis=0), f"{op} axis 0")
+        _close(getattr(a, op)(nan=True), getattr(kept, op)(), f"{op} flat")
+        _close(getattr(a.transpose(), op)(axis=1, nan=True), getattr(kept.transpose(), op)(axis=1), f"{op} transposed")
+    all_nan = T.cast([NAN] * 40)
+    for op in ("min", "max", "ptp"):
+        _close(getattr(a, op)(axis=0, nan=True), all_nan, f"{op} axis 0")
+        _close(getattr(a.transpose(), op)(axis=1, nan=True), all_nan, f"{op} transposed")
+    lo, hi = a.minmax(axis=0, nan=True)
+    _close(lo, all_nan, "minmax axis 0 min")
+    _close(hi, all_nan, "minmax axis 0 max")
+    for op in ("min", "max", "ptp"):
+        _close(getattr(kept, op)(axis=0, nan=True), getattr(kept, op)(axis=0), f"{op} axis 0 without nan")
+
+
+# ---- test/narray_test.rb:5163-5197 "a boolean mask reaches every element of a view and no others", and the literal
+# mask cases of test/bit_test.rb:37,69 --------------------------------------------------------------------------
+def case_boolean_mask(xp):
+    bits = xp.Bit.cast([0, 1, 1, 0, 1, 0, 0, 1])
+    assert bits.mask(xp.DFloat[1, 2, 3, 4, 5, 6, 7, 8]).to_a() == [2, 3, 5, 8]
+    bits2 = xp.Bit.cast([[0, 1, 1, 0], [1, 0, 0, 1]])
+    assert bits2.mask(xp.DFloat[[1, 2, 3, 4], [5, 6, 7, 8]]).to_a() == [2, 3, 5, 8]
+
+    def check(label, a, m):
+        flat, sel = _flat(a.to_a()), _flat(m.to_a())
+        assert a[m].to_a() == [v for v, b in zip(flat, sel) if b == 1], label
+    # around a word of bits, and around the size the loop is split at
+    for n in (7, 31, 32, 33, 1000, 8191, 8192, 8193, 40_000):
+        a = xp.DFloat(n).seq()
+        check(f"1d n={n} half", a, a.gt(n // 2))
+        check(f"1d n={n} none", a, a.gt(n * 2))
+        check(f"1d n={n} all", a, a.ge(0))
+        check(f"1d n={n} alternating", a, (a % 2).eq(0))
+    cols = 2_000                                   # (the reference uses rows of 20 000)
+    base = xp.DFloat(8, cols).seq()
+    order = [(i * 7919 + 13) % cols for i in range(cols)]          # a fixed permutation: 7919 and 2000 are coprime
+    views = {
+        "contiguous": base,
+        "column slice": base[True, 0:cols:2],
+        "reversed": base[True, ::-1],
+        "index array on the outer axis": base[[7, 0, 3, 5, 1], True],
+        "index array on the innermost axis": base[True, order],
+        "transposed": base.transpose(),
+    }
+    for label, v in views.items():
+        check(label, v, v.gt(8_000))
+        check(label + " on a reversed mask", v, v.reverse().gt(8_000))
+
+
+# ---- test/narray_test.rb:2858-2866 "a bit count over more than 2**32 bits" (a GPU-sized case: the oracle run of it
+# would take minutes, so it lives in tests/test_gpu_large_index.py) -------------------------------------------------
+
+
+# ---- test/cumo_test.rb:55-147: every documented reduction stays a 0-d array; Float()/Integer() read it -------------
+def case_zero_dimensional_results(xp):
+    a = xp.DFloat[3, 1, 7]
+    ones = xp.DFloat[1, 1, 1]
+    floats = [a.sum(), a.prod(), a.mean(), a.var(), a.stddev(), a.rms(), a.min(), a.max(), a.ptp(), a.mulsum(ones)]
+    ints = [a.max_index(), a.min_index(), a.argmax(), a.argmin(), (a > 2).count_true(), (a > 2).count_false()]
+    for r in floats + ints:
+        assert r.ndim == 0 and r.size == 1
+    assert [float(r) for r in floats[:3]] == [11.0, 21.0, 11.0 / 3]
+    assert [int(r) for r in ints] == [2, 1, 2, 1, 2, 1]
+    b = xp.DFloat[5, 2]
+    assert float(b.sum()) == 7.0 and int(b.max_index()) == 0
+    lo, hi = a.minmax()
+    assert lo.ndim == 0 and lo.to_a() == 1.0 and hi.to_a() == 7.0
+    m = xp.DFloat[[3, 1], [7, 2]]
+    lo, hi = m.minmax(axis=1)
+    assert lo.to_a() == [1.0, 2.0] and hi.to_a() == [3.0, 7.0]
+
+
 ALL_CASES = [v for k, v in sorted(globals().items()) if k.startswith("case_")]

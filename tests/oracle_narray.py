@@ -83,6 +83,8 @@ class ONArray:
 
     # views
     def __getitem__(self, key):
+        if isinstance(key, OBit):
+            return key.mask(self)
         if not isinstance(key, tuple):
             key = (key,)
         key = tuple(slice(None) if k is True else k for k in key)
@@ -304,6 +306,10 @@ class OBit:
 
     def where2(self):
         return ONArray._wrap(orc.where(self.b)), ONArray._wrap(orc.where(self.b, invert=True))
+
+    def mask(self, array):
+        """gen/tmpl_bit/mask.c:45-81 (the host loop): the masked array's elements at the one bits, row-major."""
+        return ONArray._wrap(np.array(array.a)[self.b])
 
     def __getitem__(self, key):
         return OBit(self.b[key])

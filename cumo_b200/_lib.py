@@ -74,6 +74,7 @@ def _declare(lib: ctypes.CDLL) -> None:
         "cb200_na_set_inplace": (None, [H, c_int]),
         "cb200_na_store_host": (c_int, [H, c_void_p, c_size_t]),
         "cb200_na_read_host": (c_int, [H, c_void_p, c_size_t]),
+        "cb200_na_read_host_async": (c_int, [H, c_void_p, c_size_t, c_void_p]),
         "cb200_synchronize": (c_int, []),
         "cb200_na_binary": (H, [c_char_p, H, H]),
         "cb200_na_binary_scalar": (H, [c_char_p, H, c_double, c_int64, c_int]),
@@ -87,6 +88,13 @@ def _declare(lib: ctypes.CDLL) -> None:
         "cb200_na_cum": (H, [c_char_p, H, c_int, c_int]),
         "cb200_na_where": (H, [H, c_int]),
         "cb200_na_arg_with_value": (c_int, [c_char_p, H, c_uint32, c_int, POINTER(H), POINTER(H)]),
+        "cb200_na_arg_with_value_into": (c_int, [c_char_p, H, c_uint32, c_int, c_int64, c_void_p, c_void_p, POINTER(H), POINTER(H)]),
+        "cb200_sfloat_rank_fold_sum_kernel_launch": (None, [c_void_p, c_int64, c_int, c_int64, c_double, c_void_p]),
+        "cb200_dfloat_rank_fold_sum_kernel_launch": (None, [c_void_p, c_int64, c_int, c_int64, c_double, c_void_p]),
+        "cb200_sfloat_rank_fold_arg_kernel_launch": (None, [c_void_p, c_void_p, c_int64, c_int, c_int64, c_int, c_int, c_void_p, c_void_p]),
+        "cb200_dfloat_rank_fold_arg_kernel_launch": (None, [c_void_p, c_void_p, c_int64, c_int, c_int64, c_int, c_int, c_void_p, c_void_p]),
+        "cb200_int32_rank_fold_arg_kernel_launch": (None, [c_void_p, c_void_p, c_int64, c_int, c_int64, c_int, c_int, c_void_p, c_void_p]),
+        "cb200_int64_rank_fold_arg_kernel_launch": (None, [c_void_p, c_void_p, c_int64, c_int, c_int64, c_int, c_int, c_void_p, c_void_p]),
         "cb200_na_take": (H, [H, c_int, H]),
         "cb200_na_mask": (H, [H, H]),
         "cb200_na_count": (H, [H, c_uint32, c_int, c_int]),

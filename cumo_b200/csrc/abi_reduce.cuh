@@ -24,22 +24,23 @@ static inline CB_C reduce_length(const cumo_na_reduction_arg_t* arg) {
 // (max|min)_index feed the element offset, arg(max|min) the position along the axes
 #define DEF_INDEX(name, IS_MAX, NANW)                                                  \
     extern "C" void CB_RED(name##_int32)(cumo_na_reduction_arg_t* arg) {                \
-        launch_reduce(arg, nullptr, red::ArgMinMax<CB_C, IS_MAX, NANW>{0}, 1); }        \
+        launch_reduce(arg, nullptr, red::ArgMinMax<CB_C, IS_MAX, NANW>{0, 0}, 1); }        \
     extern "C" void CB_RED(name##_int64)(cumo_na_reduction_arg_t* arg) {                \
-        launch_reduce(arg, nullptr, red::ArgMinMax<CB_C, IS_MAX, NANW>{1}, 1); }
+        launch_reduce(arg, nullptr, red::ArgMinMax<CB_C, IS_MAX, NANW>{1, 0}, 1); }
 #define DEF_ARG(name, IS_MAX, NANW)                                                    \
     extern "C" void CB_RED(name##_int32)(cumo_na_reduction_arg_t* arg) {                \
-        launch_reduce(arg, nullptr, red::ArgMinMax<CB_C, IS_MAX, NANW>{0}, 0); }        \
+        launch_reduce(arg, nullptr, red::ArgMinMax<CB_C, IS_MAX, NANW>{0, 0}, 0); }        \
     extern "C" void CB_RED(name##_int64)(cumo_na_reduction_arg_t* arg) {                \
-        launch_reduce(arg, nullptr, red::ArgMinMax<CB_C, IS_MAX, NANW>{1}, 0); }
+        launch_reduce(arg, nullptr, red::ArgMinMax<CB_C, IS_MAX, NANW>{1, 0}, 0); }
 
 // Index and value from one pass (no reference counterpart: the reference has no multi-GPU
-// reductions, whose per-rank partial is exactly this pair).  Indices are int64_t.
+// reductions, whose per-rank partial is exactly this pair).  Indices are int64_t; index_base is added to each
+// (the shard's offset in the global array).
 #define CB_VSYM_(t, name) cb200_##t##_##name##_with_value_kernel_launch
 #define CB_VSYM(t, name) CB_VSYM_(t, name)
 #define DEF_WITH_VALUE(name, IS_MAX, NANW, FLAT)                                                           \
-    extern "C" void CB_VSYM(CB_T, name)(cumo_na_reduction_arg_t* arg, cumo_na_iarray_t* values) {           \
-        launch_reduce(arg, values, red::ArgMinMax<CB_C, IS_MAX, NANW>{1}, FLAT); }
+    extern "C" void CB_VSYM(CB_T, name)(cumo_na_reduction_arg_t* arg, cumo_na_iarray_t* values, int64_t index_base) { \
+        launch_reduce(arg, values, red::ArgMinMax<CB_C, IS_MAX, NANW>{1, index_base}, FLAT); }
 DEF_WITH_VALUE(max_index, true, false, 1)
 DEF_WITH_VALUE(min_index, false, false, 1)
 DEF_WITH_VALUE(argmax, true, false, 0)

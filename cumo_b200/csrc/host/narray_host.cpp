@@ -516,6 +516,21 @@ int cb200_na_read_host(cb200_na_t* a, void* host, size_t bytes) {
     return cuda_ok(cudaStreamSynchronize(cb200::current_stream()), "cudaStreamSynchronize") ? 0 : 1;
 }
 
+// The copy runs on `copy_stream`, behind everything queued so far on the launch stream (an event), so the launch
+// stream is free to start the next block's kernels while this block's result is still on its way to the host.
+int cb200_na_read_host_async(cb200_na_t* a, void* host, size_t bytes, void* copy_stream) {
+    if (!is_contiguous(a)) { fail("ValueError", "read_host needs a contiguous array"); return 1; }
+    if (a->dtype == CB200_BIT && (a->offset & 31)) { fail("ValueError", "read_host needs a word-aligned Bit array"); return 1; }
+    if (bytes != buffer_bytes(a->dtype, size_of(a))) { fail("ValueError", "read_host: %zu bytes given, %zu expected", bytes, buffer_bytes(a->dtype, size_of(a))); return 1; }
+    const char* src = a->dtype == CB200_BIT ? a->st->ptr + a->offset / 8 : data_ptr(a);
+    cudaStream_t cs = (cudaStream_t)copy_stream;
+    thread_local cudaEvent_t ev = nullptr;
+    if (!ev && !cuda_ok(cudaEventCreateWithFlags(&ev, cudaEventDisableTiming), "cudaEventCreate")) return 1;
+    if (!cuda_ok(cudaEventRecord(ev, cb200::current_stream()), "cudaEventRecord")) return 1;
+    if (!cuda_ok(cudaStreamWaitEvent(cs, ev, 0), "cudaStreamWaitEvent")) return 1;
+    return cuda_ok(cudaMemcpyAsync(host, src, bytes, cudaMemcpyDeviceToHost, cs), "cudaMemcpyAsync D2H") ? 0 : 1;
+}
+
 int cb200_synchronize(void) { return cuda_ok(cudaStreamSynchronize(cb200::current_stream()), "cudaStreamSynchronize") ? 0 : 1; }
 
 cb200_na_t* cb200_na_cast(cb200_na_t* a, int dtype) { return cast_to(a, dtype); }
@@ -1017,8 +1032,11 @@ cb200_na_t* cb200_na_bincount(cb200_na_t* a, cb200_na_t* weight, int64_t minleng
     return out;
 }
 
-// index (Int64) and winning value from one pass: the per-GPU partial of a sharded arg reduction
-int cb200_na_arg_with_value(const char* op_c, cb200_na_t* a, uint32_t axis_mask, int nan, cb200_na_t** out_index, cb200_na_t** out_value) {
+// index (Int64) and winning value from one pass: the per-GPU partial of a sharded arg reduction.  The results go
+// into `idx_out` / `val_out` when those are given (contiguous device buffers of the output's size, e.g. the two
+// halves of a buffer that a collective then sends), else into new arrays returned through out_index / out_value.
+int cb200_na_arg_with_value_into(const char* op_c, cb200_na_t* a, uint32_t axis_mask, int nan, int64_t index_base, void* idx_out, void* val_out,
+                                 cb200_na_t** out_index, cb200_na_t** out_value) {
     std::string op = op_c;
     if (!is_value_type(a->dtype)) { fail("TypeError", "%s is not defined for %s", op_c, kTypeName[a->dtype]); return 1; }
     const bool index_op = op == "max_index" || op == "min_index";
@@ -1029,10 +1047,13 @@ int cb200_na_arg_with_value(const char* op_c, cb200_na_t* a, uint32_t axis_mask,
     cb200_na* copy = nullptr;
     if (index_op && !is_contiguous(a)) { copy = cast_to(a, a->dtype); if (!copy) return 1; }
     const cb200_na* in = copy ? copy : a;
-    cb200_na* oi = make(CB200_INT64, rp.n_keep, rp.out_shape, false);
-    cb200_na* ov = oi ? make(a->dtype, rp.n_keep, rp.out_shape, false) : nullptr;
+    int64_t ostep_i[kMaxD], ostep_v[kMaxD];
+    contiguous_steps(CB200_INT64, rp.n_keep, rp.out_shape, ostep_i);
+    contiguous_steps(a->dtype, rp.n_keep, rp.out_shape, ostep_v);
+    cb200_na* oi = (idx_out && val_out) ? cb200_na_wrap(CB200_INT64, rp.n_keep, rp.out_shape, ostep_i, idx_out, 0) : make(CB200_INT64, rp.n_keep, rp.out_shape, false);
+    cb200_na* ov = !oi ? nullptr : (idx_out && val_out) ? cb200_na_wrap(a->dtype, rp.n_keep, rp.out_shape, ostep_v, val_out, 0) : make(a->dtype, rp.n_keep, rp.out_shape, false);
     if (!ov) { cb200_na_release(oi); cb200_na_release(copy); return 1; }
-    using Fn = void (*)(cumo_na_reduction_arg_t*, cumo_na_iarray_t*);
+    using Fn = void (*)(cumo_na_reduction_arg_t*, cumo_na_iarray_t*, int64_t);
     Fn f = (Fn)sym(std::string("cb200_") + kTypeName[a->dtype] + "_" + op + ((nan && is_float_type(a->dtype)) ? "_nan" : "") + "_with_value_kernel_launch");
     bool ok = f != nullptr;
     if (ok) {
@@ -1042,14 +1063,18 @@ int cb200_na_arg_with_value(const char* op_c, cb200_na_t* a, uint32_t axis_mask,
         memset(&values, 0, sizeof values);
         values.ptr = data_ptr(ov);
         for (int i = 0; i < rp.n_keep; ++i) values.step[i] = (ssize_t)ov->step[i];
-        f(&arg, &values);
+        f(&arg, &values, index_base);
         ok = launch_ok();
     }
     cb200_na_release(copy);
     if (!ok) { cb200_na_release(oi); cb200_na_release(ov); return 1; }
-    *out_index = oi;
-    *out_value = ov;
+    if (out_index) *out_index = oi; else cb200_na_release(oi);
+    if (out_value) *out_value = ov; else cb200_na_release(ov);
     return 0;
+}
+
+int cb200_na_arg_with_value(const char* op_c, cb200_na_t* a, uint32_t axis_mask, int nan, cb200_na_t** out_index, cb200_na_t** out_value) {
+    return cb200_na_arg_with_value_into(op_c, a, axis_mask, nan, 0, nullptr, nullptr, out_index, out_value);
 }
 
 cb200_na_t* cb200_na_count(cb200_na_t* a, uint32_t axis_mask, int keepdims, int want_false) {

@@ -234,6 +234,7 @@ struct ArgMinMax {
     static constexpr bool kIndexed = true;
     static constexpr bool kHasScan = true;
     int idx64;
+    int64_t base = 0;          // added to every index written (a shard's offset in the global array)
     // A thread's private scan of a run visited in increasing index order.  A strict
     // comparison keeps the earlier of two equal elements, so no index is ever compared,
     // and the position is a 32-bit offset into the thread's segment.  The scan starts from
@@ -283,8 +284,8 @@ struct ArgMinMax {
     }
     // out2, when given, receives the winning value beside its index
     __device__ __forceinline__ void store(char* out, char* out2, Acc a) const {
-        if (idx64) *reinterpret_cast<int64_t*>(out) = a.index;
-        else *reinterpret_cast<int32_t*>(out) = (int32_t)a.index;
+        if (idx64) *reinterpret_cast<int64_t*>(out) = a.index + base;
+        else *reinterpret_cast<int32_t*>(out) = (int32_t)(a.index + base);
         if (out2) *reinterpret_cast<T*>(out2) = a.value;
     }
 };

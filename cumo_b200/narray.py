@@ -151,6 +151,12 @@ class NArray:
             _raise_last()
         return out
 
+    def read_into_host_async(self, ptr: int, nbytes: int, copy_stream: int):
+        """Queue the copy of this (contiguous) array into pinned host memory on `copy_stream` (a cudaStream_t handle),
+        behind the kernels queued so far; the caller keeps both alive and synchronises that stream before reading."""
+        if _lib.load().cb200_na_read_host_async(self._h, c_void_p(ptr), nbytes, c_void_p(copy_stream)):
+            _raise_last()
+
     @classmethod
     def from_torch(cls, t):
         """Borrow a CUDA tensor's memory (no copy); the tensor is kept alive by the view."""

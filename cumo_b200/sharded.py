@@ -10,13 +10,17 @@ never read another GPU's memory; what crosses NVLink is a few bytes per output:
     is replicated);
   * integer sums and Bit counts: per-rank partial -> all_reduce(SUM) on int64, exact
     and order independent;
-  * float sums/means: per-rank partial, widened to float64, all_gather, folded in
-    rank order by the library's own float64 sum kernel, so the result does not
-    depend on NCCL's algorithm choice;
-  * min/max and the index reductions: all_gather of the per-rank answers, folded by
-    the library's own min/max/arg kernels, whose rules (a NaN loses unless all are
-    NaN; ties go to the lowest global index) then hold across ranks exactly as
-    they hold across CTAs;
+  * float sums/means: per-rank partial, all_gather, added up in float64 in rank
+    order by the library's rank-fold kernel and rounded once, so the result does
+    not depend on NCCL's algorithm choice;
+  * min/max: all_gather of the per-rank answers, folded by the library's own
+    min/max kernels;
+  * index reductions: every rank writes {global index, value} of its shard in ONE
+    pass into one buffer, one all_gather moves it, and the library's rank-fold
+    kernel merges the `world` candidates per output with the same total order
+    the single-GPU kernels use (a NaN loses unless all are NaN; ties go to the
+    lowest global index), so the rules hold across ranks exactly as they hold
+    across CTAs.  Nothing is read back to the host on the way;
   * an axis-0 reduction of a row-sharded matrix folds per-column partial vectors the
     same way; an axis-1 reduction is local, and flat (max|min)_index answers get the
     shard's element offset added.
@@ -75,6 +79,16 @@ class Comm:
             out[0].copy_(src)
         return self._from_torch(out, type(arr))
 
+    def all_gather_bytes(self, buf):
+        """`buf`: this rank's contiguous torch tensor -> a (world, *buf.shape) tensor of everyone's, rank order."""
+        import torch
+        out = torch.empty((self.world,) + tuple(buf.shape), dtype=buf.dtype, device=buf.device)
+        if self.dist:
+            self.dist.all_gather_into_tensor(out.view(-1), buf.view(-1), group=self.group)
+        else:
+            out[0].copy_(buf)
+        return out
+
     def all_reduce_sum(self, arr):
         """Exact integer sum over ranks (Int64 / UInt64 containers)."""
         import torch
@@ -99,6 +113,10 @@ class ShardedArray:
     @classmethod
     def scatter_from_numpy(cls, comm: Comm, array_type, host: np.ndarray):
         """Every rank passes the same host array (or a memmap); each uploads only its own rows."""
+        if host.shape[0] < comm.world:
+            # decided from the global shape alone, so every rank raises here, before any collective: a rank with
+            # no rows could not take part in the reductions, and the others would wait for it
+            raise ValueError(f"{host.shape[0]} rows cannot be sharded over {comm.world} ranks: every rank needs at least one row")
         start, count = partition(host.shape[0], comm.world, comm.rank)
         return cls(comm, array_type.from_numpy(np.ascontiguousarray(host[start:start + count])), host.shape[0], start)
 
@@ -141,11 +159,22 @@ class ShardedArray:
         part = self.local.sum(axis=axis, nan=nan) if self._is_float() else self.local.sum(axis=axis)
         if not self._is_float():
             return comm.all_reduce_sum(part)
+        n = float(self.global_rows * self._row_elems() if axis is None else self.global_rows) if mean else 0.0
+        if comm.on_gpu:
+            # one gather of the partials as they are, one kernel that adds them in float64 in rank order
+            import torch
+            from . import _lib
+            T = type(self.local)
+            src = torch.as_tensor(part if part.contiguous() else part.dup(), device="cuda")
+            gathered = comm.all_gather_bytes(src)
+            out = T(*part.shape)
+            fold = getattr(_lib.load(), f"cb200_{T.__name__.lower()}_rank_fold_sum_kernel_launch")
+            fold(gathered.data_ptr(), src.numel() * src.element_size(), comm.world, src.numel(), n, out.data_ptr)
+            return out
         wide = xp.DFloat.cast(part)                       # float32 partials are widened before they meet
-        total = comm.all_gather(wide).sum(axis=0)          # rank-order fold by the float64 sum kernel
+        total = comm.all_gather(wide).sum(axis=0)          # rank-order fold in float64
         if mean:
-            n = self.global_rows * self._row_elems() if axis is None else self.global_rows
-            total = total / float(n)
+            total = total / n
         return type(self.local).cast(total)
 
     def mean(self, axis=None):
@@ -174,12 +203,11 @@ class ShardedArray:
             if flat:
                 idx = xp.Int64.cast(idx) + self.row_start * self._row_elems()
             return self._like(idx)
+        base = self.row_start * self._row_elems() if (axis is None or flat) else self.row_start      # local -> global index
+        if comm.on_gpu:
+            return self._arg_on_gpu(name_local, want_max, axis, nan, base)
         idx, val = self.local.arg_with_value(name_local, axis=axis, **kw)     # one pass: Int64 index and its value
-        # local -> global index
-        if axis is None or flat:
-            idx = idx + self.row_start * self._row_elems()
-        else:
-            idx = idx + self.row_start
+        idx = idx + base
         vals = comm.all_gather(val)                       # [world] or [world, C]
         idxs = comm.all_gather(idx)
         winner = getattr(vals, "argmax" if want_max else "argmin")(axis=0, **kw)   # lowest rank wins ties
@@ -188,6 +216,30 @@ class ShardedArray:
         cand = np.asarray(idxs.to_numpy(), dtype=np.int64)
         picked = np.take_along_axis(cand, w[None, ...], axis=0)[0]
         return xp.Int64.cast(picked)
+
+    def _arg_on_gpu(self, name_local, want_max, axis, nan, base):
+        """{global index, value} of this shard in one pass into one buffer -> one all_gather -> the library's rank fold.
+        Everything is queued on the stream; nothing comes back to the host."""
+        import torch
+        from ctypes import byref, c_void_p
+        from . import _lib
+        from .narray import _axis_mask, _raise_last
+
+        comm, lib, loc = self.comm, _lib.load(), self.local
+        T = type(loc)
+        n_out = int(np.prod(loc.shape[1:], dtype=np.int64)) if axis == 0 else 1
+        es = 4 if T.__name__ in ("SFloat", "Int32") else 8
+        # [n_out int64 indices | n_out values], the value part starting on a 16-byte boundary
+        val_off = (n_out * 8 + 15) // 16 * 16
+        buf = torch.empty(val_off + (n_out * es + 15) // 16 * 16, dtype=torch.uint8, device="cuda")
+        if lib.cb200_na_arg_with_value_into(name_local.encode(), loc._h, _axis_mask(axis, loc.ndim), int(bool(nan)), int(base),
+                                            c_void_p(buf.data_ptr()), c_void_p(buf.data_ptr() + val_off), None, None):
+            _raise_last()
+        gathered = comm.all_gather_bytes(buf)
+        out = comm.xp.Int64(*(loc.shape[1:] if axis == 0 else ()))
+        fold = getattr(lib, f"cb200_{T.__name__.lower()}_rank_fold_arg_kernel_launch")
+        fold(gathered.data_ptr(), gathered.data_ptr() + val_off, buf.numel(), comm.world, n_out, int(want_max), int(bool(nan)), out.data_ptr, None)
+        return out
 
     def argmax(self, axis=None, nan=False): return self._arg(True, axis, nan, False)
     def argmin(self, axis=None, nan=False): return self._arg(False, axis, nan, False)

@@ -184,10 +184,11 @@ const char* cb200_version(void);
 
 /* Index reductions that also write the winning value (same descriptor as the entry above,
  * indices as int64_t; `values` has the layout of arg->out with the element type of the input).
+ * `index_base` is added to every index (a shard's offset in the global array).
  * NOT in the reference: it is the per-GPU partial {value, index} of a sharded arg reduction,
  * produced in one pass over the data. */
 #define CB200_DECL_ACCUM_IDX_VALUE(T, C, op) \
-    void cb200_##T##_##op##_with_value_kernel_launch(cumo_na_reduction_arg_t* arg, cumo_na_iarray_t* values);
+    void cb200_##T##_##op##_with_value_kernel_launch(cumo_na_reduction_arg_t* arg, cumo_na_iarray_t* values, int64_t index_base);
 
 /* mulsum, reference: gen/tmpl/accum_binary.c:4-5, accum_binary_kernel.cu:69-92.
  * `_reduce_`: *p3 += sum_i x[i]*y[i];  plain: p3[i] += x[i]*y[i] (all steps in bytes). */
@@ -316,6 +317,20 @@ void cumo_bit_mask_kernel_launch(CUMO_BIT_DIGIT* a, size_t p, ssize_t s, size_t*
  * alignment, nothing launched; 3/4: launch; 5: an in-kernel bounded wait ran out).  Synchronises the stream. */
 int cb200_sgemm_nt_tc(int64_t M, int64_t N, int64_t K, const float* A, int64_t lda, const float* Bt, int64_t ldb,
                       float* C, int64_t ldc, char* errbuf, size_t errlen);
+
+/* Rank-order folds of per-GPU partials (no counterpart in the reference, which has no multi-GPU code): the last
+ * step of a row-sharded reduction.  The partials of all ranks lie `rank_stride` bytes apart (an all_gather's
+ * output), n_out values per rank.
+ *   sum: partials of the element type are added in float64 in rank order, divided by `divisor` unless it is 0
+ *        (mean), rounded once to the element type;
+ *   arg: {values[r][o], indices[r][o]} pairs are merged with the single-GPU kernels' own total order (NaN rule,
+ *        better value, lower index), out_value may be NULL.  Indices are int64_t. */
+void cb200_sfloat_rank_fold_sum_kernel_launch(const char* partials, int64_t rank_stride, int world, int64_t n_out, double divisor, char* out);
+void cb200_dfloat_rank_fold_sum_kernel_launch(const char* partials, int64_t rank_stride, int world, int64_t n_out, double divisor, char* out);
+#define CB200_DECL_FOLD_ARG(T) \
+    void cb200_##T##_rank_fold_arg_kernel_launch(const char* indices, const char* values, int64_t rank_stride, int world, int64_t n_out, \
+                                                 int is_max, int nan_wins, int64_t* out_index, char* out_value);
+CB200_DECL_FOLD_ARG(sfloat) CB200_DECL_FOLD_ARG(dfloat) CB200_DECL_FOLD_ARG(int32) CB200_DECL_FOLD_ARG(int64)
 
 /* kahan_sum exists for the double-precision type only (reference: gen/spec.rb:321-323,
  * float_accum_kernel.cu:196-206). */

@@ -65,6 +65,9 @@ void cb200_na_set_inplace(cb200_na_t* a, int on);      /* `x.inplace`: the next 
  * `host` is pinned; read synchronises the stream. */
 int cb200_na_store_host(cb200_na_t* a, const void* host, size_t bytes);
 int cb200_na_read_host(cb200_na_t* a, void* host, size_t bytes);
+/* The same read queued on `copy_stream` (a cudaStream_t) behind the work queued so far on the launch stream; does not
+ * synchronise: the caller keeps `a` and `host` (pinned) alive and synchronises copy_stream before reading `host`. */
+int cb200_na_read_host_async(cb200_na_t* a, void* host, size_t bytes, void* copy_stream);
 int cb200_synchronize(void);
 
 /* ---- operations (names are the reference's method names) ---- */
@@ -104,6 +107,11 @@ cb200_na_t* cb200_na_bincount(cb200_na_t* a, cb200_na_t* weight, int64_t minleng
 /* max_index / min_index / argmax / argmin together with the winning value, one pass; the index array is Int64.
  * Not a method of the reference: it exists for the sharded (multi-GPU) reductions. */
 int cb200_na_arg_with_value(const char* op, cb200_na_t* a, uint32_t axis_mask, int nan, cb200_na_t** out_index, cb200_na_t** out_value);
+/* The same with `index_base` added to every index (a shard's offset in the global array) and, when idx_out and
+ * val_out are given, the results written into those contiguous device buffers (e.g. the two halves of a buffer
+ * that a collective sends next); out_index / out_value may then be NULL. */
+int cb200_na_arg_with_value_into(const char* op, cb200_na_t* a, uint32_t axis_mask, int nan, int64_t index_base, void* idx_out, void* val_out,
+                                 cb200_na_t** out_index, cb200_na_t** out_value);
 /* `a[idx, true]`-style selection along one axis (narray/index.c index arrays + the store through an index array,
  * gen/tmpl/store_from.c:82-89): positions from a 1-D Int32/Int64 device array, not range-checked; returns the copy. */
 cb200_na_t* cb200_na_take(cb200_na_t* a, int axis, cb200_na_t* idx);

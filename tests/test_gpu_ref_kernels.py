@@ -582,22 +582,26 @@ def test_where_and_mask(libs):
         where = ac.fn(L, "cumo_bit_where_kernel_launch")
         mask = ac.fn(L, "cumo_bit_mask_kernel_launch")
         outs = []
-        for p, s, idx in ((0, 1, None), (37, 1, None), (5, 2, None), (3, 0, bit_idx)):
+        for p, s, idx in ((0, 1, None), (27, 1, None), (5, 2, None), (3, 0, bit_idx)):
             for invert in (0, 1):
                 for elmsz, dt in ((4, torch.int32), (8, torch.int64)):
                     scratch = new()
                     out = torch.full((n + 1,), -7, device="cuda", dtype=dt)
-                    half = n // 3
-                    # two launches continue one result: the cursor lives in the scratch
+                    half = (n // 3) // 32 * 32
+                    # two launches continue one result: the cursor lives in the scratch.  The second run starts `half * s`
+                    # bits further on, given as a word pointer moved on by whole words with the same small bit position:
+                    # the reference's contiguous path shifts a word by the full position (types/bit_kernel.h:45-52 with
+                    # where_kernel.cu:69), so it only serves positions inside the first word, and the comparison stays there;
+                    # positions beyond it are checked against the host-loop semantics in test_gpu_abi_more.py.
                     where(c_void_p(words.data_ptr()), c_size_t(p), c_ssize_t(s), c_void_p(idx.data_ptr() if idx is not None else None), c_uint64(half), c_int(invert),
                           c_void_p(out.data_ptr()), c_size_t(elmsz), c_uint64(0), c_void_p(scratch))
                     if idx is None:
-                        where(c_void_p(words.data_ptr()), c_size_t(p + half * s), c_ssize_t(s), None, c_uint64(n - half), c_int(invert),
+                        where(c_void_p(words.data_ptr() + 4 * (half * s // 32)), c_size_t(p), c_ssize_t(s), None, c_uint64(n - half), c_int(invert),
                               c_void_p(out.data_ptr()), c_size_t(elmsz), c_uint64(half), c_void_p(scratch))
                     torch.cuda.synchronize()
                     free(c_void_p(scratch))
                     outs.append(out)
-        for p, s, idx, p2, s2, idx2 in ((0, 1, None, 16, 8, None), (37, 1, None, 0, -8, None), (3, 0, bit_idx, 0, 0, byte_idx), (5, 2, None, 24, 0, byte_idx)):
+        for p, s, idx, p2, s2, idx2 in ((0, 1, None, 16, 8, None), (27, 1, None, 0, -8, None), (3, 0, bit_idx, 0, 0, byte_idx), (5, 2, None, 24, 0, byte_idx)):
             scratch = new()
             out = torch.full((n + 1,), -7, device="cuda", dtype=torch.int64)
             base = 8 * n if s2 < 0 else p2

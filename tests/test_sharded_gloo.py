@@ -77,6 +77,13 @@ def _worker(rank, world, port, out_dir):
         want = ((fm * 3 + fm) % 7).to_a()[start:start + count]
         assert expr.local.to_a() == want
         assert (sm > 0).count_true().extract() == int((mat > 0).sum())
+        # fewer rows than ranks: every rank refuses from the global shape alone, before any collective
+        try:
+            ShardedArray.scatter_from_numpy(comm, xp.SFloat, np.zeros((world - 1, 3), np.float32))
+            raise AssertionError("a shard without rows was accepted")
+        except ValueError as e:
+            assert "at least one row" in str(e)
+        dist.barrier()                               # all ranks got here: nobody is stuck in a collective
         (Path(out_dir) / f"ok{rank}").write_text("ok")
     finally:
         dist.destroy_process_group()

@@ -39,8 +39,8 @@ BYTES_STEP = BYTES_ADD + BYTES_EXP + BYTES_MUL
 METRIC = "effective HBM GB/s, fp32 broadcast-elementwise chain x(8192,1)+y(1,16384) -> exp -> *0.5"
 NOMINAL_HBM_GBS = 8000.0
 FALLBACK_HBM_GBS = 6650.0
-# dram__bytes_read.sum + dram__bytes_write.sum of one ew_row_kernel<Exp<float>,4> launch on this
-# workload (profiles/kernel_counters_512MiB.md, row "exp": the same 512 MiB in / 512 MiB out launch).
+# dram__bytes_read.sum + dram__bytes_write.sum of one ew_row_kernel<Exp<float>,4> launch on this workload, from one
+# ncu capture of `bench.py --case exp --mib 512` (the same 512 MiB in / 512 MiB out launch); the line says so.
 EXP_KERNEL_DRAM_TRAFFIC_BYTES = 536890624 + 485002240
 
 
@@ -163,9 +163,9 @@ def time_kernel(torch, fn, reps=10, warm=2):
     return float(np.median(ts)), float(np.min(ts))
 
 
-FULL_SIZES = {"c1": (16384, 4096), "c2": (R, C), "c3_n": 1 << 28, "c3_m": (65536, 4096), "c4_n": 1 << 27, "c4_m": (32768, 4096), "c5": (1 << 24, 64, 256)}
+FULL_SIZES = {"t": 16384, "c1": (16384, 4096), "c2": (R, C), "c3_n": 1 << 28, "c3_m": (65536, 4096), "c4_n": 1 << 27, "c4_m": (32768, 4096), "c5": (1 << 24, 64, 256)}
 # what the single-threaded CPU leg runs: the same kernels on arrays of a few MiB (the oracle streams at a few GB/s at best)
-CPU_SAMPLE_SIZES = {"c1": (1024, 512), "c2": (256, C), "c3_n": 1 << 22, "c3_m": (1024, 4096), "c4_n": 1 << 22, "c4_m": (1024, 4096), "c5": (4096, 64, 256)}
+CPU_SAMPLE_SIZES = {"t": 1024, "c1": (1024, 512), "c2": (256, C), "c3_n": 1 << 22, "c3_m": (1024, 4096), "c4_n": 1 << 22, "c4_m": (1024, 4096), "c5": (4096, 64, 256)}
 
 
 def kernel_rows(X, arr, S, copies=1):
@@ -225,6 +225,14 @@ def kernel_rows(X, arr, S, copies=1):
     im = arr("i32", (ir, ic))
     yield "C4", "max_index(axis:1)", ir * ic * 4 + ir * 4, lambda: im.max_index(axis=1)
     yield "C4", "Int32 sum -> Int64", s + 8, lambda: ia.sum()
+    # T: operands whose contiguous axes differ (a transposed operand), 1 GiB per array at full size
+    nt = S["t"]
+    ta, tb, ti = arr("f32_pm1", (nt, nt)), arr("f32_pm1", (nt, nt)), arr("i32", (nt, nt))
+    st = nt * nt * 4
+    yield "T", "a + b.transpose", 3 * st, lambda: ta + tb.transpose()
+    yield "T", "b.transpose.dup", 2 * st, lambda: tb.transpose().dup()
+    yield "T", "SFloat.cast(i32.transpose)", 2 * st, lambda: X.SFloat.cast(ti.transpose())
+    del ta, tb, ti
     # F: the rows after the hot path (scan, histogram, compaction), same sizes
     v32 = arr("f32_01", (n3,))
     yield "F", "f32 1-D cumsum", 2 * n3 * 4, lambda: v32.cumsum()
@@ -300,6 +308,13 @@ def kernel_table(torch, xp, peak):
             row["ref_gpu_GBps"] = round(row["bytes"] / (ms * 1e-3) / 1e9, 1)
             row["speedup_vs_ref_gpu"] = round(ms / row["ms"], 2)
 
+    # managed memory, which is what every buffer of the reference is (its pool hands out cudaMallocManaged blocks):
+    # exp and sum on buffers prefetched to the device, beside the cudaMalloc rows above
+    try:
+        rows += managed_rows(torch, xp, peak)
+    except Exception as e:
+        print(f"managed-memory rows skipped: {e}", file=sys.stderr)
+
     # C5 (BASELINE config 4): k-means assignment, 2^24 points x 64-D against 256 centres, fused
     from cumo_b200 import kmeans
     n, d, k = FULL_SIZES["c5"]
@@ -340,6 +355,50 @@ def kernel_table(torch, xp, peak):
                  "TFLOPs_issued_tf32": round(6.0 * gm ** 3 / (med * 1e-3) / 1e12, 1),
                  "cublas_fp32_ms": round(med_lib, 4), "cublas_fp32_TFLOPs": round(2.0 * gm ** 3 / (med_lib * 1e-3) / 1e12, 1)})
     return rows
+
+
+def managed_rows(torch, xp, peak):
+    from cuda.bindings import runtime as rt
+
+    n = 1 << 28
+    nbytes = n * 4
+    ptrs = []
+    for _ in range(2):
+        err, p = rt.cudaMallocManaged(nbytes, rt.cudaMemAttachGlobal)
+        if err != rt.cudaError_t.cudaSuccess:
+            raise RuntimeError(f"cudaMallocManaged: {err}")
+        ptrs.append(int(p))
+    try:
+        loc = rt.cudaMemLocation()
+        loc.type = rt.cudaMemLocationType.cudaMemLocationTypeDevice
+        loc.id = torch.cuda.current_device()
+        for p in ptrs:
+            try:
+                (err,) = rt.cudaMemPrefetchAsync(p, nbytes, loc, 0, 0)
+            except TypeError:
+                (err,) = rt.cudaMemPrefetchAsync(p, nbytes, loc.id, 0)
+            if err != rt.cudaError_t.cudaSuccess:
+                raise RuntimeError(f"cudaMemPrefetchAsync: {err}")
+        torch.cuda.synchronize()
+        a = xp.SFloat.from_device_pointer(ptrs[0], (n,))
+        o = xp.SFloat.from_device_pointer(ptrs[1], (n,))
+        a.fill(0.5)
+        o.fill(0.0)
+        xp.synchronize()
+        out = []
+        for name, fn, nb in (("exp, 2^28 f32 read from managed memory (prefetched)", lambda: xp.NMath.exp(a), 2 * nbytes),
+                             ("sum, 2^28 f32 in managed memory (prefetched)", lambda: o.sum(), nbytes + 4)):
+            med, best = time_kernel(torch, fn, reps=10)
+            gbs = nb / (med * 1e-3) / 1e9
+            out.append({"config": "M", "kernel": name, "bytes": int(nb), "ms": round(med, 4), "ms_min": round(best, 4), "GBps": round(gbs, 1),
+                        "frac_of_measured": round(gbs / peak, 3), "frac_of_nominal": round(gbs / NOMINAL_HBM_GBS, 3)})
+        del a, o
+        xp.synchronize()
+        return out
+    finally:
+        torch.cuda.synchronize()
+        for p in ptrs:
+            rt.cudaFree(p)
 
 
 def ref_gpu_table(torch, S):
@@ -426,6 +485,15 @@ def ref_gpu_table(torch, S):
     t("C4", "max_index(axis:1)", lambda: red("cumo_int32_max_index_int32_kernel_launch", im, idx, (1,)))
     s64 = torch.empty((), device="cuda", dtype=torch.int64)
     t("C4", "Int32 sum -> Int64", lambda: red("cumo_int32_sum_kernel_launch", ia, s64, (0,)))
+    nt = S["t"]
+    ta = torch.rand(nt, nt, device="cuda", generator=g)
+    tb = torch.rand(nt, nt, device="cuda", generator=g)
+    to = torch.empty_like(ta)
+    t("T", "a + b.transpose", lambda: ew("cumo_iter_sfloat_add_kernel_launch", ta, tb.t(), to, (nt, nt)), reps=3)
+    t("T", "b.transpose.dup", lambda: ac.fn(L, "cumo_iter_sfloat_store_sfloat_kernel_launch")(byref(ac.iarray(to)), byref(ac.iarray(tb.t())), byref(ac.indexer((nt, nt)))), reps=3)
+    ti = ia.new_empty((nt, nt)).copy_(tb * 1000)
+    t("T", "SFloat.cast(i32.transpose)", lambda: ac.fn(L, "cumo_iter_sfloat_store_int32_kernel_launch")(byref(ac.iarray(to)), byref(ac.iarray(ti.t())), byref(ac.indexer((nt, nt)))), reps=3)
+    del ta, tb, to, ti
     # the rows after the hot path: thrust scan, global-atomic histogram, compaction
     v32 = torch.rand(n3, device="cuda", generator=g)
     o32 = torch.empty_like(v32)
@@ -581,7 +649,8 @@ def run_ours(args):
                         "note": "a step cannot be shorter than its 512 MiB device->host copy; copy_alone is that copy timed by itself with all ranks copying at once"},
                 "roofline": {"bound": "hbm", "kernel": "ew_row_kernel<Exp<float>,4>", "achieved": achieved, "peak": peak, "peak_kind": peak_kind,
                              "unit": "GB/s", "frac": achieved / peak, "frac_of_nominal_8TBps": achieved / NOMINAL_HBM_GBS,
-                             "traffic": EXP_KERNEL_DRAM_TRAFFIC_BYTES, "algorithmic_bytes_per_launch": BYTES_EXP, "ms_per_launch": med},
+                             "traffic": EXP_KERNEL_DRAM_TRAFFIC_BYTES, "traffic_origin": "ncu dram__bytes_read.sum + dram__bytes_write.sum, one launch of `bench.py --case exp --mib 512`",
+                             "algorithmic_bytes_per_launch": BYTES_EXP, "ms_per_launch": med},
                 "chain_frac_of_peak": value / world / peak,
                 "repeat_blocks": {"blocks": len(block_ms), "steps_per_block": args.steps, "ms_per_step_median": float(np.median(block_ms)) / args.steps,
                                   "ms_per_step_min": float(np.min(block_ms)) / args.steps, "ms_per_step_max": float(np.max(block_ms)) / args.steps,
@@ -685,6 +754,119 @@ def sharded_section(torch, dist, xp, rank, world):
     return out
 
 
+def build_cases(xp, torch, mib: int):
+    g = torch.Generator(device="cuda").manual_seed(0)
+    n32 = mib * (1 << 20) // 4
+    n64 = mib * (1 << 20) // 8
+    cols = 4096
+    rows32, rows64 = max(1, n32 // cols), max(1, n64 // cols)
+    cache = {}
+
+    def f32():
+        if "f32" not in cache:
+            cache["f32"] = xp.SFloat.from_torch(torch.rand(rows32 * cols, device="cuda", generator=g) * 2 - 1)
+        return cache["f32"]
+
+    def f64():
+        if "f64" not in cache:
+            cache["f64"] = xp.DFloat.from_torch(torch.rand(rows64 * cols, device="cuda", dtype=torch.float64, generator=g))
+        return cache["f64"]
+
+    def i32():
+        if "i32" not in cache:
+            cache["i32"] = xp.Int32.from_torch(torch.randint(-(1 << 20), 1 << 20, (rows32 * cols,), device="cuda", dtype=torch.int32, generator=g))
+        return cache["i32"]
+
+    def outer():
+        r = max(1, n32 // 16384)
+        x = xp.SFloat.from_torch(torch.randn(r, 1, device="cuda", generator=g))
+        y = xp.SFloat.from_torch(torch.randn(1, 16384, device="cuda", generator=g))
+        return x, y
+
+    def col():
+        a = f32().reshape(rows32, cols)
+        return a, a.sum(axis=1).reshape(rows32, 1)
+
+    side = int((rows32 * cols) ** 0.5) // 64 * 64
+
+    def sq():
+        return f32()[0:side * side].reshape(side, side)
+
+    def sq2():
+        if "sq2" not in cache:
+            cache["sq2"] = xp.SFloat.from_torch(torch.rand(side, side, device="cuda", generator=g))
+        return cache["sq2"]
+
+    def km():
+        from cumo_b200 import kmeans
+        n, d, k = n32 // 64, 64, 256
+        cen = torch.randn(k, d, device="cuda", generator=g) * 4
+        pts = cen[torch.randint(0, k, (n,), device="cuda", generator=g)] + torch.randn(n, d, device="cuda", generator=g)
+        return kmeans, xp.SFloat.from_torch(pts), xp.SFloat.from_torch(cen)
+
+    def gemm():
+        from cumo_b200 import linalg
+        m, k, n = max(128, n32 // 4096), 4096, 4096
+        a = xp.SFloat.from_torch(torch.randn(m, k, device="cuda", generator=g))
+        bt = xp.SFloat.from_torch(torch.randn(n, k, device="cuda", generator=g))
+        return linalg, a, bt
+
+    cases = {
+        # name: (setup -> callable, algorithmic bytes)
+        "exp": (lambda: (lambda a=f32(): xp.NMath.exp(a)), 2 * n32 * 4),
+        "mul_scalar": (lambda: (lambda a=f32(): a * 0.5), 2 * n32 * 4),
+        "mul": (lambda: (lambda a=f32(): a * a), 3 * n32 * 4),
+        "outer_add": (lambda: (lambda xy=outer(): xy[0] + xy[1]), n32 * 4),
+        "add_col": (lambda: (lambda ac=col(): ac[0] + ac[1]), 2 * n32 * 4),
+        "sum_axis1_sq_f32": (lambda: (lambda a=f32()[0:(int((rows32 * cols) ** 0.5) // 64 * 64) ** 2].reshape(int((rows32 * cols) ** 0.5) // 64 * 64, -1): a.sum(axis=1)), (int((rows32 * cols) ** 0.5) // 64 * 64) ** 2 * 4),
+        "mul_row": (lambda: (lambda a=f32().reshape(rows32, cols), w=f32()[0:cols].reshape(1, cols): a * w), 2 * n32 * 4),
+        "sum_f32": (lambda: (lambda a=f32(): a.sum()), n32 * 4),
+        "sum_f64": (lambda: (lambda a=f64(): a.sum()), n64 * 8),
+        "max_f64": (lambda: (lambda a=f64(): a.max()), n64 * 8),
+        "argmax_f32": (lambda: (lambda a=f32(): a.argmax()), n32 * 4),
+        "sum_axis0_f32": (lambda: (lambda a=f32().reshape(rows32, cols): a.sum(axis=0)), n32 * 4),
+        "sum_axis1_f32": (lambda: (lambda a=f32().reshape(rows32, cols): a.sum(axis=1)), n32 * 4),
+        "max_index_axis1_f32": (lambda: (lambda a=f32().reshape(rows32, cols): a.max_index(axis=1)), n32 * 4),
+        "argmax_axis0_f32": (lambda: (lambda a=f32().reshape(rows32, cols): a.argmax(axis=0)), n32 * 4),
+        "gt_scalar_i32": (lambda: (lambda a=i32(): a > 0), n32 * 4 + n32 // 8),
+        "count_true": (lambda: (lambda m=(i32() > 0): m.count_true()), n32 // 8),
+        "mod_scalar_i32": (lambda: (lambda a=i32(): a % 7), 2 * n32 * 4),
+        "cumsum_f32": (lambda: (lambda a=f32(): a.cumsum()), 2 * n32 * 4),
+        "bincount_i32": (lambda: (lambda a=xp.Int32.from_torch(torch.randint(0, 256, (rows32 * cols,), device="cuda", dtype=torch.int32, generator=g)): a.bincount()), n32 * 4 + 1024),
+        "where_bits": (lambda: (lambda m=(i32() > 0): m.where()), n32 // 8 + (n32 // 2) * 4),
+        "gemm_tc": (lambda: (lambda m=gemm(): m[0].gemm_nt(m[1], m[2])), n32 * 4 + 4096 * 4096 * 4 + n32 * 4),
+        "kmeans_tensor": (lambda: (lambda m=km(): m[0].assign(m[1], m[2], algo="tensor")), n32 * 4 + n32 // 16),
+        "kmeans_cores": (lambda: (lambda m=km(): m[0].assign(m[1], m[2], algo="cores")), n32 * 4 + n32 // 16),
+        "sum_i32": (lambda: (lambda a=i32(): a.sum()), n32 * 4),
+        # operands whose contiguous axes differ: the shared-memory tile kernel
+        "add_transposed": (lambda: (lambda a=sq(), b=sq2(): a + b.transpose()), 3 * side * side * 4),
+        "copy_transposed": (lambda: (lambda b=sq(): b.transpose().dup()), 2 * side * side * 4),
+        "cast_transposed_i32": (lambda: (lambda b=i32()[0:side * side].reshape(side, side): xp.SFloat.cast(b.transpose())), 2 * side * side * 4),
+    }
+    return cases
+
+
+
+
+def run_case(args):
+    """`--case NAME`: one named kernel case on synthetic device data, a few launches, its timing printed.  This is the
+    small, self-ending command that profiler captures are taken on (one kernel, a few launches, a few hundred MiB on
+    the device) and a quick way to time a single kernel; `--mib` is the size of the main input array."""
+    import torch
+
+    import cumo_b200 as xp
+
+    torch.cuda.set_device(0)
+    cases = build_cases(xp, torch, args.mib)
+    if args.case == "list":
+        print(" ".join(cases))
+        return
+    setup, nbytes = cases[args.case]
+    fn = setup()
+    med, best = time_kernel(torch, fn, reps=args.reps, warm=args.warm)
+    print(f"{args.case}: {args.mib} MiB input, {nbytes} algorithmic bytes, median {med:.4f} ms (min {best:.4f}) over {args.reps} launches, {nbytes / (med * 1e-3) / 1e9:.1f} GB/s")
+
+
 def main():
     ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
     ap.add_argument("--gpus", type=int, default=1)
@@ -692,7 +874,14 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
     ap.add_argument("--no-kernels", action="store_true", help="skip the per-kernel table of the other BASELINE configs")
+    ap.add_argument("--case", help="run ONE named kernel case instead of the benchmark (`--case list` names them); for profiler captures")
+    ap.add_argument("--mib", type=int, default=512, help="--case: size of the main input array")
+    ap.add_argument("--reps", type=int, default=3, help="--case: timed launches")
+    ap.add_argument("--warm", type=int, default=1, help="--case: untimed launches first")
     args = ap.parse_args()
+    if args.case:
+        run_case(args)
+        return
     if args.warmup < 3:
         args.warmup = 3
     if args.impl == "reference":

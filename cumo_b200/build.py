@@ -3,7 +3,8 @@
 `python -m cumo_b200.build` compiles every translation unit under `csrc/` with
 nvcc for `arch=compute_100a,code=sm_100a` (objects in `cumo_b200/_build/`, several
 nvcc processes in parallel) and links `cumo_b200/libcumo_b200.so`.  Nothing is
-rebuilt when the library is newer than every source.  nvcc cross-compiles, so no
+rebuilt when the library is newer than every source; an object is rebuilt when
+its source or a header nvcc recorded for it (`-MD`) is newer than it.  nvcc cross-compiles, so no
 GPU is needed to build.
 """
 from __future__ import annotations
@@ -51,12 +52,28 @@ def up_to_date() -> bool:
     return all(p.stat().st_mtime <= t for p in _deps())
 
 
+def _recorded_deps(depfile: Path) -> list[Path] | None:
+    """The headers nvcc listed for one object (make-style .d file); None when there is no usable record."""
+    if not depfile.exists():
+        return None
+    text = depfile.read_text().replace("\\\n", " ")
+    parts = text.split(":", 1)
+    if len(parts) != 2:
+        return None
+    deps = [Path(p) for p in parts[1].split() if p.startswith(str(PKG.parent))]
+    return deps if all(p.exists() for p in deps) else None
+
+
 def _compile(src: Path, verbose: bool, extra: list[str]) -> Path:
     obj = OBJ / (src.relative_to(CSRC).as_posix().replace("/", "__") + ".o")
-    newest = max(p.stat().st_mtime for p in _deps() if p.suffix in (".cuh", ".h", ".py") or p == src)
+    depfile = obj.with_suffix(".d")
+    deps = _recorded_deps(depfile)
+    if deps is None:                       # no record yet: any header of the project counts
+        deps = [p for p in _deps() if p.suffix in (".cuh", ".h") or p == src]
+    newest = max([p.stat().st_mtime for p in deps] + [src.stat().st_mtime, Path(__file__).stat().st_mtime])
     if obj.exists() and obj.stat().st_mtime >= newest:
         return obj
-    cmd = [nvcc(), *NVCC_FLAGS, *extra, "-I", str(PKG.parent / "include"), "-I", str(CSRC), "-c", str(src), "-o", str(obj)]
+    cmd = [nvcc(), *NVCC_FLAGS, *extra, "-MD", "-MF", str(depfile), "-I", str(PKG.parent / "include"), "-I", str(CSRC), "-c", str(src), "-o", str(obj)]
     if src.suffix == ".cpp":
         cmd.insert(1, "-x")
         cmd.insert(2, "cu")

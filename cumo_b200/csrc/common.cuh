@@ -133,6 +133,32 @@ __device__ __forceinline__ void offsets_of(int64_t flat, int nd, const int64_t* 
     }
 }
 
+// ---- programmatic dependent launch ----------------------------------------------------------
+// A first-pass kernel says early that the kernel queued behind it may be launched (pdl_trigger); that second
+// kernel, launched with launch_dependent(), becomes resident while the first still runs and waits in pdl_wait()
+// until the first has finished and its writes are visible.  The launch latency of the second pass then overlaps the
+// tail of the first instead of following it.  Without the launch attribute both instructions do nothing.
+__device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+
+template <typename... KArgs, typename... Args>
+inline void launch_dependent(void (*kernel)(KArgs...), unsigned grid, unsigned block, cudaStream_t st, Args... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(grid);
+    cfg.blockDim = dim3(block);
+    cfg.dynamicSmemBytes = 0;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    if (cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...) != cudaSuccess) {
+        (void)cudaGetLastError();                      // e.g. a stream mode that does not take the attribute: plain launch
+        kernel<<<grid, block, 0, st>>>(KArgs(args)...);
+    }
+}
+
 inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 inline bool mult16(int64_t s) { return (s & 15) == 0; }
 

@@ -17,9 +17,12 @@
 //     operand when at most one outer dim is left (contiguous, (R,C)o(R,1),
 //     (R,C)o(1,C), (R,1)o(1,C), row-sliced views), a short division chain when
 //     several outer dims survive canonicalisation;
-//   * GEN kernel: anything else (transposed operands, negative or non-unit
-//     inner steps, operands of different element sizes).  One element per slot,
-//     consecutive threads on consecutive logical elements.
+//   * TILE kernel: an input whose contiguous axis is not the output's (a transposed
+//     operand): staged through a padded shared-memory tile so that every operand is
+//     read and written along its own contiguous axis;
+//   * GEN kernel: anything else (negative or non-unit inner steps, short extents,
+//     index patterns with no contiguous axis).  One element per slot, consecutive
+//     threads on consecutive logical elements.
 //   * comparisons write whole 32-bit words assembled with a warp OR-reduce /
 //     ballot when the Bit output is contiguous and word aligned; one atomic per
 //     element (the reference's CUMO_STORE_BIT, template_kernel.h:26-35) only
@@ -227,6 +230,10 @@ ew_rowshare_kernel(const RowGeom g, const char* __restrict__ a1, const char* __r
     constexpr int ES = sizeof(TO);
     constexpr int U = kEwUnroll;
     constexpr int B = kShareBatch;
+    // an input that is one element per row: the first kShareRows threads fetch the tile's values once and everyone
+    // reads them back from shared memory (a broadcast read), instead of every thread loading every row's element
+    __shared__ T1 row1[M1 == kRowScalar ? kShareRows : 1];
+    __shared__ T2 row2[M2 == kRowScalar ? kShareRows : 1];
 
     for (int64_t tile = blockIdx.x; tile < g.n_tiles; tile += gridDim.x) {   // one pass unless the grid was capped
         int64_t rg;
@@ -258,6 +265,14 @@ ew_rowshare_kernel(const RowGeom g, const char* __restrict__ a1, const char* __r
         const char* q1 = a1 + row0 * g.rs[0];
         const char* q2 = a2 + row0 * g.rs[1];
         char* q3 = a3 + row0 * g.rs[2];
+        if (M1 == kRowScalar || M2 == kRowScalar) {
+            __syncthreads();                   // the previous tile's values may still be read
+            if ((int)threadIdx.x < rows) {
+                if (M1 == kRowScalar) row1[threadIdx.x] = ld_one<T1>(q1 + (int64_t)threadIdx.x * g.rs[0]);
+                if (M2 == kRowScalar) row2[threadIdx.x] = ld_one<T2>(q2 + (int64_t)threadIdx.x * g.rs[1]);
+            }
+            __syncthreads();
+        }
         for (int rb = 0; rb < rows; rb += B) {
             T1 xr[B];
             T2 yr[B];
@@ -266,8 +281,8 @@ ew_rowshare_kernel(const RowGeom g, const char* __restrict__ a1, const char* __r
 #pragma unroll
             for (int r = 0; r < B; ++r) {
                 if (rb + r >= rows) continue;
-                if (M1 == kRowScalar) xr[r] = ld_one<T1>(q1 + r * g.rs[0]);
-                if (M2 == kRowScalar) yr[r] = ld_one<T2>(q2 + r * g.rs[1]);
+                if (M1 == kRowScalar) xr[r] = row1[rb + r];
+                if (M2 == kRowScalar) yr[r] = row2[rb + r];
 #pragma unroll
                 for (int j = 0; j < U; ++j) {
                     if (!ok[j]) continue;
@@ -345,6 +360,146 @@ ew_gen_kernel(const EwPlan p, int64_t n_tiles, const char* __restrict__ a1, cons
     }
 }
 
+// ----------------------------------------------------------------------------
+// TILE kernel: operands whose contiguous axes differ (a transposed operand).
+// ----------------------------------------------------------------------------
+// out[r][c] = op(x[r][c], y[r][c]) over a plane (r, c) in which the output is contiguous along c and at least one
+// input is contiguous along r instead (`a + b.transpose`, `b.transpose.dup`, `SFloat.cast(m.transpose)`).  The generic
+// kernel reads such an input with a stride between neighbouring lanes: one 32-byte sector fetched per element used.
+// Here a CTA takes a tile of kTileR x TC elements; a transposed input's tile is first read with the lanes running
+// along ITS contiguous axis (r) and parked in shared memory, rows padded by one element; then the lanes run along c,
+// pick the parked values column-wise (conflict-free thanks to the padding), load the row-like operands, and store
+// the result -- every global access of every operand is a run of consecutive elements per warp.  Dimensions other
+// than the two of the plane are walked as a batch index.  Works for any element sizes and alignments.
+constexpr int kTileR = 64;
+
+struct TilePlan {
+    int n_outer;                              // dims besides the plane
+    int64_t oshape[kMaxDim];
+    int64_t ostep[3][kMaxDim];                // [0],[1] inputs, [2] output
+    int64_t R, C;                             // extents of the plane: r = the transposed inputs' contiguous axis, c = the output's
+    int64_t rstep[3], cstep[3];               // byte steps along r and c per operand
+    int64_t tiles_r, tiles_c, n_tiles;
+};
+
+template <typename Op, bool T1, bool T2, int TC>
+__global__ void __launch_bounds__(kBlock)
+ew_tile_kernel(const TilePlan t, const char* __restrict__ a1, const char* __restrict__ a2, char* a3,
+               typename Op::In1 sx, typename Op::In2 sy, int use_scalar, int* flag) {
+    using X = typename Op::In1;
+    using Y = typename Op::In2;
+    using TO = typename Op::Out;
+    constexpr int TR = kTileR;
+    __shared__ X tile1[T1 ? TC : 1][T1 ? TR + 1 : 1];
+    __shared__ Y tile2[T2 ? TC : 1][T2 ? TR + 1 : 1];
+    const bool have1 = use_scalar != 2;
+    const bool have2 = Op::arity == 2 && use_scalar != 1;
+    for (int64_t tile = blockIdx.x; tile < t.n_tiles; tile += gridDim.x) {
+        // tiles along c vary fastest, then r, then the batch
+        const int64_t tc = tile % t.tiles_c;
+        const int64_t rest = tile / t.tiles_c;
+        const int64_t tr = rest % t.tiles_r;
+        const int64_t batch = rest / t.tiles_r;
+        int64_t off[3];
+        offsets_of<3>(batch, t.n_outer, t.oshape, t.ostep, off);
+        const int64_t r0 = tr * TR, c0 = tc * TC;
+        if (T1 || T2) {
+            __syncthreads();                   // the previous tile may still be read
+            // lanes along r: element (r0 + lr, c0 + lc) of a transposed input sits lr elements on from the start of its line
+            const int lr = threadIdx.x % TR;
+            const bool r_ok = r0 + lr < t.R;
+#pragma unroll 8
+            for (int lc = threadIdx.x / TR; lc < TC; lc += kBlock / TR) {
+                const bool ok = r_ok && c0 + lc < t.C;
+                if (T1 && ok) tile1[lc][lr] = ld_one<X>(a1 + off[0] + (r0 + lr) * t.rstep[0] + (c0 + lc) * t.cstep[0]);
+                if (T2 && ok) tile2[lc][lr] = ld_one<Y>(a2 + off[1] + (r0 + lr) * t.rstep[1] + (c0 + lc) * t.cstep[1]);
+            }
+            __syncthreads();
+        }
+        // lanes along c
+        const int lc = threadIdx.x % TC;
+        const bool c_ok = c0 + lc < t.C;
+        constexpr int RP = kBlock / TC;        // rows per pass
+        constexpr int UN = 8;                  // loads of the row-like operands in flight per thread
+        for (int lr0 = threadIdx.x / TC; lr0 < TR; lr0 += RP * UN) {
+            X x[UN];
+            Y y[UN];
+            bool ok[UN];
+#pragma unroll
+            for (int j = 0; j < UN; ++j) {
+                const int lr = lr0 + j * RP;
+                ok[j] = c_ok && lr < TR && r0 + lr < t.R;
+                x[j] = sx; y[j] = sy;
+                if (!ok[j]) continue;
+                if (T1) x[j] = tile1[lc][lr];
+                else if (have1) x[j] = ld_one<X>(a1 + off[0] + (r0 + lr) * t.rstep[0] + (c0 + lc) * t.cstep[0]);
+                if (T2) y[j] = tile2[lc][lr];
+                else if (have2) y[j] = ld_one<Y>(a2 + off[1] + (r0 + lr) * t.rstep[1] + (c0 + lc) * t.cstep[1]);
+            }
+#pragma unroll
+            for (int j = 0; j < UN; ++j) {
+                if (!ok[j]) continue;
+                const int lr = lr0 + j * RP;
+                TO z;
+                if (Op::apply(x[j], y[j], z, flag)) st_one<TO>(a3 + off[2] + (r0 + lr) * t.rstep[2] + (c0 + lc) * t.cstep[2], z);
+            }
+        }
+    }
+}
+
+// Plans the tile kernel for `p`; false when the operation is not of that shape (the generic kernel takes it).
+template <typename Op>
+bool launch_tiled(const EwPlan& p, const char* p1, const char* p2, char* p3, bool have1, bool have2,
+                  typename Op::In1 sx, typename Op::In2 sy, int use_scalar, int* flag, cudaStream_t st) {
+    constexpr int64_t ES[3] = {(int64_t)sizeof(typename Op::In1), (int64_t)sizeof(typename Op::In2), (int64_t)sizeof(typename Op::Out)};
+    if (p.nd < 2 || p.total < (1 << 14)) return false;
+    // the output's contiguous axis becomes c (an elementwise operation may walk its dims in any order)
+    int dc = -1;
+    for (int d = p.nd - 1; d >= 0; --d) if (p.step[2][d] == ES[2]) { dc = d; break; }
+    if (dc < 0) return false;
+    // inputs: row-like (contiguous or repeated along c) or transposed (contiguous along one other axis, the same for all)
+    const bool have[2] = {have1, have2};
+    bool tr[2] = {false, false};
+    int dr = -1;
+    for (int a = 0; a < 2; ++a) {
+        if (!have[a]) continue;
+        if (p.step[a][dc] == ES[a] || p.step[a][dc] == 0) continue;
+        int d_in = -1;
+        for (int d = p.nd - 1; d >= 0; --d) if (d != dc && p.step[a][d] == ES[a]) { d_in = d; break; }
+        if (d_in < 0 || (dr >= 0 && d_in != dr)) return false;
+        dr = d_in;
+        tr[a] = true;
+    }
+    if (dr < 0) return false;                                  // nothing is transposed
+    if (p.shape[dr] < 16 || p.shape[dc] < 16) return false;     // slivers: not worth a tile
+    constexpr bool wide = sizeof(typename Op::In1) > 4 || sizeof(typename Op::In2) > 4;
+    constexpr int TC = wide ? 32 : 64;                          // the parked tiles stay within 34 KiB of shared memory
+    TilePlan t;
+    t.n_outer = 0;
+    for (int d = 0; d < p.nd; ++d) {
+        if (d == dr || d == dc) continue;
+        t.oshape[t.n_outer] = p.shape[d];
+        for (int a = 0; a < 3; ++a) t.ostep[a][t.n_outer] = p.step[a][d];
+        ++t.n_outer;
+    }
+    t.R = p.shape[dr]; t.C = p.shape[dc];
+    for (int a = 0; a < 3; ++a) { t.rstep[a] = p.step[a][dr]; t.cstep[a] = p.step[a][dc]; }
+    t.tiles_r = (t.R + kTileR - 1) / kTileR;
+    t.tiles_c = (t.C + TC - 1) / TC;
+    int64_t batch = 1;
+    for (int d = 0; d < t.n_outer; ++d) batch *= t.oshape[d];
+    t.n_tiles = t.tiles_r * t.tiles_c * batch;
+    const unsigned grid = (unsigned)(t.n_tiles > kMaxGrid ? kMaxGrid : t.n_tiles);
+    if constexpr (Op::arity == 1) {
+        ew_tile_kernel<Op, true, false, TC><<<grid, kBlock, 0, st>>>(t, p1, p2, p3, sx, sy, use_scalar, flag);
+    } else {
+        if (tr[0] && tr[1])  ew_tile_kernel<Op, true, true, TC><<<grid, kBlock, 0, st>>>(t, p1, p2, p3, sx, sy, use_scalar, flag);
+        else if (tr[0])      ew_tile_kernel<Op, true, false, TC><<<grid, kBlock, 0, st>>>(t, p1, p2, p3, sx, sy, use_scalar, flag);
+        else                 ew_tile_kernel<Op, false, true, TC><<<grid, kBlock, 0, st>>>(t, p1, p2, p3, sx, sy, use_scalar, flag);
+    }
+    return true;
+}
+
 inline unsigned grid_of(int64_t n_tiles) { return (unsigned)(n_tiles < 1 ? 1 : (n_tiles > kMaxGrid ? kMaxGrid : n_tiles)); }
 
 // host side ---------------------------------------------------------------
@@ -404,8 +559,10 @@ void launch_elementwise(const cumo_na_iarray_t* a1, const cumo_na_iarray_t* a2, 
                 for (int a = 0; a < 3; ++a) g.rs[a] = p.nd == 2 ? p.step[a][0] : 0;
                 // a row vector repeated down the rows is worth holding in registers
                 const bool shared_row = p.nd == 2 && ((g.inner[0] == 1 && g.rs[0] == 0) || (g.inner[1] == 1 && g.rs[1] == 0));
+                // ... and so is one element per row against a full array, (R,C) o (R,1): the per-row value is fetched once per CTA
+                const bool row_scalar = p.nd == 2 && have1 && have2 && ((g.inner[0] == 0 && g.inner[1] == 1) || (g.inner[0] == 1 && g.inner[1] == 0));
                 if constexpr (Op::arity == 2)
-                if (v16 && shared_row && vpr >= kBlock && g.R >= 2 * kShareRows && len * ES <= 0xffffffffLL) {
+                if (v16 && (shared_row || row_scalar) && vpr >= kBlock && g.R >= 2 * kShareRows && len * ES <= 0xffffffffLL) {
                     const int64_t chunks = (vpr + kEwSlots - 1) / kEwSlots;
                     g.rows_per_tile = 1;
                     g.chunks_per_row = (uint32_t)chunks;
@@ -421,6 +578,8 @@ void launch_elementwise(const cumo_na_iarray_t* a1, const cumo_na_iarray_t* a2, 
                     if (m1 == kHeld && m2 == kHeld)           ew_rowshare_kernel<Op, VMAX, kHeld, kHeld><<<grid, kBlock, 0, st>>>(g, h1, h2, q3, sx, sy, flag);
                     else if (m1 == kHeld && m2 == kRowScalar) ew_rowshare_kernel<Op, VMAX, kHeld, kRowScalar><<<grid, kBlock, 0, st>>>(g, h1, h2, q3, sx, sy, flag);
                     else if (m1 == kRowScalar && m2 == kHeld) ew_rowshare_kernel<Op, VMAX, kRowScalar, kHeld><<<grid, kBlock, 0, st>>>(g, h1, h2, q3, sx, sy, flag);
+                    else if (m1 == kRowPack && m2 == kRowScalar) ew_rowshare_kernel<Op, VMAX, kRowPack, kRowScalar><<<grid, kBlock, 0, st>>>(g, h1, h2, q3, sx, sy, flag);
+                    else if (m1 == kRowScalar && m2 == kRowPack) ew_rowshare_kernel<Op, VMAX, kRowScalar, kRowPack><<<grid, kBlock, 0, st>>>(g, h1, h2, q3, sx, sy, flag);
                     else done = false;        // a full array against a row vector: the plain row kernel measures faster (fewer registers)
                     if (done) { ++launches; return true; }
                 }
@@ -464,6 +623,11 @@ void launch_elementwise(const cumo_na_iarray_t* a1, const cumo_na_iarray_t* a2, 
                 return;
             }
         }
+    }
+    if (launch_tiled<Op>(p, p1, p2, p3, have1, have2, sx, sy, use_scalar, flag, st)) {
+        count_launch();
+        cumo_cuda_runtime_check_kernel_launch();
+        return;
     }
     int64_t n_tiles = (p.total + kEwSlots - 1) / kEwSlots;
     ew_gen_kernel<Op><<<grid_of(n_tiles), kBlock, 0, st>>>(p, n_tiles, p1, p2, p3, sx, sy, use_scalar, flag);

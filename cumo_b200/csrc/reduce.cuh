@@ -84,8 +84,34 @@ __device__ __forceinline__ A shfl_down_acc(A v, int delta) {
     return u.a;
 }
 
+// Index reductions on 4-byte element types: the warp's extreme value by one integer reduce instruction on an
+// order-preserving key, then the lowest index among the lanes that hold it by a second one -- instead of five rounds
+// of 16-byte shuffles and comparisons.  Same total order as R::combine (NaN rule, better value, lower index).
+template <typename R, typename = void> struct redux_fold : std::false_type {};
+template <typename R> struct redux_fold<R, std::void_t<decltype(R::kReduxFold)>> : std::integral_constant<bool, R::kReduxFold> {};
+
+template <typename R>
+__device__ __forceinline__ typename R::Acc warp_fold_redux(const R& r, typename R::Acc a) {
+    const uint32_t key = r.order_key(a.value);                       // larger key = better; the losing NaN class maps to 0
+    const uint32_t best = __reduce_max_sync(0xffffffffu, key);
+    // indices of one warp's accumulators are distinct (or INT64_MAX for identities), so the minimum picks one lane;
+    // the sign bit is flipped so that the unsigned minimum follows the signed order
+    constexpr unsigned long long kBias = 0x8000000000000000ull;
+    const unsigned long long mine = key == best ? ((unsigned long long)a.index ^ kBias) : ~0ull;
+    const uint32_t lo = __reduce_min_sync(0xffffffffu, (uint32_t)(mine >> 32));
+    const uint32_t lo2 = __reduce_min_sync(0xffffffffu, (uint32_t)(mine >> 32) == lo ? (uint32_t)mine : 0xffffffffu);
+    const unsigned long long win = ((unsigned long long)lo << 32) | lo2;
+    const unsigned holder = __ballot_sync(0xffffffffu, mine == win);
+    const int src = __ffs(holder) - 1;
+    typename R::Acc out;
+    out.value = __shfl_sync(0xffffffffu, a.value, src);
+    out.index = (int64_t)(win ^ kBias);
+    return out;
+}
+
 template <typename R>
 __device__ __forceinline__ typename R::Acc warp_fold(const R& r, typename R::Acc a) {
+    if constexpr (redux_fold<R>::value) return warp_fold_redux(r, a);
 #pragma unroll
     for (int d = 1; d < 32; d <<= 1) {      // lane i folds in lane i+d: earlier positions stay on the left
         typename R::Acc b = shfl_down_acc(a, d);
@@ -244,6 +270,7 @@ red_row_kernel(const RedPlan p, const R r, const RedLaunch q, const char* __rest
     using Acc = typename R::Acc;
     constexpr int ES = sizeof(T);
     constexpr int GPB = kBlock / G;          // groups per CTA
+    pdl_trigger();                           // a second (folding) pass may be launched while this one runs
     __shared__ Acc smem[kWarpsPerBlock];
     const int gid = threadIdx.x / G, gl = threadIdx.x % G;
     const int64_t L = p.n_red;
@@ -323,6 +350,7 @@ red_col_kernel(const RedPlan p, const R r, const RedLaunch q, const char* __rest
     using Acc = typename R::Acc;
     constexpr int ES = sizeof(T);
     constexpr int W = 32 * V;                // columns per strip
+    pdl_trigger();                           // a second (folding) pass may be launched while this one runs
     __shared__ Acc smem[kWarpsPerBlock][W];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int od_in = p.n_od - 1;            // innermost out dim = the columns
@@ -375,9 +403,12 @@ red_col_kernel(const RedPlan p, const R r, const RedLaunch q, const char* __rest
 
 // ---- COL, wide rows ---------------------------------------------------------------------
 // When a row of output columns is at least half a CTA's width of packets, every thread owns
-// V columns outright: the CTA reads kBlock contiguous packets of each row (4 KiB), walks the
-// rows of its segment with kColUnroll loads in flight per thread, and nothing is folded across
-// threads at all.
+// V columns outright: the CTA reads kBlock contiguous packets of each row (4 KiB), walks its rows
+// with kColUnroll loads in flight per thread, and nothing is folded across threads at all.
+// The rows are dealt to the n_split segments in blocks of kColUnroll, round robin: segment s takes
+// row blocks s, s + n_split, s + 2 n_split, ...  So at any moment the resident CTAs read one compact
+// window of the array that slides through memory (B200 streams measurably faster that way than with
+// every CTA walking a far-apart region of its own), and all segments are equally long to within one block.
 constexpr int kColUnroll = 8;
 
 template <typename R, int V>
@@ -388,11 +419,13 @@ red_colwide_kernel(const RedPlan p, const R r, const RedLaunch q, const char* __
     constexpr int ES = sizeof(T);
     constexpr int W = kBlock * V;            // columns per strip
     constexpr int U = kColUnroll;
+    pdl_trigger();                           // a second (folding) pass may be launched while this one runs
     const int od_in = p.n_od - 1;            // innermost out dim = the columns
     const int64_t C = p.oshape[od_in];
     const int64_t n_batch = p.n_out / C;
     const int64_t items = n_batch * q.n_strips * q.n_split;
     const int64_t rstep = p.in_rstep[0];
+    const int64_t n_rows = p.n_red;
     for (int64_t item = blockIdx.x; item < items; item += gridDim.x) {
         // strips vary fastest: neighbouring CTAs read neighbouring columns of the same rows
         int64_t strip, s, b;
@@ -411,41 +444,40 @@ red_colwide_kernel(const RedPlan p, const R r, const RedLaunch q, const char* __
         const int nv = cleft >= V ? V : (cleft > 0 ? (int)cleft : 0);
         if (nv == 0) continue;
         const int64_t in_b = offset_of(b, od_in, p.oshape, p.in_ostep);
-        const int64_t r_begin = s * q.seg_len;
-        int64_t r_end = r_begin + q.seg_len; if (r_end > p.n_red) r_end = p.n_red;
-        const char* base = in + in_b + col0 * ES + r_begin * rstep;
-        const int32_t rows = (int32_t)(r_end - r_begin);
+        const char* base = in + in_b + col0 * ES;
         Runner<R, R::kHasScan> run[V];
 #pragma unroll
         for (int k = 0; k < V; ++k) run[k].init(r);
-        auto idx_of = [&](int32_t ps, int k) {
-            const int64_t row = r_begin + ps;
-            return q.flat_index ? (in_b + row * rstep) / ES + col0 + k : row;
+        // positions are row numbers (the host keeps the row count of this plan below 2^31)
+        auto idx_of = [&](int32_t row, int k) {
+            return q.flat_index ? (in_b + (int64_t)row * rstep) / ES + col0 + k : (int64_t)row;
         };
-        int32_t r0 = 0;
-        if (nv == V) {
-            for (; r0 + U <= rows; r0 += U) {
+        const int64_t first = s * U;
+        for (int64_t rb = first; rb < n_rows; rb += (int64_t)q.n_split * U) {
+            const char* a0 = base + rb * rstep;
+            if (nv == V && rb + U <= n_rows) {
                 Pack<T> v[U];
 #pragma unroll
                 for (int j = 0; j < U; ++j) {
-                    const char* a = base + (int64_t)(r0 + j) * rstep;
+                    const char* a = a0 + (int64_t)j * rstep;
                     if (V > 1) v[j] = ld_pack<T>(a); else v[j].v[0] = ld_one<T>(a);
                 }
 #pragma unroll
                 for (int j = 0; j < U; ++j)
 #pragma unroll
                     for (int k = 0; k < V; ++k)
-                        run[k].step(r, v[j].v[k], r0 + j, [&](int32_t ps) { return idx_of(ps, k); });
+                        run[k].step(r, v[j].v[k], (int32_t)(rb + j), [&](int32_t ps) { return idx_of(ps, k); });
+            } else {
+                for (int j = 0; j < U && rb + j < n_rows; ++j) {
+                    const char* a = a0 + (int64_t)j * rstep;
+#pragma unroll
+                    for (int k = 0; k < V; ++k)
+                        if (k < nv) run[k].step(r, ld_one<T>(a + k * ES), (int32_t)(rb + j), [&](int32_t ps) { return idx_of(ps, k); });
+                }
             }
         }
-        for (; r0 < rows; ++r0) {
-            const char* a = base + (int64_t)r0 * rstep;
 #pragma unroll
-            for (int k = 0; k < V; ++k)
-                if (k < nv) run[k].step(r, ld_one<T>(a + k * ES), r0, [&](int32_t ps) { return idx_of(ps, k); });
-        }
-#pragma unroll
-        for (int k = 0; k < V; ++k) run[k].settle(k < nv && rows > 0 ? 0 : -1);
+        for (int k = 0; k < V; ++k) run[k].settle(k < nv && first < n_rows ? (int32_t)first : -1);
 #pragma unroll
         for (int k = 0; k < V; ++k)
             if (k < nv)
@@ -461,6 +493,7 @@ red_gen_kernel(const RedPlan p, const R r, const RedLaunch q, const char* __rest
     using T = typename R::In;
     using Acc = typename R::Acc;
     constexpr int ES = sizeof(T);
+    pdl_trigger();                           // a second (folding) pass may be launched while this one runs
     constexpr int GPB = kBlock / G;
     __shared__ Acc smem[kWarpsPerBlock];
     const int gid = threadIdx.x / G, gl = threadIdx.x % G;
@@ -509,6 +542,7 @@ red_fold_kernel(const RedPlan p, const R r, const typename R::Acc* __restrict__ 
     constexpr int GPB = kBlock / G;
     __shared__ Acc smem[kWarpsPerBlock];
     const int gid = threadIdx.x / G, gl = threadIdx.x % G;
+    pdl_wait();                              // the first pass has finished and its partials are visible
     for (int64_t o0 = (int64_t)blockIdx.x * GPB; o0 < p.n_out; o0 += (int64_t)gridDim.x * GPB) {
         const int64_t o = o0 + gid;
         const bool live = o < p.n_out;
@@ -547,6 +581,7 @@ red_fold_big_kernel(const RedPlan p, const R r, const typename R::Acc* __restric
     __shared__ Acc smem[32];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int per = (n_split + 1023) / 1024;
+    pdl_wait();                              // the first pass has finished and its partials are visible
     for (int64_t o = blockIdx.x; o < p.n_out; o += gridDim.x) {
         const Acc* run = partial + o * n_split;
         Acc acc = r.identity();
@@ -630,7 +665,16 @@ void launch_reduce(const cumo_na_reduction_arg_t* arg, const cumo_na_iarray_t* o
         // rows of up to 256 KiB stay whole, one CTA each, when there are CTAs enough without cutting them
         const bool whole_rows = p.n_out >= kManyRows / 8 && L * ES <= 8 * kSegBytes;
         if (wide && !whole_rows) {
-            int64_t seg = kSegBytes / ES;              // a multiple of 32 elements: segment starts stay 16-byte aligned
+            // a multiple of 32 elements: segment starts stay 16-byte aligned.  Index reductions fold 16-byte {value, index}
+            // accumulators across the CTA, which costs about as much as scanning 32 KiB, so their segments are longer
+            int64_t seg = kSegBytes / ES;
+            if (R::kHasScan) {
+                // about two and a half rounds of resident CTAs (148 SMs x 8) over the row, in whole multiples of
+                // kSegBytes, at most 16 of them: a function of the row length only
+                int64_t mult = (L * ES / 3000 + kSegBytes - 1) / kSegBytes;
+                mult = mult < 1 ? 1 : (mult > 16 ? 16 : mult);
+                seg *= mult;
+            }
             int64_t ns = (L + seg - 1) / seg;
             while (ns > 8192) { seg *= 2; ns = (L + seg - 1) / seg; }
             if (ns > 1) { q.seg_len = seg; q.n_split = (int)ns; }
@@ -652,7 +696,7 @@ void launch_reduce(const cumo_na_reduction_arg_t* arg, const cumo_na_iarray_t* o
         for (int d = 0; d < od_in && vec; ++d) if (!mult16(p.in_ostep[d])) vec = false;
         for (int d = 0; d < p.n_rd && vec; ++d) if (!mult16(p.in_rstep[d])) vec = false;
         // thread-owned columns when a row of columns fills at least half a CTA; else a warp-wide strip with rows spread over warps
-        const bool wide_cols = C >= (int64_t)kBlock * (vec ? VMAX : 1) / 2;
+        const bool wide_cols = C >= (int64_t)kBlock * (vec ? VMAX : 1) / 2 && p.n_red < 0x7fffffffLL;
         const int64_t W = (wide_cols ? kBlock : 32) * (vec ? VMAX : 1);
         const int64_t seg_rows = wide_cols ? kColWideSegRows : kColSegRows;
         q.n_strips = (C + W - 1) / W;
@@ -663,16 +707,17 @@ void launch_reduce(const cumo_na_reduction_arg_t* arg, const cumo_na_iarray_t* o
             while (ns > 8192) { seg *= 2; ns = (p.n_red + seg - 1) / seg; }
             if (wide_cols) {
                 // These CTAs are large (half a MiB of input) and all alike, so they run in rounds of
-                // kColWideRound; a last round that is mostly empty costs as much as a full one.  Cut the
-                // rows so that the CTA count is just under a whole number of rounds.  The round size is a
-                // constant of the plan, not a property read from the device, so results stay the same anywhere.
+                // kColWideRound; a last round that is mostly empty costs as much as a full one.  Pick the
+                // segment count so that the CTA count is just under a whole number of rounds (the rows are
+                // dealt to the segments in blocks of kColUnroll, round robin, so any count balances).  The
+                // round size is a constant of the plan, not a property read from the device, so results stay
+                // the same anywhere.
                 const int64_t lanes = (p.n_out / C) * q.n_strips;           // CTAs per segment index
                 const int64_t rounds = (lanes * ns + kColWideRound - 1) / kColWideRound;
                 const int64_t want = rounds * kColWideRound / lanes;
-                if (want >= 2 && want <= 8192) {
-                    seg = (p.n_red + want - 1) / want;
-                    ns = (p.n_red + seg - 1) / seg;
-                }
+                const int64_t blocks = (p.n_red + kColUnroll - 1) / kColUnroll;
+                if (want >= 2 && want <= 8192) ns = want < blocks ? want : blocks;
+                seg = (p.n_red + ns - 1) / ns;                              // (not used by this kernel)
             }
             q.seg_len = seg;
             q.n_split = (int)ns;
@@ -703,12 +748,13 @@ void launch_reduce(const cumo_na_reduction_arg_t* arg, const cumo_na_iarray_t* o
     }
     int launches = 1;
     if (q.n_split > 1) {
+        const Acc* cpartial = partial;
         if (q.n_split > 1024 && p.n_out <= 64)
-            red_fold_big_kernel<R><<<red_grid(p.n_out), 1024, 0, st>>>(p, r, partial, q.n_split, out, out2);
+            launch_dependent(red_fold_big_kernel<R>, red_grid(p.n_out), 1024, st, p, r, cpartial, q.n_split, out, out2);
         else if (q.n_split > 256 && p.n_out < 4096)
-            red_fold_kernel<R, kBlock><<<red_grid(p.n_out), kBlock, 0, st>>>(p, r, partial, q.n_split, out, out2);
+            launch_dependent(red_fold_kernel<R, kBlock>, red_grid(p.n_out), kBlock, st, p, r, cpartial, q.n_split, out, out2);
         else
-            red_fold_kernel<R, 32><<<red_grid((p.n_out + kWarpsPerBlock - 1) / kWarpsPerBlock), kBlock, 0, st>>>(p, r, partial, q.n_split, out, out2);
+            launch_dependent(red_fold_kernel<R, 32>, red_grid((p.n_out + kWarpsPerBlock - 1) / kWarpsPerBlock), kBlock, st, p, r, cpartial, q.n_split, out, out2);
         ++launches;
         cumo_cuda_runtime_free(reinterpret_cast<char*>(partial));
     }

@@ -23,6 +23,7 @@
 
 #include "common.cuh"
 #include <limits>
+#include <type_traits>
 #include <math.h>
 #include <float.h>
 
@@ -233,6 +234,25 @@ struct ArgMinMax {
     struct Acc { T value; int64_t index; };
     static constexpr bool kIndexed = true;
     static constexpr bool kHasScan = true;
+    // 4-byte element types can fold a warp's accumulators with integer reduce instructions on an order-preserving key
+    static constexpr bool kReduxFold = sizeof(T) == 4;
+    // larger key = ranks better under combine()'s order; all values of the losing NaN class share key 0 (plain form:
+    // NaN loses; NaN-wins form: NaN gets the top key), so among equal keys the lower index decides, as in combine()
+    __device__ __forceinline__ uint32_t order_key(T v) const {
+        uint32_t k;
+        if constexpr (is_fp<T>::value) {
+            const uint32_t b = __float_as_uint((float)v);
+            if (v != v) return NAN_WINS ? 0xffffffffu : 0u;
+            k = (b & 0x80000000u) ? ~b : (b | 0x80000000u);           // ascending with the float order; -0 < +0 here, see below
+            if (v == 0) k = 0x80000000u;                               // both zeros compare equal: one key
+        } else {
+            k = (uint32_t)v ^ 0x80000000u;                             // ascending with the signed order
+        }
+        k = IS_MAX ? k : ~k;
+        // keep clear of the keys reserved for the NaN class
+        if constexpr (is_fp<T>::value) { if (k == 0u) k = 1u; if (k == 0xffffffffu) k = 0xfffffffeu; }
+        return k;
+    }
     int idx64;
     int64_t base = 0;          // added to every index written (a shard's offset in the global array)
     // A thread's private scan of a run visited in increasing index order.  A strict

@@ -171,6 +171,19 @@ class NArray:
         return NArray._from_handle(h, keep=t)
 
     @classmethod
+    def from_device_pointer(cls, ptr: int, shape, keep=None):
+        """Borrow device-accessible memory the caller owns (cudaMalloc, cudaMallocManaged, another library's buffer) as a
+        contiguous array of this type; `keep` is held for as long as the array lives."""
+        shape = [int(n) for n in shape]
+        es = _ESZ[cls.dtype_code]
+        steps, st = [], es
+        for n in reversed(shape):
+            steps.append(st)
+            st *= n
+        h = _lib.load().cb200_na_wrap(cls.dtype_code, len(shape), _arr64(shape), _arr64(list(reversed(steps))), c_void_p(ptr), 0)
+        return NArray._from_handle(h, keep=keep)
+
+    @classmethod
     def zeros(cls, *shape):
         if len(shape) == 1 and isinstance(shape[0], (tuple, list)):
             shape = tuple(shape[0])

@@ -371,6 +371,12 @@ int cb200_kmeans_assign_sfloat(const float* x, int64_t n, int d, const float* c,
 int cb200_kmeans_assign_sfloat_tc(const float* x, int64_t n, int d, const float* c, int k, int32_t* labels,
                                   float* min_dist, unsigned long long* counts, char* errbuf, size_t errlen);
 
+/* Self-test of the bounded mbarrier wait the tcgen05 kernels use between their warp roles (no counterpart in the
+ * reference): one CTA waits at most `spin_limit` polls on a barrier nothing arrives at.  Returns 5 when the wait gave
+ * up by its limit -- the code cb200_sgemm_nt_tc / cb200_kmeans_assign_sfloat_tc return in that case -- 0 if the barrier
+ * completed, 3/4 on launch problems.  The kernel always returns; the context stays usable. */
+int cb200_selftest_bounded_wait(unsigned spin_limit, char* errbuf, size_t errlen);
+
 /* float32 `sum` that allocates nothing (no counterpart in the reference, whose reductions
  * always take scratch from cumo_cuda_runtime_malloc).  For callers that cannot reach an
  * allocator when they need the sum: a finalizer or other context in which the Ruby

@@ -50,3 +50,23 @@ def test_gemm_refuses_unsupported_shapes(xp_gpu):
 
     with pytest.raises(xp_gpu.CumoError, match="multiples of 4"):
         linalg.gemm_nt(xp_gpu.SFloat.zeros(8, 6), xp_gpu.SFloat.zeros(8, 6))
+
+
+def test_a_bounded_wait_that_runs_out_returns_an_error_code():
+    """The waits between the warp roles of the tcgen05 kernels are bounded; when one runs out the kernel winds down and
+    the entry point returns 5.  The self-test makes such a wait run out by its (short) limit on a barrier that nothing
+    arrives at: the kernel returns, the code is 5, and the device keeps working."""
+    import ctypes
+
+    import torch
+    from cumo_b200 import _lib
+
+    L = _lib.load()
+    f = L.cb200_selftest_bounded_wait
+    f.restype = ctypes.c_int
+    f.argtypes = [ctypes.c_uint, ctypes.c_char_p, ctypes.c_size_t]
+    err = ctypes.create_string_buffer(200)
+    assert f(2000, err, len(err)) == 5, err.value
+    assert b"ran out" in err.value
+    x = torch.arange(10, device="cuda").sum().item()             # the context is still usable
+    assert x == 45

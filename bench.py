@@ -308,6 +308,27 @@ def kernel_table(torch, xp, peak):
             row["ref_gpu_GBps"] = round(row["bytes"] / (ms * 1e-3) / 1e9, 1)
             row["speedup_vs_ref_gpu"] = round(ms / row["ms"], 2)
 
+    # `%7` without the host's read-back of the division-by-zero flag: the launch function called directly, events around it
+    try:
+        sys.path.insert(0, str(ROOT / "tests"))
+        import abi_call as ac
+        from ctypes import byref, c_int, c_int32, c_void_p
+        from cumo_b200 import _lib as _l
+        n4 = FULL_SIZES["c4_n"]
+        ia = torch.randint(-(1 << 20), 1 << 20, (n4,), device="cuda", dtype=torch.int32, generator=g)
+        io = torch.empty_like(ia)
+        flag = torch.zeros(1, device="cuda", dtype=torch.int32)
+        ix = ac.indexer((n4,))
+        fn = ac.fn(_l.load(), "cumo_iter_int32_mod_s_kernel_launch")
+        med, best = time_kernel(torch, lambda: fn(byref(ac.iarray(ia)), c_int32(7), byref(ac.iarray(io)), byref(ix), c_void_p(flag.data_ptr()), c_int(0)), reps=20)
+        nb = 2 * n4 * 4
+        gbs = nb / (med * 1e-3) / 1e9
+        rows.append({"config": "C4", "kernel": "%7 kernel alone (launch function, no flag read-back)", "bytes": nb, "ms": round(med, 4), "ms_min": round(best, 4),
+                     "GBps": round(gbs, 1), "frac_of_measured": round(gbs / peak, 3), "frac_of_nominal": round(gbs / NOMINAL_HBM_GBS, 3)})
+        del ia, io
+    except Exception as e:
+        print(f"%7 kernel-alone row skipped: {e}", file=sys.stderr)
+
     # managed memory, which is what every buffer of the reference is (its pool hands out cudaMallocManaged blocks):
     # exp and sum on buffers prefetched to the device, beside the cudaMalloc rows above
     try:
@@ -354,6 +375,18 @@ def kernel_table(torch, xp, peak):
                  "TFLOPs": round(2.0 * gm ** 3 / (med * 1e-3) / 1e12, 1),
                  "TFLOPs_issued_tf32": round(6.0 * gm ** 3 / (med * 1e-3) / 1e12, 1),
                  "cublas_fp32_ms": round(med_lib, 4), "cublas_fp32_TFLOPs": round(2.0 * gm ** 3 / (med_lib * 1e-3) / 1e12, 1)})
+    # double-precision `dot` (CUDA-core tile kernel; the reference calls cublasDgemm) beside torch's fp64 cuBLAS product
+    del xa, xb, ga, gb
+    dm = 4096
+    da = torch.randn(dm, dm, device="cuda", dtype=torch.float64, generator=g)
+    db = torch.randn(dm, dm, device="cuda", dtype=torch.float64, generator=g)
+    ya, yb = xp.DFloat.from_torch(da), xp.DFloat.from_torch(db)
+    med, best = time_kernel(torch, lambda: linalg.dot(ya, yb), reps=5)
+    med_lib, _ = time_kernel(torch, lambda: da @ db, reps=5)
+    rows.append({"config": "F", "kernel": "DFloat dot 4096^3 (CUDA cores, FP64 FMA)", "bytes": 3 * dm * dm * 8, "ms": round(med, 4), "ms_min": round(best, 4),
+                 "GBps": round(3 * dm * dm * 8 / (med * 1e-3) / 1e9, 1), "frac_of_measured": None, "frac_of_nominal": None,
+                 "TFLOPs": round(2.0 * dm ** 3 / (med * 1e-3) / 1e12, 1), "cublas_fp64_ms": round(med_lib, 4),
+                 "cublas_fp64_TFLOPs": round(2.0 * dm ** 3 / (med_lib * 1e-3) / 1e12, 1)})
     return rows
 
 

@@ -395,7 +395,7 @@ ew_tile_kernel(const TilePlan t, const char* __restrict__ a1, const char* __rest
     const bool have1 = use_scalar != 2;
     const bool have2 = Op::arity == 2 && use_scalar != 1;
     for (int64_t tile = blockIdx.x; tile < t.n_tiles; tile += gridDim.x) {
-        // tiles along c vary fastest, then r, then the batch
+        // tiles along c vary fastest (the CTAs resident at one time write long runs of each output row), then r, then the batch
         const int64_t tc = tile % t.tiles_c;
         const int64_t rest = tile / t.tiles_c;
         const int64_t tr = rest % t.tiles_r;
@@ -404,15 +404,28 @@ ew_tile_kernel(const TilePlan t, const char* __restrict__ a1, const char* __rest
         offsets_of<3>(batch, t.n_outer, t.oshape, t.ostep, off);
         const int64_t r0 = tr * TR, c0 = tc * TC;
         if (T1 || T2) {
-            __syncthreads();                   // the previous tile may still be read
-            // lanes along r: element (r0 + lr, c0 + lc) of a transposed input sits lr elements on from the start of its line
+            // lanes along r: element (r0 + lr, c0 + lc) of a transposed input sits lr elements on from the start of its line.
+            // All of a thread's loads are issued before the first is parked, so that they are in flight together.
+            constexpr int CP = kBlock / TR;        // lines per pass
+            constexpr int NL = TC / CP;            // loads per thread and operand
             const int lr = threadIdx.x % TR;
+            const int lc0 = threadIdx.x / TR;
             const bool r_ok = r0 + lr < t.R;
-#pragma unroll 8
-            for (int lc = threadIdx.x / TR; lc < TC; lc += kBlock / TR) {
-                const bool ok = r_ok && c0 + lc < t.C;
-                if (T1 && ok) tile1[lc][lr] = ld_one<X>(a1 + off[0] + (r0 + lr) * t.rstep[0] + (c0 + lc) * t.cstep[0]);
-                if (T2 && ok) tile2[lc][lr] = ld_one<Y>(a2 + off[1] + (r0 + lr) * t.rstep[1] + (c0 + lc) * t.cstep[1]);
+            X xv[T1 ? NL : 1];
+            Y yv[T2 ? NL : 1];
+            const char* q1 = a1 + off[0] + (r0 + lr) * t.rstep[0] + (c0 + lc0) * t.cstep[0];
+            const char* q2 = a2 + off[1] + (r0 + lr) * t.rstep[1] + (c0 + lc0) * t.cstep[1];
+#pragma unroll
+            for (int j = 0; j < NL; ++j) {
+                const bool ok = r_ok && c0 + lc0 + j * CP < t.C;
+                if (T1) xv[j] = ok ? ld_one<X>(q1 + (int64_t)j * CP * t.cstep[0]) : X();
+                if (T2) yv[j] = ok ? ld_one<Y>(q2 + (int64_t)j * CP * t.cstep[1]) : Y();
+            }
+            __syncthreads();                   // the previous tile may still be read
+#pragma unroll
+            for (int j = 0; j < NL; ++j) {
+                if (T1) tile1[lc0 + j * CP][lr] = xv[j];
+                if (T2) tile2[lc0 + j * CP][lr] = yv[j];
             }
             __syncthreads();
         }
@@ -421,7 +434,11 @@ ew_tile_kernel(const TilePlan t, const char* __restrict__ a1, const char* __rest
         const bool c_ok = c0 + lc < t.C;
         constexpr int RP = kBlock / TC;        // rows per pass
         constexpr int UN = 8;                  // loads of the row-like operands in flight per thread
-        for (int lr0 = threadIdx.x / TC; lr0 < TR; lr0 += RP * UN) {
+        const int lrt = threadIdx.x / TC;
+        const char* w1 = a1 + off[0] + (r0 + lrt) * t.rstep[0] + (c0 + lc) * t.cstep[0];
+        const char* w2 = a2 + off[1] + (r0 + lrt) * t.rstep[1] + (c0 + lc) * t.cstep[1];
+        char* w3 = a3 + off[2] + (r0 + lrt) * t.rstep[2] + (c0 + lc) * t.cstep[2];
+        for (int lr0 = lrt; lr0 < TR; lr0 += RP * UN) {
             X x[UN];
             Y y[UN];
             bool ok[UN];
@@ -432,16 +449,16 @@ ew_tile_kernel(const TilePlan t, const char* __restrict__ a1, const char* __rest
                 x[j] = sx; y[j] = sy;
                 if (!ok[j]) continue;
                 if (T1) x[j] = tile1[lc][lr];
-                else if (have1) x[j] = ld_one<X>(a1 + off[0] + (r0 + lr) * t.rstep[0] + (c0 + lc) * t.cstep[0]);
+                else if (have1) x[j] = ld_one<X>(w1 + (int64_t)(lr - lrt) * t.rstep[0]);
                 if (T2) y[j] = tile2[lc][lr];
-                else if (have2) y[j] = ld_one<Y>(a2 + off[1] + (r0 + lr) * t.rstep[1] + (c0 + lc) * t.cstep[1]);
+                else if (have2) y[j] = ld_one<Y>(w2 + (int64_t)(lr - lrt) * t.rstep[1]);
             }
 #pragma unroll
             for (int j = 0; j < UN; ++j) {
                 if (!ok[j]) continue;
                 const int lr = lr0 + j * RP;
                 TO z;
-                if (Op::apply(x[j], y[j], z, flag)) st_one<TO>(a3 + off[2] + (r0 + lr) * t.rstep[2] + (c0 + lc) * t.cstep[2], z);
+                if (Op::apply(x[j], y[j], z, flag)) st_one<TO>(w3 + (int64_t)(lr - lrt) * t.rstep[2], z);
             }
         }
     }

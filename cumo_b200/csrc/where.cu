@@ -10,7 +10,8 @@
 // funnel shift when the run is contiguous, 32 single-bit loads otherwise).  A tile is 256 threads
 // x 4 consecutive chunks.  (1) every CTA counts the hits of its tiles, (2) one CTA turns the
 // counts into output positions and advances the cursor, (3) every CTA gathers its chunks again,
-// scans its threads' counts and writes the positions.  The reference caps the grid at 1024
+// scans its threads' counts, lays the hits of 8192 elements out in shared memory and writes them
+// as one run of consecutive stores.  The reference caps the grid at 1024
 // blocks; here it grows with the run up to 65536 CTAs.
 #include "common.cuh"
 
@@ -159,37 +160,34 @@ __global__ void __launch_bounds__(kBlock)
 where_scatter_kernel(const WhereRun r, uint64_t tiles_per_cta, uint64_t n_tiles, const unsigned long long* __restrict__ cta_pos,
                      TI* out, const Emit emit) {
     __shared__ uint32_t smem[kWarpsPerBlock + 1];
+    // the hits of one sub-tile (kBlock chunks = 8192 elements), as element numbers relative to the sub-tile, in order
+    __shared__ uint16_t rel[kBlock * 32];
     const uint64_t t_begin = blockIdx.x * tiles_per_cta;
     uint64_t t_end = t_begin + tiles_per_cta; if (t_end > n_tiles) t_end = n_tiles;
     unsigned long long off = cta_pos[blockIdx.x];
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const uint32_t below = (1u << lane) - 1u;
     for (uint64_t t = t_begin; t < t_end; ++t) {
-        const uint64_t c0 = t * kWhereTileChunks + (uint64_t)threadIdx.x * kWhereChunksPerThread;
-        uint32_t z[kWhereChunksPerThread];
-        uint32_t mine = 0;
-#pragma unroll
-        for (int j = 0; j < kWhereChunksPerThread; ++j) { z[j] = where_chunk(r, c0 + j); mine += __popc(z[j]); }
-        uint32_t total;
-        const uint32_t pre = block_exscan(mine, &total, smem);
-        // Expansion, a warp at a time over its 128 chunks: the word of chunk (lane s, j) is broadcast and every
-        // lane k writes position k if it is set, at the word's output offset plus the number of set bits below k.
-        // A word's positions leave in one coalesced store instead of up to 32 stores from one thread.
-        const int lane = threadIdx.x & 31;
-        const uint32_t below = (1u << lane) - 1u;
-        uint32_t o_local = pre;                              // my chunk j starts at off + o_local
-#pragma unroll
-        for (int j = 0; j < kWhereChunksPerThread; ++j) {
-            const uint32_t my_word = z[j];
-            const uint32_t my_off = o_local;
-            o_local += __popc(my_word);
+        for (int sub = 0; sub < kWhereChunksPerThread; ++sub) {
+            const uint64_t cbase = t * kWhereTileChunks + (uint64_t)sub * kBlock;      // first chunk of the sub-tile
+            const uint32_t z = where_chunk(r, cbase + threadIdx.x);
+            uint32_t total;
+            const uint32_t pre = block_exscan((uint32_t)__popc(z), &total, smem);
+            // Expansion into shared memory, a warp at a time over its 32 chunks: the word of lane `src` is broadcast and
+            // every lane k whose bit is set notes element (chunk, k) at the word's offset plus the set bits below k.
             for (int src = 0; src < 32; ++src) {
-                const uint32_t w = __shfl_sync(0xffffffffu, my_word, src);
-                if (w == 0) continue;                        // warp-uniform
-                const uint32_t wo = __shfl_sync(0xffffffffu, my_off, src);
-                const uint64_t c_src = c0 - (uint64_t)lane * kWhereChunksPerThread + (uint64_t)src * kWhereChunksPerThread + j;
-                if ((w >> lane) & 1u) out[off + wo + __popc(w & below)] = (TI)emit(c_src * 32 + lane);
+                const uint32_t w = __shfl_sync(0xffffffffu, z, src);
+                if (w == 0) continue;                            // warp-uniform
+                const uint32_t wo = __shfl_sync(0xffffffffu, pre, src);
+                if ((w >> lane) & 1u) rel[wo + __popc(w & below)] = (uint16_t)((warp * 32 + src) * 32 + lane);
             }
+            __syncthreads();
+            // The sub-tile's positions leave as one run of consecutive stores: whole lines except at the two ends.
+            // (Writing each word's few positions straight to global memory made L2 fetch every partly written sector.)
+            for (uint32_t o = threadIdx.x; o < total; o += kBlock) out[off + o] = (TI)emit(cbase * 32 + rel[o]);
+            off += total;
+            // the barriers inside the next block_exscan keep `rel` from being rewritten before everyone has read it
         }
-        off += total;
     }
 }
 

@@ -1,4 +1,5 @@
-"""Matrix products of SFloat arrays on the tensor cores.
+"""Matrix products: SFloat on the tensor cores, DFloat and the batched / transposed / alpha-beta forms through
+`cb200_{s,d}gemm_strided_batched` (the argument list of the cuBLAS call in the reference's gemm.c:277-296).
 
 `dot(a, b)` is the reference's `a.dot(b)` for 2-D single-precision operands (ext/cumo/narray/gen/tmpl/gemm.c:252-297
 hands it to cublasSgemm); here it runs `cb200_sgemm_nt_tc`, a tcgen05 kernel that keeps fp32-grade accuracy by
@@ -10,7 +11,7 @@ from __future__ import annotations
 from ctypes import c_char_p, c_int, c_int64, c_size_t, c_void_p, create_string_buffer
 
 from . import _lib
-from .narray import CumoError, SFloat
+from .narray import CumoError, DFloat, SFloat
 
 
 def gemm_nt(a: SFloat, bt: SFloat) -> SFloat:
@@ -33,10 +34,60 @@ def gemm_nt(a: SFloat, bt: SFloat) -> SFloat:
     return out
 
 
-def dot(a: SFloat, b: SFloat) -> SFloat:
-    """a (M, K) . b (K, N) -> (M, N); a 1-D second operand gives (M,)."""
+def gemm(a, b, alpha=1.0, beta=0.0, c=None):
+    """The reference's `Cumo::NArray#gemm` for SFloat / DFloat operands (row-major, the last two axes are the
+    matrices, leading axes are batches; either operand may be a transposed view): alpha * a . b + beta * c.
+    It hands cuBLAS's column-major bookkeeping to the library exactly as gemm.c does: c^T = b^T . a^T."""
+    from ctypes import byref, c_double, c_float, c_longlong
+
+    T = type(a)
+    if T not in (SFloat, DFloat) or type(b) is not T or a.ndim < 2 or b.ndim != a.ndim or a.shape[:-2] != b.shape[:-2]:
+        raise TypeError("gemm needs two SFloat or two DFloat arrays of the same batch shape")
+    m, k = a.shape[-2:]
+    k2, n = b.shape[-2:]
+    if k != k2:
+        raise ValueError(f"shape mismatch: {a.shape} . {b.shape}")
+    es = 4 if T is SFloat else 8
+
+    def layout(x):
+        """(array usable as it is or a contiguous copy, trans flag, leading dimension, batch stride in elements)"""
+        st = x.steps
+        rows, cols = x.shape[-2:]
+        batch_ok = all(st[d] == (x.shape[d + 1] * st[d + 1] if d + 1 < x.ndim - 2 else rows * cols * es) for d in range(x.ndim - 2))
+        if batch_ok and st[-1] == es and st[-2] >= cols * es and st[-2] % es == 0:
+            return x, 0, st[-2] // es, rows * cols            # row-major: column-major of its transpose, no flag
+        if batch_ok and st[-2] == es and st[-1] >= rows * es and st[-1] % es == 0:
+            return x, 1, st[-1] // es, rows * cols            # a transposed view: flag T
+        y = x.dup()
+        return y, 0, cols, rows * cols
+    a2, ta, lda, sa = layout(a)
+    b2, tb, ldb, sb = layout(b)
+    batch = 1
+    for d in a.shape[:-2]:
+        batch *= d
+    out = T(*a.shape[:-2], m, n) if c is None or beta == 0.0 else c.dup()
+    lib = _lib.load()
+    fn = lib.cb200_sgemm_strided_batched if T is SFloat else lib.cb200_dgemm_strided_batched
+    fn.restype = c_int
+    fn.argtypes = None
+    cT = c_float if T is SFloat else c_double
+    rc = fn(c_int(tb), c_int(ta), c_int(n), c_int(m), c_int(k), byref(cT(alpha)), c_void_p(b2.data_ptr), c_int(ldb), c_longlong(sb),
+            c_void_p(a2.data_ptr), c_int(lda), c_longlong(sa), byref(cT(beta)), c_void_p(out.data_ptr), c_int(n), c_longlong(m * n), c_int(batch))
+    if rc:
+        raise CumoError(f"gemm failed with status {rc}")
+    return out
+
+
+def dot(a, b):
+    """a (M, K) . b (K, N) -> (M, N); a 1-D second operand gives (M,).  DFloat operands take the CUDA-core product."""
+    if isinstance(a, DFloat) and isinstance(b, DFloat):
+        if a.ndim == 2 and b.ndim == 2:
+            return gemm(a, b)
+        if a.ndim == 2 and b.ndim == 1:
+            return gemm(a, b.reshape(b.shape[0], 1)).reshape(a.shape[0])
+        raise TypeError("dot takes a 2-D first operand and a 1-D or 2-D second one")
     if not (isinstance(a, SFloat) and isinstance(b, SFloat)):
-        raise TypeError("the tensor-core product is built for SFloat operands")
+        raise TypeError("dot is built for two SFloat or two DFloat operands")
     if a.ndim == 2 and b.ndim == 2:
         return gemm_nt(a, b.transpose().dup())
     if a.ndim == 2 and b.ndim == 1:

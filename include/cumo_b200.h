@@ -332,6 +332,18 @@ void cb200_dfloat_rank_fold_sum_kernel_launch(const char* partials, int64_t rank
                                                  int is_max, int nan_wins, int64_t* out_index, char* out_value);
 CB200_DECL_FOLD_ARG(sfloat) CB200_DECL_FOLD_ARG(dfloat) CB200_DECL_FOLD_ARG(int32) CB200_DECL_FOLD_ARG(int64)
 
+/* General matrix product with the argument list of cublas<T>gemmStridedBatched minus the handle (column-major:
+ * C (m x n, ldc) = alpha * op(A) * op(B) + beta * C for `batch` entries `stride*` elements apart; transa/transb 0 = N,
+ * 1 = T, 2 = C; alpha, beta host pointers).  Stands where the reference's host template calls cuBLAS for `dot`
+ * (ext/cumo/narray/gen/tmpl/gemm.c:277-296); the reference has no launch function of its own for it.  Single precision
+ * with alpha 1, beta 0 and K a multiple of 4 runs on the tensor cores (cb200_sgemm_nt_tc, an operand that is not
+ * K-contiguous is copied transposed first); everything else, double precision included, on the CUDA cores.
+ * Returns 0, 7 (invalid value) or 13 (execution failed), the cublasStatus_t codes. */
+int cb200_sgemm_strided_batched(int transa, int transb, int m, int n, int k, const float* alpha, const float* A, int lda, long long strideA,
+                                const float* B, int ldb, long long strideB, const float* beta, float* C, int ldc, long long strideC, int batch);
+int cb200_dgemm_strided_batched(int transa, int transb, int m, int n, int k, const double* alpha, const double* A, int lda, long long strideA,
+                                const double* B, int ldb, long long strideB, const double* beta, double* C, int ldc, long long strideC, int batch);
+
 /* kahan_sum exists for the double-precision type only (reference: gen/spec.rb:321-323,
  * float_accum_kernel.cu:196-206). */
 CB200_DECL_ACCUM(dfloat, double, kahan_sum)

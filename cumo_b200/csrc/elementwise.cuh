@@ -464,6 +464,124 @@ ew_tile_kernel(const TilePlan t, const char* __restrict__ a1, const char* __rest
     }
 }
 
+// The same plan with 16-byte global accesses, for operands of one element size whose lines are 16-byte aligned and
+// whose plane extents are whole packets: the transposed input is read a packet (V elements along r) at a time and parked
+// element by element; the output phase gathers V parked elements (along c) per thread, loads one packet of each row-like
+// operand and stores one packet.  About a fifth of the instructions per element of the element-wise form, which is
+// bound by instruction issue, not by DRAM (75 % of issue slots busy at 57 % of DRAM throughput when measured).
+template <typename Op, bool T1, bool T2, int TC>
+__global__ void __launch_bounds__(kBlock)
+ew_tile_vec_kernel(const TilePlan t, const char* __restrict__ a1, const char* __restrict__ a2, char* a3,
+                   typename Op::In1 sx, typename Op::In2 sy, int use_scalar, int* flag) {
+    using X = typename Op::In1;
+    using Y = typename Op::In2;
+    using TO = typename Op::Out;
+    static_assert(sizeof(X) == sizeof(TO) && sizeof(Y) == sizeof(TO), "one element size");
+    constexpr int ES = sizeof(TO);
+    constexpr int V = 16 / ES;
+    constexpr int TR = kTileR;
+    constexpr int PR = TR / V;                 // packets along r per line
+    constexpr int LP = kBlock / PR;            // lines per pass of the load phase
+    constexpr int NL = TC / LP;                // passes
+    constexpr int PC = TC / V;                 // packets along c per row
+    constexpr int RP = kBlock / PC;            // rows per pass of the output phase
+    constexpr int NR = TR / RP;                // passes
+    __shared__ X tile1[T1 ? TC : 1][T1 ? TR + 1 : 1];
+    __shared__ Y tile2[T2 ? TC : 1][T2 ? TR + 1 : 1];
+    const bool have1 = use_scalar != 2;
+    const bool have2 = Op::arity == 2 && use_scalar != 1;
+    for (int64_t tile = blockIdx.x; tile < t.n_tiles; tile += gridDim.x) {
+        const int64_t tc = tile % t.tiles_c;
+        const int64_t rest = tile / t.tiles_c;
+        const int64_t tr = rest % t.tiles_r;
+        const int64_t batch = rest / t.tiles_r;
+        int64_t off[3];
+        offsets_of<3>(batch, t.n_outer, t.oshape, t.ostep, off);
+        const int64_t r0 = tr * TR, c0 = tc * TC;
+        if (T1 || T2) {
+            const int pk = threadIdx.x % PR;                     // packet along r
+            const int l0 = threadIdx.x / PR;                     // first line
+            const bool r_ok = r0 + pk * V < t.R;                 // extents are whole packets: a packet is in or out
+            Pack<X> xv[T1 ? NL : 1];
+            Pack<Y> yv[T2 ? NL : 1];
+            const char* q1 = a1 + off[0] + (r0 + pk * V) * ES + (c0 + l0) * t.cstep[0];
+            const char* q2 = a2 + off[1] + (r0 + pk * V) * ES + (c0 + l0) * t.cstep[1];
+            const int64_t inc1 = (int64_t)LP * t.cstep[0], inc2 = (int64_t)LP * t.cstep[1];
+#pragma unroll
+            for (int j = 0; j < NL; ++j) {
+                const bool ok = r_ok && c0 + l0 + j * LP < t.C;
+                if (T1 && ok) xv[j] = ld_pack<X>(q1 + j * inc1);
+                if (T2 && ok) yv[j] = ld_pack<Y>(q2 + j * inc2);
+            }
+            __syncthreads();                   // the previous tile may still be read
+#pragma unroll
+            for (int j = 0; j < NL; ++j) {
+#pragma unroll
+                for (int e = 0; e < V; ++e) {
+                    if (T1) tile1[l0 + j * LP][pk * V + e] = xv[j].v[e];
+                    if (T2) tile2[l0 + j * LP][pk * V + e] = yv[j].v[e];
+                }
+            }
+            __syncthreads();
+        }
+        const int pc = threadIdx.x % PC;                         // packet along c
+        const int lr0 = threadIdx.x / PC;                        // first row
+        const bool c_ok = c0 + pc * V < t.C;
+        const char* w1 = a1 + off[0] + (r0 + lr0) * t.rstep[0] + (c0 + pc * V) * (t.cstep[0] ? ES : 0);
+        const char* w2 = a2 + off[1] + (r0 + lr0) * t.rstep[1] + (c0 + pc * V) * (t.cstep[1] ? ES : 0);
+        char* w3 = a3 + off[2] + (r0 + lr0) * t.rstep[2] + (c0 + pc * V) * ES;
+        const int64_t i1 = (int64_t)RP * t.rstep[0], i2 = (int64_t)RP * t.rstep[1], i3 = (int64_t)RP * t.rstep[2];
+        Pack<X> x[NR];
+        Pack<Y> y[NR];
+#pragma unroll
+        for (int j = 0; j < NR; ++j) {
+            const int lr = lr0 + j * RP;
+            const bool ok = c_ok && r0 + lr < t.R;
+#pragma unroll
+            for (int e = 0; e < V; ++e) { x[j].v[e] = sx; y[j].v[e] = sy; }
+            if (!ok) continue;
+            if (T1) {
+#pragma unroll
+                for (int e = 0; e < V; ++e) x[j].v[e] = tile1[pc * V + e][lr];
+            } else if (have1) {
+                if (t.cstep[0]) x[j] = ld_pack<X>(w1 + j * i1);
+                else { const X s = ld_one<X>(w1 + j * i1);
+#pragma unroll
+                       for (int e = 0; e < V; ++e) x[j].v[e] = s; }
+            }
+            if (T2) {
+#pragma unroll
+                for (int e = 0; e < V; ++e) y[j].v[e] = tile2[pc * V + e][lr];
+            } else if (have2) {
+                if (t.cstep[1]) y[j] = ld_pack<Y>(w2 + j * i2);
+                else { const Y s = ld_one<Y>(w2 + j * i2);
+#pragma unroll
+                       for (int e = 0; e < V; ++e) y[j].v[e] = s; }
+            }
+        }
+#pragma unroll
+        for (int j = 0; j < NR; ++j) {
+            const int lr = lr0 + j * RP;
+            if (!(c_ok && r0 + lr < t.R)) continue;
+            Pack<TO> z;
+            unsigned keep = 0;
+#pragma unroll
+            for (int e = 0; e < V; ++e) {
+                TO zv = TO();
+                if (Op::apply(x[j].v[e], y[j].v[e], zv, flag)) keep |= 1u << e;
+                z.v[e] = zv;
+            }
+            char* q = w3 + j * i3;
+            if (keep == (1u << V) - 1u) st_pack<TO>(q, z);
+            else {
+#pragma unroll
+                for (int e = 0; e < V; ++e)
+                    if (keep & (1u << e)) st_one<TO>(q + e * ES, z.v[e]);
+            }
+        }
+    }
+}
+
 // Plans the tile kernel for `p`; false when the operation is not of that shape (the generic kernel takes it).
 template <typename Op>
 bool launch_tiled(const EwPlan& p, const char* p1, const char* p2, char* p3, bool have1, bool have2,
@@ -507,6 +625,31 @@ bool launch_tiled(const EwPlan& p, const char* p1, const char* p2, char* p3, boo
     for (int d = 0; d < t.n_outer; ++d) batch *= t.oshape[d];
     t.n_tiles = t.tiles_r * t.tiles_c * batch;
     const unsigned grid = (unsigned)(t.n_tiles > kMaxGrid ? kMaxGrid : t.n_tiles);
+    // 16-byte accesses when every operand has the same element size, the plane's extents are whole packets, and every
+    // line of every operand starts on a 16-byte boundary
+    if constexpr (sizeof(typename Op::In1) == sizeof(typename Op::Out) && sizeof(typename Op::In2) == sizeof(typename Op::Out)) {
+        constexpr int V = 16 / (int)sizeof(typename Op::Out);
+        bool vec = t.R % V == 0 && t.C % V == 0 && aligned16(p3) && mult16(t.rstep[2]);
+        const char* bases[2] = {p1, p2};
+        for (int a = 0; a < 2 && vec; ++a) {
+            if (!have[a]) continue;
+            if (!aligned16(bases[a])) vec = false;
+            if (tr[a]) { if (!mult16(t.cstep[a])) vec = false; }                     // lines of a transposed input
+            else if (t.cstep[a] != 0 && !mult16(t.rstep[a])) vec = false;            // rows of a row-like input read by packets
+        }
+        for (int d = 0; d < t.n_outer && vec; ++d)
+            for (int a = 0; a < 3; ++a) if ((a == 2 || have[a]) && !mult16(t.ostep[a][d])) vec = false;
+        if (vec) {
+            if constexpr (Op::arity == 1) {
+                ew_tile_vec_kernel<Op, true, false, TC><<<grid, kBlock, 0, st>>>(t, p1, p2, p3, sx, sy, use_scalar, flag);
+            } else {
+                if (tr[0] && tr[1])  ew_tile_vec_kernel<Op, true, true, TC><<<grid, kBlock, 0, st>>>(t, p1, p2, p3, sx, sy, use_scalar, flag);
+                else if (tr[0])      ew_tile_vec_kernel<Op, true, false, TC><<<grid, kBlock, 0, st>>>(t, p1, p2, p3, sx, sy, use_scalar, flag);
+                else                 ew_tile_vec_kernel<Op, false, true, TC><<<grid, kBlock, 0, st>>>(t, p1, p2, p3, sx, sy, use_scalar, flag);
+            }
+            return true;
+        }
+    }
     if constexpr (Op::arity == 1) {
         ew_tile_kernel<Op, true, false, TC><<<grid, kBlock, 0, st>>>(t, p1, p2, p3, sx, sy, use_scalar, flag);
     } else {

@@ -1,10 +1,9 @@
 """Matrix products: SFloat on the tensor cores, DFloat and the batched / transposed / alpha-beta forms through
 `cb200_{s,d}gemm_strided_batched` (the argument list of the cuBLAS call in the reference's gemm.c:277-296).
 
-`dot(a, b)` is the reference's `a.dot(b)` for 2-D single-precision operands (ext/cumo/narray/gen/tmpl/gemm.c:252-297
-hands it to cublasSgemm); here it runs `cb200_sgemm_nt_tc`, a tcgen05 kernel that keeps fp32-grade accuracy by
-splitting every operand into two TF32 numbers.  The kernel wants the second operand with K contiguous
-(`bt[n, k]`): `dot` makes that copy with the library's own strided-copy kernel, `gemm_nt` takes it as given.
+`dot(a, b)` is the reference's `a.dot(b)` on float matrices (ext/cumo/narray/gen/tmpl/gemm.c:252-297 hands it to
+cuBLAS).  `gemm_nt` calls `cb200_sgemm_nt_tc` directly: a tcgen05 kernel that keeps fp32-grade accuracy by splitting
+every operand into two TF32 numbers and wants both operands with K contiguous.
 """
 from __future__ import annotations
 
@@ -79,17 +78,13 @@ def gemm(a, b, alpha=1.0, beta=0.0, c=None):
 
 
 def dot(a, b):
-    """a (M, K) . b (K, N) -> (M, N); a 1-D second operand gives (M,).  DFloat operands take the CUDA-core product."""
-    if isinstance(a, DFloat) and isinstance(b, DFloat):
-        if a.ndim == 2 and b.ndim == 2:
-            return gemm(a, b)
-        if a.ndim == 2 and b.ndim == 1:
-            return gemm(a, b.reshape(b.shape[0], 1)).reshape(a.shape[0])
-        raise TypeError("dot takes a 2-D first operand and a 1-D or 2-D second one")
-    if not (isinstance(a, SFloat) and isinstance(b, SFloat)):
+    """a (M, K) . b (K, N) -> (M, N); a 1-D second operand gives (M,).  Both SFloat or both DFloat: the reference's
+    `dot` on float matrices is `gemm` (lib/cumo/narray/extra.rb:1145-1196).  Large single-precision products run on the
+    tensor cores, the rest on the CUDA-core kernel."""
+    if not ((isinstance(a, SFloat) and isinstance(b, SFloat)) or (isinstance(a, DFloat) and isinstance(b, DFloat))):
         raise TypeError("dot is built for two SFloat or two DFloat operands")
     if a.ndim == 2 and b.ndim == 2:
-        return gemm_nt(a, b.transpose().dup())
+        return gemm(a, b)
     if a.ndim == 2 and b.ndim == 1:
-        return gemm_nt(a, b.reshape(1, b.shape[0])).reshape(a.shape[0])
+        return gemm(a, b.reshape(b.shape[0], 1)).reshape(a.shape[0])
     raise TypeError("dot takes a 2-D first operand and a 1-D or 2-D second one")

@@ -821,6 +821,7 @@ def build_cases(xp, torch, mib: int):
         return a, a.sum(axis=1).reshape(rows32, 1)
 
     side = int((rows32 * cols) ** 0.5) // 64 * 64
+    side64 = int((rows64 * cols) ** 0.5) // 64 * 64
 
     def sq():
         return f32()[0:side * side].reshape(side, side)
@@ -874,6 +875,8 @@ def build_cases(xp, torch, mib: int):
         # operands whose contiguous axes differ: the shared-memory tile kernel
         "add_transposed": (lambda: (lambda a=sq(), b=sq2(): a + b.transpose()), 3 * side * side * 4),
         "copy_transposed": (lambda: (lambda b=sq(): b.transpose().dup()), 2 * side * side * 4),
+        "copy_transposed_f64": (lambda: (lambda b=f64()[0:side64 * side64].reshape(side64, side64): b.transpose().dup()), 2 * side64 * side64 * 8),
+        "add_transposed_f64": (lambda: (lambda a=f64()[0:side64 * side64].reshape(side64, side64): a + a.transpose()), 3 * side64 * side64 * 8),
         "cast_transposed_i32": (lambda: (lambda b=i32()[0:side * side].reshape(side, side): xp.SFloat.cast(b.transpose())), 2 * side * side * 4),
     }
     return cases

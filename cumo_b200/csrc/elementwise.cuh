@@ -31,6 +31,7 @@
 
 #include "common.cuh"
 #include "ops.cuh"
+#include "tile_tma.cuh"
 
 namespace cb200 {
 
@@ -373,15 +374,6 @@ ew_gen_kernel(const EwPlan p, int64_t n_tiles, const char* __restrict__ a1, cons
 // than the two of the plane are walked as a batch index.  Works for any element sizes and alignments.
 constexpr int kTileR = 64;
 
-struct TilePlan {
-    int n_outer;                              // dims besides the plane
-    int64_t oshape[kMaxDim];
-    int64_t ostep[3][kMaxDim];                // [0],[1] inputs, [2] output
-    int64_t R, C;                             // extents of the plane: r = the transposed inputs' contiguous axis, c = the output's
-    int64_t rstep[3], cstep[3];               // byte steps along r and c per operand
-    int64_t tiles_r, tiles_c, n_tiles;
-};
-
 template <typename Op, bool T1, bool T2, int TC>
 __global__ void __launch_bounds__(kBlock)
 ew_tile_kernel(const TilePlan t, const char* __restrict__ a1, const char* __restrict__ a2, char* a3,
@@ -639,6 +631,7 @@ bool launch_tiled(const EwPlan& p, const char* p1, const char* p2, char* p3, boo
         }
         for (int d = 0; d < t.n_outer && vec; ++d)
             for (int a = 0; a < 3; ++a) if ((a == 2 || have[a]) && !mult16(t.ostep[a][d])) vec = false;
+        if (vec && launch_tiled_tma<Op>(t, tr, p1, p2, p3, have1, have2, sx, sy, flag, st)) return true;
         if (vec) {
             if constexpr (Op::arity == 1) {
                 ew_tile_vec_kernel<Op, true, false, TC><<<grid, kBlock, 0, st>>>(t, p1, p2, p3, sx, sy, use_scalar, flag);

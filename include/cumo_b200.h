@@ -389,6 +389,21 @@ int cb200_kmeans_assign_sfloat_tc(const float* x, int64_t n, int d, const float*
  * completed, 3/4 on launch problems.  The kernel always returns; the context stays usable. */
 int cb200_selftest_bounded_wait(unsigned spin_limit, char* errbuf, size_t errlen);
 
+/* Elementwise operations on operands whose contiguous axes differ (`a + b.transpose`, `b.transpose.dup`, a cast of a
+ * transposed view; reference: the strided branches of binary_kernel.cu:14-49, unary_kernel.cu:14-25, store_from_kernel.cu)
+ * run, when every operand is 16-byte aligned, in a kernel whose input tiles are copied into shared memory by the tensor
+ * memory accelerator several tiles ahead of the warps that use them.  Its waits are bounded; the launch functions return
+ * void, so the outcome is kept in a status word:
+ *   cb200_tile_pipeline_status(): 0 = no wait ran out on the current device since the last call, 1 = one did and that
+ *     launch's output is not valid, 2 = the kernel found its shared memory misaligned and wrote nothing, -1 = the word
+ *     could not be read.  Synchronises the device and clears the word.
+ *   cb200_tile_pipeline_launches(): launches of that kernel in this process.
+ * CB200_TILE_TMA in the environment: 0 sends such operands through the register-staged tile kernels, 1 through this
+ * kernel whenever it can take them; unset, each goes where it measured faster (8-byte elements and planes up to
+ * 256 MiB here). */
+int cb200_tile_pipeline_status(void);
+unsigned long long cb200_tile_pipeline_launches(void);
+
 /* float32 `sum` that allocates nothing (no counterpart in the reference, whose reductions
  * always take scratch from cumo_cuda_runtime_malloc).  For callers that cannot reach an
  * allocator when they need the sum: a finalizer or other context in which the Ruby

@@ -8,6 +8,7 @@
 // in a1; scalar_is_left says the numeric is the left operand, in which case the
 // array becomes the kernel's second input.
 #include "elementwise.cuh"
+#include "divmod_scalar.cuh"
 
 using namespace cb200;
 
@@ -29,6 +30,17 @@ using namespace cb200;
     DEF_BINARY(name, OP)                                                                               \
     extern "C" void CB_ITER(name, _s_kernel_launch)(cumo_na_iarray_t* a1, CB_C sv, cumo_na_iarray_t* a3, \
             cumo_na_indexer_t* ix, int* divzero, int scalar_is_left) {                                  \
+        if (scalar_is_left) launch_elementwise<op::OP<CB_C>>(nullptr, a1, a3, ix, sv, CB_C(), 2, divzero); \
+        else launch_elementwise<op::OP<CB_C>>(a1, nullptr, a3, ix, CB_C(), sv, 1, divzero);             \
+    }
+// integer division and remainder by a host scalar on the right: the divisor is turned into a multiplier on the host
+#define DEF_BINARY_S_DIVMOD(name, OP, IS_MOD)                                                          \
+    DEF_BINARY(name, OP)                                                                               \
+    extern "C" void CB_ITER(name, _s_kernel_launch)(cumo_na_iarray_t* a1, CB_C sv, cumo_na_iarray_t* a3, \
+            cumo_na_indexer_t* ix, int* divzero, int scalar_is_left) {                                  \
+        if constexpr (std::is_integral<CB_C>::value) {                                                 \
+            if (!scalar_is_left && launch_int_divmod_by_scalar<CB_C, IS_MOD>(a1, sv, a3, ix)) return;  \
+        }                                                                                              \
         if (scalar_is_left) launch_elementwise<op::OP<CB_C>>(nullptr, a1, a3, ix, sv, CB_C(), 2, divzero); \
         else launch_elementwise<op::OP<CB_C>>(a1, nullptr, a3, ix, CB_C(), sv, 1, divzero);             \
     }
@@ -95,8 +107,8 @@ DEF_STORE(uint8, uint8_t)
 DEF_BINARY_S(add, Add)
 DEF_BINARY_S(sub, Sub)
 DEF_BINARY_S(mul, Mul)
-DEF_BINARY_S(div, Div)
-DEF_BINARY_S(mod, Mod)
+DEF_BINARY_S_DIVMOD(div, Div, false)
+DEF_BINARY_S_DIVMOD(mod, Mod, true)
 DEF_UNARY(minus, Minus)
 DEF_UNARY(reciprocal, Reciprocal)
 DEF_UNARY(sign, Sign)

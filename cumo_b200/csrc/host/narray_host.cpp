@@ -156,13 +156,19 @@ void* sym(const std::string& name) {
 
 // ---- the int* flag of integer div/mod/reciprocal/abs ------------------------------------
 // One mapped pinned int per thread, as ext/cumo/cuda/runtime.c:22-47 allocates per call.
+// (bincount's second word, the offending item, shares the allocation: a mapped allocation per call costs more than the
+// kernels of a small call.)
 struct Flag {
     int* host = nullptr;
     int* dev = nullptr;
+    size_t* item_host = nullptr;
+    size_t* item_dev = nullptr;
     bool ready() {
         if (host) return true;
-        if (cudaHostAlloc((void**)&host, sizeof(int), cudaHostAllocMapped) != cudaSuccess) { host = nullptr; return false; }
+        if (cudaHostAlloc((void**)&host, 16, cudaHostAllocMapped) != cudaSuccess) { host = nullptr; return false; }
         if (cudaHostGetDevicePointer((void**)&dev, host, 0) != cudaSuccess) { cudaFreeHost(host); host = nullptr; return false; }
+        item_host = reinterpret_cast<size_t*>(reinterpret_cast<char*>(host) + 8);
+        item_dev = reinterpret_cast<size_t*>(reinterpret_cast<char*>(dev) + 8);
         return true;
     }
 };
@@ -1003,10 +1009,8 @@ cb200_na_t* cb200_na_bincount(cb200_na_t* a, cb200_na_t* weight, int64_t minleng
     // mapped pinned words: the out-of-range flag and the offending item
     bool ok = f != nullptr;
     if (ok && !tl_flag.ready()) { fail("CudaError", "cannot allocate the mapped error flag"); ok = false; }
-    size_t* item = nullptr;
-    size_t* item_dev = nullptr;
-    if (ok) ok = cuda_ok(cudaHostAlloc(reinterpret_cast<void**>(&item), sizeof(size_t), cudaHostAllocMapped), "cudaHostAlloc") &&
-                 cuda_ok(cudaHostGetDevicePointer(reinterpret_cast<void**>(&item_dev), item, 0), "cudaHostGetDevicePointer");
+    size_t* item = ok ? tl_flag.item_host : nullptr;
+    size_t* item_dev = ok ? tl_flag.item_dev : nullptr;
     if (ok && length > 0) {
         *item = 0;
         *tl_flag.host = 0;
@@ -1026,7 +1030,6 @@ cb200_na_t* cb200_na_bincount(cb200_na_t* a, cb200_na_t* weight, int64_t minleng
             ok = false;
         }
     }
-    if (item) cudaFreeHost(item);
     drop_w();
     if (!ok) { cb200_na_release(out); return nullptr; }
     return out;

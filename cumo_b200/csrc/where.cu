@@ -160,31 +160,60 @@ __global__ void __launch_bounds__(kBlock)
 where_scatter_kernel(const WhereRun r, uint64_t tiles_per_cta, uint64_t n_tiles, const unsigned long long* __restrict__ cta_pos,
                      TI* out, const Emit emit) {
     __shared__ uint32_t smem[kWarpsPerBlock + 1];
-    // the hits of one sub-tile (kBlock chunks = 8192 elements), as element numbers relative to the sub-tile, in order
-    __shared__ uint16_t rel[kBlock * 32];
+    // the hits of one sub-tile (kBlock chunks = 8192 elements), as element numbers relative to the sub-tile, in order;
+    // slot j of the sub-tile's hits sits at rel[pad + j], pad = the output position of hit 0 modulo 4, so that groups of
+    // four slots are groups of four output elements that start on a 16-byte boundary
+    __shared__ __align__(8) uint16_t rel[kBlock * 32 + 4];
+    constexpr int G = 4;                                   // slots per thread and step of the copy-out
+    constexpr int VO = 16 / (int)sizeof(TI);               // output elements per 16-byte store
     const uint64_t t_begin = blockIdx.x * tiles_per_cta;
     uint64_t t_end = t_begin + tiles_per_cta; if (t_end > n_tiles) t_end = n_tiles;
     unsigned long long off = cta_pos[blockIdx.x];
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    const uint32_t below = (1u << lane) - 1u;
+    const int sh = (lane & 7) * 4;                         // this lane's four bits of a word
+    const uint32_t below = (1u << sh) - 1u;
+    const bool out_aligned = (reinterpret_cast<uintptr_t>(out) & 15u) == 0;
     for (uint64_t t = t_begin; t < t_end; ++t) {
         for (int sub = 0; sub < kWhereChunksPerThread; ++sub) {
             const uint64_t cbase = t * kWhereTileChunks + (uint64_t)sub * kBlock;      // first chunk of the sub-tile
             const uint32_t z = where_chunk(r, cbase + threadIdx.x);
             uint32_t total;
-            const uint32_t pre = block_exscan((uint32_t)__popc(z), &total, smem);
-            // Expansion into shared memory, a warp at a time over its 32 chunks: the word of lane `src` is broadcast and
-            // every lane k whose bit is set notes element (chunk, k) at the word's offset plus the set bits below k.
-            for (int src = 0; src < 32; ++src) {
-                const uint32_t w = __shfl_sync(0xffffffffu, z, src);
-                if (w == 0) continue;                            // warp-uniform
-                const uint32_t wo = __shfl_sync(0xffffffffu, pre, src);
-                if ((w >> lane) & 1u) rel[wo + __popc(w & below)] = (uint16_t)((warp * 32 + src) * 32 + lane);
+            const uint32_t pad = (uint32_t)(off & (G - 1));
+            const uint32_t pre = block_exscan((uint32_t)__popc(z), &total, smem) + pad;
+            // Expansion into shared memory, four words of the warp at a time: a lane takes four bits of one word and
+            // notes its set bits from the word's offset plus the set bits below its own.
+#pragma unroll
+            for (int it = 0; it < 8; ++it) {
+                const int wi = it * 4 + (lane >> 3);
+                const uint32_t w = __shfl_sync(0xffffffffu, z, wi);
+                uint32_t o = __shfl_sync(0xffffffffu, pre, wi) + (uint32_t)__popc(w & below);
+                const uint32_t nib = (w >> sh) & 15u;
+                const uint32_t id = (uint32_t)((warp * 32 + wi) * 32 + sh);
+                if (nib & 1u) rel[o++] = (uint16_t)id;
+                if (nib & 2u) rel[o++] = (uint16_t)(id + 1);
+                if (nib & 4u) rel[o++] = (uint16_t)(id + 2);
+                if (nib & 8u) rel[o] = (uint16_t)(id + 3);
             }
             __syncthreads();
-            // The sub-tile's positions leave as one run of consecutive stores: whole lines except at the two ends.
+            // The sub-tile's positions leave as one run of consecutive 16-byte stores: whole lines except at the two ends.
             // (Writing each word's few positions straight to global memory made L2 fetch every partly written sector.)
-            for (uint32_t o = threadIdx.x; o < total; o += kBlock) out[off + o] = (TI)emit(cbase * 32 + rel[o]);
+            const uint64_t ebase = cbase * 32;
+            TI* const o0 = out + (off - pad);               // output element of slot 0: a multiple of four elements
+            const uint32_t end = pad + total;
+            for (uint32_t g = threadIdx.x * G; g < end; g += kBlock * G) {
+                const uint2 four = *reinterpret_cast<const uint2*>(&rel[g]);
+                const uint32_t e0 = four.x & 0xffffu, e1 = four.x >> 16, e2 = four.y & 0xffffu, e3 = four.y >> 16;
+                if (g >= pad && g + G <= end && out_aligned) {
+                    TI v[G] = {(TI)emit(ebase + e0), (TI)emit(ebase + e1), (TI)emit(ebase + e2), (TI)emit(ebase + e3)};
+#pragma unroll
+                    for (int k = 0; k < G; k += VO) *reinterpret_cast<int4*>(o0 + g + k) = *reinterpret_cast<const int4*>(&v[k]);
+                } else {
+                    const uint32_t e[G] = {e0, e1, e2, e3};
+#pragma unroll
+                    for (int k = 0; k < G; ++k)
+                        if (g + k >= pad && g + k < end) o0[g + k] = (TI)emit(ebase + e[k]);
+                }
+            }
             off += total;
             // the barriers inside the next block_exscan keep `rel` from being rewritten before everyone has read it
         }

@@ -783,7 +783,15 @@ def sharded_section(torch, dist, xp, rank, world):
             ("kmeans assign 2^24x64 vs 256 /GPU (tcgen05) + counts all_reduce", lambda: kmeans.assign_sharded(comm, px, pc), lambda: kmeans.assign(px, pc), kn * kd * 4 + kn * 4)):
         ms, ms_local = timed(fn), timed(local_fn)
         out.append({"op": name, "ms": round(ms, 4), "ms_local_only": round(ms_local, 4), "efficiency": round(ms_local / ms, 3),
-                    "aggregate_GBps": round(nbytes * world / (ms * 1e-3) / 1e9, 1), "checked": True})
+                    "aggregate_GBps": round(nbytes * world / (ms * 1e-3) / 1e9, 1), "checked": True,
+                    "gather": "peer memory" if comm.peer is not None else "nccl all_gather"})
+    comm.check()                                     # no bounded wait of a peer exchange ran out
+    if comm.peer is not None:
+        # the same reductions with NCCL's all_gather in place of the peer-memory exchange, for comparison
+        comm_nccl = Comm(xp, peer_exchange=False)
+        sv2, sm2 = ShardedArray(comm_nccl, v, n * world, n * rank), ShardedArray(comm_nccl, m, 65536 * world, 65536 * rank)
+        for entry, fn in zip(out, (lambda: sv2.sum(), lambda: sv2.argmax(), lambda: sm2.sum(axis=0), lambda: sm2.max(axis=0), lambda: sm2.argmax(axis=0))):
+            entry["ms_with_nccl_all_gather"] = round(timed(fn), 4)
     return out
 
 

@@ -16,6 +16,7 @@ namespace cb200 {
 template <typename T>
 __global__ void __launch_bounds__(kBlock)
 rank_fold_sum_kernel(const char* __restrict__ partials, int64_t rank_stride, int world, int64_t n_out, double divisor, T* out) {
+    pdl_wait();            // launched as a dependent of the exchange (or of whatever precedes it): resident early, reads late
     for (int64_t o = (int64_t)blockIdx.x * kBlock + threadIdx.x; o < n_out; o += (int64_t)gridDim.x * kBlock) {
         double acc = 0.0;
         for (int r = 0; r < world; ++r) acc += (double)reinterpret_cast<const T*>(partials + r * rank_stride)[o];
@@ -30,6 +31,7 @@ rank_fold_arg_kernel(const char* __restrict__ indices, const char* __restrict__ 
                      int64_t* out_index, T* out_value) {
     using R = red::ArgMinMax<T, IS_MAX, NAN_WINS>;
     const R r{1};
+    pdl_wait();
     for (int64_t o = (int64_t)blockIdx.x * kBlock + threadIdx.x; o < n_out; o += (int64_t)gridDim.x * kBlock) {
         typename R::Acc acc = r.identity();
         for (int k = 0; k < world; ++k) {
@@ -46,7 +48,7 @@ rank_fold_arg_kernel(const char* __restrict__ indices, const char* __restrict__ 
 template <typename T>
 static void launch_rank_fold_sum(const char* partials, int64_t rank_stride, int world, int64_t n_out, double divisor, char* out) {
     if (n_out <= 0 || world <= 0) return;
-    rank_fold_sum_kernel<T><<<grid_for((n_out + kBlock - 1) / kBlock, 8), kBlock, 0, current_stream()>>>(partials, rank_stride, world, n_out, divisor, reinterpret_cast<T*>(out));
+    launch_dependent(rank_fold_sum_kernel<T>, grid_for((n_out + kBlock - 1) / kBlock, 8), kBlock, current_stream(), partials, rank_stride, world, n_out, divisor, reinterpret_cast<T*>(out));
     count_launch();
     cumo_cuda_runtime_check_kernel_launch();
 }
@@ -60,11 +62,11 @@ static void launch_rank_fold_arg(const char* indices, const char* values, int64_
     T* ov = reinterpret_cast<T*>(out_value);
     if constexpr (!red::is_fp<T>::value) nan_wins = 0;
     if (is_max) {
-        if (nan_wins) rank_fold_arg_kernel<T, true, red::is_fp<T>::value><<<grid, kBlock, 0, st>>>(indices, values, rank_stride, world, n_out, out_index, ov);
-        else          rank_fold_arg_kernel<T, true, false><<<grid, kBlock, 0, st>>>(indices, values, rank_stride, world, n_out, out_index, ov);
+        if (nan_wins) launch_dependent(rank_fold_arg_kernel<T, true, red::is_fp<T>::value>, grid, kBlock, st, indices, values, rank_stride, world, n_out, out_index, ov);
+        else          launch_dependent(rank_fold_arg_kernel<T, true, false>, grid, kBlock, st, indices, values, rank_stride, world, n_out, out_index, ov);
     } else {
-        if (nan_wins) rank_fold_arg_kernel<T, false, red::is_fp<T>::value><<<grid, kBlock, 0, st>>>(indices, values, rank_stride, world, n_out, out_index, ov);
-        else          rank_fold_arg_kernel<T, false, false><<<grid, kBlock, 0, st>>>(indices, values, rank_stride, world, n_out, out_index, ov);
+        if (nan_wins) launch_dependent(rank_fold_arg_kernel<T, false, red::is_fp<T>::value>, grid, kBlock, st, indices, values, rank_stride, world, n_out, out_index, ov);
+        else          launch_dependent(rank_fold_arg_kernel<T, false, false>, grid, kBlock, st, indices, values, rank_stride, world, n_out, out_index, ov);
     }
     count_launch();
     cumo_cuda_runtime_check_kernel_launch();

@@ -25,11 +25,19 @@ never read another GPU's memory; what crosses NVLink is a few bytes per output:
     same way; an axis-1 reduction is local, and flat (max|min)_index answers get the
     shard's element offset added.
 
+On GPUs the gather of those partials goes through peer memory when every rank could
+open every other rank's exchange buffer (`PeerExchange`: one small kernel per rank
+stores its partial into all buffers, flags, and waits with a bound; the fold kernel
+then reads local memory) and through NCCL's all_gather otherwise; CB200_PEER_EXCHANGE=0
+forces NCCL.
+
 The array backend is a namespace `xp` (the `cumo_b200` package on GPUs; the CPU
 oracle's look-alike in the gloo tests, so the partition/fold logic is tested where
 there is no GPU).
 """
 from __future__ import annotations
+
+import os
 
 import numpy as np
 
@@ -41,10 +49,84 @@ def partition(n_rows: int, world: int, rank: int) -> tuple[int, int]:
     return start, base + (1 if rank < extra else 0)
 
 
+class PeerExchange:
+    """Exchange buffers of all ranks, opened in this process (`cb200_peer_buffer_*`, `cb200_peer_exchange_kernel_launch`).
+
+    Built collectively: every rank creates its buffer, the 64-byte handles travel through `all_gather_object`, every
+    rank opens the others', and the ranks agree (an all_reduce of a flag) whether all of that worked everywhere; if
+    not, `ok` is False on every rank and the caller stays on NCCL."""
+
+    SLOT_BYTES = 256 << 10
+
+    def __init__(self, dist, group, world, rank):
+        import ctypes
+        import torch
+        from . import _lib
+        self.lib = _lib.load()
+        self.world, self.rank = world, rank
+        self.seq = 0
+        self.base = ctypes.c_void_p()
+        self.opened = []
+        self.bases = (ctypes.c_void_p * world)()
+        handle = (ctypes.c_ubyte * 64)()
+        ok = self.lib.cb200_peer_buffer_create(ctypes.c_size_t(self.SLOT_BYTES), world, ctypes.byref(self.base), handle) == 0
+        handles = [None] * world
+        dist.all_gather_object(handles, bytes(handle) if ok else None, group=group)
+        if ok and all(h is not None for h in handles):
+            for p, h in enumerate(handles):
+                if p == rank:
+                    self.bases[p] = self.base.value
+                    continue
+                ptr = ctypes.c_void_p()
+                buf = (ctypes.c_ubyte * 64).from_buffer_copy(h)
+                if self.lib.cb200_peer_buffer_open(buf, ctypes.byref(ptr)) != 0:
+                    ok = False
+                    break
+                self.opened.append(ptr)
+                self.bases[p] = ptr.value
+        else:
+            ok = False
+        agreed = torch.tensor([1 if ok else 0], dtype=torch.int32, device="cuda")
+        dist.all_reduce(agreed, op=dist.ReduceOp.MIN, group=group)
+        self.ok = bool(agreed.item())
+        self.status = torch.zeros(1, dtype=torch.int32, device="cuda")
+        self.spin_limit = 0                                # 0 = the library's default (about ten seconds)
+        dist.barrier(group=group)                          # nobody writes into a buffer that is not there yet
+
+    def gather(self, src):
+        """`src`: this rank's contiguous CUDA byte tensor (same size on every rank, <= SLOT_BYTES).  Returns (pointer,
+        byte stride) of the `world` partials in this GPU's own memory, valid for kernels queued after this call."""
+        import ctypes
+        self.seq += 1
+        rc = self.lib.cb200_peer_exchange_kernel_launch(ctypes.c_void_p(src.data_ptr()), ctypes.c_size_t(src.numel() * src.element_size()),
+                                                        self.bases, self.world, self.rank, ctypes.c_size_t(self.SLOT_BYTES),
+                                                        ctypes.c_ulonglong(self.seq), ctypes.c_uint(self.spin_limit),
+                                                        ctypes.c_void_p(self.status.data_ptr()))
+        if rc != 0:
+            raise RuntimeError(f"peer exchange launch failed with CUDA error {rc}")
+        return self.base.value + (self.seq & 1) * self.world * self.SLOT_BYTES, self.SLOT_BYTES
+
+    def check(self):
+        """Synchronises and raises if a bounded wait of an exchange ran out since the last check."""
+        if int(self.status.item()) != 0:
+            self.status.zero_()
+            raise RuntimeError("a peer exchange gave up waiting for another rank: its result is not valid")
+
+    def close(self):
+        for ptr in self.opened:
+            self.lib.cb200_peer_buffer_close(ptr)
+        self.opened = []
+        if self.base:
+            self.lib.cb200_peer_buffer_destroy(self.base)
+            self.base = None
+
+
 class Comm:
     """The two collectives this path needs, over torch.distributed (or a single process)."""
 
-    def __init__(self, xp, group=None):
+    def __init__(self, xp, group=None, peer_exchange=None):
+        """`peer_exchange`: True/False asks for / forbids the gather through peer memory; None leaves it to the
+        environment (CB200_PEER_EXCHANGE, default on).  Must be the same on every rank."""
         self.xp = xp
         self.group = group
         try:
@@ -55,6 +137,15 @@ class Comm:
         self.world = self.dist.get_world_size(group) if self.dist else 1
         self.rank = self.dist.get_rank(group) if self.dist else 0
         self.on_gpu = getattr(xp, "__name__", "") == "cumo_b200"
+        self.peer = None
+        if peer_exchange is None:
+            peer_exchange = os.environ.get("CB200_PEER_EXCHANGE", "1") != "0"
+        if self.on_gpu and self.dist and self.world > 1 and peer_exchange:
+            px = PeerExchange(self.dist, group, self.world, self.rank)
+            if px.ok:
+                self.peer = px
+            else:
+                px.close()
 
     # xp array <-> torch tensor without copying where the backend allows it
     def _to_torch(self, arr):
@@ -88,6 +179,21 @@ class Comm:
         else:
             out[0].copy_(buf)
         return out
+
+    def gather_partials(self, buf):
+        """Every rank's `buf` (a contiguous CUDA byte/element tensor, same size everywhere) side by side in local memory:
+        (device pointer, byte stride between ranks, keep-alive object).  Peer memory when set up, NCCL otherwise."""
+        nbytes = buf.numel() * buf.element_size()
+        if self.peer is not None and nbytes <= PeerExchange.SLOT_BYTES:
+            ptr, stride = self.peer.gather(buf)
+            return ptr, stride, buf
+        out = self.all_gather_bytes(buf)
+        return out.data_ptr(), nbytes, out
+
+    def check(self):
+        """Raises if an exchange through peer memory timed out since the last check (synchronises)."""
+        if self.peer is not None:
+            self.peer.check()
 
     def all_reduce_sum(self, arr):
         """Exact integer sum over ranks (Int64 / UInt64 containers)."""
@@ -166,10 +272,10 @@ class ShardedArray:
             from . import _lib
             T = type(self.local)
             src = torch.as_tensor(part if part.contiguous() else part.dup(), device="cuda")
-            gathered = comm.all_gather_bytes(src)
+            ptr, stride, _keep = comm.gather_partials(src)
             out = T(*part.shape)
             fold = getattr(_lib.load(), f"cb200_{T.__name__.lower()}_rank_fold_sum_kernel_launch")
-            fold(gathered.data_ptr(), src.numel() * src.element_size(), comm.world, src.numel(), n, out.data_ptr)
+            fold(ptr, stride, comm.world, src.numel(), n, out.data_ptr)
             return out
         wide = xp.DFloat.cast(part)                       # float32 partials are widened before they meet
         total = comm.all_gather(wide).sum(axis=0)          # rank-order fold in float64
@@ -186,7 +292,19 @@ class ShardedArray:
         if axis not in (None, 0):
             return self._like(getattr(self.local, op)(axis=axis, nan=nan))
         part = getattr(self.local, op)(axis=axis, nan=nan) if self._is_float() else getattr(self.local, op)(axis=axis)
-        gathered = self.comm.all_gather(part)
+        comm = self.comm
+        es = 4 if type(part).__name__ in ("SFloat", "Int32") else 8
+        if comm.on_gpu and comm.peer is not None and part.size * es <= PeerExchange.SLOT_BYTES:
+            # the partials meet in this GPU's exchange buffer; the fold is the library's own min/max over a strided view of it
+            import torch
+            T = type(part)
+            src = torch.as_tensor(part if part.contiguous() else part.dup(), device="cuda")
+            ptr, stride, keep = comm.gather_partials(src)
+            slots = T.from_device_pointer(ptr, (comm.world, stride // es), keep=keep)
+            gathered = slots[:, 0:part.size]
+            folded = getattr(gathered, op)(axis=0, nan=nan) if self._is_float() else getattr(gathered, op)(axis=0)
+            return folded.reshape(*part.shape) if part.ndim != 1 else folded
+        gathered = comm.all_gather(part)
         return getattr(gathered, op)(axis=0, nan=nan) if self._is_float() else getattr(gathered, op)(axis=0)
 
     def max(self, axis=None, nan=False): return self._extreme("max", axis, nan)
@@ -235,10 +353,10 @@ class ShardedArray:
         if lib.cb200_na_arg_with_value_into(name_local.encode(), loc._h, _axis_mask(axis, loc.ndim), int(bool(nan)), int(base),
                                             c_void_p(buf.data_ptr()), c_void_p(buf.data_ptr() + val_off), None, None):
             _raise_last()
-        gathered = comm.all_gather_bytes(buf)
+        ptr, stride, _keep = comm.gather_partials(buf)
         out = comm.xp.Int64(*(loc.shape[1:] if axis == 0 else ()))
         fold = getattr(lib, f"cb200_{T.__name__.lower()}_rank_fold_arg_kernel_launch")
-        fold(gathered.data_ptr(), gathered.data_ptr() + val_off, buf.numel(), comm.world, n_out, int(want_max), int(bool(nan)), out.data_ptr, None)
+        fold(ptr, ptr + val_off, stride, comm.world, n_out, int(want_max), int(bool(nan)), out.data_ptr, None)
         return out
 
     def argmax(self, axis=None, nan=False): return self._arg(True, axis, nan, False)

@@ -383,6 +383,24 @@ int cb200_kmeans_assign_sfloat(const float* x, int64_t n, int d, const float* c,
 int cb200_kmeans_assign_sfloat_tc(const float* x, int64_t n, int d, const float* c, int k, int32_t* labels,
                                   float* min_dist, unsigned long long* counts, char* errbuf, size_t errlen);
 
+/* All-gather of a few KiB per GPU through peer memory: the exchange step of a row-sharded reduction (no counterpart in the
+ * reference, which has no multi-GPU code).  One process per GPU on one box.  Each rank creates a buffer and hands its
+ * 64-byte handle to the others (any host channel); each opens the others' handles; then, per reduction, every rank calls
+ * cb200_peer_exchange_kernel_launch with the same sequence number (1, 2, 3, ... per set of buffers): a small kernel stores
+ * the rank's partial into slot [rank] of every buffer, raises a flag at every peer and waits, bounded, for every peer's
+ * flag.  Kernels queued behind it on the stream find all partials in local memory at
+ *     bases[rank] + (seq & 1) * world * slot_bytes + r * slot_bytes,   r = 0 .. world-1
+ * (the layout cb200_<T>_rank_fold_*_kernel_launch take, rank_stride = slot_bytes).  No kernel loads from peer memory.
+ * `status` (device-writable int) receives 1 when a wait ran out after `spin_limit` polls (0 = the default, about ten
+ * seconds): the gathered data is then not valid.  All return 0 or a cudaError_t value. */
+size_t cb200_peer_buffer_bytes(size_t slot_bytes, int world);
+int cb200_peer_buffer_create(size_t slot_bytes, int world, void** base_out, unsigned char* handle_out /* [64] */);
+int cb200_peer_buffer_open(const unsigned char* handle /* [64] */, void** ptr_out);
+int cb200_peer_buffer_close(void* ptr);
+int cb200_peer_buffer_destroy(void* base);
+int cb200_peer_exchange_kernel_launch(const void* src, size_t nbytes, void* const* bases, int world, int rank, size_t slot_bytes,
+                                      unsigned long long seq, unsigned spin_limit, int* status);
+
 /* Self-test of the bounded mbarrier wait the tcgen05 kernels use between their warp roles (no counterpart in the
  * reference): one CTA waits at most `spin_limit` polls on a barrier nothing arrives at.  Returns 5 when the wait gave
  * up by its limit -- the code cb200_sgemm_nt_tc / cb200_kmeans_assign_sfloat_tc return in that case -- 0 if the barrier

@@ -82,8 +82,8 @@ def test_sharded_reductions_one_rank(xp_gpu):
     check_rank(Comm(xp_gpu), xp_gpu, OracleXP)
 
 
-def _worker(rank, world, port, out_dir):
-    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+def _worker(rank, world, port, out_dir, peer):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0", CB200_PEER_EXCHANGE=peer)
     sys.path.insert(0, str(ROOT))
     sys.path.insert(0, str(ROOT / "tests"))
     import torch
@@ -96,14 +96,19 @@ def _worker(rank, world, port, out_dir):
         from cumo_b200.sharded import Comm
         from oracle_narray import OracleXP
 
-        check_rank(Comm(xp), xp, OracleXP)
+        comm = Comm(xp)
+        check_rank(comm, xp, OracleXP)
+        comm.check()                                   # no bounded wait of a peer exchange ran out
         torch.cuda.synchronize()
-        (Path(out_dir) / f"ok{rank}").write_text("ok")
+        (Path(out_dir) / f"ok{rank}").write_text("peer" if comm.peer is not None else "nccl")
     finally:
         dist.destroy_process_group()
 
 
-def test_sharded_reductions_two_nccl_ranks(tmp_path):
+@pytest.mark.parametrize("peer", ["1", "0"])
+def test_sharded_reductions_two_nccl_ranks(tmp_path, peer):
+    """Two ranks on two GPUs; the partials are gathered through peer memory (peer == "1", when the GPUs can reach each
+    other's memory) or by NCCL's all_gather."""
     import torch
 
     if torch.cuda.device_count() < 2:
@@ -113,5 +118,84 @@ def test_sharded_reductions_two_nccl_ranks(tmp_path):
     with socket.socket() as s:
         s.bind(("127.0.0.1", 0))
         port = s.getsockname()[1]
-    mp.spawn(_worker, args=(2, port, str(tmp_path)), nprocs=2, join=True)
+    mp.spawn(_worker, args=(2, port, str(tmp_path), peer), nprocs=2, join=True)
     assert (tmp_path / "ok0").exists() and (tmp_path / "ok1").exists()
+    used = {(tmp_path / f"ok{r}").read_text() for r in (0, 1)}
+    assert len(used) == 1                              # both ranks made the same choice
+    if peer == "0":
+        assert used == {"nccl"}
+
+
+def _exchange_setup(world, slot):
+    import ctypes
+
+    import torch
+    from cumo_b200 import _lib
+
+    lib = _lib.load()
+    base = ctypes.c_void_p()
+    handle = (ctypes.c_ubyte * 64)()
+    assert lib.cb200_peer_buffer_create(slot, world, ctypes.byref(base), handle) == 0
+    bases = (ctypes.c_void_p * world)(*([base.value] * world))     # every "rank" is this GPU: no second process needed
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    return lib, base, bases, status
+
+
+def test_peer_exchange_kernel_with_a_message_made_on_the_host(xp_gpu):
+    """One GPU plays rank 0 of two.  Rank 1's partial and flag are written into the buffer from the host beforehand, so
+    the kernel finds its peer's flag already raised: nothing waits for another kernel."""
+    import ctypes
+
+    import torch
+
+    world, slot, n = 2, 64 << 10, 12_000                # three CTAs' worth of bytes
+    lib, base, bases, status = _exchange_setup(world, slot)
+    try:
+        seq = 1
+        mine = torch.arange(n, dtype=torch.float32, device="cuda")
+        theirs = torch.arange(n, dtype=torch.float32, device="cuda") * -2
+        from cumo_b200.narray import UInt32
+        total = lib.cb200_peer_buffer_bytes(slot, world)
+        whole = torch.as_tensor(UInt32.from_device_pointer(base.value, (total // 4,)), device="cuda").view(torch.uint8)   # the buffer, as torch sees it
+        data_off = ((seq & 1) * world + 1) * slot                                   # slot [seq & 1][rank 1]
+        whole[data_off:data_off + n * 4] = theirs.view(torch.uint8)
+        flags = whole[2 * world * slot:].view(torch.int64).view(2, world, 16)
+        flags[seq & 1, 1, :] = seq                                                   # rank 1's flags, for every CTA
+        torch.cuda.synchronize()
+        rc = lib.cb200_peer_exchange_kernel_launch(mine.data_ptr(), n * 4, bases, world, 0, slot, seq, 1 << 12, status.data_ptr())
+        assert rc == 0
+        torch.cuda.synchronize()
+        assert int(status.item()) == 0
+        got = whole[(seq & 1) * world * slot:][:world * slot].view(torch.float32).view(world, slot // 4).cpu().numpy()
+        assert np.array_equal(got[0, :n], mine.cpu().numpy())
+        assert np.array_equal(got[1, :n], theirs.cpu().numpy())
+        # and the fold kernel reads it where the exchange left it
+        out = xp_gpu.SFloat(n)
+        lib.cb200_sfloat_rank_fold_sum_kernel_launch(base.value + (seq & 1) * world * slot, slot, world, n, 0.0, out.data_ptr)
+        assert np.array_equal(out.to_numpy(), (mine + theirs).cpu().numpy())
+    finally:
+        torch.cuda.synchronize()
+        lib.cb200_peer_buffer_destroy(base)
+
+
+def test_peer_exchange_wait_runs_out_by_its_limit(xp_gpu):
+    """A flag that nothing sets: the wait gives up after its (short) limit, the status word says so, the kernel returns
+    and the context stays usable."""
+    import torch
+
+    world, slot = 2, 4096
+    lib, base, bases, status = _exchange_setup(world, slot)
+    try:
+        mine = torch.ones(256, dtype=torch.float32, device="cuda")
+        rc = lib.cb200_peer_exchange_kernel_launch(mine.data_ptr(), 1024, bases, world, 0, slot, 1, 2000, status.data_ptr())
+        assert rc == 0
+        torch.cuda.synchronize()
+        assert int(status.item()) == 1
+        assert float((xp_gpu.SFloat.from_torch(mine) + 1).sum().extract()) == 512.0
+        # refused arguments launch nothing
+        assert lib.cb200_peer_exchange_kernel_launch(mine.data_ptr(), slot + 16, bases, world, 0, slot, 2, 0, status.data_ptr()) != 0
+        assert lib.cb200_peer_exchange_kernel_launch(mine.data_ptr(), 1024, bases, world, 2, slot, 2, 0, status.data_ptr()) != 0
+        assert lib.cb200_peer_exchange_kernel_launch(mine.data_ptr(), 1024, bases, world, 0, slot, 0, 0, status.data_ptr()) != 0
+    finally:
+        torch.cuda.synchronize()
+        lib.cb200_peer_buffer_destroy(base)

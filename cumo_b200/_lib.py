@@ -99,6 +99,10 @@ def _declare(lib: ctypes.CDLL) -> None:
         "cb200_tile_pipeline_launches": (ctypes.c_ulonglong, []),
         "cb200_sfloat_rank_fold_sum_kernel_launch": (None, [c_void_p, c_int64, c_int, c_int64, c_double, c_void_p]),
         "cb200_dfloat_rank_fold_sum_kernel_launch": (None, [c_void_p, c_int64, c_int, c_int64, c_double, c_void_p]),
+        "cb200_sfloat_rank_fold_extreme_kernel_launch": (None, [c_void_p, c_int64, c_int, c_int64, c_int, c_int, c_void_p]),
+        "cb200_dfloat_rank_fold_extreme_kernel_launch": (None, [c_void_p, c_int64, c_int, c_int64, c_int, c_int, c_void_p]),
+        "cb200_int32_rank_fold_extreme_kernel_launch": (None, [c_void_p, c_int64, c_int, c_int64, c_int, c_int, c_void_p]),
+        "cb200_int64_rank_fold_extreme_kernel_launch": (None, [c_void_p, c_int64, c_int, c_int64, c_int, c_int, c_void_p]),
         "cb200_sfloat_rank_fold_arg_kernel_launch": (None, [c_void_p, c_void_p, c_int64, c_int, c_int64, c_int, c_int, c_void_p, c_void_p]),
         "cb200_dfloat_rank_fold_arg_kernel_launch": (None, [c_void_p, c_void_p, c_int64, c_int, c_int64, c_int, c_int, c_void_p, c_void_p]),
         "cb200_int32_rank_fold_arg_kernel_launch": (None, [c_void_p, c_void_p, c_int64, c_int, c_int64, c_int, c_int, c_void_p, c_void_p]),

@@ -57,3 +57,16 @@ extern "C" int cb200_selftest_bounded_wait(unsigned spin_limit, char* errbuf, si
     if (host[0] == 5) snprintf(errbuf, errlen, "the wait ran out after %u polls and returned (abort flag %d)", spin_limit, host[1]);
     return host[0];
 }
+
+// The multiplier and shifts that `a / s` and `a % s` use for a host scalar (divmod_scalar.cuh), for callers and tests
+// that want to check them without a GPU: |divisor| -> (multiplier, first shift, second shift), 32- and 64-bit.
+#include "divmod_scalar.cuh"
+
+extern "C" void cb200_invariant_divisor_u32(uint32_t d, uint32_t* m, int* sh1, int* sh2) {
+    const cb200::InvariantDivisor<uint32_t> k = cb200::make_invariant_divisor<uint32_t>(d, false);
+    *m = k.m; *sh1 = k.sh1; *sh2 = k.sh2;
+}
+extern "C" void cb200_invariant_divisor_u64(uint64_t d, uint64_t* m, int* sh1, int* sh2) {
+    const cb200::InvariantDivisor<uint64_t> k = cb200::make_invariant_divisor<uint64_t>(d, false);
+    *m = k.m; *sh1 = k.sh1; *sh2 = k.sh2;
+}

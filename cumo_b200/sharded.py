@@ -293,17 +293,17 @@ class ShardedArray:
             return self._like(getattr(self.local, op)(axis=axis, nan=nan))
         part = getattr(self.local, op)(axis=axis, nan=nan) if self._is_float() else getattr(self.local, op)(axis=axis)
         comm = self.comm
-        es = 4 if type(part).__name__ in ("SFloat", "Int32") else 8
-        if comm.on_gpu and comm.peer is not None and part.size * es <= PeerExchange.SLOT_BYTES:
-            # the partials meet in this GPU's exchange buffer; the fold is the library's own min/max over a strided view of it
+        if comm.on_gpu:
+            # the partials meet side by side in local memory (peer exchange or NCCL); one rank-fold kernel merges them
             import torch
+            from . import _lib
             T = type(part)
             src = torch.as_tensor(part if part.contiguous() else part.dup(), device="cuda")
-            ptr, stride, keep = comm.gather_partials(src)
-            slots = T.from_device_pointer(ptr, (comm.world, stride // es), keep=keep)
-            gathered = slots[:, 0:part.size]
-            folded = getattr(gathered, op)(axis=0, nan=nan) if self._is_float() else getattr(gathered, op)(axis=0)
-            return folded.reshape(*part.shape) if part.ndim != 1 else folded
+            ptr, stride, _keep = comm.gather_partials(src)
+            out = T(*part.shape)
+            fold = getattr(_lib.load(), f"cb200_{T.__name__.lower()}_rank_fold_extreme_kernel_launch")
+            fold(ptr, stride, comm.world, src.numel(), int(op == "max"), int(bool(nan) and self._is_float()), out.data_ptr)
+            return out
         gathered = comm.all_gather(part)
         return getattr(gathered, op)(axis=0, nan=nan) if self._is_float() else getattr(gathered, op)(axis=0)
 

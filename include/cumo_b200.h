@@ -323,6 +323,8 @@ int cb200_sgemm_nt_tc(int64_t M, int64_t N, int64_t K, const float* A, int64_t l
  * output), n_out values per rank.
  *   sum: partials of the element type are added in float64 in rank order, divided by `divisor` unless it is 0
  *        (mean), rounded once to the element type;
+ *   extreme: min (is_max == 0) or max of the per-rank answers with the single-GPU rules (nan_wins == 0: a NaN loses unless
+ *        all are NaN; else a NaN wins);
  *   arg: {values[r][o], indices[r][o]} pairs are merged with the single-GPU kernels' own total order (NaN rule,
  *        better value, lower index), out_value may be NULL.  Indices are int64_t. */
 void cb200_sfloat_rank_fold_sum_kernel_launch(const char* partials, int64_t rank_stride, int world, int64_t n_out, double divisor, char* out);
@@ -331,6 +333,10 @@ void cb200_dfloat_rank_fold_sum_kernel_launch(const char* partials, int64_t rank
     void cb200_##T##_rank_fold_arg_kernel_launch(const char* indices, const char* values, int64_t rank_stride, int world, int64_t n_out, \
                                                  int is_max, int nan_wins, int64_t* out_index, char* out_value);
 CB200_DECL_FOLD_ARG(sfloat) CB200_DECL_FOLD_ARG(dfloat) CB200_DECL_FOLD_ARG(int32) CB200_DECL_FOLD_ARG(int64)
+#define CB200_DECL_FOLD_EXTREME(T) \
+    void cb200_##T##_rank_fold_extreme_kernel_launch(const char* partials, int64_t rank_stride, int world, int64_t n_out, int is_max, \
+                                                     int nan_wins, char* out);
+CB200_DECL_FOLD_EXTREME(sfloat) CB200_DECL_FOLD_EXTREME(dfloat) CB200_DECL_FOLD_EXTREME(int32) CB200_DECL_FOLD_EXTREME(int64)
 
 /* General matrix product with the argument list of cublas<T>gemmStridedBatched minus the handle (column-major:
  * C (m x n, ldc) = alpha * op(A) * op(B) + beta * C for `batch` entries `stride*` elements apart; transa/transb 0 = N,
@@ -382,6 +388,13 @@ int cb200_kmeans_assign_sfloat(const float* x, int64_t n, int d, const float* c,
  * a bounded wait inside the kernel ran out and the outputs are not valid. */
 int cb200_kmeans_assign_sfloat_tc(const float* x, int64_t n, int d, const float* c, int k, int32_t* labels,
                                   float* min_dist, unsigned long long* counts, char* errbuf, size_t errlen);
+
+/* Integer `a / s` and `a % s` with a host scalar on the right multiply by a reciprocal that the host derives from the
+ * scalar (cumo_iter_<T>_{div,mod}_s_kernel_launch choose that kernel themselves for flat arrays).  These two return the
+ * derivation for a magnitude d >= 1 (host code, no GPU): q = (t + ((n - t) >> sh1)) >> sh2 with t = high word of m * n
+ * equals n / d for every n up to 2^31 (u32) / 2^63 (u64). */
+void cb200_invariant_divisor_u32(uint32_t d, uint32_t* m, int* sh1, int* sh2);
+void cb200_invariant_divisor_u64(uint64_t d, uint64_t* m, int* sh1, int* sh2);
 
 /* All-gather of a few KiB per GPU through peer memory: the exchange step of a row-sharded reduction (no counterpart in the
  * reference, which has no multi-GPU code).  One process per GPU on one box.  Each rank creates a buffer and hands its

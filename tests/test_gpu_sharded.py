@@ -35,6 +35,8 @@ def check_rank(comm, xp, ox):
     assert sn.argmax(nan=True).extract() == cut + 3
     assert sn.argmax().extract() == 17
     assert np.isnan(sn.sum().extract())
+    assert sn.max().extract() == 2.0 and sn.min().extract() == -1.0          # plain form: a NaN loses
+    assert np.isnan(sn.max(nan=True).extract()) and np.isnan(sn.min(nan=True).extract())
 
     mat = rng.integers(-1000, 1000, size=(4099, 257)).astype(np.int32)
     mat[[3, 3000], 5] = 5000

@@ -215,6 +215,34 @@ class NArray:
         fn(byref(dst), byref(src), byref(ix))
         _check_launch()
 
+    def store(self, other):
+        """`self.store(other)` of the reference (gen/tmpl/store.c, store_from.c): every element of `self` -- an array or
+        any view of one -- takes the matching element of `other`, which is converted to this type and repeated along
+        the dimensions where its extent is 1 or that it lacks (ndloop.c:494-516).  Returns self."""
+        if not isinstance(other, NArray):
+            other = type(self).cast(other if isinstance(other, (list, tuple, np.ndarray)) else [other])
+        shp = self.shape
+        oshp, ostp = other.shape, other.steps
+        if other.size == 1:
+            oshp, ostp = (), ()                              # a single element is repeated everywhere
+        if len(oshp) > len(shp):
+            raise ShapeError(f"cannot store an array of shape {oshp} into one of shape {shp}")
+        steps = []
+        for d in range(len(shp)):
+            od = d - (len(shp) - len(oshp))
+            if od < 0 or oshp[od] == 1:
+                steps.append(0)
+            elif oshp[od] == shp[d]:
+                steps.append(ostp[od])
+            else:
+                raise ShapeError(f"cannot store an array of shape {oshp} into one of shape {shp}")
+        self._store(other._view(list(shp), steps, 0))
+        return self
+
+    def __setitem__(self, key, value):
+        """`a[key] = value`: a store into the view that `a[key]` names (integers, slices, `True`, None, Ellipsis)."""
+        self[key].store(value)
+
     # ---- facts --------------------------------------------------------------------------------
     @property
     def _tname(self):

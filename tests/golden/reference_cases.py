@@ -951,4 +951,316 @@ def case_kahan_sum(xp):
             assert scalar(diff) <= 1e-3, (i, ax)
 
 
+# ---- test/narray_test.rb:3070-3098 "mulsum over long axes, views and broadcasts" (values are small integers held in
+# floats, so every sum is exact whatever the order) ---------------------------------------------------------------
+def case_mulsum_long_axes_views_broadcasts(xp):
+    rows, cols = 5, 40_000
+    n = rows * cols
+    xs = [float((i % 13) - 6) for i in range(n)]
+    ys = [float((i % 7) - 3) for i in range(n)]
+    a, b = xp.DFloat.cast(xs), xp.DFloat.cast(ys)
+    assert scalar(a.mulsum(b)) == sum(x * y for x, y in zip(xs, ys))
+    assert scalar(a[0:n:3].mulsum(b[0:n:3])) == sum(xs[i] * ys[i] for i in range(0, n, 3))
+    assert scalar(a[::-1].mulsum(b)) == sum(xs[n - 1 - i] * ys[i] for i in range(n))
+    g, h = a.reshape(rows, cols), b.reshape(rows, cols)
+    assert g.mulsum(h, axis=1).to_a() == [sum(xs[r * cols + c] * ys[r * cols + c] for c in range(cols)) for r in range(rows)]
+    v = [float((i % 5) - 2) for i in range(cols)]
+    assert g.mulsum(xp.DFloat.cast(v), axis=1).to_a() == [sum(xs[r * cols + c] * v[c] for c in range(cols)) for r in range(rows)]
+
+
+# ---- test/narray_test.rb:3111-3131 "mulsum accumulates over reduce axes that cannot be flattened" -------------------
+def case_mulsum_over_axes_that_cannot_be_flattened(xp):
+    shape = [2, 3, 4, 5]
+    n = math.prod(shape)
+    xs = [float((i % 13) - 6) for i in range(n)]
+    ys = [float((i % 7) - 3) for i in range(n)]
+    a, b = _nd(xp.DFloat, xs, shape), _nd(xp.DFloat, ys, shape)
+    for axes in ([0, 2], [1, 3], [0, 2, 3]):
+        kept = [d for d in range(len(shape)) if d not in axes]
+        exp = {}
+        for i in range(n):
+            idx, rest = [], i
+            for d in reversed(shape):
+                idx.insert(0, rest % d)
+                rest //= d
+            key = tuple(idx[d] for d in kept)
+            exp[key] = exp.get(key, 0.0) + xs[i] * ys[i]
+        assert _flat(a.mulsum(b, axis=axes).to_a()) == [exp[k] for k in sorted(exp)], axes
+
+
+# ---- test/narray_test.rb:3133-3150 "mulsum with nan: true drops the pair rather than spreading it" ------------------
+def case_mulsum_nan_drops_the_pair(xp):
+    n = 20_000
+    xs = [float((i % 13) - 6) for i in range(n)]
+    ys = [float((i % 7) - 3) for i in range(n)]
+    for at in (0, n // 2, n - 1):
+        for which in ("x", "y"):
+            a, b = list(xs), list(ys)
+            (a if which == "x" else b)[at] = NAN
+            ca, cb = xp.DFloat.cast(a), xp.DFloat.cast(b)
+            assert math.isnan(scalar(ca.mulsum(cb))), (which, at)
+            assert scalar(ca.mulsum(cb, nan=True)) == sum(a[i] * b[i] for i in range(n) if i != at), (which, at)
+
+
+# ---- test/narray_test.rb:3152-3188 "store into and out of views that ndloop cannot flatten" -------------------------
+def case_store_into_and_out_of_views(xp):
+    rows, cols = 40, 12
+    xs = [(i % 11) + 1.0 for i in range(rows * cols)]
+    src = _nd(xp.DFloat, xs, [rows, cols])
+    grid = [xs[r * cols:(r + 1) * cols] for r in range(rows)]
+    assert xp.DFloat.zeros(rows, cols - 3).store(src[True, 2:cols - 1]).to_a() == [row[2:cols - 1] for row in grid]
+    assert xp.DFloat.zeros(cols, rows).store(src.transpose()).to_a() == [list(col) for col in zip(*grid)]
+    idx = [((i * 7) + 3) % rows for i in range(rows)]
+    assert xp.DFloat.zeros(rows, cols).store(src[idx, True]).to_a() == [grid[i] for i in idx]
+    # a store into a slice must leave the columns on either side alone
+    dst = xp.DFloat.zeros(rows, cols)
+    dst[True, 2:cols - 1] = src[True, 0:cols - 3]
+    assert dst.to_a() == [[0.0, 0.0] + row[0:cols - 3] + [0.0] for row in grid]
+    # a 5-d shape runs past the dimension-specialised kernels
+    deep = [2, 2, 3, 2, 5]
+    ys = [(i % 7) + 1.0 for i in range(math.prod(deep))]
+    a = _nd(xp.DFloat, ys, deep)
+    assert _flat(xp.DFloat.zeros(*deep).store(a).to_a()) == ys
+    assert _flat(xp.DFloat.zeros(*reversed(deep)).store(a.transpose()).to_a()) == _flat(a.transpose().to_a())
+    # broadcast and dtype conversion still reach every element
+    assert xp.DFloat.zeros(4, 3).store(xp.Int32[1, 2, 3]).to_a() == [[1.0, 2.0, 3.0]] * 4
+    assert xp.Int32.zeros(rows, cols).store(src).to_a() == [[int(x) for x in row] for row in grid]
+
+
+# ---- test/narray_test.rb:3190-3233 "unary operations on views that ndloop cannot flatten", "the unary error flags still
+# fire from the indexer kernel" --------------------------------------------------------------------------------------
+def case_unary_operations_on_views(xp):
+    rows, cols = 40, 12
+    xs = [float((i % 9) - 4) for i in range(rows * cols)]
+    a = _nd(xp.DFloat, xs, [rows, cols])
+    grid = [xs[r * cols:(r + 1) * cols] for r in range(rows)]
+    idx = [((i * 7) + 3) % rows for i in range(rows)]
+    views = [
+        ("flat", a, grid),
+        ("colslice", a[True, 2:cols - 1], [row[2:cols - 1] for row in grid]),
+        ("transpose", a.transpose(), [list(col) for col in zip(*grid)]),
+        ("idxview", a[idx, True], [grid[i] for i in idx]),
+    ]
+    for label, v, want in views:
+        assert (-v).to_a() == [[-x for x in row] for row in want], f"minus {label}"
+        assert v.square().to_a() == [[x * x for x in row] for row in want], f"square {label}"
+        assert v.abs().to_a() == [[abs(x) for x in row] for row in want], f"abs {label}"
+        got = xp.NMath.exp(v).to_a()
+        for r, row in enumerate(want):
+            for c, x in enumerate(row):
+                assert abs(math.exp(x) - got[r][c]) <= 1e-6 * max(1.0, math.exp(x)), f"exp {label} {r},{c}"
+    deep = [2, 2, 3, 2, 5]
+    ys = [float((i % 7) - 3) for i in range(math.prod(deep))]
+    b = _nd(xp.DFloat, ys, deep)
+    assert _flat((-b).to_a()) == [-y for y in ys]
+    assert _flat(b.transpose().abs().to_a()) == [abs(y) for y in _flat(b.transpose().to_a())]
+    # the flags are read after the launch
+    for bad, err in ((lambda: xp.Int32.cast([[1, 0], [2, 3]])[True, 0:2].reciprocal().to_a(), ZeroDivisionError),
+                     (lambda: xp.Int32.cast([[-2_147_483_648, 1], [2, 3]])[True, 0:2].abs().to_a(), ValueError)):
+        try:
+            bad()
+            raise AssertionError(f"{err.__name__} expected")
+        except err:
+            pass
+    assert xp.Int32.cast([[1, 2], [3, 4]]).reciprocal().to_a() == [[1, 0], [0, 0]]
+
+
+# ---- test/narray_test.rb:3293-3328 "copy of a view built from an index array" ---------------------------------------
+def case_copy_of_a_view_built_from_an_index_array(xp):
+    rows, cols = 50, 9
+    xs = [((i * 11) % 23) - 11.0 for i in range(rows * cols)]
+    a = _nd(xp.DFloat, xs, [rows, cols])
+    grid = [xs[r * cols:(r + 1) * cols] for r in range(rows)]
+    idx = [((i * 7) + 3) % rows for i in range(rows)]
+    assert a[idx, True].dup().to_a() == [grid[i] for i in idx]
+    assert a[idx, 2:cols - 1].dup().to_a() == [grid[i][2:cols - 1] for i in idx]
+    assert a.dup().to_a() == grid
+    assert a.transpose().dup().to_a() == [list(col) for col in zip(*grid)]
+    # a reduction over such a view copies it first, so it must agree
+    assert a[idx, True].sum(axis=1).to_a() == [sum(grid[i]) for i in idx]
+    assert a[idx, True].sum(axis=0).to_a() == [sum(grid[i][c] for i in idx) for c in range(cols)]
+    # the copy must not alias the source
+    mutable = _nd(xp.DFloat, xs, [rows, cols])
+    taken = mutable[idx, True].dup()
+    mutable[idx[0], 0] = 999.0
+    assert scalar(taken[0, 0]) == grid[idx[0]][0]
+    assert scalar(mutable[idx[0], 0]) == 999.0
+    deep = [2, 2, 3, 2, 5]
+    ys = [((i * 13) % 29) - 14.0 for i in range(math.prod(deep))]
+    b = _nd(xp.DFloat, ys, deep)
+    assert _flat(b.dup().to_a()) == ys
+    assert _flat(b.transpose().dup().to_a()) == _flat(b.transpose().to_a())
+    assert _flat(b[[1, 0], True, True, True, True].dup().to_a()) == ys[len(ys) // 2:] + ys[:len(ys) // 2]
+
+
+# ---- test/narray_test.rb:3330-3407 "elementwise kernels reach every element of a view they cannot flatten" (the
+# operations of this path: pow, pow by an integer, maximum, minimum, fill, seq; each view against a contiguous copy) ----
+def case_elementwise_kernels_reach_every_element_of_a_view(xp):
+    rows, cols = 9, 7
+    xs = [((i * 3) % 13) + 1.0 for i in range(rows * cols)]
+    src = _nd(xp.DFloat, xs, [rows, cols])
+    idx = [5, 0, 3, 8, 1]
+    views = {
+        "column slice": lambda a: a[True, 1:cols - 1],
+        "reversed": lambda a: a[True, ::-1],
+        "row stride": lambda a: a[0:rows:2, True],
+        "index view": lambda a: a[idx, True],
+        "transpose": lambda a: a.transpose(),
+    }
+    ops = {
+        "pow": lambda a: a ** 2.0,
+        "pow_int32": lambda a: a ** 3,
+        "maximum": lambda a: xp.DFloat.maximum(a, xp.DFloat[6.0]),
+        "minimum": lambda a: xp.DFloat.minimum(a, xp.DFloat[6.0]),
+    }
+    for what, take in views.items():
+        view = take(src)
+        flat = view.dup()
+        assert flat.to_a() == view.to_a(), f"{what} itself"
+        for op, f in ops.items():
+            assert f(view).to_a() == f(flat).to_a(), f"{op} of {what}"
+    assert (src ** 2.0).to_a() == [[x * x for x in xs[r * cols:(r + 1) * cols]] for r in range(rows)]
+    assert (src ** 3).to_a() == [[x * x * x for x in xs[r * cols:(r + 1) * cols]] for r in range(rows)]
+    # fill and seq write through the view: the elements outside it stay, the ones inside are all reached
+    for what, take in views.items():
+        if what == "index view":
+            continue                                   # an index view is a copy on this path, not a window to write through
+        cells = [int(v) for v in _flat(take(_nd(xp.DFloat, list(range(rows * cols)), [rows, cols])).to_a())]
+        dst = xp.DFloat.zeros(rows, cols)
+        take(dst).fill(5.0)
+        assert _flat(dst.to_a()) == [5.0 if i in cells else 0.0 for i in range(rows * cols)], f"fill {what}"
+        dst = xp.DFloat.zeros(rows, cols)
+        take(dst).seq(2.0, 0.5)
+        seen = {cell: 2.0 + 0.5 * i for i, cell in enumerate(cells)}
+        assert _flat(dst.to_a()) == [seen.get(i, 0.0) for i in range(rows * cols)], f"seq {what}"
+    deep = [2, 2, 3, 2, 5]
+    n = math.prod(deep)
+    ys = [(i % 7) + 1.0 for i in range(n)]
+    a = _nd(xp.DFloat, ys, deep)
+    assert _flat((a ** 2.0).to_a()) == [y * y for y in ys]
+    d = xp.DFloat.zeros(*deep)
+    d.transpose().seq(1.0)
+    assert _flat(d.transpose().to_a()) == [1.0 + i for i in range(n)]
+
+
+# ---- test/narray_test.rb:2426-2447 "cond_unary over long arrays and views", 2449-2457 "signbit over a view" -----------
+def case_classifications_over_long_arrays_and_views(xp):
+    n = 200
+    specials = {0: NAN, 1: INF, 2: -INF}
+    values = [specials.get(i % 7, i - 100.0) for i in range(n)]
+    a = xp.DFloat.cast(values)
+    stepped = list(range(0, n, 3))
+    picked = [5, 0, 199, 64, 63, 32, 31, 100]
+    # a strided 2-d view: each row of the result starts at a bit offset that is not a multiple of the word width
+    cols = list(range(0, 25, 2))
+    grid = [r * 25 + c for r in range(8) for c in cols]
+    expect = {
+        "isnan": math.isnan,
+        "isinf": math.isinf,
+        "isposinf": lambda v: v == INF,
+        "isneginf": lambda v: v == -INF,
+        "isfinite": math.isfinite,
+    }
+    for meth, f in expect.items():
+        bits = lambda idxs: [1 if f(values[i]) else 0 for i in idxs]
+        assert getattr(a, meth)().to_a() == bits(range(n)), meth
+        assert getattr(a[0:n:3], meth)().to_a() == bits(stepped), meth
+        assert getattr(a[picked], meth)().to_a() == bits(picked), meth
+        got = getattr(a.reshape(8, 25)[True, 0:25:2], meth)().to_a()
+        flat = bits(grid)
+        assert got == [flat[r * len(cols):(r + 1) * len(cols)] for r in range(8)], meth
+    values = [1.0, -2.0, 0.0, -0.0, 3.5, -0.25] * 20
+    a = xp.SFloat.cast(values)
+    expected = [1 if math.copysign(1.0, x) < 0 else 0 for x in values]
+    assert a.signbit().to_a() == expected
+    assert a[0:len(values):2].signbit().to_a() == expected[0::2]
+
+
+# ---- test/narray_test.rb:4641-4686 "NMath binary functions on views that ndloop cannot flatten" ---------------------
+def case_nmath_binary_functions_on_views(xp):
+    rows, cols = 40, 12
+    xs = [float((i % 9) - 4) for i in range(rows * cols)]
+    a = _nd(xp.DFloat, xs, [rows, cols])
+    grid = [xs[r * cols:(r + 1) * cols] for r in range(rows)]
+    idx = [((i * 7) + 3) % rows for i in range(rows)]
+    views = [
+        ("flat", a, grid),
+        ("colslice", a[True, 2:cols - 1], [row[2:cols - 1] for row in grid]),
+        ("transpose", a.transpose(), [list(col) for col in zip(*grid)]),
+        ("idxview", a[idx, True], [grid[i] for i in idx]),
+    ]
+    fm = xp.NMath
+    for label, v, want in views:
+        spread = xp.DFloat(*v.shape).fill(1.5)
+        # the scalar operand reads the same elements the array one does
+        assert fm.atan2(v, spread).to_a() == fm.atan2(v, 1.5).to_a(), f"atan2 {label}, numeric right"
+        assert fm.atan2(spread, v).to_a() == fm.atan2(1.5, v).to_a(), f"atan2 {label}, numeric left"
+        assert fm.hypot(spread, v).to_a() == fm.hypot(1.5, v).to_a(), f"hypot {label}, numeric left"
+        got, back, hyp = fm.atan2(v, 1.5).to_a(), fm.atan2(1.5, v).to_a(), fm.hypot(v, 1.5).to_a()
+        for r, row in enumerate(want):
+            for c, x in enumerate(row):
+                assert abs(math.atan2(x, 1.5) - got[r][c]) <= 1e-12, f"atan2 {label} {r},{c}"
+                assert abs(math.atan2(1.5, x) - back[r][c]) <= 1e-12, f"atan2 reversed {label} {r},{c}"
+                assert abs(math.hypot(x, 1.5) - hyp[r][c]) <= 1e-12, f"hypot {label} {r},{c}"
+    # a 9-d shape runs past the dimension-specialised kernels
+    ys = [float((i % 7) - 3) for i in range(512)]
+    b = _nd(xp.DFloat, ys, [2] * 9)
+    got = _flat(fm.atan2(b, 1.5).to_a())
+    for i, x in enumerate(ys):
+        assert abs(math.atan2(x, 1.5) - got[i]) <= 1e-12, f"atan2 9-d {i}"
+    assert _flat(fm.atan2(b, xp.DFloat(*([2] * 9)).fill(1.5)).to_a()) == got
+
+
+# ---- test/narray_test.rb:3500-3604 "Bit results reach every element of a view they cannot flatten" (the comparison and
+# classification results of this path; the expectation is spelled out in Python as well as taken from a copy) ---------
+def case_bit_results_reach_every_element_of_a_view(xp):
+    rows, cols = 9, 7
+    xs = [((i * 3) % 13) - 6.0 for i in range(rows * cols)]
+    rot = xs[5:] + xs[:5]
+    src, other = _nd(xp.DFloat, xs, [rows, cols]), _nd(xp.DFloat, rot, [rows, cols])
+    idx = [5, 0, 3, 8, 1]
+    views = {
+        "column slice": lambda a: a[True, 1:cols - 1],
+        "reversed": lambda a: a[True, ::-1],
+        "row stride": lambda a: a[0:rows:2, True],
+        "index view": lambda a: a[idx, True],
+        "transpose": lambda a: a.transpose(),
+    }
+    py = {"gt": lambda u, v: u > v, "ge": lambda u, v: u >= v, "lt": lambda u, v: u < v, "le": lambda u, v: u <= v,
+          "eq": lambda u, v: u == v, "ne": lambda u, v: u != v}
+    for what, take in views.items():
+        a, b = take(src), take(other)
+        fa, fb = a.dup(), b.dup()
+        wa, wb = _flat(a.to_a()), _flat(b.to_a())
+        for op, f in py.items():
+            got = getattr(a, op)(b)
+            assert got.to_a() == getattr(fa, op)(fb).to_a(), f"{op} of {what}"
+            assert _flat(got.to_a()) == [1 if f(u, v) else 0 for u, v in zip(wa, wb)], f"{op} of {what}"
+            assert scalar(got.count_true()) == sum(1 for u, v in zip(wa, wb) if f(u, v)), f"count_true of {op} of {what}"
+        for op in ("isnan", "isinf", "isfinite", "signbit"):
+            assert getattr(a, op)().to_a() == getattr(fa, op)().to_a(), f"{op} of {what}"
+    # one dimension
+    n = 40
+    ys = [((i * 5) % 17) - 8.0 for i in range(n)]
+    flat, flat2 = xp.DFloat.cast(ys), xp.DFloat.cast(ys[3:] + ys[:3])
+    one_d = {
+        "step 3": lambda a: a[0:n:3],
+        "reversed": lambda a: a[::-1],
+        "reversed by 2": lambda a: a[::-2],
+        "fancy": lambda a: a[[7, 2, 39, 0, 15, 15]],
+        "tail": lambda a: a[3:-3],
+    }
+    for what, take in one_d.items():
+        a, b = take(flat), take(flat2)
+        assert a.gt(b).to_a() == a.dup().gt(b.dup()).to_a(), f"1-d gt of {what}"
+        assert a.gt(b).to_a() == [1 if u > v else 0 for u, v in zip(a.to_a(), b.to_a())], f"1-d gt of {what}"
+        assert a.signbit().to_a() == [1 if math.copysign(1.0, u) < 0 else 0 for u in a.to_a()], f"1-d signbit of {what}"
+    # a 5-d shape runs past the dimension-specialised kernels
+    deep = [2, 2, 3, 2, 5]
+    zs = [((i * 7) % 11) - 5.0 for i in range(math.prod(deep))]
+    a = _nd(xp.DFloat, zs, deep)
+    assert _flat(a.gt(0).to_a()) == [1 if x > 0 else 0 for x in zs]
+    assert _flat(a.transpose().gt(0).to_a()) == _flat(a.transpose().dup().gt(0).to_a())
+
+
 ALL_CASES = [v for k, v in sorted(globals().items()) if k.startswith("case_")]

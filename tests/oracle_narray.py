@@ -90,6 +90,21 @@ class ONArray:
         key = tuple(slice(None) if k is True else k for k in key)
         return self._wrap(self.a[key])
 
+    def store(self, other):
+        """self[...] = other, converted to this type and repeated along missing or unit dimensions (a copy loop, no arithmetic)."""
+        src = other.a if isinstance(other, ONArray) else np.array(other if isinstance(other, (list, tuple, np.ndarray)) else [other])
+        if src.size == 1:
+            src = src.reshape(())
+        self.a[...] = np.broadcast_to(src.astype(self.np_dtype), self.a.shape)
+        return self
+
+    def __setitem__(self, key, value):
+        if not isinstance(key, tuple):
+            key = (key,)
+        key = tuple(slice(None) if k is True else k for k in key)
+        src = value.a if isinstance(value, ONArray) else np.array(value)
+        self.a[key] = src.reshape(()) if src.size == 1 else src          # numpy repeats it; the assignment converts
+
     def transpose(self, *perm):
         return self._wrap(self.a.transpose(*perm) if perm else self.a.T)
 

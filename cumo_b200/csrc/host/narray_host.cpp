@@ -557,6 +557,29 @@ cb200_na_t* cb200_na_binary(const char* op_c, cb200_na_t* a, cb200_na_t* b) {
     std::string op = op_c;
     if (!is_value_type(a->dtype) || !is_value_type(b->dtype)) return (cb200_na*)fail("TypeError", "%s is not defined for %s and %s", op_c, kTypeName[a->dtype], kTypeName[b->dtype]);
     int dtype = upcast(a->dtype, b->dtype);
+    // an Int32 array as the exponent does not widen the base: the power is taken by repeated multiplication
+    // (gen/tmpl/pow.c:178-182: `other` is an Int32 -> the pow_int32 iterator)
+    if (op == "pow" && b->dtype == CB200_INT32 && dtype == a->dtype) {
+        Loop lp;
+        if (!broadcast(a, b, &lp)) return nullptr;
+        cb200_na* out = output_for(a, dtype, lp);
+        if (!out) return nullptr;
+        using Fn = void (*)(cumo_na_iarray_t*, cumo_na_iarray_t*, cumo_na_iarray_t*, cumo_na_indexer_t*);
+        Fn f = (Fn)sym(std::string("cumo_iter_") + kTypeName[dtype] + "_pow_int32_kernel_launch");
+        bool ok = f != nullptr;
+        if (ok) {
+            cumo_na_indexer_t ix;
+            cumo_na_iarray_t a1, a2, a3;
+            fill_indexer(&ix, lp);
+            fill_iarray(&a1, a, lp);
+            fill_iarray(&a2, b, lp);
+            fill_iarray(&a3, out, lp);
+            f(&a1, &a2, &a3, &ix);
+            ok = launch_ok();
+        }
+        if (!ok) { cb200_na_release(out); return nullptr; }
+        return out;
+    }
     Family fam = binary_family(op, is_float_type(dtype));
     if (fam == F_NONE) return (cb200_na*)fail("NoMethodError", "undefined method %s for %s", op_c, kTypeName[dtype]);
     Loop lp;

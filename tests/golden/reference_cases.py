@@ -1263,4 +1263,121 @@ def case_bit_results_reach_every_element_of_a_view(xp):
     assert _flat(a.transpose().gt(0).to_a()) == _flat(a.transpose().dup().gt(0).to_a())
 
 
+# ---- test/narray_test.rb:2100-2181 bincount: "every element of a view is counted", "an array large enough that the
+# filling kernel is still running" (expectations tallied in Python, not taken from a contiguous copy) --------------------
+def _bincount_expect(nested, length, weights=None):
+    if nested and isinstance(nested[0], list):
+        return [_bincount_expect(row, length, None if weights is None else weights[r]) for r, row in enumerate(nested)]
+    counts = [0.0 if weights is not None else 0] * length
+    for i, x in enumerate(nested):
+        counts[x] += 1 if weights is None else weights[i]
+    return counts
+
+
+def case_bincount_counts_every_element_of_a_view(xp):
+    rows, cols, lim = 12, 25, 37
+    xs = [(i * 7) % lim for i in range(rows * cols)]
+    idx = [9, 0, 4, 11, 2]
+    views = {
+        "contiguous": lambda a: a,
+        "column slice": lambda a: a[True, 3:cols - 4],
+        "reversed": lambda a: a[True, ::-1],
+        "row stride": lambda a: a[0:rows:3, True],
+        "index view": lambda a: a[idx, True],
+        "column index": lambda a: a[True, [7, 0, 19, 3, 24, 11]],
+        "transpose": lambda a: a.transpose(),
+    }
+    for T in (xp.Int32, xp.Int64):
+        src = _nd(T, xs, [rows, cols])
+        for what, take in views.items():
+            v = take(src)
+            length = max(_flat(v.to_a())) + 1
+            assert v.bincount().to_a() == _bincount_expect(v.to_a(), length), f"{T.__name__} {what}"
+            assert v.bincount(minlength=length + 9).to_a() == _bincount_expect(v.to_a(), length + 9), f"{T.__name__} {what} minlength"
+        flat = T.cast(xs)
+        for i, v in enumerate((flat[[13, 2, 40, 7, 99, 0, 61]], flat[0:rows * cols:5], flat[::-2])):
+            assert v.bincount().to_a() == _bincount_expect(v.to_a(), max(v.to_a()) + 1), f"{T.__name__} 1-d view {i}"
+    # weights whose sums stay exact, so the order of the additions cannot show
+    ws = [((i * 3) % 11) - 5.0 for i in range(rows * cols)]
+    for W in float_types(xp):
+        src, weight = _nd(xp.Int32, xs, [rows, cols]), _nd(W, ws, [rows, cols])
+        for what, take in views.items():
+            v, w = take(src), take(weight)
+            length = max(_flat(v.to_a())) + 1
+            assert v.bincount(w).to_a() == _bincount_expect(v.to_a(), length, w.to_a()), f"{W.__name__} {what}"
+    r = (xp.Int32(1 << 20).seq() % 997).bincount()
+    assert r.size == 997 and sum(r.to_a()) == 1 << 20
+
+
+# ---- test/narray_test.rb:4467-4486 "a numeric exponent answers what the same exponent as an array answers" -----------
+def case_numeric_exponent(xp):
+    nine = [2] * 9
+    for T in value_types(xp):
+        a = T[1, 2, 3, 4]
+        assert (a ** 3).to_a() == (a ** xp.Int32(4).fill(3)).to_a() == [1, 8, 27, 64], T.__name__
+        deep = T(*nine).seq(1)
+        assert _flat((deep ** 2).to_a()) == _flat((deep ** xp.Int32(*nine).fill(2)).to_a()) == [(i + 1) ** 2 for i in range(512)]
+    for T in float_types(xp):
+        a = T[1, 2, 3, 4]
+        assert (a ** 2.5).to_a() == (a ** T(4).fill(2.5)).to_a(), T.__name__
+        deep = T(*nine).seq(1)
+        assert _flat((deep ** 0.5).to_a()) == _flat((deep ** T(*nine).fill(0.5)).to_a()), T.__name__
+
+
+# ---- test/narray_test.rb:4530-4566 "a numeric operand answers what the same operand as an array answers" -------------
+def case_numeric_operand_of_a_comparison(xp):
+    nine = [2] * 9
+    py = {"eq": lambda u, v: u == v, "ne": lambda u, v: u != v, "gt": lambda u, v: u > v, "ge": lambda u, v: u >= v,
+          "lt": lambda u, v: u < v, "le": lambda u, v: u <= v}
+    for T in value_types(xp):
+        a = T[1, 2, 3, 4]
+        for op, f in py.items():
+            want = [1 if f(u, 3) else 0 for u in (1, 2, 3, 4)]
+            assert getattr(a, op)(3).to_a() == getattr(a, op)(T(4).fill(3)).to_a() == want, f"{T.__name__} {op} 3"
+        deep = T(*nine).seq(1)
+        assert _flat(deep.eq(7).to_a()) == _flat(deep.eq(T(*nine).fill(7)).to_a()) == [1 if i + 1 == 7 else 0 for i in range(512)]
+    for T in float_types(xp):
+        a = T[-1, 0, 1, NAN, INF]
+        for op in list(py) + ["nearly_eq"]:
+            for v in (1.0, NAN, INF):
+                assert getattr(a, op)(v).to_a() == getattr(a, op)(T(5).fill(v)).to_a(), f"{T.__name__} {op} {v}"
+        for op, f in py.items():
+            assert getattr(a, op)(1.0).to_a() == [1 if f(u, 1.0) else 0 for u in (-1.0, 0.0, 1.0, NAN, INF)], f"{T.__name__} {op} 1.0"
+    view = xp.Int32(3, 4).seq().transpose()
+    assert view.gt(5).to_a() == view.gt(xp.Int32(4, 3).fill(5)).to_a() == [[1 if r * 4 + c > 5 else 0 for r in range(3)] for c in range(4)]
+
+
+# ---- test/narray_test.rb:4811-4841 "a numeric on the left answers what the same value as an array answers" -----------
+def case_numeric_on_the_left(xp):
+    for T in value_types(xp):
+        a = T[1, 2, 3, 4]
+        spread = T(4).fill(2)
+        assert (2 + a).to_a() == (spread + a).to_a() == [3, 4, 5, 6]
+        assert (2 - a).to_a() == (spread - a).to_a() == [1, 0, -1, -2]
+        assert (2 * a).to_a() == (spread * a).to_a() == [2, 4, 6, 8]
+        assert (2 / a).to_a() == (spread / a).to_a(), T.__name__
+        assert (2 % a).to_a() == (spread % a).to_a() == [0, 0, 2, 2], T.__name__
+        assert (2 ** a).to_a() == (spread ** a).to_a() == [2, 4, 8, 16], T.__name__
+        assert (spread.lt(a)).to_a() == [0, 0, 1, 1] and (spread.le(a)).to_a() == [0, 1, 1, 1]
+    for T in (xp.Int32, xp.Int64):
+        assert (2 / T[1, 2, 3, 4]).to_a() == [2, 1, 0, 0]
+    for T in float_types(xp):
+        assert (2 / T[1, 2, 4, 8]).to_a() == [2.0, 1.0, 0.5, 0.25]
+    # the operand order is not commuted: a view, an index-backed view and a 9-d shape all reach the same elements
+    view = xp.SFloat(2, 3).seq(1).transpose()
+    assert (2.0 - view).to_a() == (xp.SFloat(3, 2).fill(2.0) - view).to_a() == [[1.0, -2.0], [0.0, -3.0], [-1.0, -4.0]]
+    idx = xp.SFloat(6).seq(1)[[3, 1, 2]]
+    assert (2.0 - idx).to_a() == (xp.SFloat(3).fill(2.0) - idx).to_a() == [-2.0, 0.0, -1.0]
+    nine = [2] * 9
+    deep = xp.SFloat(*nine).seq(1)
+    assert _flat((2.0 / deep).to_a()) == _flat((xp.SFloat(*nine).fill(2.0) / deep).to_a())
+    # dividing by an element that is zero still raises from the left
+    for bad in (lambda: (3 / xp.Int32[1, 0, 2]).to_a(), lambda: (3 % xp.Int32[1, 0, 2]).to_a()):
+        try:
+            bad()
+            raise AssertionError("ZeroDivisionError expected")
+        except ZeroDivisionError:
+            pass
+
+
 ALL_CASES = [v for k, v in sorted(globals().items()) if k.startswith("case_")]

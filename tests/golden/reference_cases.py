@@ -1380,4 +1380,49 @@ def case_numeric_on_the_left(xp):
             pass
 
 
+# ---- test/math_test.rb:13-516: every NMath function on the reference's literal inputs, real types; assert_close is
+# max |expected - actual| < 1e-6 * max(1, max |expected|) (math_test.rb:533-536), assert_equal where the reference has it --
+def case_nmath_literals(xp):
+    E, PI = math.e, math.pi
+    table = [
+        ("sqrt", [0, 1, 4, 9, 16], [0, 1, 2, 3, 4]),
+        ("cbrt", [-8, -1, 0, 1, 8], [-2, -1, 0, 1, 2]),
+        ("log", [1, E, 0.1, 10], [0, 1, math.log(0.1), math.log(10)]),
+        ("log2", [1, 0.5, 2, 4], [0, -1, 1, 2]),
+        ("log10", [1, 0.1, 5, 10, 100], [0, -1, math.log10(5), 1, 2]),
+        ("exp", [-2, -1, 0, 1, 2], [math.exp(v) for v in (-2, -1, 0, 1, 2)]),
+        ("exp2", [-2, -1, 0, 1, 2], [0.25, 0.5, 1, 2, 4]),
+        ("exp10", [-2, -1, 0, 1, 2], [0.01, 0.1, 1, 10, 100]),
+        ("sin", [-2, -1, 0, 1, 2], [math.sin(v) for v in (-2, -1, 0, 1, 2)]),
+        ("cos", [-2, -1, 0, 1, 2], [math.cos(v) for v in (-2, -1, 0, 1, 2)]),
+        ("tan", [-2, -1, 0, 1, 2], [math.tan(v) for v in (-2, -1, 0, 1, 2)]),
+        ("asin", [-1, -0.5, 0, 0.5, 1], [-PI / 2, math.asin(-0.5), 0, math.asin(0.5), PI / 2]),
+        ("acos", [-1, -0.5, 0, 0.5, 1], [PI, math.acos(-0.5), PI / 2, math.acos(0.5), 0]),
+        ("atan", [-2, -1, 0, 1, 2], [math.atan(v) for v in (-2, -1, 0, 1, 2)]),
+        ("sinh", [-2, -1, 0, 1, 2], [math.sinh(v) for v in (-2, -1, 0, 1, 2)]),
+        ("cosh", [-2, -1, 0, 1, 2], [math.cosh(v) for v in (-2, -1, 0, 1, 2)]),
+        ("tanh", [-2, -1, 0, 1, 2], [math.tanh(v) for v in (-2, -1, 0, 1, 2)]),
+        ("asinh", [-2, -1, 0, 1, 2], [math.asinh(v) for v in (-2, -1, 0, 1, 2)]),
+        ("acosh", [1, 2, 3, 4], [math.acosh(v) for v in (1, 2, 3, 4)]),
+        ("atanh", [-0.2, -0.1, 0, 0.1, 0.2], [math.atanh(v) for v in (-0.2, -0.1, 0, 0.1, 0.2)]),
+        ("sinc", [-2, -1, 0, 1, 2], [math.sin(-2) / -2, math.sin(-1) / -1, 1, math.sin(1), math.sin(2) / 2]),
+        ("erf", [-2, -1, 0, 1, 2], [math.erf(-2), math.erf(-1), 0, math.erf(1), math.erf(2)]),
+        ("erfc", [-2, -1, 0, 1, 2], [math.erfc(-2), math.erfc(-1), 1, math.erfc(1), math.erfc(2)]),
+        ("log1p", [-0.5, 0, 1, 2], [math.log(0.5), 0, math.log(2), math.log(3)]),
+        ("expm1", [-1.0, 0.0, 1.0, 2.0], [math.exp(-1) - 1, 0, math.exp(1) - 1, math.exp(2) - 1]),
+    ]
+    for T in float_types(xp):
+        for name, inputs, expected in table:
+            got = getattr(xp.NMath, name)(T.cast(inputs))
+            assert type(got) is T, name
+            want = T.cast(expected).to_a()                       # the reference rounds its expectation to the type too
+            scale = max(1.0, max(abs(v) for v in want))
+            assert max(abs(g - w) for g, w in zip(got.to_a(), want)) < 1e-6 * scale, (T.__name__, name, got.to_a(), want)
+        # math_test.rb:450-468, 508-516: these three are compared with assert_equal
+        c = xp.NMath.atan2(T[0, 1, 0, -1], T[1, 0, -1, 0])
+        assert type(c) is T and c.to_a() == T.cast([0, PI / 2, PI, -PI / 2]).to_a()
+        assert xp.NMath.hypot(T[3, 5, 8], T[4, 12, 15]).to_a() == [5, 13, 17]
+        assert xp.NMath.ldexp(T[0.0, 0.5, 0.5, 0.75, 0.5, 0.625], xp.Int32[0, 1, 2, 2, 3, 3]).to_a() == [0.0, 1.0, 2.0, 3.0, 4.0, 5.0]
+
+
 ALL_CASES = [v for k, v in sorted(globals().items()) if k.startswith("case_")]

@@ -35,17 +35,26 @@ def gemm_nt(a: SFloat, bt: SFloat) -> SFloat:
 
 def gemm(a, b, alpha=1.0, beta=0.0, c=None):
     """The reference's `Cumo::NArray#gemm` for SFloat / DFloat operands (row-major, the last two axes are the
-    matrices, leading axes are batches; either operand may be a transposed view): alpha * a . b + beta * c.
+    matrices, leading axes are batches; either operand may be a transposed view; an operand that holds one matrix is
+    used for every batch of the other): alpha * a . b + beta * c.
     It hands cuBLAS's column-major bookkeeping to the library exactly as gemm.c does: c^T = b^T . a^T."""
     from ctypes import byref, c_double, c_float, c_longlong
 
+    from .narray import ShapeError
+
     T = type(a)
-    if T not in (SFloat, DFloat) or type(b) is not T or a.ndim < 2 or b.ndim != a.ndim or a.shape[:-2] != b.shape[:-2]:
-        raise TypeError("gemm needs two SFloat or two DFloat arrays of the same batch shape")
+    if T not in (SFloat, DFloat) or type(b) is not T or a.ndim < 2 or b.ndim < 2:
+        raise TypeError("gemm needs two SFloat or two DFloat arrays of two or more dimensions")
     m, k = a.shape[-2:]
     k2, n = b.shape[-2:]
     if k != k2:
-        raise ValueError(f"shape mismatch: {a.shape} . {b.shape}")
+        raise ShapeError(f"shape mismatch: {a.shape} . {b.shape}")
+    if 0 in (m, n, k):
+        raise ShapeError("gemm of an empty operand")
+    batch_a, batch_b = a.shape[:-2], b.shape[:-2]
+    if batch_a and batch_b and batch_a != batch_b:
+        raise ShapeError(f"batch dimensions differ: {batch_a} and {batch_b}")
+    batch_shape = batch_a or batch_b                       # (gemm.c takes them from whichever operand has them)
     es = 4 if T is SFloat else 8
 
     def layout(x):
@@ -53,18 +62,21 @@ def gemm(a, b, alpha=1.0, beta=0.0, c=None):
         st = x.steps
         rows, cols = x.shape[-2:]
         batch_ok = all(st[d] == (x.shape[d + 1] * st[d + 1] if d + 1 < x.ndim - 2 else rows * cols * es) for d in range(x.ndim - 2))
-        if batch_ok and st[-1] == es and st[-2] >= cols * es and st[-2] % es == 0:
-            return x, 0, st[-2] // es, rows * cols            # row-major: column-major of its transpose, no flag
-        if batch_ok and st[-2] == es and st[-1] >= rows * es and st[-1] % es == 0:
-            return x, 1, st[-1] // es, rows * cols            # a transposed view: flag T
+        stride = rows * cols if x.ndim > 2 else 0          # one matrix serves every batch
+        if batch_ok and st[-1] == es and st[-2] >= cols * es and st[-2] % es == 0 and (x.ndim == 2 or st[-2] == cols * es):
+            return x, 0, st[-2] // es, stride               # row-major: column-major of its transpose, no flag
+        if batch_ok and st[-2] == es and st[-1] >= rows * es and st[-1] % es == 0 and (x.ndim == 2 or st[-1] == rows * es):
+            return x, 1, st[-1] // es, stride               # a transposed view: flag T
         y = x.dup()
-        return y, 0, cols, rows * cols
+        return y, 0, cols, stride
     a2, ta, lda, sa = layout(a)
     b2, tb, ldb, sb = layout(b)
     batch = 1
-    for d in a.shape[:-2]:
+    for d in batch_shape:
         batch *= d
-    out = T(*a.shape[:-2], m, n) if c is None or beta == 0.0 else c.dup()
+    if c is not None and tuple(c.shape) != tuple(batch_shape) + (m, n):
+        raise ShapeError(f"c has shape {c.shape}, the product {tuple(batch_shape) + (m, n)}")
+    out = T(*batch_shape, m, n) if c is None or beta == 0.0 else c.dup()
     lib = _lib.load()
     fn = lib.cb200_sgemm_strided_batched if T is SFloat else lib.cb200_dgemm_strided_batched
     fn.restype = c_int
@@ -82,9 +94,5 @@ def dot(a, b):
     `dot` on float matrices is `gemm` (lib/cumo/narray/extra.rb:1145-1196).  Large single-precision products run on the
     tensor cores, the rest on the CUDA-core kernel."""
     if not ((isinstance(a, SFloat) and isinstance(b, SFloat)) or (isinstance(a, DFloat) and isinstance(b, DFloat))):
-        raise TypeError("dot is built for two SFloat or two DFloat operands")
-    if a.ndim == 2 and b.ndim == 2:
-        return gemm(a, b)
-    if a.ndim == 2 and b.ndim == 1:
-        return gemm(a, b.reshape(b.shape[0], 1)).reshape(a.shape[0])
-    raise TypeError("dot takes a 2-D first operand and a 1-D or 2-D second one")
+        raise TypeError("dot is built for two SFloat or two DFloat operands (NArray#dot takes the other types)")
+    return a.dot(b)

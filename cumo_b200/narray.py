@@ -596,6 +596,45 @@ class NArray:
             _raise_last()
         return NArray._from_handle(idx.value), NArray._from_handle(val.value)
 
+    def gemm(self, b, c=None, alpha=1, beta=0):
+        """`a.gemm(b, c, alpha:, beta:)` of the reference for the float types (gen/tmpl/gemm.c): alpha * a . b + beta * c
+        over the last two axes, leading axes are batches; `b` is converted to this array's type."""
+        from . import linalg
+        if not isinstance(b, NArray) or type(b) is not type(self):
+            b = type(self).cast(b)
+        return linalg.gemm(self, b, alpha=float(alpha), beta=float(beta), c=c)
+
+    def dot(self, b):
+        """`a.dot(b)` as lib/cumo/narray/extra.rb:1145-1196 spells it: the float types go to gemm (vectors get a unit
+        axis for the call), the integer types to mulsum over a new axis."""
+        if not isinstance(b, NArray):
+            b = type(self).cast(b)
+        code = max(self.dtype_code, b.dtype_code) if {self.dtype_code, b.dtype_code} <= {INT32, INT64} else None
+        if code is None:
+            floats = [t for t in (self, b) if t.dtype_code in (SFLOAT, DFLOAT)]
+            T = DFloat if any(t.dtype_code == DFLOAT for t in floats) else SFloat
+        else:
+            T = Int64 if code == INT64 else Int32
+        if self.ndim == 0 and b.ndim == 0:
+            return self * b
+        a = self if type(self) is T else T.cast(self)
+        b = b if type(b) is T else T.cast(b)
+        if T in (SFloat, DFloat):
+            if a.ndim == 1:
+                if b.ndim == 1:
+                    return a.mulsum(b, axis=-1)
+                return a[None, ...].gemm(b).flatten()
+            if b.ndim == 1:
+                return a.gemm(b[..., None]).flatten()
+            return a.gemm(b)
+        if b.ndim == 1:
+            return a.mulsum(b, axis=-1)
+        if a.ndim == 0:
+            return b.mulsum(a, axis=-2)
+        if a.ndim == 1:
+            return a[True, None].mulsum(b, axis=-2)
+        return a[..., None].mulsum(b[..., None, True, True], axis=-2)
+
     def mulsum(self, other, axis=None, keepdims=False, nan=False):
         other = other if isinstance(other, NArray) else type(self).cast(other)
         nd = max(self.ndim, other.ndim)

@@ -1425,4 +1425,145 @@ def case_nmath_literals(xp):
         assert xp.NMath.ldexp(T[0.0, 0.5, 0.5, 0.75, 0.5, 0.625], xp.Int32[0, 1, 2, 2, 3, 3]).to_a() == [0.0, 1.0, 2.0, 3.0, 4.0, 5.0]
 
 
+# ---- test/narray_alt_coverage_test.rb:99-261, 348-487, 712-745: unary operations, classifications, comparisons and
+# integer division on literals (the real and the two integer types of this path) -------------------------------------
+def _raises(err, f):
+    try:
+        f()
+    except err:
+        return True
+    return False
+
+
+def case_alt_coverage_literals(xp):
+    for T in float_types(xp):
+        got = T[3.5, -2.1, 0.0, -0.7, -0.9].abs()
+        assert type(got) is T and got.to_a() == T[3.5, 2.1, 0.0, 0.7, 0.9].to_a()
+        assert T[2, 4, 8, 10].reciprocal().to_a() == T[0.5, 0.25, 0.125, 0.1].to_a()
+        assert T[3.5, -2.1, 0.0, 0.7, -0.9].sign().to_a() == [1, -1, 0, 1, -1]
+        x = T[1.5, -2.3, 3.0, -4.7, 5.9]
+        assert x.floor().to_a() == [1.0, -3.0, 3.0, -5.0, 5.0]
+        assert x.round().to_a() == [2.0, -2.0, 3.0, -5.0, 6.0]
+        assert x.ceil().to_a() == [2.0, -2.0, 3.0, -4.0, 6.0]
+        assert x.trunc().to_a() == [1.0, -2.0, 3.0, -4.0, 5.0]
+        assert T[1.5, -2.5, 3.0, -4.5, 5.9].rint().to_a() == [2.0, -2.0, 3.0, -4.0, 6.0]
+        got = T[1, -2, 3, -4, 5].copysign(T[-1, 1, -1, 1, 0])
+        assert type(got) is T and got.to_a() == [-1, 2, -3, 4, 5]
+        assert T[1.0, -2.0, 0.0, -0.0, 3.5].signbit().to_a() == [0, 1, 0, 1, 0]
+        assert T[1.0, NAN, 2.0, NAN, 3.0].isnan().to_a() == [0, 1, 0, 1, 0]
+        y = T[1.0, INF, -INF, 2.0, NAN]
+        assert y.isinf().to_a() == [0, 1, 1, 0, 0]
+        assert y.isposinf().to_a() == [0, 1, 0, 0, 0]
+        assert y.isneginf().to_a() == [0, 0, 1, 0, 0]
+        assert y.isfinite().to_a() == [1, 0, 0, 1, 0]
+    a = xp.SFloat[1.0, 1.0, 1.0, 1.0]
+    assert a.nearly_eq(xp.SFloat[1.0 + 1e-7, 1.0 - 1e-7, 1.0 + 1e-6, 1.0 - 1e-6]).to_a() == [1, 1, 0, 0]
+    a = xp.DFloat[1.0, 1.0, 1.0, 1.0]
+    assert a.nearly_eq(xp.DFloat[1.0 + 1e-16, 1.0 - 1e-16, 1.0 + 1e-15, 1.0 - 1e-15]).to_a() == [1, 1, 0, 0]
+    a, threes = xp.DFloat[1, 2, 3, 4, 5], xp.DFloat[3, 3, 3, 3, 3]
+    i = xp.Int32[-2, -1, 0, 1, 2]
+    for op, want3, want0, wantm1 in (("gt", [0, 0, 0, 1, 1], [0, 0, 0, 1, 1], [0, 0, 1, 1, 1]),
+                                     ("ge", [0, 0, 1, 1, 1], [0, 0, 1, 1, 1], [0, 1, 1, 1, 1]),
+                                     ("lt", [1, 1, 0, 0, 0], [1, 1, 0, 0, 0], [1, 0, 0, 0, 0]),
+                                     ("le", [1, 1, 1, 0, 0], [1, 1, 1, 0, 0], [1, 1, 0, 0, 0])):
+        assert getattr(a, op)(3).to_a() == want3 and getattr(a, op)(threes).to_a() == want3, op
+        assert getattr(i, op)(0).to_a() == want0 and getattr(i, op)(-1).to_a() == wantm1, op
+    for T in (xp.Int32, xp.Int64):
+        got = T[3, -2, 0, -7, -9].abs()
+        assert type(got) is T and got.to_a() == [3, 2, 0, 7, 9]
+        assert T[1, -1, 2, -2].reciprocal().to_a() == [1, -1, 0, 0]
+        assert T[3, -2, 0, 7, -9].sign().to_a() == [1, -1, 0, 1, -1]
+        # division by zero, also through a view, also in place
+        assert _raises(ZeroDivisionError, lambda: T[1, 0].reciprocal().to_a())
+        assert _raises(ZeroDivisionError, lambda: (T[1] / T[0]).to_a())
+        assert _raises(ZeroDivisionError, lambda: (T[1, 2, 3] / T[1, 0, 3]).to_a())
+        assert _raises(ZeroDivisionError, lambda: (T[1, 2, 3] / 0).to_a())
+        assert _raises(ZeroDivisionError, lambda: (T[1, 2, 3] % T[1, 0, 3]).to_a())
+        assert _raises(ZeroDivisionError, lambda: (T[1, 2, 3].inplace() / T[1, 0, 3]).to_a())
+        divisor = T[1, 9, 0, 9, 3, 9][0:6:2]
+        assert _raises(ZeroDivisionError, lambda: (T[1, 2, 3] / divisor).to_a())
+        assert _raises(ZeroDivisionError, lambda: (T[1, 2, 3] % divisor).to_a())
+        assert _raises(ZeroDivisionError, lambda: T[1, 0, 3][[0, 1, 2]].reciprocal().to_a())
+        a, b = T[10, 20, 30], T[3, 4, 5]
+        assert (a / b).to_a() == [3, 5, 6] and (a % b).to_a() == [1, 0, 0]
+        assert T[1, 2, 3].reciprocal().to_a() == [1, 0, 0]
+        assert (a / T[3, 3, 3]).to_a() == [3, 6, 10]
+
+
+# ---- test/narray_test.rb:805-914 "#dot" ---------------------------------------------------------------------------
+def case_dot(xp):
+    for T in value_types(xp):
+        seq = lambda n: T.cast(list(range(1, n + 1)))
+        assert scalar(T[1].sum().dot(T[3].sum())) == 3
+        assert scalar(T[1].dot(T[3])) == 3
+        assert scalar(T[1, 2, 3].dot(T[2, 3, 4])) == 1 * 2 + 2 * 3 + 3 * 4
+        assert seq(6).reshape(3, 2).dot(T[1, 2]).to_a() == [5, 11, 17]
+        assert T[1, 2].dot(seq(6).reshape(2, 3)).to_a() == [9, 12, 15]
+        assert T[1, 2, 3].dot(T[4, 5, 6].reshape(3, 1)).to_a() == [32]
+        a, b = seq(6).reshape(3, 2), seq(6).reshape(2, 3)
+        assert a.dot(b).to_a() == [[9, 12, 15], [19, 26, 33], [29, 40, 51]]
+        assert b.dot(a).to_a() == [[22, 28], [49, 64]]
+        b = seq(6).reshape(3, 2).transpose()
+        assert a.dot(b).to_a() == [[5, 11, 17], [11, 25, 39], [17, 39, 61]]
+        assert b.dot(a).to_a() == [[35, 44], [44, 56]]
+        a, b = T(4, 3).seq(0)[1:3, 0:3], T(3, 2).seq(0)               # a contiguous view
+        assert a.dot(b).to_a() == [[28, 40], [46, 67]]
+        assert b.dot(a).to_a() == [[6, 7, 8], [24, 29, 34], [42, 51, 60]]
+        a = T(4, 4).seq(0)[1:3, 0:3]                                   # a view that is not contiguous
+        assert a.dot(b).to_a() == [[34, 49], [58, 85]]
+        assert b.dot(a).to_a() == [[8, 9, 10], [32, 37, 42], [56, 65, 74]]
+        a, b = seq(12).reshape(2, 3, 2), seq(12).reshape(2, 2, 3)
+        ab = [[[9, 12, 15], [19, 26, 33], [29, 40, 51]], [[129, 144, 159], [163, 182, 201], [197, 220, 243]]]
+        ba = [[[22, 28], [49, 64]], [[220, 244], [301, 334]]]
+        assert a.dot(b).to_a() == ab and b.dot(a).to_a() == ba
+        a, b = seq(12).reshape(1, 2, 3, 2), seq(12).reshape(1, 2, 2, 3)
+        assert a.dot(b).to_a() == [ab] and b.dot(a).to_a() == [ba]
+        a, b = seq(12).reshape(2, 3, 2), seq(12).reshape(3, 2, 2).transpose()
+        assert a.dot(b).to_a() == [[[7, 19, 31], [15, 43, 71], [23, 67, 111]], [[46, 106, 166], [58, 134, 210], [70, 162, 254]]]
+        assert b.dot(a).to_a() == [[[61, 76], [79, 100]], [[178, 196], [232, 256]]]
+        assert _raises(xp.ShapeError, lambda: seq(6).reshape(3, 2).dot(seq(9).reshape(3, 3)).to_a())
+
+
+# ---- test/narray_test.rb:916-994 "#gemm" (the real float types) --------------------------------------------------------
+def case_gemm(xp):
+    for T in float_types(xp):
+        seq = lambda n: T.cast(list(range(1, n + 1)))
+        a, b = seq(6).reshape(2, 3), seq(6).reshape(2, 3)
+        assert (a.gemm(b.transpose()) * 3).to_a() == a.gemm(b.transpose(), alpha=3).to_a()
+        for B in (xp.Int32, xp.SFloat, xp.DFloat):
+            c = a.gemm(B.cast(list(range(1, 7))).reshape(3, 2))
+            assert type(c) is T and c.to_a() == [[22, 28], [49, 64]]
+        assert a.gemm([[1, 2], [3, 4], [5, 6]]).to_a() == [[22, 28], [49, 64]]
+        # an operand that holds one matrix is used for every batch
+        b = T(3, 4).seq()
+        neighbour = [T(200).fill(7) for _ in range(2)]                 # next to b in the pool: a read past b would show up as 7
+        a = T(10, 2, 3).seq()
+        c = a.gemm(b)
+        assert list(c.shape) == [10, 2, 4]
+        for i in range(10):
+            assert c[i, True, True].to_a() == a[i, True, True].gemm(b).to_a()
+        assert all(nb.to_a() == [7] * 200 for nb in neighbour)
+        a, b = T(2, 3).seq(), T(4, 3, 4).seq()
+        c = a.gemm(b)
+        assert list(c.shape) == [4, 2, 4]
+        for i in range(4):
+            assert c[i, True, True].to_a() == a.gemm(b[i, True, True]).to_a()
+        assert _raises(xp.ShapeError, lambda: T(4, 2, 3).seq().gemm(T(3, 3, 4).seq()))
+        assert _raises(xp.ShapeError, lambda: T(2, 3).seq().gemm(T(3, 0)))
+        assert _raises(xp.ShapeError, lambda: T(0, 3).gemm(T(3, 4).seq()))
+        assert _raises(xp.ShapeError, lambda: T(2, 0).gemm(T(0, 4)))
+        # a transposed batch, and batches that are not whole matrix transposes
+        a, b = T(2, 3, 2, 4).seq(), T(2, 3, 5, 4).seq().transpose(0, 1, 3, 2)
+        assert a.gemm(b).to_a() == a.gemm(b.dup()).to_a()
+        c, d = T(3, 2, 4).seq(), T(3, 5, 4).seq().transpose(0, 2, 1)
+        assert c.gemm(d).to_a() == c.gemm(d.dup()).to_a()
+        a, b = T(3, 2, 4).seq(), T(5, 4, 3).seq().transpose()
+        assert a.gemm(b).to_a() == a.gemm(b.dup()).to_a()
+        c, d = T(2, 2, 3, 4).seq(), T(2, 2, 5, 4).seq()[True, True, 0:4, True].transpose(0, 1, 3, 2)
+        assert c.gemm(d).to_a() == c.gemm(d.dup()).to_a()
+        a, b = T(4, 2, 3).seq(), T(3, 4).seq()
+        assert _raises(xp.ShapeError, lambda: a.gemm(b, T.zeros(2, 4)))
+        assert a.gemm(b, T.zeros(4, 2, 4)).to_a() == a.gemm(b).to_a()
+
+
 ALL_CASES = [v for k, v in sorted(globals().items()) if k.startswith("case_")]

@@ -259,8 +259,56 @@ class ONArray:
         val = self._reduce("max" if "max" in op else "min", axis, False, nan)
         return idx, val
 
+    def gemm(self, b, c=None, alpha=1, beta=0):
+        """alpha * a . b + beta * c over the last two axes, spelled with the oracle's mulsum (one output at a time)."""
+        if not isinstance(b, ONArray) or type(b) is not type(self):
+            b = type(self).cast(b)
+        m, k = self.a.shape[-2:]
+        k2, n = b.a.shape[-2:]
+        ba, bb = self.a.shape[:-2], b.a.shape[:-2]
+        if k != k2 or 0 in (m, n, k) or (ba and bb and ba != bb):
+            raise ShapeErrorO(f"gemm of {self.a.shape} and {b.a.shape}")
+        prod = self._wrap(orc.mulsum(self.a[..., :, :, None], b.a[..., None, :, :], axis=-2))
+        if alpha != 1:
+            prod = prod * type(self).cast([alpha]).a.reshape(()).item()
+        if c is not None:
+            if tuple(c.a.shape) != tuple(prod.a.shape):
+                raise ShapeErrorO("c has another shape than the product")
+            if beta != 0:
+                prod = prod + c * beta
+        return prod
+
+    def dot(self, b):
+        """lib/cumo/narray/extra.rb:1145-1196 on the oracle's operations."""
+        if not isinstance(b, ONArray):
+            b = type(self).cast(b)
+        t = _upcast(self.a.dtype, b.a.dtype)
+        T = _BY_DTYPE[np.dtype(t)]
+        if self.a.ndim == 0 and b.a.ndim == 0:
+            return self * b
+        a, b = T.cast(self) if type(self) is not T else self, T.cast(b) if type(b) is not T else b
+        if np.issubdtype(t, np.floating):
+            if a.a.ndim == 1:
+                if b.a.ndim == 1:
+                    return a.mulsum(b, axis=-1)
+                return a[None, ...].gemm(b).flatten()
+            if b.a.ndim == 1:
+                return a.gemm(b[..., None]).flatten()
+            return a.gemm(b)
+        if b.a.ndim == 1:
+            return a.mulsum(b, axis=-1)
+        if a.a.ndim == 0:
+            return b.mulsum(a, axis=-2)
+        if a.a.ndim == 1:
+            return a[True, None].mulsum(b, axis=-2)
+        return a[..., None].mulsum(b[..., None, True, True], axis=-2)
+
     def mulsum(self, other, axis=None, keepdims=False, nan=False):
         x, y = self._operand(other)
+        try:
+            np.broadcast_shapes(x.shape, np.shape(y))
+        except ValueError as e:
+            raise ShapeErrorO(str(e)) from None
         return self._wrap(orc.mulsum(x, y, axis=axis, nan=nan))
 
 

@@ -28,6 +28,11 @@ NVCC_FLAGS = [
     "--expt-relaxed-constexpr",
     "-Xcudafe", "--diag_suppress=550",
 ]
+# CB200_NVTX=1 in the environment of the build puts an NVTX range (the launch function's full name, template arguments
+# included) around every host-side launch function; without it the ranges compile to nothing.  (A change of this
+# variable needs `--force`: objects are not keyed by it.)
+if os.environ.get("CB200_NVTX", "0") not in ("", "0"):
+    NVCC_FLAGS.append("-DCB200_NVTX")
 
 
 def nvcc() -> str:

@@ -93,6 +93,7 @@ bincount_kernel(const char* __restrict__ p1, int64_t s1, const size_t* __restric
 template <typename TI, typename TC, typename TW>
 void launch_bincount(char* p1, ssize_t s1, size_t* idx1, uint64_t count, char* pw, ssize_t sw, char* out, ssize_t so,
                      uint64_t n, int* oor, size_t* item) {
+    CB200_TRACE_LAUNCH();
     constexpr bool WEIGHTED = !std::is_same<TW, void>::value;
     cudaStream_t st = current_stream();
     int launches = 0;

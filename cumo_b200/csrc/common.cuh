@@ -32,6 +32,27 @@ inline unsigned grid_for(int64_t work_items, int per_sm) {
     return (unsigned)(work_items < cap ? work_items : cap);
 }
 
+// ---- tracing ----------------------------------------------------------------
+// The reference has no tracer (its `NArray.profile` is a stub).  A build with -DCB200_NVTX brackets every host-side launch
+// function with an NVTX range named after the function and its template arguments, which a timeline tool then shows
+// around the kernels it launched; the default build has none of it.
+#ifdef CB200_NVTX
+}  // namespace cb200
+#include <nvtx3/nvToolsExt.h>
+namespace cb200 {
+struct TraceRange {
+    explicit TraceRange(const char* name) { nvtxRangePushA(name); }
+    ~TraceRange() { nvtxRangePop(); }
+    TraceRange(const TraceRange&) = delete;
+    TraceRange& operator=(const TraceRange&) = delete;
+};
+#else
+struct TraceRange {
+    explicit TraceRange(const char*) {}
+};
+#endif
+#define CB200_TRACE_LAUNCH() ::cb200::TraceRange cb200_trace_range_(__PRETTY_FUNCTION__)
+
 // ---- vector access ----------------------------------------------------------
 // 16-byte packets: 4 x 32-bit or 2 x 64-bit elements.
 template <typename T> struct VecOf { static constexpr int n = 16 / sizeof(T); };

@@ -660,6 +660,7 @@ template <typename Op>
 void launch_elementwise(const cumo_na_iarray_t* a1, const cumo_na_iarray_t* a2, cumo_na_iarray_t* a3,
                         const cumo_na_indexer_t* ix, typename Op::In1 sx, typename Op::In2 sy,
                         int use_scalar, int* flag) {
+    CB200_TRACE_LAUNCH();
     using T1 = typename Op::In1;
     using T2 = typename Op::In2;
     using TO = typename Op::Out;
@@ -935,6 +936,7 @@ cmp_gen_kernel(const EwPlan p, int64_t n_tiles, const char* __restrict__ a1, con
 template <typename Op>
 void launch_compare(const cumo_na_iarray_t* a1, const cumo_na_iarray_t* a2, cumo_na_bit_iarray_t* a3,
                     const cumo_na_indexer_t* ix, typename Op::In1 sx, typename Op::In2 sy, int use_scalar) {
+    CB200_TRACE_LAUNCH();
     using T1 = typename Op::In1;
     constexpr int ES = sizeof(T1);
     const bool have1 = use_scalar != 2 && a1 != nullptr;

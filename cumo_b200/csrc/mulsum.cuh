@@ -90,6 +90,7 @@ mulsum_each_kernel(const char* __restrict__ p1, const char* __restrict__ p2, cha
 
 template <typename T, bool NAN_SKIP>
 void launch_mulsum_reduce(char* p1, char* p2, char* p3, ssize_t s1, ssize_t s2, uint64_t n) {
+    CB200_TRACE_LAUNCH();
     constexpr int ES = sizeof(T);
     constexpr int VMAX = 16 / ES;
     cudaStream_t st = current_stream();
@@ -118,6 +119,7 @@ void launch_mulsum_reduce(char* p1, char* p2, char* p3, ssize_t s1, ssize_t s2, 
 
 template <typename T, bool NAN_SKIP>
 void launch_mulsum_each(char* p1, char* p2, char* p3, ssize_t s1, ssize_t s2, ssize_t s3, uint64_t n) {
+    CB200_TRACE_LAUNCH();
     if (n == 0) return;
     int64_t blocks = ((int64_t)n + kBlock - 1) / kBlock;
     mulsum_each_kernel<T, NAN_SKIP><<<grid_for(blocks, 8), kBlock, 0, current_stream()>>>(p1, p2, p3, s1, s2, s3, (int64_t)n);

@@ -623,6 +623,7 @@ inline unsigned red_grid(int64_t ctas) { return (unsigned)(ctas < 1 ? 1 : (ctas 
 // flat_index: 0 = feed the position along the reduce axes, 1 = feed the element offset.
 template <typename R>
 void launch_reduce(const cumo_na_reduction_arg_t* arg, const cumo_na_iarray_t* out2_arr, const R& r, int flat_index) {
+    CB200_TRACE_LAUNCH();
     using T = typename R::In;
     using Acc = typename R::Acc;
     constexpr int ES = sizeof(T);

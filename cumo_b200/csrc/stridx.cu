@@ -57,6 +57,7 @@ stridx_copy_kernel(const StridxPlan p, char* dst, const char* __restrict__ src) 
 
 template <typename W>
 static void launch_stridx_store(const cumo_na_iarray_stridx_t* a1, const cumo_na_iarray_stridx_t* a2, const cumo_na_indexer_t* ix) {
+    CB200_TRACE_LAUNCH();
     StridxPlan p;
     p.nd = ix->ndim;
     p.total = 1;

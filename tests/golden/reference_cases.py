@@ -1566,4 +1566,48 @@ def case_gemm(xp):
         assert a.gemm(b, T.zeros(4, 2, 4)).to_a() == a.gemm(b).to_a()
 
 
+# ---- test/narray_test.rb:2817-2856 "bit where and where2 over long arrays and views", "bit where along the rows of a
+# 2-d view" (the slice views; an index-array view of a Bit array is not on this path) ----------------------------------
+def case_bit_where_over_long_arrays_and_views(xp):
+    n = 20_000
+    xs = [((i * 2_654_435_761) >> 11) & 1 for i in range(n)]
+    views = [
+        ("flat", list(range(n)), lambda v: v),
+        ("offset 13", list(range(13, n)), lambda v: v[13:n]),
+        ("step 2", list(range(0, n, 2)), lambda v: v[0:n:2]),
+        ("reversed", list(range(n - 1, -1, -1)), lambda v: v[::-1]),
+    ]
+    a = xp.Bit.cast(xs)
+    for label, idxs, cut in views:
+        seq = [xs[i] for i in idxs]
+        want_one = [i for i, b in enumerate(seq) if b == 1]
+        want_zero = [i for i, b in enumerate(seq) if b == 0]
+        v = cut(a)
+        assert v.where().to_a() == want_one, label
+        w1, w0 = v.where2()
+        assert w1.to_a() == want_one and w0.to_a() == want_zero, label
+        assert scalar(v.count_true()) == len(want_one) and scalar(v.count_false()) == len(want_zero), label
+    rows, cols = 4, 20_000
+    xs = [((i * 40_503) >> 7) & 1 for i in range(rows * cols)]
+    a = xp.Bit.cast(xs).reshape(rows, cols)
+    v = a[True, 1:-1]                                   # drops a column at either end: the rows stay separate runs
+    seq = [b for r in range(rows) for b in xs[r * cols + 1:r * cols + cols - 1]]
+    assert v.where().to_a() == [i for i, b in enumerate(seq) if b == 1]
+    w1, w0 = v.where2()
+    assert w1.to_a() == [i for i, b in enumerate(seq) if b == 1] and w0.to_a() == [i for i, b in enumerate(seq) if b == 0]
+
+
+# ---- test/narray_test.rb:4699-4702, 4719, 4724-4728: integer arrays raised to negative and small powers (the signed
+# lines: "unsigned now answers what signed has always answered", and the exponents around the guard) -----------------
+def case_integer_powers_around_zero(xp):
+    assert (xp.Int32[1, 2, 3, 4] ** -3).to_a() == [0, 0, 0, 0]
+    assert (xp.Int64[1, 2, 3, 4] ** (-2 ** 31)).to_a() == [0, 0, 0, 0]
+    for T in (xp.Int32, xp.Int64):
+        u = T[1, 2, 3, 4]
+        assert (u ** 0).to_a() == [1, 1, 1, 1]
+        assert (u ** 1).to_a() == [1, 2, 3, 4]
+        assert (u ** 3).to_a() == [1, 8, 27, 64]
+        assert (u ** xp.Int32[-2, -1, 2, 3]).to_a() == [0, 0, 9, 64]
+
+
 ALL_CASES = [v for k, v in sorted(globals().items()) if k.startswith("case_")]

@@ -375,7 +375,12 @@ class OBit:
         return ONArray._wrap(np.array(array.a)[self.b])
 
     def __getitem__(self, key):
-        return OBit(self.b[key])
+        if not isinstance(key, tuple):
+            key = (key,)
+        return OBit(self.b[tuple(slice(None) if k is True else k for k in key)])
+
+    def reshape(self, *shape):
+        return OBit(np.array(self.b).reshape(shape))
 
     def _count(self, axis, keepdims, want_false):
         nd = self.b.ndim

@@ -27,7 +27,8 @@ from pathlib import Path
 HERE = Path(__file__).resolve().parent
 OUT = HERE / "_ref"
 LIB = OUT / "libcumo_ref_kernels.so"
-DEFAULT_REF = Path("/root/reference")
+# where the reference checkout is looked for: CUMO_REFERENCE_ROOT, else a `reference` directory beside this repository
+DEFAULT_REF = Path(os.environ.get("CUMO_REFERENCE_ROOT") or HERE.parent.parent / "reference")
 
 # templates (by erb_base) expanded per element type: the hot path and the rows next to it
 VALUE_TEMPLATES = {"binary", "binary_s", "unary", "unary_s", "unary2", "cond_binary", "cond_unary", "pow", "ewcomp",

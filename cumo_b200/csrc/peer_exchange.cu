@@ -21,7 +21,7 @@
 #include <cstdint>
 #include <cstring>
 
-#include "common.cuh"
+#include "reducers.cuh"
 
 namespace cb200 {
 
@@ -35,17 +35,13 @@ __device__ __forceinline__ size_t peer_flag_offset(size_t slot_bytes, int world,
     return 2 * (size_t)world * slot_bytes + (((size_t)slot * world + rank) * kPeerMaxCtas + cta) * sizeof(unsigned long long);
 }
 
-__global__ void __launch_bounds__(kBlock)
-peer_exchange_kernel(const char* __restrict__ src, size_t nbytes, const PeerBases peers, int world, int rank, size_t slot_bytes,
-                     unsigned long long seq, unsigned spin_limit, int* status) {
-    pdl_trigger();                      // the fold queued behind may become resident; it waits for this grid to finish
-    pdl_wait();                         // this grid itself is launched as a dependent of the local reduction's last kernel
+// Steps 1-3 for this CTA's slice [p_begin, p_end) of 16-byte packets; false when a wait ran out.
+__device__ __forceinline__ bool exchange_slice(const char* __restrict__ src, size_t p_begin, size_t p_end, const PeerBases& peers, int world, int rank,
+                                               size_t slot_bytes, unsigned long long seq, unsigned spin_limit, int* status) {
+    __shared__ int gave_up;
     const int slot = (int)(seq & 1ull);
-    const size_t packets = (nbytes + 15) / 16;                                   // the source is padded to whole packets by the host
-    const size_t per_cta = (packets + gridDim.x - 1) / gridDim.x;
-    const size_t p_begin = (size_t)blockIdx.x * per_cta;
-    size_t p_end = p_begin + per_cta; if (p_end > packets) p_end = packets;
     const size_t mine = p_end > p_begin ? p_end - p_begin : 0;
+    if (threadIdx.x == 0) gave_up = 0;
     // 1. my slice into everyone's slot [rank]
     const size_t dst_off = ((size_t)slot * world + rank) * slot_bytes;
     for (size_t i = threadIdx.x; i < mine * world; i += kBlock) {
@@ -67,10 +63,79 @@ peer_exchange_kernel(const char* __restrict__ src, size_t nbytes, const PeerBase
             if (*here >= seq) { seen = true; break; }
             if (spin > 64) __nanosleep(200);
         }
-        if (!seen) atomicExch(status, 1);
+        if (!seen) { atomicExch(status, 1); gave_up = 1; }
         __threadfence_system();
     }
     __syncthreads();
+    return gave_up == 0;
+}
+
+__device__ __forceinline__ void slice_of(size_t nbytes, size_t& p_begin, size_t& p_end) {
+    const size_t packets = (nbytes + 15) / 16;                                   // the source is padded to whole packets by the host
+    const size_t per_cta = (packets + gridDim.x - 1) / gridDim.x;
+    p_begin = (size_t)blockIdx.x * per_cta;
+    p_end = p_begin + per_cta;
+    if (p_end > packets) p_end = packets;
+}
+
+__global__ void __launch_bounds__(kBlock)
+peer_exchange_kernel(const char* __restrict__ src, size_t nbytes, const PeerBases peers, int world, int rank, size_t slot_bytes,
+                     unsigned long long seq, unsigned spin_limit, int* status) {
+    pdl_trigger();                      // the fold queued behind may become resident; it waits for this grid to finish
+    pdl_wait();                         // this grid itself is launched as a dependent of the local reduction's last kernel
+    size_t p_begin, p_end;
+    slice_of(nbytes, p_begin, p_end);
+    exchange_slice(src, p_begin, p_end, peers, world, rank, slot_bytes, seq, spin_limit, status);
+}
+
+// The exchange and the rank fold in one kernel, for folds that work element by element (sums, min, max): a CTA folds the
+// slice it exchanged as soon as its own peers' flags are up -- one launch and one launch gap less per reduction.
+// MODE 0: sum in float64 in rank order, divided by `divisor` unless 0, rounded once.  MODE 1: min / max with the
+// single-GPU functor's NaN rules.
+template <typename T, int MODE, bool IS_MAX, bool NAN_WINS>
+__global__ void __launch_bounds__(kBlock)
+peer_exchange_fold_kernel(const char* __restrict__ src, size_t nbytes, const PeerBases peers, int world, int rank, size_t slot_bytes,
+                          unsigned long long seq, unsigned spin_limit, int* status, int64_t n_out, double divisor, T* out) {
+    pdl_trigger();
+    pdl_wait();
+    size_t p_begin, p_end;
+    slice_of(nbytes, p_begin, p_end);
+    if (!exchange_slice(src, p_begin, p_end, peers, world, rank, slot_bytes, seq, spin_limit, status)) return;
+    constexpr int V = 16 / (int)sizeof(T);
+    const char* mine = peers.base[rank] + (size_t)(seq & 1ull) * world * slot_bytes;
+    const int64_t o_begin = (int64_t)p_begin * V;
+    int64_t o_end = (int64_t)p_end * V;
+    if (o_end > n_out) o_end = n_out;
+    using R = red::MinMax<T, IS_MAX, NAN_WINS>;
+    const R r{};
+    for (int64_t o = o_begin + threadIdx.x; o < o_end; o += kBlock) {
+        if (MODE == 0) {
+            double acc = 0.0;
+            for (int k = 0; k < world; ++k) acc += (double)__ldcg(reinterpret_cast<const T*>(mine + (size_t)k * slot_bytes) + o);
+            if (divisor != 0.0) acc /= divisor;
+            out[o] = (T)acc;
+        } else {
+            T acc = __ldcg(reinterpret_cast<const T*>(mine) + o);
+            for (int k = 1; k < world; ++k) acc = r.combine(acc, __ldcg(reinterpret_cast<const T*>(mine + (size_t)k * slot_bytes) + o));
+            out[o] = acc;
+        }
+    }
+}
+
+template <typename T>
+static void launch_exchange_fold(const char* s, size_t nbytes, const PeerBases& pb, int world, int rank, size_t slot_bytes, unsigned long long seq,
+                                 unsigned limit, int* status, int64_t n_out, double divisor, int op, int nan_wins, void* out, unsigned ctas,
+                                 cudaStream_t st) {
+    T* o = static_cast<T*>(out);
+    constexpr bool fp = red::is_fp<T>::value;
+    auto go = [&](auto kernel) { launch_dependent(kernel, ctas, kBlock, st, s, nbytes, pb, world, rank, slot_bytes, seq, limit, status, n_out, divisor, o); };
+    if (op == 0) {
+        if constexpr (fp) go(peer_exchange_fold_kernel<T, 0, false, false>);
+    } else if (op == 2) {
+        if (nan_wins && fp) go(peer_exchange_fold_kernel<T, 1, true, fp>); else go(peer_exchange_fold_kernel<T, 1, true, false>);
+    } else {
+        if (nan_wins && fp) go(peer_exchange_fold_kernel<T, 1, false, fp>); else go(peer_exchange_fold_kernel<T, 1, false, false>);
+    }
 }
 
 }  // namespace cb200
@@ -131,6 +196,35 @@ int cb200_peer_exchange_kernel_launch(const void* src, size_t nbytes, void* cons
     if (ctas > (size_t)kPeerMaxCtas) ctas = kPeerMaxCtas;
     launch_dependent(peer_exchange_kernel, (unsigned)ctas, kBlock, current_stream(), static_cast<const char*>(src), nbytes, pb, world, rank, slot_bytes, seq,
                      spin_limit ? spin_limit : (1u << 25), status);
+    count_launch();
+    return (int)cudaGetLastError();
+}
+
+// The same exchange with the rank fold done by the same kernel: `op` 0 = sum (float types; `divisor` as in
+// cb200_<T>_rank_fold_sum_kernel_launch), 1 = min, 2 = max (`nan_wins` as in the extreme fold); `dtype` 0 sfloat, 1 dfloat,
+// 2 int32, 3 int64 (min / max only for the integer types); `src` holds n_out elements, `out` receives n_out.
+int cb200_peer_exchange_fold_kernel_launch(const void* src, int dtype, int op, int64_t n_out, double divisor, int nan_wins, void* out,
+                                           void* const* bases, int world, int rank, size_t slot_bytes, unsigned long long seq,
+                                           unsigned spin_limit, int* status) {
+    static const size_t es_of[4] = {4, 8, 4, 8};
+    if (dtype < 0 || dtype > 3 || op < 0 || op > 2 || n_out <= 0 || !out || (op == 0 && dtype > 1)) return (int)cudaErrorInvalidValue;
+    const size_t nbytes = (size_t)n_out * es_of[dtype];
+    if (!src || !bases || !status || world < 1 || world > kPeerMaxWorld || rank < 0 || rank >= world || nbytes > slot_bytes ||
+        slot_bytes % 16 != 0 || seq == 0 || (reinterpret_cast<uintptr_t>(src) & 15) != 0)
+        return (int)cudaErrorInvalidValue;
+    PeerBases pb;
+    for (int p = 0; p < kPeerMaxWorld; ++p) pb.base[p] = p < world ? static_cast<char*>(bases[p]) : nullptr;
+    size_t ctas = (nbytes + kPeerSliceBytes - 1) / kPeerSliceBytes;
+    if (ctas > (size_t)kPeerMaxCtas) ctas = kPeerMaxCtas;
+    const unsigned limit = spin_limit ? spin_limit : (1u << 25);
+    const char* s = static_cast<const char*>(src);
+    cudaStream_t st = current_stream();
+    switch (dtype) {
+    case 0: launch_exchange_fold<float>(s, nbytes, pb, world, rank, slot_bytes, seq, limit, status, n_out, divisor, op, nan_wins, out, (unsigned)ctas, st); break;
+    case 1: launch_exchange_fold<double>(s, nbytes, pb, world, rank, slot_bytes, seq, limit, status, n_out, divisor, op, nan_wins, out, (unsigned)ctas, st); break;
+    case 2: launch_exchange_fold<int32_t>(s, nbytes, pb, world, rank, slot_bytes, seq, limit, status, n_out, divisor, op, nan_wins, out, (unsigned)ctas, st); break;
+    default: launch_exchange_fold<int64_t>(s, nbytes, pb, world, rank, slot_bytes, seq, limit, status, n_out, divisor, op, nan_wins, out, (unsigned)ctas, st); break;
+    }
     count_launch();
     return (int)cudaGetLastError();
 }

@@ -106,6 +106,21 @@ class PeerExchange:
             raise RuntimeError(f"peer exchange launch failed with CUDA error {rc}")
         return self.base.value + (self.seq & 1) * self.world * self.SLOT_BYTES, self.SLOT_BYTES
 
+    _DTYPES = {"SFloat": 0, "DFloat": 1, "Int32": 2, "Int64": 3}
+
+    def gather_fold(self, src, out, op, divisor=0.0, nan_wins=False):
+        """Exchange and rank fold in one kernel: `src` (this rank's partial, an array of the library) against everyone's,
+        folded element by element into `out` (same type and size).  op: "sum", "min" or "max"."""
+        import ctypes
+        self.seq += 1
+        rc = self.lib.cb200_peer_exchange_fold_kernel_launch(
+            ctypes.c_void_p(src.data_ptr), self._DTYPES[type(src).__name__], {"sum": 0, "min": 1, "max": 2}[op], src.size, float(divisor),
+            int(bool(nan_wins)), ctypes.c_void_p(out.data_ptr), self.bases, self.world, self.rank, ctypes.c_size_t(self.SLOT_BYTES),
+            ctypes.c_ulonglong(self.seq), ctypes.c_uint(self.spin_limit), ctypes.c_void_p(self.status.data_ptr()))
+        if rc != 0:
+            raise RuntimeError(f"peer exchange launch failed with CUDA error {rc}")
+        return out
+
     def check(self):
         """Synchronises and raises if a bounded wait of an exchange ran out since the last check."""
         if int(self.status.item()) != 0:
@@ -271,9 +286,12 @@ class ShardedArray:
             import torch
             from . import _lib
             T = type(self.local)
-            src = torch.as_tensor(part if part.contiguous() else part.dup(), device="cuda")
-            ptr, stride, _keep = comm.gather_partials(src)
+            part = part if part.contiguous() else part.dup()
             out = T(*part.shape)
+            if comm.peer is not None and part.size * (4 if T.__name__ == "SFloat" else 8) <= PeerExchange.SLOT_BYTES:
+                return comm.peer.gather_fold(part, out, "sum", divisor=n)          # exchange and fold in one kernel
+            src = torch.as_tensor(part, device="cuda")
+            ptr, stride, _keep = comm.gather_partials(src)
             fold = getattr(_lib.load(), f"cb200_{T.__name__.lower()}_rank_fold_sum_kernel_launch")
             fold(ptr, stride, comm.world, src.numel(), n, out.data_ptr)
             return out
@@ -298,9 +316,12 @@ class ShardedArray:
             import torch
             from . import _lib
             T = type(part)
-            src = torch.as_tensor(part if part.contiguous() else part.dup(), device="cuda")
-            ptr, stride, _keep = comm.gather_partials(src)
+            part = part if part.contiguous() else part.dup()
             out = T(*part.shape)
+            if comm.peer is not None and part.size * (4 if T.__name__ in ("SFloat", "Int32") else 8) <= PeerExchange.SLOT_BYTES:
+                return comm.peer.gather_fold(part, out, op, nan_wins=bool(nan) and self._is_float())
+            src = torch.as_tensor(part, device="cuda")
+            ptr, stride, _keep = comm.gather_partials(src)
             fold = getattr(_lib.load(), f"cb200_{T.__name__.lower()}_rank_fold_extreme_kernel_launch")
             fold(ptr, stride, comm.world, src.numel(), int(op == "max"), int(bool(nan) and self._is_float()), out.data_ptr)
             return out

@@ -413,6 +413,13 @@ int cb200_peer_buffer_close(void* ptr);
 int cb200_peer_buffer_destroy(void* base);
 int cb200_peer_exchange_kernel_launch(const void* src, size_t nbytes, void* const* bases, int world, int rank, size_t slot_bytes,
                                       unsigned long long seq, unsigned spin_limit, int* status);
+/* The same exchange with the rank fold done by the same kernel, for the folds that work element by element: a CTA folds the
+ * slice it exchanged as soon as its peers' flags for that slice are up.  op 0 = sum (float types; float64 accumulation in rank
+ * order, `divisor` as in cb200_<T>_rank_fold_sum_kernel_launch), 1 = min, 2 = max (`nan_wins` as in the extreme fold);
+ * dtype 0 sfloat, 1 dfloat, 2 int32, 3 int64; `src` holds this rank's n_out partials, `out` receives the n_out results. */
+int cb200_peer_exchange_fold_kernel_launch(const void* src, int dtype, int op, int64_t n_out, double divisor, int nan_wins, void* out,
+                                           void* const* bases, int world, int rank, size_t slot_bytes, unsigned long long seq,
+                                           unsigned spin_limit, int* status);
 
 /* Self-test of the bounded mbarrier wait the tcgen05 kernels use between their warp roles (no counterpart in the
  * reference): one CTA waits at most `spin_limit` polls on a barrier nothing arrives at.  Returns 5 when the wait gave

@@ -180,6 +180,50 @@ def test_peer_exchange_kernel_with_a_message_made_on_the_host(xp_gpu):
         lib.cb200_peer_buffer_destroy(base)
 
 
+@pytest.mark.parametrize("op,tname", [("sum", "SFloat"), ("sum", "DFloat"), ("max", "SFloat"), ("min", "Int32"), ("max", "Int64")])
+def test_fused_exchange_and_fold_with_a_message_made_on_the_host(xp_gpu, op, tname):
+    """The one-kernel form (exchange + element-wise rank fold) as rank 0 of two on one GPU, rank 1's partial and flags
+    written from the host beforehand; a ragged length so that the last packet and the last CTA are partial."""
+    import torch
+    from cumo_b200.narray import UInt32
+
+    world, slot, n = 2, 64 << 10, 4099
+    lib, base, bases, status = _exchange_setup(world, slot)
+    try:
+        seq = 3
+        rng = np.random.default_rng(7)
+        T = getattr(xp_gpu, tname)
+        dt = {"SFloat": np.float32, "DFloat": np.float64, "Int32": np.int32, "Int64": np.int64}[tname]
+        h_mine = (rng.standard_normal(n) * 100).astype(dt)
+        h_theirs = (rng.standard_normal(n) * 100).astype(dt)
+        if tname.endswith("Float") and op != "sum":
+            h_mine[5], h_theirs[9], h_mine[11], h_theirs[11] = np.nan, np.nan, np.nan, np.nan
+        mine = T.from_numpy(h_mine)
+        total = lib.cb200_peer_buffer_bytes(slot, world)
+        whole = torch.as_tensor(UInt32.from_device_pointer(base.value, (total // 4,)), device="cuda").view(torch.uint8)
+        data_off = ((seq & 1) * world + 1) * slot
+        whole[data_off:data_off + h_theirs.nbytes] = torch.from_numpy(h_theirs.view(np.uint8)).cuda()
+        whole[2 * world * slot:].view(torch.int64).view(2, world, 16)[seq & 1, 1, :] = seq
+        torch.cuda.synchronize()
+        out = T(n)
+        code = {"SFloat": 0, "DFloat": 1, "Int32": 2, "Int64": 3}[tname]
+        rc = lib.cb200_peer_exchange_fold_kernel_launch(mine.data_ptr, code, {"sum": 0, "min": 1, "max": 2}[op], n, 0.0, 0, out.data_ptr,
+                                                        bases, world, 0, slot, seq, 1 << 12, status.data_ptr())
+        assert rc == 0
+        torch.cuda.synchronize()
+        assert int(status.item()) == 0
+        got = out.to_numpy()
+        if op == "sum":
+            want = (h_mine.astype(np.float64) + h_theirs.astype(np.float64)).astype(dt)
+        else:
+            f = np.fmax if op == "max" else np.fmin          # the plain form: a NaN loses unless both are NaN
+            want = f(h_mine, h_theirs)
+        assert np.array_equal(got, want, equal_nan=True)
+    finally:
+        torch.cuda.synchronize()
+        lib.cb200_peer_buffer_destroy(base)
+
+
 def test_peer_exchange_wait_runs_out_by_its_limit(xp_gpu):
     """A flag that nothing sets: the wait gives up after its (short) limit, the status word says so, the kernel returns
     and the context stays usable."""

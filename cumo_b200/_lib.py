@@ -97,6 +97,8 @@ def _declare(lib: ctypes.CDLL) -> None:
         "cb200_peer_exchange_kernel_launch": (c_int, [c_void_p, c_size_t, POINTER(c_void_p), c_int, c_int, c_size_t, ctypes.c_ulonglong, ctypes.c_uint, c_void_p]),
         "cb200_peer_exchange_fold_kernel_launch": (c_int, [c_void_p, c_int, c_int, c_int64, c_double, c_int, c_void_p, POINTER(c_void_p), c_int, c_int,
                                                    c_size_t, ctypes.c_ulonglong, ctypes.c_uint, c_void_p]),
+        "cb200_peer_exchange_arg_kernel_launch": (c_int, [c_void_p, c_int, c_int64, c_size_t, c_int, c_int, c_void_p, POINTER(c_void_p), c_int, c_int,
+                                                  c_size_t, ctypes.c_ulonglong, ctypes.c_uint, c_void_p]),
         "cb200_tile_pipeline_status": (c_int, []),
         "cb200_tile_pipeline_launches": (ctypes.c_ulonglong, []),
         "cb200_sfloat_rank_fold_sum_kernel_launch": (None, [c_void_p, c_int64, c_int, c_int64, c_double, c_void_p]),

@@ -70,6 +70,31 @@ __device__ __forceinline__ bool exchange_slice(const char* __restrict__ src, siz
     return gave_up == 0;
 }
 
+// Steps 2 and 3 alone (the data of this CTA's slice has been stored and fenced): raise my flag at every peer, wait for theirs.
+__device__ __forceinline__ bool signal_and_wait(const PeerBases& peers, int world, int rank, size_t slot_bytes, unsigned long long seq,
+                                                unsigned spin_limit, int* status) {
+    __shared__ int gave_up2;
+    const int slot = (int)(seq & 1ull);
+    if (threadIdx.x == 0) gave_up2 = 0;
+    __threadfence_system();
+    __syncthreads();
+    if (threadIdx.x < world) {
+        const int p = threadIdx.x;
+        volatile unsigned long long* there = reinterpret_cast<volatile unsigned long long*>(peers.base[p] + peer_flag_offset(slot_bytes, world, slot, rank, blockIdx.x));
+        *there = seq;
+        volatile unsigned long long* here = reinterpret_cast<volatile unsigned long long*>(peers.base[rank] + peer_flag_offset(slot_bytes, world, slot, p, blockIdx.x));
+        bool seen = false;
+        for (unsigned spin = 0; spin < spin_limit; ++spin) {
+            if (*here >= seq) { seen = true; break; }
+            if (spin > 64) __nanosleep(200);
+        }
+        if (!seen) { atomicExch(status, 1); gave_up2 = 1; }
+        __threadfence_system();
+    }
+    __syncthreads();
+    return gave_up2 == 0;
+}
+
 __device__ __forceinline__ void slice_of(size_t nbytes, size_t& p_begin, size_t& p_end) {
     const size_t packets = (nbytes + 15) / 16;                                   // the source is padded to whole packets by the host
     const size_t per_cta = (packets + gridDim.x - 1) / gridDim.x;
@@ -119,6 +144,64 @@ peer_exchange_fold_kernel(const char* __restrict__ src, size_t nbytes, const Pee
             for (int k = 1; k < world; ++k) acc = r.combine(acc, __ldcg(reinterpret_cast<const T*>(mine + (size_t)k * slot_bytes) + o));
             out[o] = acc;
         }
+    }
+}
+
+// Index reductions: a rank's partial is {int64 global index, value} per output, indices first, the values starting
+// `val_off` bytes into the buffer (a multiple of 16).  A CTA takes a run of outputs, stores their indices and their values
+// into every rank's slot, and once its peers' flags are up merges the `world` candidates of each of those outputs with the
+// single-GPU functor's total order (NaN rule, better value, lower index).
+template <typename T, bool IS_MAX, bool NAN_WINS>
+__global__ void __launch_bounds__(kBlock)
+peer_exchange_arg_kernel(const char* __restrict__ src, int64_t n_out, size_t val_off, const PeerBases peers, int world, int rank, size_t slot_bytes,
+                         unsigned long long seq, unsigned spin_limit, int* status, int64_t* out_index) {
+    pdl_trigger();
+    pdl_wait();
+    constexpr int64_t G = 16 / (int64_t)sizeof(T);                 // outputs per 16 bytes of values (and per 16 * 8 / sizeof(T) bytes of indices)
+    int64_t per_cta = (n_out + gridDim.x - 1) / gridDim.x;
+    per_cta = (per_cta + G - 1) / G * G;
+    const int64_t o_begin = (int64_t)blockIdx.x * per_cta;
+    int64_t o_end = o_begin + per_cta;
+    const int64_t padded = (n_out + G - 1) / G * G;                 // the host pads both parts of the buffer to whole packets
+    if (o_end > padded) o_end = padded;
+    const int64_t mine = o_end > o_begin ? o_end - o_begin : 0;
+    const int slot = (int)(seq & 1ull);
+    const size_t dst_off = ((size_t)slot * world + rank) * slot_bytes;
+    const int64_t idx_packets = mine * 8 / 16, val_packets = mine * (int64_t)sizeof(T) / 16;
+    const int64_t per_peer = idx_packets + val_packets;
+    for (int64_t i = threadIdx.x; i < per_peer * world; i += kBlock) {
+        const int p = (int)(i / per_peer);
+        const int64_t k = i - (int64_t)p * per_peer;
+        const size_t off = k < idx_packets ? (size_t)o_begin * 8 + (size_t)k * 16 : val_off + (size_t)o_begin * sizeof(T) + (size_t)(k - idx_packets) * 16;
+        const int4 v = *reinterpret_cast<const int4*>(src + off);
+        *reinterpret_cast<int4*>(peers.base[p] + dst_off + off) = v;
+    }
+    if (!signal_and_wait(peers, world, rank, slot_bytes, seq, spin_limit, status)) return;
+    using R = red::ArgMinMax<T, IS_MAX, NAN_WINS>;
+    const R r{1};
+    const char* base = peers.base[rank] + (size_t)slot * world * slot_bytes;
+    const int64_t stop = o_end < n_out ? o_end : n_out;
+    for (int64_t o = o_begin + threadIdx.x; o < stop; o += kBlock) {
+        typename R::Acc acc = r.identity();
+        for (int k = 0; k < world; ++k) {
+            typename R::Acc b;
+            b.index = __ldcg(reinterpret_cast<const long long*>(base + (size_t)k * slot_bytes) + o);
+            b.value = __ldcg(reinterpret_cast<const T*>(base + (size_t)k * slot_bytes + val_off) + o);
+            acc = r.combine(acc, b);
+        }
+        out_index[o] = acc.index;
+    }
+}
+
+template <typename T>
+static void launch_exchange_arg(const char* s, int64_t n_out, size_t val_off, const PeerBases& pb, int world, int rank, size_t slot_bytes,
+                                unsigned long long seq, unsigned limit, int* status, int is_max, int nan_wins, int64_t* out, unsigned ctas, cudaStream_t st) {
+    constexpr bool fp = red::is_fp<T>::value;
+    auto go = [&](auto kernel) { launch_dependent(kernel, ctas, kBlock, st, s, n_out, val_off, pb, world, rank, slot_bytes, seq, limit, status, out); };
+    if (is_max) {
+        if (nan_wins && fp) go(peer_exchange_arg_kernel<T, true, fp>); else go(peer_exchange_arg_kernel<T, true, false>);
+    } else {
+        if (nan_wins && fp) go(peer_exchange_arg_kernel<T, false, fp>); else go(peer_exchange_arg_kernel<T, false, false>);
     }
 }
 
@@ -224,6 +307,36 @@ int cb200_peer_exchange_fold_kernel_launch(const void* src, int dtype, int op, i
     case 1: launch_exchange_fold<double>(s, nbytes, pb, world, rank, slot_bytes, seq, limit, status, n_out, divisor, op, nan_wins, out, (unsigned)ctas, st); break;
     case 2: launch_exchange_fold<int32_t>(s, nbytes, pb, world, rank, slot_bytes, seq, limit, status, n_out, divisor, op, nan_wins, out, (unsigned)ctas, st); break;
     default: launch_exchange_fold<int64_t>(s, nbytes, pb, world, rank, slot_bytes, seq, limit, status, n_out, divisor, op, nan_wins, out, (unsigned)ctas, st); break;
+    }
+    count_launch();
+    return (int)cudaGetLastError();
+}
+
+// The exchange and the merge of an index reduction's partials in one kernel.  `src`: this rank's buffer, n_out int64 global
+// indices followed, `val_off` bytes in (a multiple of 16, >= 8 * n_out), by the n_out winning values of type `dtype`; both parts
+// readable up to the next multiple of 16 bytes.  `out_index` receives the n_out merged indices.
+int cb200_peer_exchange_arg_kernel_launch(const void* src, int dtype, int64_t n_out, size_t val_off, int is_max, int nan_wins, int64_t* out_index,
+                                          void* const* bases, int world, int rank, size_t slot_bytes, unsigned long long seq,
+                                          unsigned spin_limit, int* status) {
+    static const size_t es_of[4] = {4, 8, 4, 8};
+    if (dtype < 0 || dtype > 3 || n_out <= 0 || !out_index || val_off % 16 != 0 || val_off < (size_t)n_out * 8) return (int)cudaErrorInvalidValue;
+    const size_t es = es_of[dtype];
+    const size_t nbytes = val_off + ((size_t)n_out * es + 15) / 16 * 16;
+    if (!src || !bases || !status || world < 1 || world > kPeerMaxWorld || rank < 0 || rank >= world || nbytes > slot_bytes ||
+        slot_bytes % 16 != 0 || seq == 0 || (reinterpret_cast<uintptr_t>(src) & 15) != 0)
+        return (int)cudaErrorInvalidValue;
+    PeerBases pb;
+    for (int p = 0; p < kPeerMaxWorld; ++p) pb.base[p] = p < world ? static_cast<char*>(bases[p]) : nullptr;
+    size_t ctas = (nbytes + kPeerSliceBytes - 1) / kPeerSliceBytes;
+    if (ctas > (size_t)kPeerMaxCtas) ctas = kPeerMaxCtas;
+    const unsigned limit = spin_limit ? spin_limit : (1u << 25);
+    const char* s = static_cast<const char*>(src);
+    cudaStream_t st = current_stream();
+    switch (dtype) {
+    case 0: launch_exchange_arg<float>(s, n_out, val_off, pb, world, rank, slot_bytes, seq, limit, status, is_max, nan_wins, out_index, (unsigned)ctas, st); break;
+    case 1: launch_exchange_arg<double>(s, n_out, val_off, pb, world, rank, slot_bytes, seq, limit, status, is_max, nan_wins, out_index, (unsigned)ctas, st); break;
+    case 2: launch_exchange_arg<int32_t>(s, n_out, val_off, pb, world, rank, slot_bytes, seq, limit, status, is_max, nan_wins, out_index, (unsigned)ctas, st); break;
+    default: launch_exchange_arg<int64_t>(s, n_out, val_off, pb, world, rank, slot_bytes, seq, limit, status, is_max, nan_wins, out_index, (unsigned)ctas, st); break;
     }
     count_launch();
     return (int)cudaGetLastError();

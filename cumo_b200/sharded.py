@@ -121,6 +121,18 @@ class PeerExchange:
             raise RuntimeError(f"peer exchange launch failed with CUDA error {rc}")
         return out
 
+    def gather_merge_arg(self, buf, tname, n_out, val_off, want_max, nan_wins, out):
+        """Exchange and merge of an index reduction's {index, value} partials in one kernel (`buf`: a CUDA byte tensor)."""
+        import ctypes
+        self.seq += 1
+        rc = self.lib.cb200_peer_exchange_arg_kernel_launch(
+            ctypes.c_void_p(buf.data_ptr()), self._DTYPES[tname], n_out, ctypes.c_size_t(val_off), int(want_max), int(bool(nan_wins)),
+            ctypes.c_void_p(out.data_ptr), self.bases, self.world, self.rank, ctypes.c_size_t(self.SLOT_BYTES),
+            ctypes.c_ulonglong(self.seq), ctypes.c_uint(self.spin_limit), ctypes.c_void_p(self.status.data_ptr()))
+        if rc != 0:
+            raise RuntimeError(f"peer exchange launch failed with CUDA error {rc}")
+        return out
+
     def check(self):
         """Synchronises and raises if a bounded wait of an exchange ran out since the last check."""
         if int(self.status.item()) != 0:
@@ -374,8 +386,10 @@ class ShardedArray:
         if lib.cb200_na_arg_with_value_into(name_local.encode(), loc._h, _axis_mask(axis, loc.ndim), int(bool(nan)), int(base),
                                             c_void_p(buf.data_ptr()), c_void_p(buf.data_ptr() + val_off), None, None):
             _raise_last()
-        ptr, stride, _keep = comm.gather_partials(buf)
         out = comm.xp.Int64(*(loc.shape[1:] if axis == 0 else ()))
+        if comm.peer is not None and buf.numel() <= PeerExchange.SLOT_BYTES:
+            return comm.peer.gather_merge_arg(buf, T.__name__, n_out, val_off, want_max, bool(nan), out)
+        ptr, stride, _keep = comm.gather_partials(buf)
         fold = getattr(lib, f"cb200_{T.__name__.lower()}_rank_fold_arg_kernel_launch")
         fold(ptr, ptr + val_off, stride, comm.world, n_out, int(want_max), int(bool(nan)), out.data_ptr, None)
         return out

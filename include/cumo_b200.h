@@ -420,6 +420,12 @@ int cb200_peer_exchange_kernel_launch(const void* src, size_t nbytes, void* cons
 int cb200_peer_exchange_fold_kernel_launch(const void* src, int dtype, int op, int64_t n_out, double divisor, int nan_wins, void* out,
                                            void* const* bases, int world, int rank, size_t slot_bytes, unsigned long long seq,
                                            unsigned spin_limit, int* status);
+/* ... and for index reductions: `src` holds this rank's n_out int64 global indices followed, `val_off` bytes in (a multiple
+ * of 16), by the n_out winning values (what cb200_<T>_<op>_with_value_kernel_launch writes), both parts readable to the next
+ * multiple of 16 bytes; `out_index` receives the indices merged with the single-GPU total order. */
+int cb200_peer_exchange_arg_kernel_launch(const void* src, int dtype, int64_t n_out, size_t val_off, int is_max, int nan_wins, int64_t* out_index,
+                                          void* const* bases, int world, int rank, size_t slot_bytes, unsigned long long seq,
+                                          unsigned spin_limit, int* status);
 
 /* Self-test of the bounded mbarrier wait the tcgen05 kernels use between their warp roles (no counterpart in the
  * reference): one CTA waits at most `spin_limit` polls on a barrier nothing arrives at.  Returns 5 when the wait gave

@@ -224,6 +224,57 @@ def test_fused_exchange_and_fold_with_a_message_made_on_the_host(xp_gpu, op, tna
         lib.cb200_peer_buffer_destroy(base)
 
 
+@pytest.mark.parametrize("tname,n", [("SFloat", 4099), ("DFloat", 1), ("Int32", 6), ("Int64", 2050)])
+def test_fused_exchange_and_index_merge_with_a_message_made_on_the_host(xp_gpu, tname, n):
+    """The one-kernel form for index reductions as rank 0 of two on one GPU: rank 1's {index, value} partial and its flags
+    come from the host.  Ties go to the lower index, a NaN loses (plain form), lengths that are not whole packets."""
+    import torch
+    from cumo_b200.narray import UInt32
+
+    world, slot = 2, 64 << 10
+    lib, base, bases, status = _exchange_setup(world, slot)
+    try:
+        seq = 2
+        rng = np.random.default_rng(n)
+        dt = {"SFloat": np.float32, "DFloat": np.float64, "Int32": np.int32, "Int64": np.int64}[tname]
+        es = np.dtype(dt).itemsize
+        v0 = rng.integers(-50, 50, n).astype(dt)
+        v1 = rng.integers(-50, 50, n).astype(dt)
+        i0 = rng.integers(0, 1000, n).astype(np.int64)
+        i1 = rng.integers(1000, 2000, n).astype(np.int64)
+        if tname.endswith("Float") and n > 8:
+            v0[3], v1[5] = np.nan, np.nan
+        val_off = (n * 8 + 15) // 16 * 16
+        nbytes = val_off + (n * es + 15) // 16 * 16
+
+        def pack(idx, val):
+            b = np.zeros(nbytes, dtype=np.uint8)
+            b[:n * 8] = idx.view(np.uint8)
+            b[val_off:val_off + n * es] = val.view(np.uint8)
+            return b
+        mine = torch.from_numpy(pack(i0, v0)).cuda()
+        total = lib.cb200_peer_buffer_bytes(slot, world)
+        whole = torch.as_tensor(UInt32.from_device_pointer(base.value, (total // 4,)), device="cuda").view(torch.uint8)
+        data_off = ((seq & 1) * world + 1) * slot
+        whole[data_off:data_off + nbytes] = torch.from_numpy(pack(i1, v1)).cuda()
+        whole[2 * world * slot:].view(torch.int64).view(2, world, 16)[seq & 1, 1, :] = seq
+        torch.cuda.synchronize()
+        out = xp_gpu.Int64(n)
+        code = {"SFloat": 0, "DFloat": 1, "Int32": 2, "Int64": 3}[tname]
+        rc = lib.cb200_peer_exchange_arg_kernel_launch(mine.data_ptr(), code, n, val_off, 1, 0, out.data_ptr, bases, world, 0, slot, seq,
+                                                       1 << 12, status.data_ptr())
+        assert rc == 0
+        torch.cuda.synchronize()
+        assert int(status.item()) == 0
+        f0, f1 = v0.astype(np.float64), v1.astype(np.float64)
+        take1 = np.where(np.isnan(f0), ~np.isnan(f1), (f1 > f0))        # rank 0 keeps ties (its indices are the lower ones)
+        take1 = np.where(np.isnan(f0) & np.isnan(f1), False, take1)
+        assert np.array_equal(out.to_numpy(), np.where(take1, i1, i0))
+    finally:
+        torch.cuda.synchronize()
+        lib.cb200_peer_buffer_destroy(base)
+
+
 def test_peer_exchange_wait_runs_out_by_its_limit(xp_gpu):
     """A flag that nothing sets: the wait gives up after its (short) limit, the status word says so, the kernel returns
     and the context stays usable."""

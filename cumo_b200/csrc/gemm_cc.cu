@@ -44,7 +44,10 @@ gemm_cc_kernel(const GemmCc<T> g) {
     const T* B = g.B + (int64_t)batch * g.b_batch;
     T* C = g.C + (int64_t)batch * g.c_batch;
     const int i0 = tm * kGcM, j0 = tn * kGcN;
-    const int ti = threadIdx.x % 16, tj = threadIdx.x / 16;          // 16 x 16 threads, 8 x 8 outputs each
+    // 16 x 16 threads, 8 x 8 outputs each: rows ti, ti + 16, ... (neighbouring lanes read neighbouring elements of the A
+    // tile: no bank conflicts, and their stores to a column of C are consecutive), columns tj * 8 .. tj * 8 + 7 (a warp
+    // holds two values of tj: its reads of the B tile are broadcasts)
+    const int ti = threadIdx.x % 16, tj = threadIdx.x / 16;
     T acc[8][8];
 #pragma unroll
     for (int a = 0; a < 8; ++a)
@@ -53,9 +56,9 @@ gemm_cc_kernel(const GemmCc<T> g) {
     // lanes run along whichever axis of each operand is contiguous in memory
     const bool a_along_i = g.a_i == 1 || g.a_k != 1;
     const bool b_along_j = g.b_j == 1 || g.b_k != 1;
-    for (int k0 = 0; k0 < g.k; k0 += kGcK) {
-        constexpr int PER = kGcM * kGcK / kBlock;                     // 8 elements per thread and operand
-        T ra[PER], rb[PER];
+    constexpr int PER = kGcM * kGcK / kBlock;                         // 8 elements per thread and operand
+    T ra[PER], rb[PER];
+    auto fetch = [&](int k0) {
 #pragma unroll
         for (int e = 0; e < PER; ++e) {
             const int f = e * kBlock + threadIdx.x;
@@ -64,6 +67,9 @@ gemm_cc_kernel(const GemmCc<T> g) {
             const int jj = b_along_j ? f % kGcN : f / kGcK, kb = b_along_j ? f / kGcN : f % kGcK;
             rb[e] = (j0 + jj < g.n && k0 + kb < g.k) ? B[(int64_t)(k0 + kb) * g.b_k + (int64_t)(j0 + jj) * g.b_j] : T(0);
         }
+    };
+    fetch(0);
+    for (int k0 = 0; k0 < g.k; k0 += kGcK) {
         __syncthreads();                                             // the previous block's tiles are no longer read
 #pragma unroll
         for (int e = 0; e < PER; ++e) {
@@ -74,11 +80,12 @@ gemm_cc_kernel(const GemmCc<T> g) {
             Bs[kb][jj] = rb[e];
         }
         __syncthreads();
+        if (k0 + kGcK < g.k) fetch(k0 + kGcK);                       // the next block's loads fly while this one is multiplied
 #pragma unroll
         for (int kk = 0; kk < kGcK; ++kk) {
             T a[8], b[8];
 #pragma unroll
-            for (int x = 0; x < 8; ++x) { a[x] = As[kk][ti * 8 + x]; b[x] = Bs[kk][tj * 8 + x]; }
+            for (int x = 0; x < 8; ++x) { a[x] = As[kk][ti + 16 * x]; b[x] = Bs[kk][tj * 8 + x]; }
 #pragma unroll
             for (int x = 0; x < 8; ++x)
 #pragma unroll
@@ -91,7 +98,7 @@ gemm_cc_kernel(const GemmCc<T> g) {
         if (j >= g.n) continue;
 #pragma unroll
         for (int x = 0; x < 8; ++x) {
-            const int i = i0 + ti * 8 + x;
+            const int i = i0 + ti + 16 * x;
             if (i >= g.m) continue;
             T* c = C + (int64_t)j * g.ldc + i;
             // beta == 0 must not read C (it may hold NaN or be uninitialised), as in BLAS

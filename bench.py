@@ -233,6 +233,16 @@ def kernel_rows(X, arr, S, copies=1):
     yield "T", "b.transpose.dup", 2 * st, lambda: tb.transpose().dup()
     yield "T", "SFloat.cast(i32.transpose)", 2 * st, lambda: X.SFloat.cast(ti.transpose())
     del ta, tb, ti
+    # ... and with 8-byte elements and on a small plane, the shapes that take the copy-engine (TMA) form of the tile kernel
+    nd = nt * 3 // 4 // 64 * 64
+    td = arr("f64_01", (nd, nd))
+    yield "T", "f64 a + a.transpose (TMA tile kernel)", 3 * nd * nd * 8, lambda: td + td.transpose()
+    yield "T", "f64 a.transpose.dup (TMA tile kernel)", 2 * nd * nd * 8, lambda: td.transpose().dup()
+    del td
+    ns = max(64, nt // 4)
+    tsm = arr("f32_pm1", (ns, ns))
+    yield "T", "f32 b.transpose.dup, plane/16 (TMA tile kernel)", 2 * ns * ns * 4, lambda: tsm.transpose().dup()
+    del tsm
     # F: the rows after the hot path (scan, histogram, compaction), same sizes
     v32 = arr("f32_01", (n3,))
     yield "F", "f32 1-D cumsum", 2 * n3 * 4, lambda: v32.cumsum()

@@ -114,6 +114,8 @@ def _declare(lib: ctypes.CDLL) -> None:
         "cb200_na_take": (H, [H, c_int, H]),
         "cb200_na_mask": (H, [H, H]),
         "cb200_na_count": (H, [H, c_uint32, c_int, c_int]),
+        "cb200_na_bit_op": (H, [c_char_p, H, H]),
+        "cb200_na_bit_reduce": (H, [c_char_p, H, c_uint32, c_int]),
         "cb200_na_mulsum": (H, [H, H, c_uint32, c_int, c_int]),
         "cb200_na_cast": (H, [H, c_int]),
         "cb200_na_copy": (H, [H]),

@@ -1137,6 +1137,119 @@ cb200_na_t* cb200_na_count(cb200_na_t* a, uint32_t axis_mask, int keepdims, int 
     return out;
 }
 
+// ---- Bit o Bit: and or xor eq (b given), copy not (b null) -------------------------------------------------------------
+// gen/tmpl_bit/binary.c:11-33, unary.c:11-30: operands laid end to end after the loop is contracted take the word-at-a-time
+// launch, anything else the launch that addresses every operand per dimension.
+cb200_na_t* cb200_na_bit_op(const char* op_c, cb200_na_t* a, cb200_na_t* b) {
+    const std::string op = op_c;
+    const bool binary = b != nullptr;
+    if (a->dtype != CB200_BIT || (binary && b->dtype != CB200_BIT)) return (cb200_na*)fail("TypeError", "%s needs Bit arrays", op_c);
+    if (binary ? !(op == "and" || op == "or" || op == "xor" || op == "eq") : !(op == "copy" || op == "not"))
+        return (cb200_na*)fail("NoMethodError", "undefined method %s for bit", op_c);
+    Loop lp;
+    if (binary) { if (!broadcast(a, b, &lp)) return nullptr; }
+    else { lp.ndim = a->ndim; memcpy(lp.shape, a->shape, sizeof(int64_t) * a->ndim); }
+    cb200_na* out = make(CB200_BIT, lp.ndim, lp.shape, true);
+    if (!out) return nullptr;
+    if (size_of(out) == 0) return out;
+    const cb200_na* ops[3] = {a, binary ? b : a, out};
+    StrideLoop L;
+    L.nd = lp.ndim;
+    for (int i = 0; i < lp.ndim; ++i) {
+        L.n[i] = lp.shape[i];
+        for (int o = 0; o < 3; ++o) {
+            const int d = i - (lp.ndim - ops[o]->ndim);
+            L.s[o][i] = (d >= 0 && ops[o]->shape[d] != 1) ? ops[o]->step[d] : 0;
+        }
+    }
+    if (L.nd == 0) { L.nd = 1; L.n[0] = 1; for (int o = 0; o < 3; ++o) L.s[o][0] = 0; }
+    contract(&L, 3);
+    auto words = [](const cb200_na* x) { return reinterpret_cast<CUMO_BIT_DIGIT*>(x->st->ptr); };
+    const std::string base = std::string("cumo_iter_bit_") + op;
+    const bool flat = L.nd == 1 && L.s[0][0] == 1 && L.s[2][0] == 1 && (!binary || L.s[1][0] == 1);
+    bool ok = true;
+    if (flat) {
+        void* f = sym(base + "_contiguous_kernel_launch");
+        ok = f != nullptr;
+        if (ok) {
+            const size_t q1 = (size_t)a->offset, q3 = (size_t)out->offset;
+            if (binary) {
+                const size_t q2 = (size_t)b->offset;
+                ((void (*)(CUMO_BIT_DIGIT*, size_t, CUMO_BIT_DIGIT*, size_t, CUMO_BIT_DIGIT*, size_t, uint64_t))f)(
+                    words(a) + q1 / 32, q1 % 32, words(b) + q2 / 32, q2 % 32, words(out) + q3 / 32, q3 % 32, (uint64_t)L.n[0]);
+            } else {
+                ((void (*)(CUMO_BIT_DIGIT*, size_t, CUMO_BIT_DIGIT*, size_t, uint64_t))f)(words(a) + q1 / 32, q1 % 32, words(out) + q3 / 32, q3 % 32,
+                                                                                     (uint64_t)L.n[0]);
+            }
+        }
+    } else {
+        void* f = sym(base + "_kernel_launch");
+        ok = f != nullptr;
+        if (ok) {
+            cumo_na_bit_iarray_stridx_t v[3];
+            cumo_na_indexer_t ix;
+            memset(&ix, 0, sizeof ix);
+            ix.ndim = (unsigned char)L.nd;
+            ix.total_size = 1;
+            for (int d = 0; d < L.nd; ++d) { ix.shape[d] = (size_t)L.n[d]; ix.total_size *= (size_t)L.n[d]; }
+            for (int o = 0; o < 3; ++o) {
+                memset(&v[o], 0, sizeof v[o]);
+                v[o].ptr = words(ops[o]);
+                v[o].pos = (size_t)ops[o]->offset;
+                for (int d = 0; d < L.nd; ++d) v[o].stridx[d].stride = (ssize_t)((L.s[o][d] << 1) | 1);     // a step, not an index array
+            }
+            if (binary) ((void (*)(cumo_na_bit_iarray_stridx_t*, cumo_na_bit_iarray_stridx_t*, cumo_na_bit_iarray_stridx_t*, cumo_na_indexer_t*))f)(&v[0], &v[1], &v[2], &ix);
+            else ((void (*)(cumo_na_bit_iarray_stridx_t*, cumo_na_bit_iarray_stridx_t*, cumo_na_indexer_t*))f)(&v[0], &v[2], &ix);
+        }
+    }
+    if (!ok || !launch_ok()) { cb200_na_release(out); return nullptr; }
+    return out;
+}
+
+// ---- Bit#all? / #any? (gen/tmpl_bit/bit_reduce.c:5-33): the output starts at the identity, runs of the input flip it ----------
+cb200_na_t* cb200_na_bit_reduce(const char* op_c, cb200_na_t* a, uint32_t axis_mask, int keepdims) {
+    const std::string op = op_c;
+    if (a->dtype != CB200_BIT) return (cb200_na*)fail("TypeError", "%s needs a Bit array", op_c);
+    if (op != "all" && op != "any") return (cb200_na*)fail("NoMethodError", "undefined method %s? for bit", op_c);
+    ReducePlan rp;
+    if (!plan_reduce(a, axis_mask, &rp)) return nullptr;
+    cb200_na* out = make(CB200_BIT, rp.n_keep, rp.out_shape, true);
+    if (!out) return nullptr;
+    if (op == "all" && !cuda_ok(cudaMemsetAsync(out->st->ptr, 0xff, out->st->bytes ? out->st->bytes : 4, cb200::current_stream()), "cudaMemsetAsync")) {
+        cb200_na_release(out);
+        return nullptr;
+    }
+    if (size_of(a) > 0) {
+        StrideLoop L;
+        L.nd = a->ndim;
+        int k = 0;
+        for (int i = 0; i < rp.n_keep; ++i, ++k) { L.n[k] = a->shape[rp.keep[i]]; L.s[0][k] = a->step[rp.keep[i]]; L.s[1][k] = out->step[i]; }
+        for (int i = 0; i < rp.n_red; ++i, ++k) { L.n[k] = a->shape[rp.red[i]]; L.s[0][k] = a->step[rp.red[i]]; L.s[1][k] = 0; }
+        if (L.nd == 0) { L.nd = 1; L.n[0] = 1; L.s[0][0] = L.s[1][0] = 0; }
+        contract(&L, 2);
+        const std::string base = std::string("cumo_iter_bit_") + op + "_p_";
+        using FnE = void (*)(CUMO_BIT_DIGIT*, size_t, ssize_t, size_t*, CUMO_BIT_DIGIT*, size_t, ssize_t, size_t*, uint64_t);
+        using FnR = void (*)(CUMO_BIT_DIGIT*, size_t, ssize_t, size_t*, CUMO_BIT_DIGIT*, size_t, uint64_t);
+        using FnC = void (*)(CUMO_BIT_DIGIT*, size_t, CUMO_BIT_DIGIT*, size_t, uint64_t);
+        FnE fe = (FnE)sym(base + "elementwise_kernel_launch");
+        FnR fr = (FnR)sym(base + "reduce_kernel_launch");
+        FnC fc = (FnC)sym(base + "contiguous_reduce_kernel_launch");
+        if (!fe || !fr || !fc) { cb200_na_release(out); return nullptr; }
+        const int in = L.nd - 1;
+        CUMO_BIT_DIGIT* w1 = reinterpret_cast<CUMO_BIT_DIGIT*>(a->st->ptr);
+        CUMO_BIT_DIGIT* w2 = reinterpret_cast<CUMO_BIT_DIGIT*>(out->st->ptr);
+        for_outer(L, 2, [&](const int64_t* off) {
+            const size_t p1 = (size_t)(a->offset + off[0]), p2 = (size_t)(out->offset + off[1]);
+            if (L.s[1][in] != 0) fe(w1, p1, (ssize_t)L.s[0][in], nullptr, w2, p2, (ssize_t)L.s[1][in], nullptr, (uint64_t)L.n[in]);
+            else if (L.s[0][in] != 1) fr(w1, p1, (ssize_t)L.s[0][in], nullptr, w2, p2, (uint64_t)L.n[in]);
+            else fc(w1, p1, w2, p2, (uint64_t)L.n[in]);
+        });
+        if (!launch_ok()) { cb200_na_release(out); return nullptr; }
+    }
+    apply_keepdims(out, a, rp, keepdims);
+    return out;
+}
+
 cb200_na_t* cb200_na_mulsum(cb200_na_t* a, cb200_na_t* b, uint32_t axis_mask, int keepdims, int nan) {
     if (!is_value_type(a->dtype) || !is_value_type(b->dtype)) return (cb200_na*)fail("TypeError", "mulsum needs numeric arrays");
     int dtype = upcast(a->dtype, b->dtype);

@@ -674,7 +674,7 @@ class Bit(NArray):
     def to_numpy(self) -> np.ndarray:
         lib = _lib.load()
         if not (self.contiguous() and self.offset % 32 == 0):
-            raise TypeError("reading back a strided or unaligned Bit view is not on this path")
+            return self.dup().to_numpy()                      # a view: through the copy kernel into words of its own
         n = self.size
         words = np.empty((n + 31) // 32, dtype=np.uint32)
         if words.size and lib.cb200_na_read_host(self._h, words.ctypes.data_as(c_void_p), words.nbytes):
@@ -705,6 +705,42 @@ class Bit(NArray):
 
     count = count_1 = count_true
     count_0 = count_false
+
+    # ---- Bit o Bit (gen/spec.rb:169-174: copy, not, and, or, xor, eq) and all? / any? / none? (:185-186, tmpl_bit/none_p.c) --
+    def _bit_operand(self, o):
+        if isinstance(o, Bit):
+            return o
+        return Bit.cast(o if isinstance(o, (list, tuple, np.ndarray)) else [o])
+
+    def _bit_op(self, op, o=None):
+        other = None if o is None else self._bit_operand(o)
+        return NArray._from_handle(_lib.load().cb200_na_bit_op(op.encode(), self._h, other._h if other is not None else None))
+
+    def __and__(self, o): return self._bit_op("and", o)
+    def __or__(self, o): return self._bit_op("or", o)
+    def __xor__(self, o): return self._bit_op("xor", o)
+    __rand__, __ror__, __rxor__ = __and__, __or__, __xor__
+    def __invert__(self): return self._bit_op("not")
+    def eq(self, o): return self._bit_op("eq", o)
+    def dup(self): return self._bit_op("copy")
+    copy = dup
+
+    def _bit_reduce(self, op, axis, keepdims):
+        out = NArray._from_handle(_lib.load().cb200_na_bit_reduce(op.encode(), self._h, _axis_mask(axis, self.ndim), int(keepdims)))
+        if axis is None and not keepdims:
+            return bool(out.to_numpy().reshape(-1)[0])          # without an axis the reference answers true / false
+        return out
+
+    def all(self, axis=None, keepdims=False):
+        """`all?`: every bit is one (an empty array answers false, as in tmpl_bit/bit_reduce.c:137-139)."""
+        return False if self.size == 0 else self._bit_reduce("all", axis, keepdims)
+
+    def any(self, axis=None, keepdims=False):
+        return False if self.size == 0 else self._bit_reduce("any", axis, keepdims)
+
+    def none(self, axis=None, keepdims=False):
+        r = self.any(axis=axis, keepdims=keepdims)
+        return (not r) if isinstance(r, bool) else ~r
 
     @property
     def data_ptr(self):

@@ -79,6 +79,12 @@ typedef struct {
 } cumo_na_iarray_stridx_t;
 
 typedef struct {
+    CUMO_BIT_DIGIT* ptr;                     /* first 32-bit word of the Bit array */
+    size_t pos;                              /* BIT position of the first element  */
+    cumo_stridx_t stridx[CUMO_NA_MAX_DIMENSION];   /* BIT step ((s << 1) | 1) or array of bit offsets per dimension */
+} cumo_na_bit_iarray_stridx_t;
+
+typedef struct {
     cumo_na_iarray_t in;                     /* reduce dimensions are the LAST dims of `in` */
     cumo_na_iarray_t out;                    /* steps for the leading out_indexer.ndim dims */
     cumo_na_indexer_t in_indexer;
@@ -432,6 +438,26 @@ int cb200_peer_exchange_arg_kernel_launch(const void* src, int dtype, int64_t n_
  * up by its limit -- the code cb200_sgemm_nt_tc / cb200_kmeans_assign_sfloat_tc return in that case -- 0 if the barrier
  * completed, 3/4 on launch problems.  The kernel always returns; the context stays usable. */
 int cb200_selftest_bounded_wait(unsigned spin_limit, char* errbuf, size_t errlen);
+
+/* Bit o Bit operations and the all? / any? reductions (reference: gen/tmpl_bit/binary.c:1-2, unary.c:1-2,
+ * bit_reduce.c:1-3; kernels in binary_kernel.cu, unary_kernel.cu, bit_reduce_kernel.cu).  The `_contiguous` forms take, per
+ * operand, the word that holds its first bit and that bit's position in the word (0..31), and n bits that lie end to end;
+ * the general forms address every operand per dimension by a bit step or an index array.  For the reductions the output
+ * bit(s) must hold the identity on entry (1 for all?, 0 for any?): `elementwise` folds run i of the input into output bit i,
+ * `reduce` and `contiguous_reduce` fold n input bits into the one bit at p2. */
+#define CB200_DECL_BIT_BINARY(op) \
+    void cumo_iter_bit_##op##_kernel_launch(cumo_na_bit_iarray_stridx_t* a1, cumo_na_bit_iarray_stridx_t* a2, cumo_na_bit_iarray_stridx_t* a3, cumo_na_indexer_t* indexer); \
+    void cumo_iter_bit_##op##_contiguous_kernel_launch(CUMO_BIT_DIGIT* a1, size_t p1, CUMO_BIT_DIGIT* a2, size_t p2, CUMO_BIT_DIGIT* a3, size_t p3, uint64_t n);
+#define CB200_DECL_BIT_UNARY(op) \
+    void cumo_iter_bit_##op##_kernel_launch(cumo_na_bit_iarray_stridx_t* a1, cumo_na_bit_iarray_stridx_t* a3, cumo_na_indexer_t* indexer); \
+    void cumo_iter_bit_##op##_contiguous_kernel_launch(CUMO_BIT_DIGIT* a1, size_t p1, CUMO_BIT_DIGIT* a3, size_t p3, uint64_t n);
+#define CB200_DECL_BIT_REDUCE(op) \
+    void cumo_iter_bit_##op##_elementwise_kernel_launch(CUMO_BIT_DIGIT* a1, size_t p1, ssize_t s1, size_t* idx1, CUMO_BIT_DIGIT* a2, size_t p2, ssize_t s2, size_t* idx2, uint64_t n); \
+    void cumo_iter_bit_##op##_reduce_kernel_launch(CUMO_BIT_DIGIT* a1, size_t p1, ssize_t s1, size_t* idx1, CUMO_BIT_DIGIT* a2, size_t p2, uint64_t n); \
+    void cumo_iter_bit_##op##_contiguous_reduce_kernel_launch(CUMO_BIT_DIGIT* a1, size_t p1, CUMO_BIT_DIGIT* a2, size_t p2, uint64_t n);
+CB200_DECL_BIT_BINARY(and) CB200_DECL_BIT_BINARY(or) CB200_DECL_BIT_BINARY(xor) CB200_DECL_BIT_BINARY(eq)
+CB200_DECL_BIT_UNARY(copy) CB200_DECL_BIT_UNARY(not)
+CB200_DECL_BIT_REDUCE(all_p) CB200_DECL_BIT_REDUCE(any_p)
 
 /* Elementwise operations on operands whose contiguous axes differ (`a + b.transpose`, `b.transpose.dup`, a cast of a
  * transposed view; reference: the strided branches of binary_kernel.cu:14-49, unary_kernel.cu:14-25, store_from_kernel.cu)

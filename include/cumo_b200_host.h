@@ -120,6 +120,10 @@ cb200_na_t* cb200_na_take(cb200_na_t* a, int axis, cb200_na_t* idx);
 cb200_na_t* cb200_na_mask(cb200_na_t* bits, cb200_na_t* a);
 /* count_true / count_false of a Bit array -> UInt64 */
 cb200_na_t* cb200_na_count(cb200_na_t* a, uint32_t axis_mask, int keepdims, int want_false);
+/* Bit o Bit: op = "and" | "or" | "xor" | "eq" with b, "copy" | "not" with b == NULL; operands broadcast like the value types. */
+cb200_na_t* cb200_na_bit_op(const char* op, cb200_na_t* a, cb200_na_t* b);
+/* Bit#all? / #any? over the axes of axis_mask (0 = all): a Bit array of the kept dims. */
+cb200_na_t* cb200_na_bit_reduce(const char* op, cb200_na_t* a, uint32_t axis_mask, int keepdims);
 /* mulsum(a, b, axis...) = (a*b).sum(axis...) in one pass over the inputs */
 cb200_na_t* cb200_na_mulsum(cb200_na_t* a, cb200_na_t* b, uint32_t axis_mask, int keepdims, int nan);
 /* contiguous copy / cast (the reference's `dup`, `reshape` copy and `Type.cast`) */

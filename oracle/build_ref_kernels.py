@@ -33,7 +33,7 @@ DEFAULT_REF = Path(os.environ.get("CUMO_REFERENCE_ROOT") or HERE.parent.parent /
 # templates (by erb_base) expanded per element type: the hot path and the rows next to it
 VALUE_TEMPLATES = {"binary", "binary_s", "unary", "unary_s", "unary2", "cond_binary", "cond_unary", "pow", "ewcomp",
                    "store_from", "accum", "accum_index", "accum_arg", "accum_binary", "bincount", "cum"}
-BIT_TEMPLATES = {"bit_count", "where", "mask"}
+BIT_TEMPLATES = {"bit_count", "where", "mask", "binary", "unary", "bit_reduce"}
 TYPES = ("sfloat", "dfloat", "int32", "int64", "bit")
 
 NVCC_FLAGS = ["-gencode", "arch=compute_100,code=sm_100", "-O3", "-std=c++17", "-Xcompiler", "-fPIC",
@@ -99,4 +99,5 @@ def build(ref_root: Path = DEFAULT_REF, force: bool = False) -> Path | None:
 
 
 if __name__ == "__main__":
-    print(build(Path(sys.argv[1]) if len(sys.argv) > 1 else DEFAULT_REF, force="--force" in sys.argv))
+    paths = [a for a in sys.argv[1:] if not a.startswith("--")]
+    print(build(Path(paths[0]) if paths else DEFAULT_REF, force="--force" in sys.argv))

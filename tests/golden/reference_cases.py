@@ -1610,4 +1610,111 @@ def case_integer_powers_around_zero(xp):
         assert (u ** xp.Int32[-2, -1, 2, 3]).to_a() == [0, 0, 9, 64]
 
 
+# ---- test/bit_test.rb:19-44, 51-76: Bit o Bit on the literal arrays, whole and through views that name every element ----
+def case_bit_operators_on_literals(xp):
+    src = [0, 1, 1, 0, 1, 0, 0, 1]
+    n = len(src)
+    for a in (xp.Bit.cast(src), xp.Bit.cast(src)[True], xp.Bit.cast(src)[0:n]):
+        assert a.to_a() == src
+        assert (a & 0).to_a() == [0] * n and (a & 1).to_a() == src
+        assert (a | 0).to_a() == src and (a | 1).to_a() == [1] * n
+        assert (a ^ 0).to_a() == src and (a ^ 1).to_a() == [x ^ 1 for x in src]
+        assert (~a).to_a() == [1 - x for x in src]
+        assert scalar(a.count_true()) == 4 and scalar(a.count_false()) == 4
+        assert not a.all() and a.any() and not a.none()
+    src2 = [[0, 1, 1, 0], [1, 0, 0, 1]]
+    for a in (xp.Bit.cast(src2), xp.Bit.cast(src2)[True, 0:4]):
+        assert a[0, 1:3].to_a() == [1, 1] and a[True, 1].to_a() == [1, 0]
+        assert scalar(a.count_true()) == 4 and scalar(a.count_false()) == 4
+        assert not a.all() and a.any() and not a.none()
+        assert (~a).to_a() == [[1, 0, 0, 1], [0, 1, 1, 0]]
+        assert (a & a[::-1, True]).to_a() == [[0, 0, 0, 0], [0, 0, 0, 0]]
+        assert (a | a[::-1, True]).to_a() == [[1, 1, 1, 1], [1, 1, 1, 1]]
+        assert a.eq(a).to_a() == [[1, 1, 1, 1], [1, 1, 1, 1]]
+
+
+# ---- test/narray_test.rb:2667-2705 "bit operators over long arrays and views" (slice views), 2725-2739 "a bit view with a
+# negative step reads the elements below its first one" ------------------------------------------------------------
+def case_bit_operators_over_long_arrays_and_views(xp):
+    n = 200
+    xs = [1 if i % 3 == 0 else 0 for i in range(n)]
+    ys = [1 if i % 5 < 2 else 0 for i in range(n)]
+    a, b = xp.Bit.cast(xs), xp.Bit.cast(ys)
+    views = [
+        ("flat", list(range(n)), lambda v: v),
+        ("offset 13", list(range(13, n)), lambda v: v[13:n]),
+        ("offset 33", list(range(33, n)), lambda v: v[33:n]),
+        ("step 2", list(range(0, n, 2)), lambda v: v[0:n:2]),
+    ]
+    py = {"&": lambda u, v: u & v, "|": lambda u, v: u | v, "^": lambda u, v: u ^ v}
+    for label, idxs, cut in views:
+        va, vb = cut(a), cut(b)
+        assert (~va).to_a() == [1 - xs[i] for i in idxs], label
+        assert (va & vb).to_a() == [xs[i] & ys[i] for i in idxs], label
+        assert (va | vb).to_a() == [xs[i] | ys[i] for i in idxs], label
+        assert (va ^ vb).to_a() == [xs[i] ^ ys[i] for i in idxs], label
+        assert va.eq(vb).to_a() == [1 - (xs[i] ^ ys[i]) for i in idxs], label
+    # a strided 2-d view: every row starts at another bit offset
+    cols = list(range(0, 25, 2))
+    grid = [r * 25 + c for r in range(8) for c in cols]
+    ga, gb = a.reshape(8, 25)[True, 0:25:2], b.reshape(8, 25)[True, 0:25:2]
+    rows = lambda flat: [flat[r * len(cols):(r + 1) * len(cols)] for r in range(8)]
+    assert (~ga).to_a() == rows([1 - xs[i] for i in grid])
+    for name, f in py.items():
+        got = {"&": ga & gb, "|": ga | gb, "^": ga ^ gb}[name]
+        assert got.to_a() == rows([f(xs[i], ys[i]) for i in grid]), name
+    for m in (8, 32, 33, 64, 65, 200):
+        zs = [1 if i % 3 == 0 else 0 for i in range(m)]
+        rev = xp.Bit.cast(zs)[::-1]
+        assert rev.to_a() == zs[::-1], m
+        assert (~rev).to_a() == [1 - x for x in zs[::-1]], m
+        assert rev.where().to_a() == [i for i, x in enumerate(zs[::-1]) if x == 1], m
+        assert rev.all() is False and rev.any() is True, m
+        assert scalar(rev.count_true()) == sum(zs), m
+
+
+# ---- test/narray_test.rb:2747-2815 "a bit reduction along an axis of a reversed 2-d view", "bit reductions over long arrays
+# and views", "bit reductions along an axis" (slice views) -----------------------------------------------------------------
+def case_bit_reductions(xp):
+    rows, cols = 7, 33
+    xs = [1 if i % 3 == 0 else 0 for i in range(rows * cols)]
+    a = xp.Bit.cast(xs).reshape(rows, cols)
+    rev = a[True, ::-1]
+    grid = [[xs[r * cols + (cols - 1 - c)] for c in range(cols)] for r in range(rows)]
+    assert rev.to_a() == grid
+    assert rev.all(axis=1).to_a() == [1 if all(row) else 0 for row in grid]
+    assert rev.any(axis=0).to_a() == [1 if any(col) else 0 for col in zip(*grid)]
+    # long enough to run on the device, and not a multiple of the word width
+    n = 20_000
+    views = [
+        ("flat", list(range(n)), lambda v: v),
+        ("offset 13", list(range(13, n)), lambda v: v[13:n]),
+        ("offset 32", list(range(32, n)), lambda v: v[32:n]),
+        ("step 2", list(range(0, n, 2)), lambda v: v[0:n:2]),
+    ]
+    for zero_at in (None, 0, n // 2, n - 1):
+        ys = [1] * n
+        if zero_at is not None:
+            ys[zero_at] = 0
+        a = xp.Bit.cast(ys)
+        b = ~a
+        for label, idxs, cut in views:
+            want_all = all(ys[i] == 1 for i in idxs)
+            assert cut(a).all() is want_all, (label, zero_at)
+            assert cut(b).any() is (not want_all), (label, zero_at)
+            assert cut(b).none() is want_all, (label, zero_at)
+    rows, cols = 6, 20_000
+    xs = [0 if i % 20_001 == 0 else 1 for i in range(rows * cols)]
+    a = xp.Bit.cast(xs).reshape(rows, cols)
+    grid = [xs[r * cols:(r + 1) * cols] for r in range(rows)]
+    assert a.all(axis=1).to_a() == [1 if all(row) else 0 for row in grid]
+    assert a.any(axis=1).to_a() == [1 if any(row) else 0 for row in grid]
+    assert a.all(axis=0).to_a() == [1 if all(col) else 0 for col in zip(*grid)]
+    assert a.all(axis=1, keepdims=True).to_a() == [[1 if all(row) else 0] for row in grid]
+    v = a[True, 0:cols:2]
+    want = [[row[c] for c in range(0, cols, 2)] for row in grid]
+    assert v.all(axis=1).to_a() == [1 if all(row) else 0 for row in want]
+    assert (~v).all(axis=1).to_a() == [1 if not any(row) else 0 for row in want]
+
+
 ALL_CASES = [v for k, v in sorted(globals().items()) if k.startswith("case_")]

@@ -408,6 +408,33 @@ class OBit:
     count = count_1 = count_true
     count_0 = count_false
 
+    # Bit o Bit and all? / any? / none?, spelled with the host loops' meaning (one bit at a time: numpy's boolean operators)
+    def _other(self, o):
+        return o.b if isinstance(o, OBit) else np.array(o).astype(bool)
+
+    __and__ = lambda s, o: OBit(np.logical_and(s.b, s._other(o)))
+    __or__ = lambda s, o: OBit(np.logical_or(s.b, s._other(o)))
+    __xor__ = lambda s, o: OBit(np.logical_xor(s.b, s._other(o)))
+    __rand__, __ror__, __rxor__ = __and__, __or__, __xor__
+    __invert__ = lambda s: OBit(np.logical_not(s.b))
+    eq = lambda s, o: OBit(np.logical_not(np.logical_xor(s.b, s._other(o))))
+    dup = copy = lambda s: OBit(np.array(s.b))
+
+    def _reduce(self, f, axis, keepdims):
+        if self.b.size == 0:
+            return False
+        if axis is None and not keepdims:
+            return bool(f(self.b))
+        ax = axis if axis is None or isinstance(axis, int) else tuple(axis)
+        return OBit(f(self.b, axis=ax, keepdims=keepdims))
+
+    def all(self, axis=None, keepdims=False): return self._reduce(np.all, axis, keepdims)
+    def any(self, axis=None, keepdims=False): return self._reduce(np.any, axis, keepdims)
+
+    def none(self, axis=None, keepdims=False):
+        r = self.any(axis=axis, keepdims=keepdims)
+        return (not r) if isinstance(r, bool) else ~r
+
 
 _BY_DTYPE = {np.dtype(np.float32): OSFloat, np.dtype(np.float64): ODFloat, np.dtype(np.int32): OInt32,
              np.dtype(np.int64): OInt64, np.dtype(np.uint64): OUInt64, np.dtype(np.uint32): OUInt32}

@@ -617,3 +617,102 @@ def test_where_and_mask(libs):
             bad = torch.nonzero(u != v).view(-1)
             k = int(bad[0])
             raise AssertionError(f"case {i}: {bad.numel()} of {u.numel()} differ, first at {k}: ours {u[max(0, k - 2):k + 3].tolist()} reference {v[max(0, k - 2):k + 3].tolist()}")
+
+
+class _BitStridx(ctypes.Structure):
+    """cumo_na_bit_iarray_stridx_t (include/cumo/indexer.h:57-61)."""
+    import abi_call as _ac
+    _fields_ = [("ptr", c_void_p), ("pos", c_size_t), ("stridx", _ac.Stridx * _ac.MAX_DIM)]
+
+
+def _bit_stridx(words, pos, steps, index_arrays=None):
+    v = _BitStridx()
+    v.ptr, v.pos = words.data_ptr(), pos
+    for d, s in enumerate(steps):
+        ia = (index_arrays or {}).get(d)
+        if ia is not None:
+            v.stridx[d].index = ia.data_ptr()
+        else:
+            v.stridx[d].stride = (s << 1) | 1
+    return v
+
+
+def test_bit_operators_and_reductions_word_for_word(libs):
+    """Bit o Bit and all? / any? through both launch forms, against the reference's own kernels: contiguous runs at every
+    combination of bit offsets around a word boundary, strided / reversed / 2-d / index-array views, the three reduce forms."""
+    import torch
+    import abi_call as ac
+
+    g = torch.Generator(device="cuda").manual_seed(21)
+
+    def words(n_words):
+        return torch.randint(-(1 << 31), 1 << 31, (n_words,), device="cuda", generator=g, dtype=torch.int64).to(torch.int32)
+
+    n = 70_001
+    w1, w2 = words(n // 32 + 4), words(n // 32 + 4)
+    base3 = words(n // 32 + 4)
+    for op in ("and", "or", "xor", "eq"):
+        for p1, p2, p3 in ((0, 0, 0), (5, 5, 5), (0, 7, 31), (31, 0, 1), (13, 29, 2)):
+            def run(L):
+                out = base3.clone()                     # the bits outside the run must come back untouched
+                ac.fn(L, f"cumo_iter_bit_{op}_contiguous_kernel_launch")(c_void_p(w1.data_ptr()), c_size_t(p1), c_void_p(w2.data_ptr()), c_size_t(p2),
+                                                                          c_void_p(out.data_ptr()), c_size_t(p3), c_uint64(n))
+                return out
+            a, b = run_both(libs, run)
+            assert torch.equal(a, b), (op, p1, p2, p3)
+    for op in ("copy", "not"):
+        for p1, p3 in ((0, 0), (9, 9), (3, 30), (30, 3)):
+            def run(L):
+                out = base3.clone()
+                ac.fn(L, f"cumo_iter_bit_{op}_contiguous_kernel_launch")(c_void_p(w1.data_ptr()), c_size_t(p1), c_void_p(out.data_ptr()), c_size_t(p3), c_uint64(n))
+                return out
+            a, b = run_both(libs, run)
+            assert torch.equal(a, b), (op, p1, p3)
+    # general views: (rows, cols) with a reversed first operand, a column-strided second one, an index array on the output rows
+    rows, cols = 37, 301
+    big1, big2 = words(rows * cols * 3 // 32 + 8), words(rows * cols * 3 // 32 + 8)
+    row_index = (torch.randperm(rows, device="cuda", generator=g) * (cols + 11)).to(torch.int64)        # bit offsets of the output rows
+    shape = (rows, cols)
+    for op in ("and", "or", "xor", "eq", "copy", "not"):
+        def run(L):
+            out = words((rows + 1) * (cols + 11) // 32 + 8)
+            v1 = _bit_stridx(big1, 17 + (rows * cols - 1), (-cols, -1))                                  # walks backwards from its last element
+            v2 = _bit_stridx(big2, 3, (2 * cols + 5, 2))
+            v3 = _bit_stridx(out, 6, (0, 1), {0: row_index})
+            ix = ac.indexer(shape)
+            if op in ("copy", "not"):
+                ac.fn(L, f"cumo_iter_bit_{op}_kernel_launch")(byref(v1), byref(v3), byref(ix))
+            else:
+                ac.fn(L, f"cumo_iter_bit_{op}_kernel_launch")(byref(v1), byref(v2), byref(v3), byref(ix))
+            return out
+        # the output's untouched bits differ between the two runs (fresh random words), so compare what was written
+        ours, ref = libs
+        torch.manual_seed(0)
+        state = g.get_state()
+        a = run(ours)
+        torch.cuda.synchronize()
+        g.set_state(state)
+        b = run(ref)
+        torch.cuda.synchronize()
+        assert ref.refk_last_error() == 0
+        assert torch.equal(a, b), op
+    # all? / any?: one flipping bit at the start, in the middle, at the end, nowhere; the three launch forms
+    m = 50_003
+    idx = (torch.randperm(3 * m, device="cuda", generator=g)[:m]).to(torch.int64)
+    for name, init in (("all_p", 1), ("any_p", 0)):
+        for flip_at in (None, 0, m // 2, m - 1):
+            src = torch.full((3 * m // 32 + 4,), -1 if init else 0, device="cuda", dtype=torch.int32)
+            if flip_at is not None:
+                for q in (11 + flip_at, 11 + 3 * flip_at, 11 + int(idx[flip_at])):                     # the contiguous, the strided and the indexed run
+                    src[q // 32] ^= (1 << (q % 32)) if q % 32 != 31 else -(1 << 31)
+
+            def run(L):
+                out = torch.full((4,), -1 if init else 0, device="cuda", dtype=torch.int32)
+                ac.fn(L, f"cumo_iter_bit_{name}_contiguous_reduce_kernel_launch")(c_void_p(src.data_ptr()), c_size_t(11), c_void_p(out.data_ptr()), c_size_t(3), c_uint64(m))
+                ac.fn(L, f"cumo_iter_bit_{name}_reduce_kernel_launch")(c_void_p(src.data_ptr()), c_size_t(11), c_ssize_t(3), None, c_void_p(out.data_ptr()), c_size_t(40), c_uint64(m))
+                ac.fn(L, f"cumo_iter_bit_{name}_reduce_kernel_launch")(c_void_p(src.data_ptr()), c_size_t(11), c_ssize_t(0), c_void_p(idx.data_ptr()), c_void_p(out.data_ptr()), c_size_t(70), c_uint64(m))
+                each = torch.full((m // 32 + 2,), -1 if init else 0, device="cuda", dtype=torch.int32)
+                ac.fn(L, f"cumo_iter_bit_{name}_elementwise_kernel_launch")(c_void_p(src.data_ptr()), c_size_t(11), c_ssize_t(3), None, c_void_p(each.data_ptr()), c_size_t(5), c_ssize_t(1), None, c_uint64(m))
+                return [out, each]
+            (a1, a2), (b1, b2) = run_both(libs, run)
+            assert torch.equal(a1, b1) and torch.equal(a2, b2), (name, flip_at)

@@ -247,6 +247,18 @@ def kernel_rows(X, arr, S, copies=1):
     v32 = arr("f32_01", (n3,))
     yield "F", "f32 1-D cumsum", 2 * n3 * 4, lambda: v32.cumsum()
     del v32
+    # ... and the elementwise operations with a third operand, a second result or a position-dependent value
+    c32 = arr("f32_01", (n3,))
+    yield "F", "f32 clip(0.25, 0.75)", 2 * n3 * 4, lambda: c32.clip(0.25, 0.75)
+    lo32 = c32 * 0.5
+    hi32 = lo32 + 0.25
+    yield "F", "f32 clip(lo array, hi array)", 4 * n3 * 4, lambda: c32.clip(lo32, hi32)
+    yield "F", "f32 divmod(array)", 4 * n3 * 4, lambda: c32.divmod(hi32)
+    del lo32, hi32
+    yield "F", "f32 modf", 3 * n3 * 4, lambda: c32.modf()
+    yield "F", "f32 fill", n3 * 4, lambda: c32.fill(0.5)
+    yield "F", "f32 seq", n3 * 4, lambda: c32.seq(0.0, 1.0)
+    del c32
     lab = arr("labels256", (n4,))
     yield "F", "Int32 bincount (256 bins)", n4 * 4 + 256 * 4, lambda: lab.bincount()
     yield "F", "Bit where (half set)", n4 // 8 + (n4 // 2) * 4, lambda: mask.where()
@@ -890,6 +902,12 @@ def build_cases(xp, torch, mib: int):
         "kmeans_tensor": (lambda: (lambda m=km(): m[0].assign(m[1], m[2], algo="tensor")), n32 * 4 + n32 // 16),
         "kmeans_cores": (lambda: (lambda m=km(): m[0].assign(m[1], m[2], algo="cores")), n32 * 4 + n32 // 16),
         "sum_i32": (lambda: (lambda a=i32(): a.sum()), n32 * 4),
+        "clip_scalars_f32": (lambda: (lambda a=f32(): a.clip(-0.5, 0.5)), 2 * n32 * 4),
+        "clip_arrays_f32": (lambda: (lambda a=f32(), lo=f32() * 0.5 - 0.5, hi=f32() * 0.5 + 0.5: a.clip(lo, hi)), 4 * n32 * 4),
+        "divmod_f32": (lambda: (lambda a=f32(), b=f32() * 0.5 + 1.0: a.divmod(b)), 4 * n32 * 4),
+        "modf_f32": (lambda: (lambda a=f32(): a.modf()), 3 * n32 * 4),
+        "fill_f32": (lambda: (lambda a=xp.SFloat.new(rows32 * cols): a.fill(0.5)), n32 * 4),
+        "seq_f32": (lambda: (lambda a=xp.SFloat.new(rows32 * cols): a.seq(0.0, 1.0)), n32 * 4),
         # operands whose contiguous axes differ: the shared-memory tile kernel
         "add_transposed": (lambda: (lambda a=sq(), b=sq2(): a + b.transpose()), 3 * side * side * 4),
         "copy_transposed": (lambda: (lambda b=sq(): b.transpose().dup()), 2 * side * side * 4),

@@ -5,8 +5,8 @@ The product is `libcumo_b200.so` (hand-written CUDA kernels behind the reference
 sources (`csrc/`), its build (`build.py`), a ctypes binding, the Python face of the
 host layer (`narray`), and leading-axis sharding over several GPUs (`sharded`).
 """
-from .narray import (Bit, CudaError, CumoError, DFloat, Int32, Int64, NArray, NMath, SFloat, ShapeError,
+from .narray import (Bit, CudaError, CumoError, DFloat, Int32, Int64, NArray, NMath, OperationError, SFloat, ShapeError,
                      UInt32, UInt64, pack_bits, synchronize, unpack_bits)
 
-__all__ = ["Bit", "CudaError", "CumoError", "DFloat", "Int32", "Int64", "NArray", "NMath", "SFloat",
+__all__ = ["Bit", "CudaError", "CumoError", "DFloat", "Int32", "Int64", "NArray", "NMath", "OperationError", "SFloat",
            "ShapeError", "UInt32", "UInt64", "pack_bits", "synchronize", "unpack_bits"]

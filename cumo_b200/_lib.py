@@ -117,6 +117,12 @@ def _declare(lib: ctypes.CDLL) -> None:
         "cb200_na_bit_op": (H, [c_char_p, H, H]),
         "cb200_na_bit_reduce": (H, [c_char_p, H, c_uint32, c_int]),
         "cb200_na_mulsum": (H, [H, H, c_uint32, c_int, c_int]),
+        "cb200_na_clip": (H, [H, c_int, H, c_double, c_int64, c_int, H, c_double, c_int64]),
+        "cb200_na_fill": (c_int, [H, c_double, c_int64]),
+        "cb200_na_seq": (c_int, [H, c_double, c_double]),
+        "cb200_na_divmod": (c_int, [H, H, POINTER(H), POINTER(H)]),
+        "cb200_na_modf": (c_int, [H, POINTER(H), POINTER(H)]),
+        "cb200_na_frexp": (c_int, [H, POINTER(H), POINTER(H)]),
         "cb200_na_cast": (H, [H, c_int]),
         "cb200_na_copy": (H, [H]),
         "cb200_set_stream": (None, [c_void_p]),

@@ -9,6 +9,7 @@
 // array becomes the kernel's second input.
 #include "elementwise.cuh"
 #include "divmod_scalar.cuh"
+#include "multi.cuh"
 
 using namespace cb200;
 
@@ -141,7 +142,54 @@ extern "C" void CB_ITER(pow_int32, _s_left_kernel_launch)(CB_C sv_base, cumo_na_
     launch_elementwise<op::PowInt32<CB_C>>(nullptr, a2, a3, ix, sv_base, 0, 2, nullptr);
 }
 
+// clip: one bound through the two-input kernels, two numeric bounds as a one-input operation carrying both
+// scalars, two arrays of bounds through the three-input kernel (which can refuse an empty range)
+extern "C" void CB_ITER(clip_min, _kernel_launch)(cumo_na_iarray_t* a1, cumo_na_iarray_t* a2, cumo_na_iarray_t* a3, cumo_na_indexer_t* ix) {
+    launch_elementwise<op::ClipLow<CB_C>>(a1, a2, a3, ix, CB_C(), CB_C(), 0, nullptr);
+}
+extern "C" void CB_ITER(clip_min_s, _kernel_launch)(cumo_na_iarray_t* a1, CB_C sv, cumo_na_iarray_t* a3, cumo_na_indexer_t* ix) {
+    launch_elementwise<op::ClipLow<CB_C>>(a1, nullptr, a3, ix, CB_C(), sv, 1, nullptr);
+}
+extern "C" void CB_ITER(clip_max, _kernel_launch)(cumo_na_iarray_t* a1, cumo_na_iarray_t* a2, cumo_na_iarray_t* a3, cumo_na_indexer_t* ix) {
+    launch_elementwise<op::ClipHigh<CB_C>>(a1, a2, a3, ix, CB_C(), CB_C(), 0, nullptr);
+}
+extern "C" void CB_ITER(clip_max_s, _kernel_launch)(cumo_na_iarray_t* a1, CB_C sv, cumo_na_iarray_t* a3, cumo_na_indexer_t* ix) {
+    launch_elementwise<op::ClipHigh<CB_C>>(a1, nullptr, a3, ix, CB_C(), sv, 1, nullptr);
+}
+extern "C" void CB_ITER(clip_s, _kernel_launch)(cumo_na_iarray_t* a1, CB_C sv_min, CB_C sv_max, cumo_na_iarray_t* a4, cumo_na_indexer_t* ix) {
+    launch_elementwise<op::ClipScalars<CB_C>>(a1, nullptr, a4, ix, sv_min, sv_max, 0, nullptr);
+}
+extern "C" void CB_ITER(clip, _kernel_launch)(cumo_na_iarray_t* a1, cumo_na_iarray_t* a2, cumo_na_iarray_t* a3, cumo_na_iarray_t* a4,
+        cumo_na_indexer_t* ix, int* invalid) {
+    const cumo_na_iarray_t* a[4] = {a1, a2, a3, a4};
+    launch_multi<op::ClipArrays<CB_C>>(a, ix, op::NoParams(), invalid);
+}
+// fill: the store kernels with the value as their (repeated) input
+extern "C" void CB_ITER(fill, _kernel_launch)(cumo_na_iarray_t* a1, cumo_na_indexer_t* ix, CB_C sv) {
+    launch_elementwise<op::Cast<CB_C, CB_C>>(nullptr, nullptr, a1, ix, sv, CB_C(), 2, nullptr);
+}
+extern "C" void CB_ITER(seq, _kernel_launch)(cumo_na_iarray_t* a1, cumo_na_indexer_t* ix, op::SeqParams<CB_C>::Data beg,
+        op::SeqParams<CB_C>::Data step, double count) {
+    const cumo_na_iarray_t* a[1] = {a1};
+    op::SeqParams<CB_C> prm;
+    prm.beg = beg; prm.step = step; prm.count = count;
+    launch_multi<op::Seq<CB_C>>(a, ix, prm, nullptr);
+}
+extern "C" void CB_ITER(divmod, _kernel_launch)(cumo_na_iarray_t* a1, cumo_na_iarray_t* a2, cumo_na_iarray_t* a3, cumo_na_iarray_t* a4,
+        cumo_na_indexer_t* ix, int* divzero) {
+    const cumo_na_iarray_t* a[4] = {a1, a2, a3, a4};
+    launch_multi<op::DivMod<CB_C>>(a, ix, op::NoParams(), divzero);
+}
+
 #if CB_FLOAT
+extern "C" void CB_ITER(modf, _kernel_launch)(cumo_na_iarray_t* a1, cumo_na_iarray_t* a2, cumo_na_iarray_t* a3, cumo_na_indexer_t* ix) {
+    const cumo_na_iarray_t* a[3] = {a1, a2, a3};
+    launch_multi<op::Modf<CB_C>>(a, ix, op::NoParams(), nullptr);
+}
+extern "C" void CB_ITER(math_s_frexp, _kernel_launch)(cumo_na_iarray_t* a1, cumo_na_iarray_t* a2, cumo_na_iarray_t* a3, cumo_na_indexer_t* ix) {
+    const cumo_na_iarray_t* a[3] = {a1, a2, a3};
+    launch_multi<op::Frexp<CB_C>>(a, ix, op::NoParams(), nullptr);
+}
 DEF_BINARY_S(copysign, CopySign)
 DEF_UNARY(floor, Floor)
 DEF_UNARY(round, Round)

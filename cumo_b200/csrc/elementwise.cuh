@@ -190,7 +190,7 @@ ew_row_kernel(const EwPlan p, const RowGeom g, const char* __restrict__ a1, cons
 #pragma unroll
             for (int e = 0; e < V; ++e) {
                 TO zv = TO();
-                if (Op::apply(x[j].v[e], y[j].v[e], zv, flag)) keep |= 1u << e;
+                if (ew_apply<Op>(x[j].v[e], y[j].v[e], sx, zv, flag)) keep |= 1u << e;
                 z.v[e] = zv;
             }
             if (keep == (1u << V) - 1u) {
@@ -305,7 +305,7 @@ ew_rowshare_kernel(const RowGeom g, const char* __restrict__ a1, const char* __r
                         const T1 xv = M1 == kHeld ? xs[j].v[e] : M1 == kRowScalar ? xr[r] : xp[r][j].v[e];
                         const T2 yv = M2 == kHeld ? ys[j].v[e] : M2 == kRowScalar ? yr[r] : yp[r][j].v[e];
                         TO zv = TO();
-                        if (Op::apply(xv, yv, zv, flag)) keep |= 1u << e;
+                        if (ew_apply<Op>(xv, yv, sx, zv, flag)) keep |= 1u << e;
                         z.v[e] = zv;
                     }
                     if (keep == (1u << V) - 1u) {
@@ -356,7 +356,7 @@ ew_gen_kernel(const EwPlan p, int64_t n_tiles, const char* __restrict__ a1, cons
         for (int j = 0; j < U; ++j) {
             if (!ok[j]) continue;
             TO z;
-            if (Op::apply(x[j], y[j], z, flag)) st_one<TO>(a3 + off[j][2], z);
+            if (ew_apply<Op>(x[j], y[j], sx, z, flag)) st_one<TO>(a3 + off[j][2], z);
         }
     }
 }
@@ -450,7 +450,7 @@ ew_tile_kernel(const TilePlan t, const char* __restrict__ a1, const char* __rest
                 if (!ok[j]) continue;
                 const int lr = lr0 + j * RP;
                 TO z;
-                if (Op::apply(x[j], y[j], z, flag)) st_one<TO>(w3 + (int64_t)(lr - lrt) * t.rstep[2], z);
+                if (ew_apply<Op>(x[j], y[j], sx, z, flag)) st_one<TO>(w3 + (int64_t)(lr - lrt) * t.rstep[2], z);
             }
         }
     }
@@ -560,7 +560,7 @@ ew_tile_vec_kernel(const TilePlan t, const char* __restrict__ a1, const char* __
 #pragma unroll
             for (int e = 0; e < V; ++e) {
                 TO zv = TO();
-                if (Op::apply(x[j].v[e], y[j].v[e], zv, flag)) keep |= 1u << e;
+                if (ew_apply<Op>(x[j].v[e], y[j].v[e], sx, zv, flag)) keep |= 1u << e;
                 z.v[e] = zv;
             }
             char* q = w3 + j * i3;

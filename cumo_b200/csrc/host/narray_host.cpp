@@ -268,8 +268,9 @@ Family binary_family(const std::string& op, bool is_float) {
 }
 
 bool needs_flag(const std::string& op, int dtype) {
+    if (op == "clip") return true;                 // an empty range, whatever the type (gen/tmpl/clip.c:47-53)
     if (is_float_type(dtype)) return false;
-    return op == "div" || op == "mod" || op == "reciprocal" || op == "abs";
+    return op == "div" || op == "mod" || op == "reciprocal" || op == "abs" || op == "divmod";
 }
 
 // run `launch(flag_ptr)`, then apply the flag protocol: synchronise and raise
@@ -287,6 +288,7 @@ bool with_flag(const std::string& op, int dtype, L launch) {
         if (!cuda_ok(cudaStreamSynchronize(cb200::current_stream()), "cudaStreamSynchronize")) return false;
         if (*tl_flag.host) {
             if (op == "abs") fail("ValueError", "cannot convert the minimum integer");
+            else if (op == "clip") fail("OperationError", "min is greater than max");
             else fail("ZeroDivisionError", "divided by 0");
             return false;
         }
@@ -1248,6 +1250,244 @@ cb200_na_t* cb200_na_bit_reduce(const char* op_c, cb200_na_t* a, uint32_t axis_m
     }
     apply_keepdims(out, a, rp, keepdims);
     return out;
+}
+
+// ---- clip, fill, seq, divmod, modf, frexp ----------------------------------------------------------
+extern "C++" {
+namespace {
+
+Loop loop_of(const cb200_na* a) {
+    Loop lp;
+    lp.ndim = a->ndim;
+    memcpy(lp.shape, a->shape, sizeof(int64_t) * a->ndim);
+    return lp;
+}
+
+template <typename C>
+void call_fill(void* f, cumo_na_iarray_t* a1, cumo_na_indexer_t* ix, double vf, int64_t vi) {
+    ((void (*)(cumo_na_iarray_t*, cumo_na_indexer_t*, C))f)(a1, ix, pick<C>(vf, vi));
+}
+
+bool fill_with(cb200_na* a, double vf, int64_t vi) {
+    void* f = sym(std::string("cumo_iter_") + kTypeName[a->dtype] + "_fill_kernel_launch");
+    if (!f) return false;
+    Loop lp = loop_of(a);
+    cumo_na_indexer_t ix;
+    cumo_na_iarray_t a1;
+    fill_indexer(&ix, lp);
+    fill_iarray(&a1, a, lp);
+    switch (a->dtype) {
+    case CB200_SFLOAT: call_fill<float>(f, &a1, &ix, vf, vi); break;
+    case CB200_DFLOAT: call_fill<double>(f, &a1, &ix, vf, vi); break;
+    case CB200_INT32:  call_fill<int32_t>(f, &a1, &ix, vf, vi); break;
+    default:           call_fill<int64_t>(f, &a1, &ix, vf, vi); break;
+    }
+    return launch_ok();
+}
+
+// a bound of clip as an array of the clipped array's type: the array itself, a converted copy, or one element
+// holding the numeric (the reference casts a numeric against an array bound the same way, ndloop.c's cast of ain {cT,0})
+cb200_na* bound_array(cb200_na* arr, int kind, double vf, int64_t vi, int dtype) {
+    if (kind == 2) return arr->dtype == dtype ? share(arr) : cast_to(arr, dtype);
+    const int64_t one = 1;
+    cb200_na* b = make(dtype, 1, &one, false);
+    if (b && !fill_with(b, vf, vi)) { cb200_na_release(b); b = nullptr; }
+    return b;
+}
+
+template <typename C>
+void call_clip_s(void* f, cumo_na_iarray_t* a1, double lf, int64_t li, double hf, int64_t hi, cumo_na_iarray_t* a4, cumo_na_indexer_t* ix) {
+    ((void (*)(cumo_na_iarray_t*, C, C, cumo_na_iarray_t*, cumo_na_indexer_t*))f)(a1, pick<C>(lf, li), pick<C>(hf, hi), a4, ix);
+}
+template <typename C>
+void call_clip_one_s(void* f, cumo_na_iarray_t* a1, double vf, int64_t vi, cumo_na_iarray_t* a3, cumo_na_indexer_t* ix) {
+    ((void (*)(cumo_na_iarray_t*, C, cumo_na_iarray_t*, cumo_na_indexer_t*))f)(a1, pick<C>(vf, vi), a3, ix);
+}
+template <typename C> bool empty_range(double lf, int64_t li, double hf, int64_t hi) { return pick<C>(lf, li) > pick<C>(hf, hi); }
+
+}  // namespace
+}  // extern "C++"
+
+// `a.clip(min, max)` (gen/tmpl/clip.c:218-276).  A bound is absent (kind 0), a host numeric (1) or an array (2).
+// Two numerics are compared here and go by value; one numeric with no other bound goes by value too; every other
+// combination runs the array forms, a numeric becoming a one-element array that is repeated.
+cb200_na_t* cb200_na_clip(cb200_na_t* a, int lo_kind, cb200_na_t* lo, double lo_f, int64_t lo_i,
+                          int hi_kind, cb200_na_t* hi, double hi_f, int64_t hi_i) {
+    if (!is_value_type(a->dtype)) return (cb200_na*)fail("TypeError", "clip is not defined for %s", kTypeName[a->dtype]);
+    if (lo_kind == 0 && hi_kind == 0) return (cb200_na*)fail("ArgumentError", "min and max are not given");
+    const int dtype = a->dtype;
+    const std::string t = kTypeName[dtype];
+    if (lo_kind != 2 && hi_kind != 2) {
+        Loop lp = loop_of(a);
+        if (lo_kind == 1 && hi_kind == 1) {
+            bool empty;
+            switch (dtype) {
+            case CB200_SFLOAT: empty = empty_range<float>(lo_f, lo_i, hi_f, hi_i); break;
+            case CB200_DFLOAT: empty = empty_range<double>(lo_f, lo_i, hi_f, hi_i); break;
+            case CB200_INT32:  empty = empty_range<int32_t>(lo_f, lo_i, hi_f, hi_i); break;
+            default:           empty = empty_range<int64_t>(lo_f, lo_i, hi_f, hi_i); break;
+            }
+            if (empty) return (cb200_na*)fail("OperationError", "min is greater than max");
+        }
+        void* f = sym("cumo_iter_" + t + (lo_kind && hi_kind ? "_clip_s" : lo_kind ? "_clip_min_s" : "_clip_max_s") + "_kernel_launch");
+        if (!f) return nullptr;
+        cb200_na* out = output_for(a, dtype, lp);
+        if (!out) return nullptr;
+        cumo_na_indexer_t ix;
+        cumo_na_iarray_t a1, a4;
+        fill_indexer(&ix, lp);
+        fill_iarray(&a1, a, lp);
+        fill_iarray(&a4, out, lp);
+        const double vf = lo_kind ? lo_f : hi_f;
+        const int64_t vi = lo_kind ? lo_i : hi_i;
+        if (lo_kind && hi_kind) {
+            switch (dtype) {
+            case CB200_SFLOAT: call_clip_s<float>(f, &a1, lo_f, lo_i, hi_f, hi_i, &a4, &ix); break;
+            case CB200_DFLOAT: call_clip_s<double>(f, &a1, lo_f, lo_i, hi_f, hi_i, &a4, &ix); break;
+            case CB200_INT32:  call_clip_s<int32_t>(f, &a1, lo_f, lo_i, hi_f, hi_i, &a4, &ix); break;
+            default:           call_clip_s<int64_t>(f, &a1, lo_f, lo_i, hi_f, hi_i, &a4, &ix); break;
+            }
+        } else {
+            switch (dtype) {
+            case CB200_SFLOAT: call_clip_one_s<float>(f, &a1, vf, vi, &a4, &ix); break;
+            case CB200_DFLOAT: call_clip_one_s<double>(f, &a1, vf, vi, &a4, &ix); break;
+            case CB200_INT32:  call_clip_one_s<int32_t>(f, &a1, vf, vi, &a4, &ix); break;
+            default:           call_clip_one_s<int64_t>(f, &a1, vf, vi, &a4, &ix); break;
+            }
+        }
+        if (!launch_ok()) { cb200_na_release(out); return nullptr; }
+        return out;
+    }
+    cb200_na* bl = lo_kind ? bound_array(lo, lo_kind, lo_f, lo_i, dtype) : nullptr;
+    cb200_na* bh = hi_kind ? bound_array(hi, hi_kind, hi_f, hi_i, dtype) : nullptr;
+    cb200_na* out = nullptr;
+    bool ok = (!lo_kind || bl) && (!hi_kind || bh);
+    Loop lp, l2;
+    if (ok) ok = broadcast(a, bl ? bl : bh, &lp);
+    if (ok && bl && bh) {
+        // the loop shape of three operands: fold the third into the shape of the first two
+        cb200_na tmp = *a;
+        tmp.ndim = lp.ndim;
+        memcpy(tmp.shape, lp.shape, sizeof(int64_t) * lp.ndim);
+        ok = broadcast(&tmp, bh, &l2);
+        if (ok) lp = l2;
+    }
+    if (ok) { out = output_for(a, dtype, lp); ok = out != nullptr; }
+    if (ok) {
+        void* f = sym("cumo_iter_" + t + (bl && bh ? "_clip" : bl ? "_clip_min" : "_clip_max") + "_kernel_launch");
+        ok = f != nullptr;
+        if (ok) {
+            cumo_na_indexer_t ix;
+            cumo_na_iarray_t a1, a2, a3, a4;
+            fill_indexer(&ix, lp);
+            fill_iarray(&a1, a, lp);
+            fill_iarray(&a4, out, lp);
+            if (bl && bh) {
+                fill_iarray(&a2, bl, lp);
+                fill_iarray(&a3, bh, lp);
+                ok = with_flag("clip", dtype, [&](int* flag) {
+                    ((void (*)(cumo_na_iarray_t*, cumo_na_iarray_t*, cumo_na_iarray_t*, cumo_na_iarray_t*, cumo_na_indexer_t*, int*))f)(&a1, &a2, &a3, &a4, &ix, flag);
+                });
+            } else {
+                fill_iarray(&a2, bl ? bl : bh, lp);
+                ((void (*)(cumo_na_iarray_t*, cumo_na_iarray_t*, cumo_na_iarray_t*, cumo_na_indexer_t*))f)(&a1, &a2, &a4, &ix);
+                ok = launch_ok();
+            }
+        }
+    }
+    cb200_na_release(bl);
+    cb200_na_release(bh);
+    if (!ok) { cb200_na_release(out); return nullptr; }
+    return out;
+}
+
+// `a.fill(value)` (gen/tmpl/fill.c:18-27): through any view; 0 on success
+int cb200_na_fill(cb200_na_t* a, double value_f, int64_t value_i) {
+    if (!is_value_type(a->dtype)) { fail("TypeError", "fill is not defined for %s", kTypeName[a->dtype]); return -1; }
+    return fill_with(a, value_f, value_i) ? 0 : -1;
+}
+
+// `a.seq(beg, step)` (gen/tmpl/seq.c:21-117): element i in row-major order takes beg + i*step
+int cb200_na_seq(cb200_na_t* a, double beg, double step) {
+    if (!is_value_type(a->dtype)) { fail("TypeError", "seq is not defined for %s", kTypeName[a->dtype]); return -1; }
+    void* f = sym(std::string("cumo_iter_") + kTypeName[a->dtype] + "_seq_kernel_launch");
+    if (!f) return -1;
+    Loop lp = loop_of(a);
+    cumo_na_indexer_t ix;
+    cumo_na_iarray_t a1;
+    fill_indexer(&ix, lp);
+    fill_iarray(&a1, a, lp);
+    if (a->dtype == CB200_SFLOAT) ((void (*)(cumo_na_iarray_t*, cumo_na_indexer_t*, float, float, double))f)(&a1, &ix, (float)beg, (float)step, 0.0);
+    else ((void (*)(cumo_na_iarray_t*, cumo_na_indexer_t*, double, double, double))f)(&a1, &ix, beg, step, 0.0);
+    return launch_ok() ? 0 : -1;
+}
+
+// `a.divmod(b)` (gen/tmpl/binary2.c:58-95): both results of the broadcast pair, in the upcast type
+int cb200_na_divmod(cb200_na_t* a, cb200_na_t* b, cb200_na_t** out_quot, cb200_na_t** out_rem) {
+    *out_quot = *out_rem = nullptr;
+    if (!is_value_type(a->dtype) || !is_value_type(b->dtype)) { fail("TypeError", "divmod is not defined for %s and %s", kTypeName[a->dtype], kTypeName[b->dtype]); return -1; }
+    const int dtype = upcast(a->dtype, b->dtype);
+    Loop lp;
+    if (!broadcast(a, b, &lp)) return -1;
+    cb200_na *ca = nullptr, *cb = nullptr;
+    if (a->dtype != dtype) { ca = cast_to(a, dtype); if (!ca) return -1; }
+    if (b->dtype != dtype) { cb = cast_to(b, dtype); if (!cb) { cb200_na_release(ca); return -1; } }
+    cb200_na* q = make(dtype, lp.ndim, lp.shape, false);
+    cb200_na* r = make(dtype, lp.ndim, lp.shape, false);
+    void* f = sym(std::string("cumo_iter_") + kTypeName[dtype] + "_divmod_kernel_launch");
+    bool ok = q && r && f;
+    if (ok) {
+        cumo_na_indexer_t ix;
+        cumo_na_iarray_t a1, a2, a3, a4;
+        fill_indexer(&ix, lp);
+        fill_iarray(&a1, ca ? ca : a, lp);
+        fill_iarray(&a2, cb ? cb : b, lp);
+        fill_iarray(&a3, q, lp);
+        fill_iarray(&a4, r, lp);
+        ok = with_flag("divmod", dtype, [&](int* flag) {
+            ((void (*)(cumo_na_iarray_t*, cumo_na_iarray_t*, cumo_na_iarray_t*, cumo_na_iarray_t*, cumo_na_indexer_t*, int*))f)(&a1, &a2, &a3, &a4, &ix, flag);
+        });
+    }
+    cb200_na_release(ca);
+    cb200_na_release(cb);
+    if (!ok) { cb200_na_release(q); cb200_na_release(r); return -1; }
+    *out_quot = q;
+    *out_rem = r;
+    return 0;
+}
+
+// `a.modf` (gen/tmpl/unary_ret2.c:33-44) and `NMath.frexp(a)` (gen/tmpl/frexp.c:36-48): float arrays only;
+// the second result of frexp is an Int32 array
+static int two_results(cb200_na_t* a, const char* what, const std::string& symbol, int second_dtype, cb200_na_t** out1, cb200_na_t** out2) {
+    *out1 = *out2 = nullptr;
+    if (!is_float_type(a->dtype)) { fail("NoMethodError", "%s needs a float array", what); return -1; }
+    Loop lp = loop_of(a);
+    cb200_na* r1 = make(a->dtype, lp.ndim, lp.shape, false);
+    cb200_na* r2 = make(second_dtype, lp.ndim, lp.shape, false);
+    void* f = sym(symbol);
+    bool ok = r1 && r2 && f;
+    if (ok) {
+        cumo_na_indexer_t ix;
+        cumo_na_iarray_t a1, a2, a3;
+        fill_indexer(&ix, lp);
+        fill_iarray(&a1, a, lp);
+        fill_iarray(&a2, r1, lp);
+        fill_iarray(&a3, r2, lp);
+        ((void (*)(cumo_na_iarray_t*, cumo_na_iarray_t*, cumo_na_iarray_t*, cumo_na_indexer_t*))f)(&a1, &a2, &a3, &ix);
+        ok = launch_ok();
+    }
+    if (!ok) { cb200_na_release(r1); cb200_na_release(r2); return -1; }
+    *out1 = r1;
+    *out2 = r2;
+    return 0;
+}
+
+int cb200_na_modf(cb200_na_t* a, cb200_na_t** out_frac, cb200_na_t** out_whole) {
+    return two_results(a, "modf", std::string("cumo_iter_") + kTypeName[a->dtype] + "_modf_kernel_launch", a->dtype, out_frac, out_whole);
+}
+
+int cb200_na_frexp(cb200_na_t* a, cb200_na_t** out_mantissa, cb200_na_t** out_exponent) {
+    return two_results(a, "frexp", std::string("cumo_iter_") + kTypeName[a->dtype] + "_math_s_frexp_kernel_launch", CB200_INT32, out_mantissa, out_exponent);
 }
 
 cb200_na_t* cb200_na_mulsum(cb200_na_t* a, cb200_na_t* b, uint32_t axis_mask, int keepdims, int nan) {

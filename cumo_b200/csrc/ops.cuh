@@ -171,6 +171,32 @@ template <typename T> struct MinimumNan {
     }
 };
 
+// clip against one bound (clip_kernel.cu:24-42): a comparison with a NaN on either side is false, so the element
+// passes through
+template <typename T> struct ClipLow {
+    using In1 = T; using In2 = T; using Out = T;
+    static constexpr int arity = 2;
+    __device__ __forceinline__ static bool apply(T x, T lo, T& z, int*) { z = x < lo ? lo : x; return true; }
+};
+template <typename T> struct ClipHigh {
+    using In1 = T; using In2 = T; using Out = T;
+    static constexpr int arity = 2;
+    __device__ __forceinline__ static bool apply(T x, T hi, T& z, int*) { z = x > hi ? hi : x; return true; }
+};
+// clip against two host numerics (clip_kernel.cu:8-22 with use_scalar): the lower bound rides in the kernels' first
+// scalar argument, the upper in the second; the caller has already refused lo > hi
+template <typename T> struct ClipScalars {
+    using In1 = T; using In2 = T; using Out = T;
+    static constexpr int arity = 1;
+    static constexpr bool two_scalars = true;
+    __device__ __forceinline__ static bool apply2(T x, T lo, T hi, T& z) {
+        if (x < lo) x = lo;
+        if (x > hi) x = hi;
+        z = x;
+        return true;
+    }
+};
+
 // store / cast between element types (m_from_real, m_from_int32, ... are plain C casts)
 template <typename TO, typename TF> struct Cast {
     using In1 = TF; using In2 = TF; using Out = TO;
@@ -288,4 +314,15 @@ CB200_CMP1(SignBit, signbit(x))
 #undef CB200_CMP1
 
 }  // namespace op
+
+// How the kernels of elementwise.cuh call an operation.  One that declares `two_scalars` takes both scalar arguments
+// of the launch beside its array input; every other gets (x, y) as loaded or repeated.
+template <typename Op, typename = void> struct takes_two_scalars : std::false_type {};
+template <typename Op> struct takes_two_scalars<Op, std::void_t<decltype(Op::two_scalars)>> : std::true_type {};
+template <typename Op, typename X, typename Y, typename Z>
+__device__ __forceinline__ bool ew_apply(X x, Y y, typename Op::In1 sx, Z& z, int* flag) {
+    if constexpr (takes_two_scalars<Op>::value) return Op::apply2(x, sx, y, z);
+    else return Op::apply(x, y, z, flag);
+}
+
 }  // namespace cb200

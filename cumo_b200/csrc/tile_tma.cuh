@@ -224,7 +224,7 @@ ew_tile_tma_kernel(const TmaTileArgs t, const __grid_constant__ CUtensorMap map1
 #pragma unroll
                         for (int e = 0; e < V; ++e) {
                             TO zv = TO();
-                            if (Op::apply(x[i].v[e], y[i].v[e], zv, flag)) keep |= 1u << e;
+                            if (ew_apply<Op>(x[i].v[e], y[i].v[e], sx, zv, flag)) keep |= 1u << e;
                             z.v[e] = zv;
                         }
                         char* q = w + i * t.out_rstep;

@@ -35,9 +35,13 @@ class CudaError(CumoError):
     pass
 
 
+class OperationError(CumoError):
+    """`Cumo::NArray::OperationError`"""
+
+
 _ERRORS = {"ShapeError": ShapeError, "ZeroDivisionError": ZeroDivisionError, "ValueError": ValueError,
            "TypeError": TypeError, "CudaError": CudaError, "NoMethodError": AttributeError,
-           "IndexError": IndexError, "ArgumentError": ValueError}
+           "IndexError": IndexError, "ArgumentError": ValueError, "OperationError": OperationError}
 
 
 def _raise_last():
@@ -194,15 +198,32 @@ class NArray:
         return cls.zeros(*shape).fill(1)
 
     def fill(self, value):
-        host = np.full(self.shape, value, dtype=_NP[self.dtype_code])
-        tmp = type(self).from_numpy(host)
-        self._store(tmp)
+        """`a.fill(v)` (gen/tmpl/fill.c:18-27): every element of `a` -- an array or any view of one -- takes `v`,
+        converted to the element type the way a cast converts it."""
+        if self.dtype_code not in (SFLOAT, DFLOAT, INT32, INT64):       # index and count types: filled from the host
+            self._store(type(self).from_numpy(np.full(self.shape, value, dtype=_NP[self.dtype_code])))
+            return self
+        f, i = self._numeric(value)
+        if _lib.load().cb200_na_fill(self._h, f, i):
+            _raise_last()
         return self
 
     def seq(self, start=0, step=1):
-        host = (start + step * np.arange(self.size)).astype(_NP[self.dtype_code]).reshape(self.shape)
-        self._store(type(self).from_numpy(host))
+        """`a.seq(beg, step)` (gen/tmpl/seq.c:21-117): element i, counted in row-major order over `a`'s own shape,
+        takes beg + i*step."""
+        if self.dtype_code not in (SFLOAT, DFLOAT, INT32, INT64):
+            host = (start + step * np.arange(self.size)).astype(_NP[self.dtype_code]).reshape(self.shape)
+            self._store(type(self).from_numpy(host))
+            return self
+        if _lib.load().cb200_na_seq(self._h, float(start), float(step)):
+            _raise_last()
         return self
+
+    def _numeric(self, value):
+        """A host numeric as the (float, int) pair the host layer picks from by element type."""
+        if self.dtype_code in (SFLOAT, DFLOAT):
+            return float(value), 0
+        return 0.0, int(value)                                # a Float against an integer type truncates (NUM2INT)
 
     def _store(self, other):
         """self[...] = other through the store kernel (same shape)."""
@@ -499,6 +520,46 @@ class NArray:
     @classmethod
     def minimum(cls, a, b, nan=False): return cls.cast(a)._binary("minimum_nan" if nan else "minimum", cls.cast(b))
 
+    def clip(self, min=None, max=None):
+        """`a.clip(min, max)` (gen/tmpl/clip.c:218-276): each bound is None, a number or an array (converted to
+        `a`'s type and repeated like any operand).  The result has `a`'s type; `a.inplace.clip(..)` writes into `a`.
+        OperationError when min > max anywhere, ValueError when neither bound is given."""
+        def bound(b):
+            if b is None:
+                return 0, None, 0.0, 0
+            if isinstance(b, (list, tuple, np.ndarray)):
+                b = type(self).cast(b)
+            if isinstance(b, NArray):
+                return 2, b._h, 0.0, 0
+            f, i = self._numeric(b)
+            return 1, None, f, i
+        lo, hi = bound(min), bound(max)
+        return NArray._from_handle(_lib.load().cb200_na_clip(self._h, *lo, *hi))
+
+    def divmod(self, other):
+        """`a.divmod(b)` (gen/tmpl/binary2.c:58-95): quotient and remainder of one pass, both in the upcast type."""
+        if not isinstance(other, NArray):
+            if isinstance(other, (list, tuple, np.ndarray)):
+                other = type(self).cast(other)
+            else:
+                a, f, i = self._scalar_operand(other)
+                if a is not self:
+                    return a.divmod(other)
+                other = type(self).cast([other])
+        q, r = c_void_p(), c_void_p()
+        if _lib.load().cb200_na_divmod(self._h, other._h, byref(q), byref(r)):
+            _raise_last()
+        return NArray._from_handle(q.value), NArray._from_handle(r.value)
+
+    def __divmod__(self, other): return self.divmod(other)
+
+    def modf(self):
+        """`a.modf` (gen/tmpl/unary_ret2.c:33-44): fractional and integral parts, float types only."""
+        x, y = c_void_p(), c_void_p()
+        if _lib.load().cb200_na_modf(self._h, byref(x), byref(y)):
+            _raise_last()
+        return NArray._from_handle(x.value), NArray._from_handle(y.value)
+
     def _unary(self, op):
         return NArray._from_handle(_lib.load().cb200_na_unary(op.encode(), self._h))
 
@@ -769,6 +830,16 @@ class _NMath:
                 return y._binary(name, x, True)
             return g
         raise AttributeError(name)
+
+    def frexp(self, x):
+        """`NMath.frexp(x)` (gen/tmpl/frexp.c:36-48): mantissas in x's type and exponents as an Int32 array."""
+        x = x if isinstance(x, NArray) else DFloat.cast(x)
+        if x.dtype_code in (INT32, INT64):
+            x = DFloat.cast(x)
+        m, e = c_void_p(), c_void_p()
+        if _lib.load().cb200_na_frexp(x._h, byref(m), byref(e)):
+            _raise_last()
+        return NArray._from_handle(m.value), NArray._from_handle(e.value)
 
 
 NMath = _NMath()

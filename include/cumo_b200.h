@@ -171,6 +171,34 @@ const char* cb200_version(void);
 #define CB200_DECL_EWCOMP(T, C, op) \
     void cumo_##T##_##op##_kernel_launch(cumo_na_iarray_t* a1, cumo_na_iarray_t* a2, cumo_na_iarray_t* a3, cumo_na_indexer_t* indexer);
 
+/* clip, reference: gen/tmpl/clip.c:2-7, clip_kernel.cu:60-129.  x limited to [min, max]; `_min` / `_max` limit one
+ * side only; `_s` carries host numerics.  With two arrays of bounds an element whose min > max sets *invalid and is
+ * left unwritten; with two numerics the caller has compared them. */
+#define CB200_DECL_CLIP(T, C) \
+    void cumo_iter_##T##_clip_kernel_launch(cumo_na_iarray_t* a1, cumo_na_iarray_t* a2, cumo_na_iarray_t* a3, cumo_na_iarray_t* a4, cumo_na_indexer_t* indexer, int* invalid); \
+    void cumo_iter_##T##_clip_s_kernel_launch(cumo_na_iarray_t* a1, C sv_min, C sv_max, cumo_na_iarray_t* a4, cumo_na_indexer_t* indexer); \
+    void cumo_iter_##T##_clip_min_kernel_launch(cumo_na_iarray_t* a1, cumo_na_iarray_t* a2, cumo_na_iarray_t* a3, cumo_na_indexer_t* indexer); \
+    void cumo_iter_##T##_clip_min_s_kernel_launch(cumo_na_iarray_t* a1, C sv, cumo_na_iarray_t* a3, cumo_na_indexer_t* indexer); \
+    void cumo_iter_##T##_clip_max_kernel_launch(cumo_na_iarray_t* a1, cumo_na_iarray_t* a2, cumo_na_iarray_t* a3, cumo_na_indexer_t* indexer); \
+    void cumo_iter_##T##_clip_max_s_kernel_launch(cumo_na_iarray_t* a1, C sv, cumo_na_iarray_t* a3, cumo_na_indexer_t* indexer);
+
+/* fill, reference: gen/tmpl/fill.c:2, fill_kernel.cu:13-29.  Every element of a1 takes val.
+ * seq, reference: gen/tmpl/seq.c:19, seq_kernel.cu:37-53.  Element i (row-major over the indexer) takes
+ * beg + step * (count + i); D is the reference's seq_data_t: the element type for the float types, double for the
+ * integer types, whose value then goes through int64_t.
+ * divmod, reference: gen/tmpl/binary2.c:2, binary2_kernel.cu:28-44.  a3 = a1 / a2 and a4 = a1 % a2 in one pass; an
+ * integer zero divisor sets *divzero and leaves both elements unwritten. */
+#define CB200_DECL_FILL_SEQ_DIVMOD(T, C, D) \
+    void cumo_iter_##T##_fill_kernel_launch(cumo_na_iarray_t* a1, cumo_na_indexer_t* indexer, C val); \
+    void cumo_iter_##T##_seq_kernel_launch(cumo_na_iarray_t* a1, cumo_na_indexer_t* indexer, D beg, D step, double count); \
+    void cumo_iter_##T##_divmod_kernel_launch(cumo_na_iarray_t* a1, cumo_na_iarray_t* a2, cumo_na_iarray_t* a3, cumo_na_iarray_t* a4, cumo_na_indexer_t* indexer, int* divzero);
+
+/* modf, reference: gen/tmpl/unary_ret2.c:2, unary_ret2_kernel.cu:16-31: a2 = fractional part, a3 = integral part.
+ * frexp, reference: gen/tmpl/frexp.c:2, frexp_kernel.cu:15-31: a2 = mantissa, a3 = exponent (an Int32 array). */
+#define CB200_DECL_MODF_FREXP(T) \
+    void cumo_iter_##T##_modf_kernel_launch(cumo_na_iarray_t* a1, cumo_na_iarray_t* a2, cumo_na_iarray_t* a3, cumo_na_indexer_t* indexer); \
+    void cumo_iter_##T##_math_s_frexp_kernel_launch(cumo_na_iarray_t* a1, cumo_na_iarray_t* a2, cumo_na_iarray_t* a3, cumo_na_indexer_t* indexer);
+
 /* value reductions, reference: gen/tmpl/accum.c:6-9, real_accum_kernel.cu:166-226,
  * float_accum_kernel.cu:155-206.  Integer sum/prod write int64_t. */
 #define CB200_DECL_ACCUM(T, C, op) \
@@ -270,6 +298,10 @@ CB200_DECL_FLOAT(sfloat, float)
 CB200_DECL_FLOAT(dfloat, double)
 CB200_DECL_INT(int32, int32_t)
 CB200_DECL_INT(int64, int64_t)
+CB200_DECL_CLIP(sfloat, float) CB200_DECL_CLIP(dfloat, double) CB200_DECL_CLIP(int32, int32_t) CB200_DECL_CLIP(int64, int64_t)
+CB200_DECL_FILL_SEQ_DIVMOD(sfloat, float, float) CB200_DECL_FILL_SEQ_DIVMOD(dfloat, double, double)
+CB200_DECL_FILL_SEQ_DIVMOD(int32, int32_t, double) CB200_DECL_FILL_SEQ_DIVMOD(int64, int64_t, double)
+CB200_DECL_MODF_FREXP(sfloat) CB200_DECL_MODF_FREXP(dfloat)
 
 /* bincount along one run (integer types only), reference: gen/tmpl/bincount.c:18,70, bincount_kernel.cu:32-97.
  * The output run (n elements, byte step s2/s3) is cleared, then every element x of the input run (count elements

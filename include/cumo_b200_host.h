@@ -124,6 +124,21 @@ cb200_na_t* cb200_na_count(cb200_na_t* a, uint32_t axis_mask, int keepdims, int 
 cb200_na_t* cb200_na_bit_op(const char* op, cb200_na_t* a, cb200_na_t* b);
 /* Bit#all? / #any? over the axes of axis_mask (0 = all): a Bit array of the kept dims. */
 cb200_na_t* cb200_na_bit_reduce(const char* op, cb200_na_t* a, uint32_t axis_mask, int keepdims);
+
+/* `a.clip(min, max)`, reference: gen/tmpl/clip.c:218-276.  Each bound is absent (kind 0), a host numeric (kind 1:
+ * the value in *_f for the float types, *_i for the integer types) or an array (kind 2).  OperationError when
+ * min > max anywhere; ArgumentError when neither bound is given.  Writes into `a` when it is marked in-place. */
+cb200_na_t* cb200_na_clip(cb200_na_t* a, int lo_kind, cb200_na_t* lo, double lo_f, int64_t lo_i,
+                          int hi_kind, cb200_na_t* hi, double hi_f, int64_t hi_i);
+/* `a.fill(v)` and `a.seq(beg, step)`, reference: gen/tmpl/fill.c:18-27, seq.c:21-117: write through `a`, which may
+ * be any view; 0 on success */
+int cb200_na_fill(cb200_na_t* a, double value_f, int64_t value_i);
+int cb200_na_seq(cb200_na_t* a, double beg, double step);
+/* `a.divmod(b)`, reference: gen/tmpl/binary2.c:58-95; `a.modf`, gen/tmpl/unary_ret2.c:33-44; `NMath.frexp(a)`,
+ * gen/tmpl/frexp.c:36-48 (the exponents as an Int32 array).  Two results each; 0 on success. */
+int cb200_na_divmod(cb200_na_t* a, cb200_na_t* b, cb200_na_t** out_quot, cb200_na_t** out_rem);
+int cb200_na_modf(cb200_na_t* a, cb200_na_t** out_frac, cb200_na_t** out_whole);
+int cb200_na_frexp(cb200_na_t* a, cb200_na_t** out_mantissa, cb200_na_t** out_exponent);
 /* mulsum(a, b, axis...) = (a*b).sum(axis...) in one pass over the inputs */
 cb200_na_t* cb200_na_mulsum(cb200_na_t* a, cb200_na_t* b, uint32_t axis_mask, int keepdims, int nan);
 /* contiguous copy / cast (the reference's `dup`, `reshape` copy and `Type.cast`) */

@@ -49,6 +49,9 @@ enum {
     RED_MIN_INDEX, RED_MAX_INDEX, RED_ARGMIN, RED_ARGMAX, RED_VAR, RED_STDDEV, RED_RMS, RED_KAHAN
 };
 
+/* clip / divmod / modf / frexp / seq (multi_flat in oracle_type.inc) */
+enum { MULTI_CLIP = 0, MULTI_CLIP_MIN, MULTI_CLIP_MAX, MULTI_DIVMOD, MULTI_MODF, MULTI_FREXP, MULTI_SEQ };
+
 #define TN sfloat
 #define DT float
 #define ACC float
@@ -127,6 +130,19 @@ int oracle_pow_int32(int dtype, int ndim, const int64_t* shape, const char* a, c
     case DT_DFLOAT: pow_int32_loop_dfloat(ndim, shape, a, sa, b, sb, c, sc, base_f, sv_exp); return 0;
     case DT_INT32:  pow_int32_loop_int32(ndim, shape, a, sa, b, sb, c, sc, (int32_t)base_i, sv_exp); return 0;
     case DT_INT64:  pow_int32_loop_int64(ndim, shape, a, sa, b, sb, c, sc, base_i, sv_exp); return 0;
+    }
+    return -1;
+}
+
+/* clip / clip_min / clip_max / divmod / modf / frexp / seq over contiguous arrays of n elements (op: the MULTI_
+ * codes of oracle_type.inc); operands an operation does not use are NULL. */
+int oracle_multi(int dtype, int op, int64_t n, const void* x, const void* y, const void* z, void* o0, void* o1,
+                 double beg, double step, double count, int* flag) {
+    switch (dtype) {
+    case DT_SFLOAT: return multi_flat_sfloat(op, n, x, y, z, o0, o1, beg, step, count, flag);
+    case DT_DFLOAT: return multi_flat_dfloat(op, n, x, y, z, o0, o1, beg, step, count, flag);
+    case DT_INT32:  return multi_flat_int32(op, n, x, y, z, o0, o1, beg, step, count, flag);
+    case DT_INT64:  return multi_flat_int64(op, n, x, y, z, o0, o1, beg, step, count, flag);
     }
     return -1;
 }

@@ -54,6 +54,9 @@ def lib():
                                          c_double, c_int64, POINTER(c_int), c_void_p, c_uint64]
         L.oracle_pow_int32.restype = c_int
         L.oracle_pow_int32.argtypes = [c_int, c_int, P, c_void_p, P, c_void_p, P, c_void_p, P, c_double, c_int64, c_int32]
+        L.oracle_multi.restype = c_int
+        L.oracle_multi.argtypes = [c_int, c_int, c_int64, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                                   c_double, c_double, c_double, POINTER(c_int)]
         L.oracle_reduce.restype = c_int
         L.oracle_reduce.argtypes = [c_int, c_int, c_int, c_int, P, P, P, P, c_int, P, P, c_void_p, c_void_p, c_void_p, c_int]
         L.oracle_mulsum.restype = c_int
@@ -164,6 +167,37 @@ def pow_int32(base, exponent):
                            _i64(exp.strides) if exp is not None else _i64([]), out.ctypes.data, _i64(out.strides), sv_f, sv_i,
                            0 if exp is not None else int(exponent))
     return out
+
+
+MULTI = {"clip": 0, "clip_min": 1, "clip_max": 2, "divmod": 3, "modf": 4, "frexp": 5, "seq": 6}
+
+
+def multi(op, inputs=(), shape=None, dtype=None, beg=0.0, step=0.0, count=0.0):
+    """clip (x, lo, hi), clip_min (x, lo), clip_max (x, hi), divmod (x, y), modf (x), frexp (x): `inputs` are arrays
+    of one element type, repeated here to their common shape; seq takes `shape` and `dtype` instead.  Answers
+    (out0, out1 or None, flag): the flag is 1 when clip met lo > hi or an integer divmod met a zero divisor, and
+    those elements of the outputs are left as zero."""
+    if op == "seq":
+        shape, dtype = tuple(shape), np.dtype(dtype)
+        ins = []
+    else:
+        shape = np.broadcast_shapes(*[x.shape for x in inputs])
+        dtype = inputs[0].dtype
+        ins = [np.ascontiguousarray(np.broadcast_to(x, shape)) for x in inputs]
+    n = int(np.prod(shape, dtype=np.int64))
+    o0 = np.zeros(shape, dtype=dtype)
+    o1 = None
+    if op in ("divmod", "modf"):
+        o1 = np.zeros(shape, dtype=dtype)
+    elif op == "frexp":
+        o1 = np.zeros(shape, dtype=np.int32)
+    ptr = [x.ctypes.data for x in ins] + [None] * (3 - len(ins))
+    flag = c_int(0)
+    rc = lib().oracle_multi(DT[dtype], MULTI[op], n, ptr[0], ptr[1], ptr[2], o0.ctypes.data,
+                            o1.ctypes.data if o1 is not None else None, float(beg), float(step), float(count), ctypes.byref(flag))
+    if rc:
+        raise ValueError(f"oracle: {op} is not defined for {dtype}")
+    return o0, o1, flag.value
 
 
 def reduce(op, a, axis=None, nan=False, keepdims=False, idx64=None):

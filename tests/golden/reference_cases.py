@@ -1717,4 +1717,183 @@ def case_bit_reductions(xp):
     assert (~v).all(axis=1).to_a() == [1 if not any(row) else 0 for row in want]
 
 
+# ---- test/narray_test.rb:677-750 "#clip" ----------------------------------------------------------------------------
+def case_clip(xp):
+    for T in value_types(xp):
+        a = T.cast(list(range(10)))
+        assert a.clip(1, 8).to_a() == [1, 1, 2, 3, 4, 5, 6, 7, 8, 8]
+        assert a.clip(None, 8).to_a() == [0, 1, 2, 3, 4, 5, 6, 7, 8, 8]
+        assert a.clip(3, None).to_a() == [3, 3, 3, 3, 4, 5, 6, 7, 8, 9]
+        # array bounds
+        assert a.clip(T[3, 4, 1, 1, 1, 4, 4, 4, 4, 4], 8).to_a() == [3, 4, 2, 3, 4, 5, 6, 7, 8, 8]
+        assert a.clip(1, T[9, 9, 9, 5, 5, 5, 5, 5, 5, 5]).to_a() == [1, 1, 2, 3, 4, 5, 5, 5, 5, 5]
+        assert a.clip(T.new(10).fill(2), T.new(10).fill(7)).to_a() == [2, 2, 2, 3, 4, 5, 6, 7, 7, 7]
+        # in place
+        b = T.cast(list(range(10)))
+        b.inplace().clip(3, 6)
+        assert b.to_a() == [3, 3, 3, 3, 4, 5, 6, 6, 6, 6]
+        # over views
+        m = T.cast(list(range(12))).reshape(3, 4)
+        assert m[1:3, 1:3].clip(6, 9).to_a() == [[6, 6], [9, 9]]
+        assert m.transpose().clip(2, 8).to_a() == [[2, 4, 8], [2, 5, 8], [2, 6, 8], [3, 7, 8]]
+        assert m.reverse(1).clip(2, 8).to_a() == [[3, 2, 2, 2], [7, 6, 5, 4], [8, 8, 8, 8]]
+        # more than one block
+        big = T.cast([i % 100 for i in range(100_000)])
+        c = big.clip(20, 80)
+        assert scalar(c.min()) == 20
+        assert scalar(c.max()) == 80
+        assert c[0:25].to_a() == [20] * 21 + [21, 22, 23, 24]
+        # no usable range
+        assert _raises(xp.OperationError, lambda: a.clip(6, 3))
+        assert _raises(ValueError, lambda: a.clip(None, None))
+        # ... and the array is left untouched when it raises
+        d = T.cast(list(range(10)))
+        assert _raises(xp.OperationError, lambda: d.inplace().clip(6, 3))
+        assert d.to_a() == list(range(10))
+        # a numeric bound answers what the same bound as an array answers
+        assert a.clip(1.5, 7.5).to_a() == a.clip(T.new(10).fill(1.5), T.new(10).fill(7.5)).to_a()
+        assert a.clip(1.5, None).to_a() == a.clip(T.new(10).fill(1.5), None).to_a()
+        assert a.clip(None, 7.5).to_a() == a.clip(None, T.new(10).fill(7.5)).to_a()
+        # ... also in a shape of nine dimensions
+        deep = [2] * 9
+        e = T.new(*deep).seq()
+        assert e.clip(1, 2).to_a() == e.clip(T.new(*deep).fill(1), T.new(*deep).fill(2)).to_a()
+        assert e.clip(1, None).to_a() == e.clip(T.new(*deep).fill(1), None).to_a()
+    for T in float_types(xp):
+        a = T.cast(list(range(6)))
+        nan = T.new(6).fill(NAN)
+        assert a.clip(NAN, 4).to_a() == a.clip(nan, 4).to_a() == [0, 1, 2, 3, 4, 4]
+        assert a.clip(1, NAN).to_a() == a.clip(1, nan).to_a() == [1, 1, 2, 3, 4, 5]
+
+
+# ---- test/narray_test.rb:3330-3401: clip, divmod, frexp, modf over views they cannot flatten; the error paths ---------
+def case_clip_divmod_frexp_modf_reach_every_element_of_a_view(xp):
+    rows, cols = 9, 7
+    xs = [((i * 3) % 13) + 1.0 for i in range(rows * cols)]
+    src = _nd(xp.DFloat, xs, [rows, cols])
+    idx = [5, 0, 3, 8, 1]
+    views = {
+        "column slice": lambda a: a[True, 1:cols - 1],
+        "reversed": lambda a: a[True, ::-1],
+        "row stride": lambda a: a[0:rows:2, True],
+        "index view": lambda a: a[idx, True],
+        "transpose": lambda a: a.transpose(),
+    }
+    ops = {
+        "clip": lambda a: [a.clip(4.0, 9.0)],
+        "clip min": lambda a: [a.clip(4.0, None)],
+        "clip max": lambda a: [a.clip(None, 9.0)],
+        "clip array": lambda a: [a.clip(a - 1.0, a + 1.0)],
+        "divmod": lambda a: list(a.divmod(4.0)),
+        "frexp": lambda a: list(xp.NMath.frexp(a)),
+        "modf": lambda a: list(a.modf()),
+    }
+    for what, take in views.items():
+        view = take(src)
+        flat = view.dup()
+        for op, f in ops.items():
+            assert [r.to_a() for r in f(view)] == [r.to_a() for r in f(flat)], f"{op} of {what}"
+    assert _flat(src.clip(4.0, 9.0).to_a()) == [min(max(x, 4.0), 9.0) for x in xs]
+    q, r = src.divmod(4.0)
+    assert _flat(q.to_a()) == [x / 4.0 for x in xs] and _flat(r.to_a()) == [math.fmod(x, 4.0) for x in xs]
+    deep = [2, 2, 3, 2, 5]
+    n = math.prod(deep)
+    ys = [(i % 7) + 1.0 for i in range(n)]
+    a = _nd(xp.DFloat, ys, deep)
+    assert _flat(a.clip(2.0, 5.0).to_a()) == [min(max(y, 2.0), 5.0) for y in ys]
+    assert [r.to_a() for r in a.transpose().modf()] == [r.to_a() for r in a.transpose().dup().modf()]
+    # the error paths still fire from the kernel
+    assert _raises(xp.OperationError, lambda: src[True, 1:-1].clip(9.0, 1.0))
+    assert _raises(xp.OperationError, lambda: src[True, 1:-1].clip(src[True, 1:-1] + 1.0, src[True, 1:-1] - 1.0))
+    ints = _nd(xp.Int32, [int(x) for x in xs], [rows, cols])
+    assert _raises(ZeroDivisionError, lambda: ints[True, 1:-1].divmod(0))
+
+
+# ---- test/narray_test.rb:1413-1420 "divmod returns quotient and remainder", narray_alt_coverage_test.rb:719, 736-742 --
+def case_divmod(xp):
+    for T in (xp.Int32, xp.Int64):
+        q, r = T[17, 20, 23].divmod(T[5, 6, 7])
+        assert q.to_a() == [3, 3, 3]
+        assert r.to_a() == [2, 2, 2]
+        assert _raises(ZeroDivisionError, lambda: T[1, 2, 3].divmod(T[1, 0, 3]))
+        assert [v.to_a() for v in T[10, 20, 30].divmod(T[3, 4, 5])] == [[3, 5, 6], [1, 0, 0]]
+
+
+# ---- test/narray_test.rb:2248-2258 "modf", "frexp" (n = 1 << 20); math_test.rb:519-530; -----------------------------
+# ---- narray_test.rb:2459-2517 "modf and frexp over long arrays and views" -------------------------------------------
+def _zero_tags(values):
+    out = []
+    for v in values:
+        if isinstance(v, float) and math.isnan(v):
+            out.append("nan")
+        elif v == 0:
+            out.append("negative_zero" if math.copysign(1.0, v) < 0 else "zero")
+        else:
+            out.append(v)
+    return out
+
+
+def _modf_expect(val):
+    if math.isnan(val) or val == 0:
+        return val, val
+    signed_zero = -0.0 if val < 0 else 0.0
+    if math.isinf(val):
+        return signed_zero, val
+    whole = float(math.floor(abs(val)))
+    whole = -whole if val < 0 else whole
+    frac = val - whole
+    return (signed_zero if frac == 0 else frac), whole
+
+
+def case_modf_and_frexp(xp):
+    n = 1 << 20
+    frac, whole = (xp.DFloat.new(n).seq(1) / 4).modf()
+    assert frac[0:2].to_a() == [0.25, 0.5]
+    assert whole[0:2].to_a() == [0.0, 0.0]
+    mant, expo = xp.NMath.frexp(xp.DFloat.new(n).seq(1))
+    assert mant[0:2].to_a() == [0.5, 0.5]
+    assert expo[0:2].to_a() == [1, 2]
+    for T in float_types(xp):
+        mant, expo = xp.NMath.frexp(T[0.0, 1.0, 2.0, 3.0, 4.0, 5.0])
+        assert type(mant) is T and type(expo) is xp.Int32
+        assert mant.to_a() == [0.0, 0.5, 0.5, 0.75, 0.5, 0.625]
+        assert expo.to_a() == [0, 1, 2, 2, 3, 3]
+    specials = {0: NAN, 1: INF, 2: -INF, 3: -0.0}
+    values = [specials.get(i % 9, (i - 100) / 8.0) for i in range(200)]
+    stepped = list(range(0, 200, 3))
+    backwards = list(reversed(range(200)))
+    for T in (xp.DFloat, xp.SFloat):
+        a = T.cast(values)
+        stored = a.to_a()
+        for what, view, idxs in (("flat", a, list(range(200))), ("stepped", a[0:200:3], stepped), ("reversed", a[backwards], backwards)):
+            src = [stored[i] for i in idxs]
+            expected = [_modf_expect(x) for x in src]
+            frac, whole = view.modf()
+            assert _zero_tags(frac.to_a()) == _zero_tags([e[0] for e in expected]), f"{what} frac"
+            assert _zero_tags(whole.to_a()) == _zero_tags([e[1] for e in expected]), f"{what} whole"
+            finite = [(i, x) for i, x in enumerate(src) if math.isfinite(x)]
+            mant, expo = xp.NMath.frexp(view)
+            assert type(expo) is xp.Int32
+            got_m, got_e = mant.to_a(), expo.to_a()
+            assert _zero_tags([got_m[i] for i, _ in finite]) == _zero_tags([math.frexp(x)[0] for _, x in finite]), f"{what} mantissa"
+            assert [got_e[i] for i, _ in finite] == [math.frexp(x)[1] for _, x in finite], f"{what} exponent"
+            for i, x in enumerate(src):                      # NaN and the infinities come back as themselves
+                if not math.isfinite(x):
+                    assert _zero_tags([got_m[i]]) == _zero_tags([x])
+
+
+# ---- narray_alt_coverage_test.rb:262-268 "seq"; narray_test.rb:180, 391 "fill"; 648-649 (a NaN fill) ------------------
+def case_seq_and_fill_literals(xp):
+    for T in value_types(xp):
+        assert T.new(5).seq().to_a() == [0, 1, 2, 3, 4]
+        assert T.new(5).seq(2).to_a() == [2, 3, 4, 5, 6]
+        assert T.new(5).seq(5, 3).to_a() == [5, 8, 11, 14, 17]
+        assert T[1, 2, 3, 5, 7, 11].dup().fill(12).to_a() == [12] * 6
+        assert T[[1, 2, 3], [5, 7, 11]].dup().fill(12).to_a() == [[12] * 3] * 2
+    for T in float_types(xp):
+        assert math.isnan(scalar(T.new(5000).fill(NAN).max()))
+        assert math.isnan(scalar(T.new(5000).fill(NAN).min()))
+    assert xp.DFloat.new(3).seq(1)[1].extract() == 2.0        # extra_test.rb:190
+
+
 ALL_CASES = [v for k, v in sorted(globals().items()) if k.startswith("case_")]

@@ -61,8 +61,53 @@ class ONArray:
         return self
 
     def seq(self, start=0, step=1):
-        self.a[...] = (start + step * np.arange(self.a.size)).astype(self.np_dtype).reshape(self.a.shape)
+        vals, _, _ = orc.multi("seq", shape=self.a.shape, dtype=self.a.dtype, beg=start, step=step)
+        self.a[...] = vals
         return self
+
+    def _bound(self, b):
+        """A clip bound as an array of this type: numerics convert the way NUM2INT / NUM2DBL do (truncation)."""
+        if isinstance(b, ONArray):
+            return b.a.astype(self.a.dtype) if b.a.dtype != self.a.dtype else b.a
+        if isinstance(b, (list, tuple, np.ndarray)):
+            return np.array(b, dtype=self.a.dtype)
+        if np.issubdtype(self.a.dtype, np.integer):
+            return np.array(int(b), dtype=self.a.dtype)
+        return np.array(b, dtype=self.a.dtype)
+
+    def clip(self, min=None, max=None):
+        if min is None and max is None:
+            raise ValueError("min and max are not given")
+        if min is not None and max is not None:
+            res, _, flag = orc.multi("clip", [self.a, self._bound(min), self._bound(max)])
+            if flag:
+                raise OperationErrorO("min is greater than max")
+        elif min is not None:
+            res, _, _ = orc.multi("clip_min", [self.a, self._bound(min)])
+        else:
+            res, _, _ = orc.multi("clip_max", [self.a, self._bound(max)])
+        if getattr(self, "_inplace", False) and res.shape == self.a.shape:
+            self._inplace = False
+            self.a[...] = res
+            return self
+        return self._wrap(res)
+
+    def divmod(self, o):
+        x, y = self._operand(o)
+        if not isinstance(y, np.ndarray):
+            y = np.array(y, dtype=x.dtype)
+        q, r, flag = orc.multi("divmod", [x, y])
+        if flag:
+            raise ZeroDivisionError("divided by 0")
+        return self._wrap(q), self._wrap(r)
+
+    __divmod__ = divmod
+
+    def modf(self):
+        if not np.issubdtype(self.a.dtype, np.floating):
+            raise AttributeError("modf needs a float array")
+        f, w, _ = orc.multi("modf", [self.a])
+        return self._wrap(f), self._wrap(w)
 
     # facts / host copies
     shape = property(lambda self: tuple(self.a.shape))
@@ -312,6 +357,10 @@ class ONArray:
         return self._wrap(orc.mulsum(x, y, axis=axis, nan=nan))
 
 
+class OperationErrorO(Exception):
+    pass
+
+
 class ShapeErrorO(Exception):
     pass
 
@@ -467,10 +516,17 @@ class _ONMath:
             return lambda x, y: x._binary(name, y) if isinstance(x, ONArray) else y._binary(name, x, True)
         raise AttributeError(name)
 
+    def frexp(self, x):
+        if np.issubdtype(x.a.dtype, np.integer):
+            x = ODFloat.cast(x)
+        m, e, _ = orc.multi("frexp", [x.a])
+        return ONArray._wrap(m), ONArray._wrap(e)
+
 
 class OracleXP:
     """Namespace with the same names as the cumo_b200 package."""
     SFloat, DFloat, Int32, Int64, UInt64, UInt32, Bit = OSFloat, ODFloat, OInt32, OInt64, OUInt64, OUInt32, OBit
     NMath = _ONMath()
     ShapeError = ShapeErrorO
+    OperationError = OperationErrorO
     name = "oracle"

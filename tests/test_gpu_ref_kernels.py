@@ -157,6 +157,123 @@ def test_scalar_forms_bit_for_bit(libs, tname):
         assert ac.bits_equal(a, b), f"{tname} pow_s left={left}"
 
 
+@pytest.mark.parametrize("layout", LAYOUTS)
+@pytest.mark.parametrize("tname", TYPES)
+def test_clip_fill_seq_divmod_modf_frexp_bit_for_bit(libs, tname, layout):
+    """The operations with three inputs, two outputs or a position-dependent value, on every layout: outputs that
+    an operation refuses to write (an empty clip range, an integer zero divisor) must stay untouched in both."""
+    import torch
+    import abi_call as ac
+
+    g = torch.Generator(device="cuda").manual_seed(sum(map(ord, tname + layout)) + 1)
+    x, y, shape = operands(tname, layout, g)
+    z = values(tname, shape, g)
+
+    def put(t, every, value, first=0):
+        """value into every `every`-th element of t (any view), counted row-major from `first`"""
+        pos = torch.arange(t.numel(), device="cuda").reshape(t.shape)
+        t[(pos % every == first % every) & (pos >= first)] = value
+    if tname in FLOATS:                                     # NaN on either side of a comparison
+        put(z, 97, float("nan"))
+        put(y, 89, float("nan"))
+    ix = ac.indexer(shape)
+
+    def descs(out_list):
+        dx, dy, dz = ac.iarray(x, shape), ac.iarray(y, shape), ac.iarray(z, shape)
+        if layout == "reversed":
+            flip(dx, x)
+        return dx, dy, dz, [ac.iarray(o) for o in out_list]
+
+    def fresh(n=1, dtype=None):
+        return [torch.full(shape, 77, device="cuda", dtype=dtype or x.dtype) for _ in range(n)]
+
+    def clip_arrays(L):
+        out, flag = fresh(), torch.zeros(1, dtype=torch.int32, device="cuda")
+        dx, dy, dz, (do,) = descs(out)
+        ac.fn(L, f"cumo_iter_{tname}_clip_kernel_launch")(byref(dx), byref(dy), byref(dz), byref(do), byref(ix), c_void_p(flag.data_ptr()))
+        return out + [flag]
+    (a, fa), (b, fb) = run_both(libs, clip_arrays)
+    assert ac.bits_equal(a, b) and fa.item() == fb.item() == 1, f"{tname} clip {layout}"
+
+    for name in ("clip_min", "clip_max"):
+        def one_bound(L):
+            out = fresh()
+            dx, dy, _, (do,) = descs(out)
+            ac.fn(L, f"cumo_iter_{tname}_{name}_kernel_launch")(byref(dx), byref(dy), byref(do), byref(ix))
+            return out
+        (a,), (b,) = run_both(libs, one_bound)
+        assert ac.bits_equal(a, b), f"{tname} {name} {layout}"
+
+        def one_bound_s(L):
+            out = fresh()
+            dx, _, _, (do,) = descs(out)
+            ac.fn(L, f"cumo_iter_{tname}_{name}_s_kernel_launch")(byref(dx), ac.scalar(tname, 2), byref(do), byref(ix))
+            return out
+        (a,), (b,) = run_both(libs, one_bound_s)
+        assert ac.bits_equal(a, b), f"{tname} {name}_s {layout}"
+
+    def clip_s(L):
+        out = fresh()
+        dx, _, _, (do,) = descs(out)
+        ac.fn(L, f"cumo_iter_{tname}_clip_s_kernel_launch")(byref(dx), ac.scalar(tname, -4), ac.scalar(tname, 5), byref(do), byref(ix))
+        return out
+    (a,), (b,) = run_both(libs, clip_s)
+    assert ac.bits_equal(a, b), f"{tname} clip_s {layout}"
+
+    def divmod_(L):
+        out, flag = fresh(2), torch.zeros(1, dtype=torch.int32, device="cuda")
+        dx, dy, _, (dq, dr) = descs(out)
+        ac.fn(L, f"cumo_iter_{tname}_divmod_kernel_launch")(byref(dx), byref(dy), byref(dq), byref(dr), byref(ix), c_void_p(flag.data_ptr()))
+        return out + [flag]
+    (q1, r1, fa), (q2, r2, fb) = run_both(libs, divmod_)
+    assert ac.bits_equal(q1, q2) and ac.bits_equal(r1, r2) and fa.item() == fb.item(), f"{tname} divmod {layout}"
+
+    # fill and seq write THROUGH a layout; what lies outside the window must stay
+    from ctypes import c_double, c_float
+    D = c_float if tname == "sfloat" else c_double
+
+    def window(base):
+        if layout == "view3d":
+            return base[:, ::2, 3:99]
+        if layout == "transposed":
+            return base[1].t()
+        if layout in ("rowcol", "outer"):
+            return base[2:5]
+        return base.view(-1)
+
+    for what in ("fill", "seq"):
+        def write(L):
+            base = torch.full((7, 66, 130), 77, device="cuda", dtype=x.dtype)
+            target = window(base)
+            d = ac.iarray(target)
+            if layout == "reversed":
+                flip(d, target)
+            if what == "fill":
+                ac.fn(L, f"cumo_iter_{tname}_fill_kernel_launch")(byref(d), byref(ac.indexer(target.shape)), ac.scalar(tname, 3))
+            else:
+                ac.fn(L, f"cumo_iter_{tname}_seq_kernel_launch")(byref(d), byref(ac.indexer(target.shape)), D(-1.7), D(0.37), c_double(5.0))
+            return [base]
+        (a,), (b,) = run_both(libs, write)
+        assert ac.bits_equal(a, b), f"{tname} {what} {layout}"
+        if what == "fill":
+            assert (a == 3).sum().item() == window(a).numel() and (a == 77).sum().item() == a.numel() - window(a).numel()
+
+    if tname in FLOATS:
+        w = x
+        for k, v in enumerate((float("nan"), float("inf"), -float("inf"), -0.0, 0.0, 1e-40)):
+            put(w, w.numel() + 1, v, first=k)
+        for name, second in ((f"cumo_iter_{tname}_modf_kernel_launch", None), (f"cumo_iter_{tname}_math_s_frexp_kernel_launch", torch.int32)):
+            def two(L):
+                o1, o2 = fresh()[0], fresh(dtype=second)[0]
+                dw = ac.iarray(w, shape)
+                if layout == "reversed":
+                    flip(dw, w)
+                ac.fn(L, name)(byref(dw), byref(ac.iarray(o1)), byref(ac.iarray(o2)), byref(ix))
+                return [o1, o2]
+            (a1, a2), (b1, b2) = run_both(libs, two)
+            assert ac.bits_equal(a1, b1) and ac.bits_equal(a2, b2), f"{name} {layout}"
+
+
 UNARY = {"sfloat": ["minus", "reciprocal", "sign", "square", "abs", "floor", "round", "ceil", "trunc", "rint"], "int32": ["minus", "reciprocal", "sign", "square", "abs", "bit_not"]}
 UNARY["dfloat"], UNARY["int64"] = UNARY["sfloat"], UNARY["int32"]
 MATH = ["sqrt", "cbrt", "log", "log2", "log10", "exp", "exp2", "exp10", "sin", "cos", "tan", "asin", "acos", "atan", "sinh", "cosh", "tanh",

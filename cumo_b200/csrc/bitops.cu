@@ -282,6 +282,7 @@ CB200_DEF_BIT_BINARY(or, kBitOr)
 CB200_DEF_BIT_BINARY(xor, kBitXor)
 CB200_DEF_BIT_BINARY(eq, kBitEq)
 CB200_DEF_BIT_UNARY(copy, kBitCopy)
+CB200_DEF_BIT_UNARY(store_bit, kBitCopy)      // Bit#store(Bit): tmpl_bit/store_bit.c, store_bit_kernel.cu:22-46 -- the same walk as copy
 CB200_DEF_BIT_UNARY(not, kBitNot)
 CB200_DEF_BIT_REDUCE(all_p, 1u)
 CB200_DEF_BIT_REDUCE(any_p, 0u)

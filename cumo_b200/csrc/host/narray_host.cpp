@@ -233,7 +233,54 @@ int upcast(int ta, int tb) {   // gen/def/{sfloat,dfloat,int32,int64}.rb
 bool is_value_type(int t) { return t >= CB200_SFLOAT && t <= CB200_INT64; }
 bool is_float_type(int t) { return t == CB200_SFLOAT || t == CB200_DFLOAT; }
 
+// Bit <-> value conversion: `SFloat.cast(mask)` runs the value type's store_bit (gen/tmpl/store_bit.c:14-27),
+// `Bit.cast(values)` the Bit type's store_<source> (gen/tmpl_bit/store_from.c:14-27).  Both take operands addressed by
+// step-or-index per dimension; a view reaches them with plain steps.
+cb200_na* cast_bit(cb200_na* a, int dtype) {
+    const bool to_bit = dtype == CB200_BIT;
+    const cb200_na* val_src = to_bit ? a : nullptr;
+    if (to_bit ? (a->dtype == CB200_BIT) : (a->dtype != CB200_BIT || !is_value_type(dtype)))
+        return (cb200_na*)fail("TypeError", "cannot cast %s to %s", kTypeName[a->dtype], kTypeName[dtype]);
+    cb200_na* out = make(dtype, a->ndim, a->shape, to_bit);
+    if (!out) return nullptr;
+    if (size_of(out) == 0) return out;
+    const cb200_na* bits = to_bit ? out : a;
+    const cb200_na* vals = to_bit ? val_src : out;
+    cumo_na_indexer_t ix;
+    cumo_na_iarray_stridx_t v;
+    cumo_na_bit_iarray_stridx_t b;
+    memset(&ix, 0, sizeof ix);
+    memset(&v, 0, sizeof v);
+    memset(&b, 0, sizeof b);
+    ix.ndim = (unsigned char)a->ndim;
+    ix.total_size = 1;
+    v.ptr = data_ptr(vals);
+    b.ptr = reinterpret_cast<CUMO_BIT_DIGIT*>(bits->st->ptr);
+    b.pos = (size_t)bits->offset;
+    for (int d = 0; d < a->ndim; ++d) {
+        ix.shape[d] = (size_t)a->shape[d];
+        ix.total_size *= (size_t)a->shape[d];
+        v.stridx[d].stride = (ssize_t)((vals->step[d] << 1) | 1);        // a step, not an index array
+        b.stridx[d].stride = (ssize_t)((bits->step[d] << 1) | 1);
+    }
+    bool ok;
+    if (to_bit) {
+        auto f = (void (*)(cumo_na_bit_iarray_stridx_t*, cumo_na_iarray_stridx_t*, cumo_na_indexer_t*))
+            sym(std::string("cumo_iter_bit_store_") + kTypeName[a->dtype] + "_kernel_launch");
+        ok = f != nullptr;
+        if (ok) f(&b, &v, &ix);
+    } else {
+        auto f = (void (*)(cumo_na_iarray_stridx_t*, cumo_na_bit_iarray_stridx_t*, cumo_na_indexer_t*))
+            sym(std::string("cumo_iter_") + kTypeName[dtype] + "_store_bit_kernel_launch");
+        ok = f != nullptr;
+        if (ok) f(&v, &b, &ix);
+    }
+    if (!ok || !launch_ok()) { cb200_na_release(out); return nullptr; }
+    return out;
+}
+
 cb200_na* cast_to(cb200_na* a, int dtype) {
+    if ((a->dtype == CB200_BIT) != (dtype == CB200_BIT)) return cast_bit(a, dtype);
     if (!is_value_type(a->dtype) || !is_value_type(dtype)) return (cb200_na*)fail("TypeError", "cannot cast %s to %s", kTypeName[a->dtype], kTypeName[dtype]);
     cb200_na* out = make(dtype, a->ndim, a->shape, false);
     if (!out) return nullptr;
@@ -1403,6 +1450,26 @@ cb200_na_t* cb200_na_clip(cb200_na_t* a, int lo_kind, cb200_na_t* lo, double lo_
 
 // `a.fill(value)` (gen/tmpl/fill.c:18-27): through any view; 0 on success
 int cb200_na_fill(cb200_na_t* a, double value_f, int64_t value_i) {
+    if (a->dtype == CB200_BIT) {                 // Bit#fill (gen/tmpl_bit/fill.c:16-49): the low bit of the value
+        if (size_of(a) == 0) return 0;
+        auto f = (void (*)(cumo_na_bit_iarray_stridx_t*, CUMO_BIT_DIGIT, cumo_na_indexer_t*))sym("cumo_iter_bit_fill_kernel_launch");
+        if (!f) return -1;
+        cumo_na_indexer_t ix;
+        cumo_na_bit_iarray_stridx_t b;
+        memset(&ix, 0, sizeof ix);
+        memset(&b, 0, sizeof b);
+        ix.ndim = (unsigned char)a->ndim;
+        ix.total_size = 1;
+        b.ptr = reinterpret_cast<CUMO_BIT_DIGIT*>(a->st->ptr);
+        b.pos = (size_t)a->offset;
+        for (int d = 0; d < a->ndim; ++d) {
+            ix.shape[d] = (size_t)a->shape[d];
+            ix.total_size *= (size_t)a->shape[d];
+            b.stridx[d].stride = (ssize_t)((a->step[d] << 1) | 1);
+        }
+        f(&b, (CUMO_BIT_DIGIT)((value_f != 0.0 || value_i != 0) ? 1u : 0u), &ix);
+        return launch_ok() ? 0 : -1;
+    }
     if (!is_value_type(a->dtype)) { fail("TypeError", "fill is not defined for %s", kTypeName[a->dtype]); return -1; }
     return fill_with(a, value_f, value_i) ? 0 : -1;
 }

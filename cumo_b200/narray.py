@@ -200,6 +200,10 @@ class NArray:
     def fill(self, value):
         """`a.fill(v)` (gen/tmpl/fill.c:18-27): every element of `a` -- an array or any view of one -- takes `v`,
         converted to the element type the way a cast converts it."""
+        if self.dtype_code == BIT:                                       # Bit#fill: the value's low bit
+            if _lib.load().cb200_na_fill(self._h, 0.0, int(value) & 1):
+                _raise_last()
+            return self
         if self.dtype_code not in (SFLOAT, DFLOAT, INT32, INT64):       # index and count types: filled from the host
             self._store(type(self).from_numpy(np.full(self.shape, value, dtype=_NP[self.dtype_code])))
             return self

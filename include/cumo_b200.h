@@ -491,6 +491,25 @@ CB200_DECL_BIT_BINARY(and) CB200_DECL_BIT_BINARY(or) CB200_DECL_BIT_BINARY(xor) 
 CB200_DECL_BIT_UNARY(copy) CB200_DECL_BIT_UNARY(not)
 CB200_DECL_BIT_REDUCE(all_p) CB200_DECL_BIT_REDUCE(any_p)
 
+/* Conversions between Bit and value arrays, and Bit#fill.  Every operand is addressed per dimension by a step or an
+ * index array (cumo_na_iarray_stridx_t: byte steps; cumo_na_bit_iarray_stridx_t: bit steps).
+ * value <- Bit (0 or 1 in the element type), reference: gen/tmpl/store_bit.c:2, store_bit_kernel.cu:14-30.
+ * Bit <- value (set where the value is not zero; a NaN sets it), one per source class as the reference instantiates
+ * them (gen/spec.rb:125-139), reference: gen/tmpl_bit/store_from.c:2, store_from_kernel.cu:14-29.
+ * Bit <- Bit, reference: gen/tmpl_bit/store_bit.c:1-2, store_bit_kernel.cu:22-46 (same argument lists as `copy`).
+ * fill, reference: gen/tmpl_bit/fill.c:1-2, fill_kernel.cu:21-41: every addressed bit takes the low bit of y. */
+#define CB200_DECL_STORE_BIT(T) \
+    void cumo_iter_##T##_store_bit_kernel_launch(cumo_na_iarray_stridx_t* a1, cumo_na_bit_iarray_stridx_t* a2, cumo_na_indexer_t* indexer);
+#define CB200_DECL_BIT_STORE(S) \
+    void cumo_iter_bit_store_##S##_kernel_launch(cumo_na_bit_iarray_stridx_t* a1, cumo_na_iarray_stridx_t* a2, cumo_na_indexer_t* indexer);
+CB200_DECL_STORE_BIT(sfloat) CB200_DECL_STORE_BIT(dfloat) CB200_DECL_STORE_BIT(int32) CB200_DECL_STORE_BIT(int64)
+CB200_DECL_BIT_STORE(dfloat) CB200_DECL_BIT_STORE(sfloat) CB200_DECL_BIT_STORE(int64) CB200_DECL_BIT_STORE(int32)
+CB200_DECL_BIT_STORE(int16) CB200_DECL_BIT_STORE(int8) CB200_DECL_BIT_STORE(uint64) CB200_DECL_BIT_STORE(uint32)
+CB200_DECL_BIT_STORE(uint16) CB200_DECL_BIT_STORE(uint8)
+CB200_DECL_BIT_UNARY(store_bit)
+void cumo_iter_bit_fill_kernel_launch(cumo_na_bit_iarray_stridx_t* a3, CUMO_BIT_DIGIT y, cumo_na_indexer_t* indexer);
+void cumo_iter_bit_fill_contiguous_kernel_launch(CUMO_BIT_DIGIT* a3, size_t p3, uint64_t n, CUMO_BIT_DIGIT y);
+
 /* Elementwise operations on operands whose contiguous axes differ (`a + b.transpose`, `b.transpose.dup`, a cast of a
  * transposed view; reference: the strided branches of binary_kernel.cu:14-49, unary_kernel.cu:14-25, store_from_kernel.cu)
  * run, when every operand is 16-byte aligned, in a kernel whose input tiles are copied into shared memory by the tensor

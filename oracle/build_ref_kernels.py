@@ -33,8 +33,8 @@ DEFAULT_REF = Path(os.environ.get("CUMO_REFERENCE_ROOT") or HERE.parent.parent /
 # templates (by erb_base) expanded per element type: the hot path and the rows next to it
 VALUE_TEMPLATES = {"binary", "binary_s", "unary", "unary_s", "unary2", "cond_binary", "cond_unary", "pow", "ewcomp",
                    "store_from", "accum", "accum_index", "accum_arg", "accum_binary", "bincount", "cum",
-                   "clip", "fill", "seq", "binary2", "unary_ret2", "frexp"}
-BIT_TEMPLATES = {"bit_count", "where", "mask", "binary", "unary", "bit_reduce"}
+                   "clip", "fill", "seq", "binary2", "unary_ret2", "frexp", "store_bit"}
+BIT_TEMPLATES = {"bit_count", "where", "mask", "binary", "unary", "bit_reduce", "store_from", "store_bit", "fill"}
 TYPES = ("sfloat", "dfloat", "int32", "int64", "bit")
 
 NVCC_FLAGS = ["-gencode", "arch=compute_100,code=sm_100", "-O3", "-std=c++17", "-Xcompiler", "-fPIC",

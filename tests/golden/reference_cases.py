@@ -1896,4 +1896,67 @@ def case_seq_and_fill_literals(xp):
     assert xp.DFloat.new(3).seq(1)[1].extract() == 2.0        # extra_test.rb:190
 
 
+# ---- test/narray_test.rb:3549-3554, 3588-3592 "Bit fill of <view>"; 2862, 3615-3675 (fill(0) / fill(1) of whole arrays) -----
+def case_bit_fill_through_views(xp):
+    rows, cols = 9, 7
+    views = {
+        "column slice": lambda a: a[True, 1:cols - 1],
+        "reversed": lambda a: a[True, ::-1],
+        "row stride": lambda a: a[0:rows:2, True],
+        "transpose": lambda a: a.transpose(),
+    }
+    for what, take in views.items():
+        cells = [int(v) for v in _flat(take(_nd(xp.DFloat, list(range(rows * cols)), [rows, cols])).to_a())]
+        d = xp.Bit.new(rows, cols).fill(0)
+        take(d).fill(1)
+        assert _flat(d.to_a()) == [1 if i in cells else 0 for i in range(rows * cols)], f"Bit fill of {what}"
+    n = 40
+    one_d = {
+        "step 3": lambda a: a[0:n:3],
+        "reversed": lambda a: a[::-1],
+        "reversed by 2": lambda a: a[::-2],
+        "tail": lambda a: a[3:-3],
+    }
+    for what, take in one_d.items():
+        cells = [int(v) for v in take(xp.DFloat.cast(list(range(n)))).to_a()]
+        d = xp.Bit.new(n).fill(0)
+        take(d).fill(1)
+        assert d.to_a() == [1 if i in cells else 0 for i in range(n)], f"1-d Bit fill of {what}"
+    for n in (1, 31, 32, 33, 100, 4099):
+        assert xp.Bit.new(n).fill(1).to_a() == [1] * n
+        a = xp.Bit.new(n).fill(1)
+        a[1:n - 1].fill(0)                                    # the words at both ends keep their other bits
+        assert a.to_a() == ([1] + [0] * (n - 2) + [1] if n > 1 else [1])
+        assert scalar(xp.Bit.new(n).fill(1).count_true()) == n
+
+
+# ---- Bit <-> value conversion: gen/tmpl/store_bit.c:14-27 (0 or 1 in the element type), gen/tmpl_bit/store_from.c:14-27 with
+# ---- types/bit.h:12-18 (set where the value is not zero); test/bit_test.rb:194 casts 0..63 to [0] + [1]*63 ------------------
+def case_bit_value_conversions(xp):
+    for T in value_types(xp):
+        assert xp.Bit.cast(T.cast(list(range(64)))).to_a() == [0] + [1] * 63
+        for n in (1, 5, 32, 33, 1000, 4097):
+            vals = [((i * 7) % 5) - 2 for i in range(n)]
+            bits = xp.Bit.cast(T.cast(vals))
+            assert bits.to_a() == [1 if v != 0 else 0 for v in vals]
+            back = T.cast(bits)
+            assert type(back) is T and back.to_a() == [1 if v != 0 else 0 for v in vals]
+        # through views on either side
+        m = _nd(T, [(i % 3) - 1 for i in range(63)], [9, 7])
+        want = [[1 if ((r * 7 + c) % 3) - 1 != 0 else 0 for c in range(7)] for r in range(9)]
+        assert xp.Bit.cast(m).to_a() == want
+        assert xp.Bit.cast(m.transpose()).to_a() == [list(col) for col in zip(*want)]
+        assert xp.Bit.cast(m[True, ::-1]).to_a() == [row[::-1] for row in want]
+        assert xp.Bit.cast(m[1:8:2, 1:6]).to_a() == [row[1:6] for row in want[1:8:2]]
+        b = xp.Bit.cast(m)
+        assert T.cast(b.transpose()).to_a() == [list(col) for col in zip(*want)]
+        assert T.cast(b[True, ::-1]).to_a() == [row[::-1] for row in want]
+        assert T.cast(b[1:8:2, 1:6]).to_a() == [row[1:6] for row in want[1:8:2]]
+        # a mask re-entering arithmetic
+        x = T.cast([3, -4, 0, 5, -6, 7])
+        assert (T.cast(x.gt(0)) * x).to_a() == [3, 0, 0, 5, 0, 7]
+    for T in float_types(xp):
+        assert xp.Bit.cast(T[0.0, -0.0, NAN, INF, 1e-30, -2.5]).to_a() == [0, 0, 1, 1, 1, 1]
+
+
 ALL_CASES = [v for k, v in sorted(globals().items()) if k.startswith("case_")]

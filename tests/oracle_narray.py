@@ -44,6 +44,8 @@ class ONArray:
     def cast(cls, data):
         if isinstance(data, ONArray):
             return cls._wrap(data.a.astype(cls.np_dtype))
+        if isinstance(data, OBit):                              # 0 or 1 in the element type (gen/tmpl/store_bit.c:14-27)
+            return cls._wrap(data.b.astype(cls.np_dtype))
         return cls._wrap(np.array(data, dtype=cls.np_dtype))
 
     from_numpy = cast
@@ -401,8 +403,31 @@ class OBit:
         data = list(item) if isinstance(item, tuple) else [item]
         return cls(np.array(data).astype(bool))
 
-    cast = classmethod(lambda cls, data: cls(np.array(data).astype(bool)))
+    @classmethod
+    def cast(cls, data):
+        """A bit is set where the value is not zero (types/bit.h:12-18), so a NaN sets it."""
+        if isinstance(data, ONArray):
+            return cls(data.a != 0)
+        if isinstance(data, OBit):
+            return cls(np.array(data.b))
+        return cls(np.array(data) != 0)
+
     from_numpy = cast
+    new = classmethod(lambda cls, *shape: cls(np.zeros(shape, dtype=bool)))
+    zeros = new
+
+    def fill(self, v):
+        self.b[...] = bool(int(v) & 1)
+        return self
+
+    def transpose(self, *perm):
+        return OBit._view_of(self.b.transpose(*perm) if perm else self.b.T)
+
+    @classmethod
+    def _view_of(cls, bits):
+        o = object.__new__(cls)
+        o.b = bits                                              # a numpy view: writes go through to the parent
+        return o
     shape = property(lambda self: tuple(self.b.shape))
     ndim = property(lambda self: self.b.ndim)
     size = property(lambda self: int(self.b.size))

@@ -777,7 +777,7 @@ def test_bit_operators_and_reductions_word_for_word(libs):
                 return out
             a, b = run_both(libs, run)
             assert torch.equal(a, b), (op, p1, p2, p3)
-    for op in ("copy", "not"):
+    for op in ("copy", "not", "store_bit"):
         for p1, p3 in ((0, 0), (9, 9), (3, 30), (30, 3)):
             def run(L):
                 out = base3.clone()
@@ -790,14 +790,14 @@ def test_bit_operators_and_reductions_word_for_word(libs):
     big1, big2 = words(rows * cols * 3 // 32 + 8), words(rows * cols * 3 // 32 + 8)
     row_index = (torch.randperm(rows, device="cuda", generator=g) * (cols + 11)).to(torch.int64)        # bit offsets of the output rows
     shape = (rows, cols)
-    for op in ("and", "or", "xor", "eq", "copy", "not"):
+    for op in ("and", "or", "xor", "eq", "copy", "not", "store_bit"):
         def run(L):
             out = words((rows + 1) * (cols + 11) // 32 + 8)
             v1 = _bit_stridx(big1, 17 + (rows * cols - 1), (-cols, -1))                                  # walks backwards from its last element
             v2 = _bit_stridx(big2, 3, (2 * cols + 5, 2))
             v3 = _bit_stridx(out, 6, (0, 1), {0: row_index})
             ix = ac.indexer(shape)
-            if op in ("copy", "not"):
+            if op in ("copy", "not", "store_bit"):
                 ac.fn(L, f"cumo_iter_bit_{op}_kernel_launch")(byref(v1), byref(v3), byref(ix))
             else:
                 ac.fn(L, f"cumo_iter_bit_{op}_kernel_launch")(byref(v1), byref(v2), byref(v3), byref(ix))
@@ -833,3 +833,104 @@ def test_bit_operators_and_reductions_word_for_word(libs):
                 return [out, each]
             (a1, a2), (b1, b2) = run_both(libs, run)
             assert torch.equal(a1, b1) and torch.equal(a2, b2), (name, flip_at)
+
+
+BIT_SOURCES = {"dfloat": "float64", "sfloat": "float32", "int64": "int64", "int32": "int32", "int16": "int16", "int8": "int8",
+               "uint64": "uint64", "uint32": "uint32", "uint16": "uint16", "uint8": "uint8"}
+
+
+def test_bit_value_conversions_and_fill_word_for_word(libs):
+    """value <- Bit, Bit <- value (all ten source classes) and Bit#fill against the reference's own kernels: runs laid end
+    to end at several bit offsets (the other bits of the end words must come back untouched), strided and reversed views,
+    index arrays on either side."""
+    import torch
+    import abi_call as ac
+
+    g = torch.Generator(device="cuda").manual_seed(33)
+
+    def words(n_words):
+        return torch.randint(-(1 << 31), 1 << 31, (n_words,), device="cuda", generator=g, dtype=torch.int64).to(torch.int32)
+
+    def source(name, shape):
+        dt = getattr(torch, BIT_SOURCES[name])
+        v = torch.randint(-2, 3, shape, device="cuda", generator=g, dtype=torch.int64)
+        if name.startswith("uint"):
+            v = v.abs()
+        if dt.is_floating_point:
+            v = v.to(dt) * 0.5
+            flat = v.view(-1)
+            flat[3], flat[4], flat[5] = float("nan"), -0.0, float("inf")
+            return v
+        return v.to(dt)
+
+    n = 70_001
+    mask = words(n // 32 + 4)
+    ix1 = ac.indexer((n,))
+    # value <- Bit
+    for tname in TYPES:
+        for pos in (0, 5, 31, 37):
+            def run(L):
+                out = torch.full((n,), 77, device="cuda", dtype=ac.torch_dtype(tname))
+                ac.fn(L, f"cumo_iter_{tname}_store_bit_kernel_launch")(byref(ac.stridx_iarray(out)), byref(_bit_stridx(mask, pos, (1,))), byref(ix1))
+                return [out]
+            (a,), (b,) = run_both(libs, run)
+            assert ac.bits_equal(a, b), (tname, pos)
+        rows, cols = 37, 301
+        big = words(rows * cols * 3 // 32 + 8)
+        pick = (torch.randperm(rows, device="cuda", generator=g) * cols * 3).to(torch.int64)              # bit offsets of the rows
+
+        def run(L):
+            out = torch.full((rows, 2 * cols), 77, device="cuda", dtype=ac.torch_dtype(tname))
+            view = out[:, ::2]
+            ac.fn(L, f"cumo_iter_{tname}_store_bit_kernel_launch")(byref(ac.stridx_iarray(view)), byref(_bit_stridx(big, 9, (0, 3), {0: pick})), byref(ac.indexer((rows, cols))))
+            rev = torch.full((n,), 77, device="cuda", dtype=ac.torch_dtype(tname))
+            d = ac.stridx_iarray(rev)
+            d.ptr = rev.data_ptr() + (n - 1) * rev.element_size()
+            d.stridx[0].stride = ((-rev.element_size()) << 1) | 1
+            ac.fn(L, f"cumo_iter_{tname}_store_bit_kernel_launch")(byref(d), byref(_bit_stridx(mask, 2, (1,))), byref(ix1))
+            return [out, rev]
+        (a1, a2), (b1, b2) = run_both(libs, run)
+        assert ac.bits_equal(a1, b1) and ac.bits_equal(a2, b2), tname
+    # Bit <- value
+    base = words(n // 32 + 4)
+    for sname in BIT_SOURCES:
+        src = source(sname, (n,))
+        for pos in (0, 5, 31, 37):
+            def run(L):
+                out = base.clone()
+                ac.fn(L, f"cumo_iter_bit_store_{sname}_kernel_launch")(byref(_bit_stridx(out, pos, (1,))), byref(ac.stridx_iarray(src)), byref(ix1))
+                return [out]
+            (a,), (b,) = run_both(libs, run)
+            assert torch.equal(a, b), (sname, pos)
+        rows, cols = 37, 301
+        src2 = source(sname, (rows, 2 * cols))
+        rowpos = (torch.randperm(rows, device="cuda", generator=g) * (cols + 11)).to(torch.int64)
+
+        def run(L):
+            out = base.clone()
+            ac.fn(L, f"cumo_iter_bit_store_{sname}_kernel_launch")(byref(_bit_stridx(out, 6, (0, 1), {0: rowpos})), byref(ac.stridx_iarray(src2[:, ::2])), byref(ac.indexer((rows, cols))))
+            out2 = base.clone()
+            ac.fn(L, f"cumo_iter_bit_store_{sname}_kernel_launch")(byref(_bit_stridx(out2, 3 + 2 * (cols - 1), (2 * cols + 5, -2))), byref(ac.stridx_iarray(src2.t()[:cols, :rows].t())), byref(ac.indexer((rows, cols))))
+            return [out, out2]
+        (a1, a2), (b1, b2) = run_both(libs, run)
+        assert torch.equal(a1, b1) and torch.equal(a2, b2), sname
+    # fill
+    for y in (0, 1):
+        for pos, m in ((0, n), (5, n), (31, 2), (37, 27), (3, 64), (0, 32)):
+            def run(L):
+                o1, o2 = base.clone(), base.clone()
+                # the word-at-a-time form takes the run's first word and the offset inside it (tmpl_bit/fill.c calls it so)
+                ac.fn(L, "cumo_iter_bit_fill_contiguous_kernel_launch")(c_void_p(o1.data_ptr() + 4 * (pos // 32)), c_size_t(pos % 32), c_uint64(m), ctypes.c_uint32(0xffffffff if y else 0))
+                ac.fn(L, "cumo_iter_bit_fill_kernel_launch")(byref(_bit_stridx(o2, pos, (1,))), ctypes.c_uint32(y), byref(ac.indexer((m,))))
+                return [o1, o2]
+            (a1, a2), (b1, b2) = run_both(libs, run)
+            assert torch.equal(a1, b1) and torch.equal(a2, b2) and torch.equal(a1, a2), (y, pos, m)
+        rows, cols = 37, 301
+        rowpos = (torch.randperm(rows, device="cuda", generator=g) * (cols * 2 + 11)).to(torch.int64)
+
+        def run(L):
+            out = base.clone()
+            ac.fn(L, "cumo_iter_bit_fill_kernel_launch")(byref(_bit_stridx(out, 6, (0, 2), {0: rowpos})), ctypes.c_uint32(y), byref(ac.indexer((rows, cols))))
+            return [out]
+        (a,), (b,) = run_both(libs, run)
+        assert torch.equal(a, b), y

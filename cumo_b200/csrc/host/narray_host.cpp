@@ -1174,6 +1174,22 @@ cb200_na_t* cb200_na_count(cb200_na_t* a, uint32_t axis_mask, int keepdims, int 
         if (!fs || !fss) { cb200_na_release(out); return nullptr; }
         const int in = L.nd - 1;
         CUMO_BIT_DIGIT* words = reinterpret_cast<CUMO_BIT_DIGIT*>(a->st->ptr);
+        int64_t outer = 1;
+        for (int d = 0; d < in; ++d) outer *= L.n[d];
+        if (outer > 1) {
+            // several runs (a per-axis count): the whole loop in one launch instead of one launch per run
+            using FnAxes = void (*)(CUMO_BIT_DIGIT*, size_t, int, int, const size_t*, const ssize_t*, const ssize_t*, int, const size_t*, const ssize_t*, char*);
+            FnAxes fa = (FnAxes)sym("cb200_bit_count_axes_kernel_launch");
+            if (!fa) { cb200_na_release(out); return nullptr; }
+            size_t kshape[kMaxD], rshape[kMaxD];
+            ssize_t kbit[kMaxD], kout[kMaxD], rbit[kMaxD];
+            for (int i = 0; i < rp.n_keep; ++i) { kshape[i] = (size_t)a->shape[rp.keep[i]]; kbit[i] = (ssize_t)a->step[rp.keep[i]]; kout[i] = (ssize_t)out->step[i]; }
+            for (int i = 0; i < rp.n_red; ++i) { rshape[i] = (size_t)a->shape[rp.red[i]]; rbit[i] = (ssize_t)a->step[rp.red[i]]; }
+            fa(words, (size_t)a->offset, want_false, rp.n_keep, kshape, kbit, kout, rp.n_red, rshape, rbit, data_ptr(out));
+            if (!launch_ok()) { cb200_na_release(out); return nullptr; }
+            apply_keepdims(out, a, rp, keepdims);
+            return out;
+        }
         for_outer(L, 2, [&](const int64_t* off) {
             size_t p1 = (size_t)(a->offset + off[0]);
             char* p2 = data_ptr(out) + off[1];

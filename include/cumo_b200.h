@@ -491,6 +491,16 @@ CB200_DECL_BIT_BINARY(and) CB200_DECL_BIT_BINARY(or) CB200_DECL_BIT_BINARY(xor) 
 CB200_DECL_BIT_UNARY(copy) CB200_DECL_BIT_UNARY(not)
 CB200_DECL_BIT_REDUCE(all_p) CB200_DECL_BIT_REDUCE(any_p)
 
+/* count_true / count_false along some axes, every output in one launch.  NOT in the reference, whose ndloop calls the
+ * four functions above once per innermost run (gen/tmpl_bit/bit_count.c:9-36: one launch per row of a per-axis
+ * count).  The bits of output k = (k_0 .. k_{n_keep-1}) are p1 + sum k_i*keep_bit_step[i] + sum r_j*red_bit_step[j]
+ * over all r; the number of ones (zeros when want_false) among them is ADDED to the uint64_t at
+ * out + sum k_i*keep_out_step[i], which the caller has filled with 0 as ndloop's `init` argument does.  The shape and
+ * step arrays are host arrays. */
+void cb200_bit_count_axes_kernel_launch(CUMO_BIT_DIGIT* a1, size_t p1, int want_false,
+                                        int n_keep, const size_t* keep_shape, const ssize_t* keep_bit_step, const ssize_t* keep_out_step,
+                                        int n_red, const size_t* red_shape, const ssize_t* red_bit_step, char* out);
+
 /* Conversions between Bit and value arrays, and Bit#fill.  Every operand is addressed per dimension by a step or an
  * index array (cumo_na_iarray_stridx_t: byte steps; cumo_na_bit_iarray_stridx_t: bit steps).
  * value <- Bit (0 or 1 in the element type), reference: gen/tmpl/store_bit.c:2, store_bit_kernel.cu:14-30.

@@ -199,16 +199,10 @@ scan_tiles_kernel(T* tile_sums, int64_t n_tiles) {
 }
 
 // pass 3 (or the only pass of a short run): the scan itself, a CTA walking its tiles with the fold so far
+// tiles [t_begin, t_end) of one run, scanned in order by the CTA, starting from `carry` when there is one
 template <typename T, typename Op>
-__global__ void __launch_bounds__(kBlock, sizeof(T) <= 4 ? 4 : 3)      // 4 CTAs per SM measured 8 % faster than 3 for 4-byte elements
-scan_write_kernel(const char* __restrict__ p1, int64_t s1, char* p2, int64_t s2, int64_t n, bool packed_in, bool packed_out,
-                  int64_t tiles_per_cta, int64_t n_tiles, const T* __restrict__ cta_sums) {
-    __shared__ T smem[2 * kWarpsPerBlock];
-    __shared__ __align__(16) char stage[ScanStage<T>::kBytes];
-    const int64_t t_begin = (int64_t)blockIdx.x * tiles_per_cta;
-    int64_t t_end = t_begin + tiles_per_cta; if (t_end > n_tiles) t_end = n_tiles;
-    bool have_carry = blockIdx.x > 0;            // everything before this CTA's first tile
-    T carry = have_carry ? cta_sums[blockIdx.x - 1] : T();
+__device__ __forceinline__ void scan_tiles_of_run(const char* __restrict__ p1, int64_t s1, char* p2, int64_t s2, int64_t n, bool packed_in,
+                                                  bool packed_out, int64_t t_begin, int64_t t_end, bool have_carry, T carry, T* smem, char* stage) {
     for (int64_t tile = t_begin; tile < t_end; ++tile) {
         const int64_t first = tile * kScanTile + (int64_t)threadIdx.x * kScanItems;
         const bool whole = (tile + 1) * kScanTile <= n;       // the same for every thread of the CTA
@@ -251,6 +245,213 @@ scan_write_kernel(const char* __restrict__ p1, int64_t s1, char* p2, int64_t s2,
     }
 }
 
+template <typename T, typename Op>
+__global__ void __launch_bounds__(kBlock, sizeof(T) <= 4 ? 4 : 3)      // 4 CTAs per SM measured 8 % faster than 3 for 4-byte elements
+scan_write_kernel(const char* __restrict__ p1, int64_t s1, char* p2, int64_t s2, int64_t n, bool packed_in, bool packed_out,
+                  int64_t tiles_per_cta, int64_t n_tiles, const T* __restrict__ cta_sums) {
+    __shared__ T smem[2 * kWarpsPerBlock];
+    __shared__ __align__(16) char stage[ScanStage<T>::kBytes];
+    const int64_t t_begin = (int64_t)blockIdx.x * tiles_per_cta;
+    int64_t t_end = t_begin + tiles_per_cta; if (t_end > n_tiles) t_end = n_tiles;
+    const bool have_carry = blockIdx.x > 0;      // everything before this CTA's first tile
+    const T carry = have_carry ? cta_sums[blockIdx.x - 1] : T();
+    scan_tiles_of_run<T, Op>(p1, s1, p2, s2, n, packed_in, packed_out, t_begin, t_end, have_carry, carry, smem, stage);
+}
+
+template <typename T, bool PROD, bool NANSKIP>
+cudaError_t launch_scan(char* p1, char* p2, ssize_t s1, ssize_t s2, uint64_t n64);
+
+// ---- many runs in one launch ---------------------------------------------------------------------------------------------
+// `cumsum(axis: k)` of an array with other dimensions is one scan per run along k.  The reference's ndloop launches its
+// scan once per run (cum.c:9-24); here the whole loop is one launch.  The other dimensions arrive as extents with the byte
+// step of input and output; run r (row-major over them) starts at the two offsets they give.
+struct ScanRuns {
+    int nd;
+    int64_t runs;
+    int64_t shape[kMaxDim], step1[kMaxDim], step2[kMaxDim];
+};
+
+__device__ __forceinline__ void run_offsets(const ScanRuns& o, int64_t r, int64_t* off1, int64_t* off2) {
+    int64_t a = 0, b = 0;
+    for (int d = o.nd - 1; d >= 0; --d) {
+        const int64_t n = o.shape[d];
+        const int64_t k = d > 0 ? r % n : r;
+        r = d > 0 ? r / n : 0;
+        a += k * o.step1[d];
+        b += k * o.step2[d];
+    }
+    *off1 = a;
+    *off2 = b;
+}
+
+// ROWS: a CTA per run, walking the run's tiles in order with the fold so far (runs of a few hundred elements or more)
+template <typename T, typename Op>
+__global__ void __launch_bounds__(kBlock, sizeof(T) <= 4 ? 4 : 3)
+scan_rows_kernel(const ScanRuns o, const char* __restrict__ p1, int64_t s1, char* p2, int64_t s2, int64_t n, bool packed_in, bool packed_out) {
+    __shared__ T smem[2 * kWarpsPerBlock];
+    __shared__ __align__(16) char stage[ScanStage<T>::kBytes];
+    const int64_t n_tiles = (n + kScanTile - 1) / kScanTile;
+    for (int64_t r = blockIdx.x; r < o.runs; r += gridDim.x) {
+        int64_t off1, off2;
+        run_offsets(o, r, &off1, &off2);
+        scan_tiles_of_run<T, Op>(p1 + off1, s1, p2 + off2, s2, n, packed_in, packed_out, 0, n_tiles, false, T(), smem, stage);
+        __syncthreads();
+    }
+}
+
+// COLUMNS: a thread per run, in element order; consecutive threads are consecutive runs, so when the runs lie side by
+// side in memory (a scan along an outer axis) every step of a warp is one coalesced access.  Loads run kColAhead
+// elements ahead of the dependent chain of combines.
+constexpr int kColAhead = 8;
+template <typename T, typename Op>
+__global__ void __launch_bounds__(kBlock)
+scan_columns_kernel(const ScanRuns o, const char* __restrict__ p1, int64_t s1, char* p2, int64_t s2, int64_t n) {
+    for (int64_t r = (int64_t)blockIdx.x * kBlock + threadIdx.x; r < o.runs; r += (int64_t)gridDim.x * kBlock) {
+        int64_t off1, off2;
+        run_offsets(o, r, &off1, &off2);
+        const char* src = p1 + off1;
+        char* dst = p2 + off2;
+        T acc = T();
+        for (int64_t j0 = 0; j0 < n; j0 += kColAhead) {
+            T x[kColAhead];
+#pragma unroll
+            for (int k = 0; k < kColAhead; ++k)
+                if (j0 + k < n) x[k] = *reinterpret_cast<const T*>(src + (j0 + k) * s1);
+#pragma unroll
+            for (int k = 0; k < kColAhead; ++k) {
+                if (j0 + k >= n) break;
+                acc = (j0 + k == 0) ? x[k] : Op::combine(acc, x[k]);
+                *reinterpret_cast<T*>(dst + (j0 + k) * s2) = acc;
+            }
+        }
+    }
+}
+
+// COLUMNS with few runs (a scan down the rows of a matrix with a few thousand columns): a thread per run leaves most of
+// the GPU idle, so every run is cut into `segs` segments of `seg_len` elements and a thread takes one (segment, run):
+// (1) fold of each segment, (2) per run, the folds become the fold of everything before each segment, (3) the scan of
+// each segment starting from that.  Consecutive threads are still consecutive runs, so every access stays coalesced.
+template <typename T, typename Op>
+__global__ void __launch_bounds__(kBlock)
+scan_columns_fold_kernel(const ScanRuns o, const char* __restrict__ p1, int64_t s1, int64_t n, int64_t seg_len, int64_t segs, T* partial) {
+    const int64_t total = segs * o.runs;
+    for (int64_t t = (int64_t)blockIdx.x * kBlock + threadIdx.x; t < total; t += (int64_t)gridDim.x * kBlock) {
+        const int64_t seg = t / o.runs, r = t - seg * o.runs;
+        int64_t off1, off2;
+        run_offsets(o, r, &off1, &off2);
+        const char* src = p1 + off1;
+        const int64_t j_begin = seg * seg_len;
+        const int64_t j_end = j_begin + seg_len < n ? j_begin + seg_len : n;
+        T acc = T();
+        for (int64_t j0 = j_begin; j0 < j_end; j0 += kColAhead) {
+            T x[kColAhead];
+#pragma unroll
+            for (int k = 0; k < kColAhead; ++k)
+                if (j0 + k < j_end) x[k] = *reinterpret_cast<const T*>(src + (j0 + k) * s1);
+#pragma unroll
+            for (int k = 0; k < kColAhead; ++k) {
+                if (j0 + k >= j_end) break;
+                acc = (j0 + k == j_begin) ? x[k] : Op::combine(acc, x[k]);
+            }
+        }
+        partial[t] = acc;
+    }
+}
+
+template <typename T, typename Op>
+__global__ void __launch_bounds__(kBlock)
+scan_columns_carry_kernel(int64_t runs, int64_t segs, T* partial) {
+    for (int64_t r = (int64_t)blockIdx.x * kBlock + threadIdx.x; r < runs; r += (int64_t)gridDim.x * kBlock) {
+        T acc = partial[r];
+        for (int64_t seg = 1; seg < segs; ++seg) {
+            const T mine = partial[seg * runs + r];
+            partial[seg * runs + r] = acc;                 // everything before this segment
+            acc = Op::combine(acc, mine);
+        }
+    }
+}
+
+template <typename T, typename Op>
+__global__ void __launch_bounds__(kBlock)
+scan_columns_write_kernel(const ScanRuns o, const char* __restrict__ p1, int64_t s1, char* p2, int64_t s2, int64_t n, int64_t seg_len, int64_t segs,
+                          const T* __restrict__ partial) {
+    const int64_t total = segs * o.runs;
+    for (int64_t t = (int64_t)blockIdx.x * kBlock + threadIdx.x; t < total; t += (int64_t)gridDim.x * kBlock) {
+        const int64_t seg = t / o.runs, r = t - seg * o.runs;
+        int64_t off1, off2;
+        run_offsets(o, r, &off1, &off2);
+        const char* src = p1 + off1;
+        char* dst = p2 + off2;
+        const int64_t j_begin = seg * seg_len;
+        const int64_t j_end = j_begin + seg_len < n ? j_begin + seg_len : n;
+        const bool have_carry = seg > 0;
+        T acc = have_carry ? partial[t] : T();
+        for (int64_t j0 = j_begin; j0 < j_end; j0 += kColAhead) {
+            T x[kColAhead];
+#pragma unroll
+            for (int k = 0; k < kColAhead; ++k)
+                if (j0 + k < j_end) x[k] = *reinterpret_cast<const T*>(src + (j0 + k) * s1);
+#pragma unroll
+            for (int k = 0; k < kColAhead; ++k) {
+                if (j0 + k >= j_end) break;
+                acc = (j0 + k == j_begin && !have_carry) ? x[k] : Op::combine(acc, x[k]);
+                *reinterpret_cast<T*>(dst + (j0 + k) * s2) = acc;
+            }
+        }
+    }
+}
+
+template <typename T, bool PROD, bool NANSKIP>
+cudaError_t launch_scan_runs(char* p1, char* p2, ssize_t s1, ssize_t s2, uint64_t n64, int n_outer, const size_t* oshape,
+                             const ssize_t* ostep1, const ssize_t* ostep2) {
+    using Op = ScanOp<T, PROD, NANSKIP>;
+    if (n64 == 0 || n_outer < 0 || n_outer > kMaxDim) return n64 == 0 ? cudaSuccess : cudaErrorInvalidValue;
+    ScanRuns o;
+    o.nd = 0;
+    o.runs = 1;
+    bool steps16 = true, side_by_side = false;
+    for (int d = 0; d < kMaxDim; ++d) { o.shape[d] = 1; o.step1[d] = o.step2[d] = 0; }
+    for (int d = 0; d < n_outer; ++d) {
+        if (oshape[d] == 0) return cudaSuccess;
+        if (oshape[d] == 1) continue;
+        o.shape[o.nd] = (int64_t)oshape[d]; o.step1[o.nd] = (int64_t)ostep1[d]; o.step2[o.nd] = (int64_t)ostep2[d];
+        o.runs *= o.shape[o.nd];
+        if (!mult16(o.step1[o.nd]) || !mult16(o.step2[o.nd])) steps16 = false;
+        ++o.nd;
+    }
+    if (o.nd > 0) side_by_side = o.step1[o.nd - 1] == (int64_t)sizeof(T) && o.step2[o.nd - 1] == (int64_t)sizeof(T);
+    const int64_t n = (int64_t)n64;
+    cudaStream_t st = current_stream();
+    if (o.runs == 1) return launch_scan<T, PROD, NANSKIP>(p1, p2, s1, s2, n64);
+    if (!side_by_side && n >= 256) {
+        const bool packed_in = s1 == (ssize_t)sizeof(T) && aligned16(p1) && steps16;
+        const bool packed_out = s2 == (ssize_t)sizeof(T) && aligned16(p2) && steps16;
+        scan_rows_kernel<T, Op><<<grid_for(o.runs, sizeof(T) <= 4 ? 4 : 3), kBlock, 0, st>>>(o, p1, s1, p2, s2, n, packed_in, packed_out);
+    } else {
+        // enough threads to fill the GPU: cut the runs into segments of at least 64 elements when the runs alone are too few
+        const int64_t wanted = (int64_t)sm_count() * 2048;
+        int64_t segs = (wanted + o.runs - 1) / o.runs;
+        if (segs > n / 64) segs = n / 64;
+        if (segs >= 2) {
+            const int64_t seg_len = (n + segs - 1) / segs;
+            segs = (n + seg_len - 1) / seg_len;
+            const int64_t total = segs * o.runs;
+            T* partial = reinterpret_cast<T*>(cumo_cuda_runtime_malloc(sizeof(T) * (size_t)total));
+            if (!partial) return cudaErrorMemoryAllocation;
+            scan_columns_fold_kernel<T, Op><<<grid_for((total + kBlock - 1) / kBlock, 8), kBlock, 0, st>>>(o, p1, s1, n, seg_len, segs, partial);
+            scan_columns_carry_kernel<T, Op><<<grid_for((o.runs + kBlock - 1) / kBlock, 8), kBlock, 0, st>>>(o.runs, segs, partial);
+            scan_columns_write_kernel<T, Op><<<grid_for((total + kBlock - 1) / kBlock, 8), kBlock, 0, st>>>(o, p1, s1, p2, s2, n, seg_len, segs, partial);
+            count_launch(3);
+            const cudaError_t e = cudaGetLastError();
+            cumo_cuda_runtime_free(reinterpret_cast<char*>(partial));     // stream-ordered reuse: later kernels queue behind these
+            return e;
+        }
+        scan_columns_kernel<T, Op><<<grid_for((o.runs + kBlock - 1) / kBlock, 8), kBlock, 0, st>>>(o, p1, s1, p2, s2, n);
+    }
+    count_launch();
+    return cudaGetLastError();
+}
+
 template <typename T, bool PROD, bool NANSKIP>
 cudaError_t launch_scan(char* p1, char* p2, ssize_t s1, ssize_t s2, uint64_t n64) {
     using Op = ScanOp<T, PROD, NANSKIP>;
@@ -283,12 +484,18 @@ cudaError_t launch_scan(char* p1, char* p2, ssize_t s1, ssize_t s2, uint64_t n64
 
 using namespace cb200;
 
+#define CB200_RUNS_ARGS char* p1, char* p2, ssize_t s1, ssize_t s2, uint64_t n, int n_outer, const size_t* outer_shape, const ssize_t* outer_step1, const ssize_t* outer_step2
+#define CB200_RUNS_PASS p1, p2, s1, s2, n, n_outer, outer_shape, outer_step1, outer_step2
 #define CB200_DEF_CUM(T, C)                                                                                          \
+    extern "C" cudaError_t cb200_##T##_cumsum_runs_kernel_launch(CB200_RUNS_ARGS) { return launch_scan_runs<C, false, false>(CB200_RUNS_PASS); }  \
+    extern "C" cudaError_t cb200_##T##_cumprod_runs_kernel_launch(CB200_RUNS_ARGS) { return launch_scan_runs<C, true, false>(CB200_RUNS_PASS); }  \
     extern "C" cudaError_t cumo_##T##_cumsum_kernel_launch(char* p1, char* p2, ssize_t s1, ssize_t s2, uint64_t n) {  \
         return launch_scan<C, false, false>(p1, p2, s1, s2, n); }                                                    \
     extern "C" cudaError_t cumo_##T##_cumprod_kernel_launch(char* p1, char* p2, ssize_t s1, ssize_t s2, uint64_t n) { \
         return launch_scan<C, true, false>(p1, p2, s1, s2, n); }
 #define CB200_DEF_CUM_NAN(T, C)                                                                                          \
+    extern "C" cudaError_t cb200_##T##_cumsum_nan_runs_kernel_launch(CB200_RUNS_ARGS) { return launch_scan_runs<C, false, true>(CB200_RUNS_PASS); }  \
+    extern "C" cudaError_t cb200_##T##_cumprod_nan_runs_kernel_launch(CB200_RUNS_ARGS) { return launch_scan_runs<C, true, true>(CB200_RUNS_PASS); }  \
     extern "C" cudaError_t cumo_##T##_cumsum_nan_kernel_launch(char* p1, char* p2, ssize_t s1, ssize_t s2, uint64_t n) {  \
         return launch_scan<C, false, true>(p1, p2, s1, s2, n); }                                                         \
     extern "C" cudaError_t cumo_##T##_cumprod_nan_kernel_launch(char* p1, char* p2, ssize_t s1, ssize_t s2, uint64_t n) { \

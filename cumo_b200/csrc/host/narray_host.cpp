@@ -1013,16 +1013,19 @@ cb200_na_t* cb200_na_cum(const char* op_c, cb200_na_t* a, int axis, int nan) {
         }
         status = f(data_ptr(in), data_ptr(out), (ssize_t)L.s[0][0], (ssize_t)L.s[1][0], (uint64_t)L.n[0]);
     } else {
-        // one launch per run along `axis`, as ndloop does for this iterator
-        set_loop(in);
-        const int last = L.nd - 1;
-        std::swap(L.n[axis], L.n[last]);
-        std::swap(L.s[0][axis], L.s[0][last]);
-        std::swap(L.s[1][axis], L.s[1][last]);
-        for_outer(L, 2, [&](const int64_t* off) {
-            if (status) return;
-            status = f(data_ptr(in) + off[0], data_ptr(out) + off[1], (ssize_t)L.s[0][last], (ssize_t)L.s[1][last], (uint64_t)L.n[last]);
-        });
+        // every run along `axis` in one launch (ndloop would call the per-run function once per run)
+        using FnRuns = int (*)(char*, char*, ssize_t, ssize_t, uint64_t, int, const size_t*, const ssize_t*, const ssize_t*);
+        FnRuns fr = (FnRuns)sym(std::string("cb200_") + kTypeName[a->dtype] + "_" + op + ((nan && is_float_type(a->dtype)) ? "_nan" : "") + "_runs_kernel_launch");
+        if (!fr) { cb200_na_release(out); return nullptr; }
+        size_t oshape[kMaxD];
+        ssize_t ostep1[kMaxD], ostep2[kMaxD];
+        int n_outer = 0;
+        for (int d = 0; d < in->ndim; ++d) {
+            if (d == axis) continue;
+            oshape[n_outer] = (size_t)in->shape[d]; ostep1[n_outer] = (ssize_t)in->step[d]; ostep2[n_outer] = (ssize_t)out->step[d];
+            ++n_outer;
+        }
+        status = fr(data_ptr(in), data_ptr(out), (ssize_t)in->step[axis], (ssize_t)out->step[axis], (uint64_t)in->shape[axis], n_outer, oshape, ostep1, ostep2);
     }
     cb200_na_release(copy);
     if (status) { fail("CudaError", "%s: %s", op_c, cudaGetErrorString((cudaError_t)status)); cb200_na_release(out); return nullptr; }

@@ -331,6 +331,16 @@ typedef int cb200_cuda_status_t;          /* cudaError_t: an int-sized enum, 0 =
 CB200_DECL_CUM(sfloat, ) CB200_DECL_CUM(dfloat, ) CB200_DECL_CUM(int32, ) CB200_DECL_CUM(int64, )
 CB200_DECL_CUM(sfloat, _nan) CB200_DECL_CUM(dfloat, _nan)
 
+/* The same scans over MANY runs in one launch: run r (row-major over outer_shape) starts at p1 + sum k_i*outer_step1[i]
+ * and writes from p2 + sum k_i*outer_step2[i]; s1, s2, n describe every run as above.  NOT in the reference, whose
+ * ndloop calls the functions above once per run (gen/tmpl/cum.c:9-24): `cumsum(axis: 1)` of a 65536 x 2048 array is
+ * 65536 calls.  The outer arrays are host arrays. */
+#define CB200_DECL_CUM_RUNS(T, sfx) \
+    cb200_cuda_status_t cb200_##T##_cumsum##sfx##_runs_kernel_launch(char* p1, char* p2, ssize_t s1, ssize_t s2, uint64_t n, int n_outer, const size_t* outer_shape, const ssize_t* outer_step1, const ssize_t* outer_step2); \
+    cb200_cuda_status_t cb200_##T##_cumprod##sfx##_runs_kernel_launch(char* p1, char* p2, ssize_t s1, ssize_t s2, uint64_t n, int n_outer, const size_t* outer_shape, const ssize_t* outer_step1, const ssize_t* outer_step2);
+CB200_DECL_CUM_RUNS(sfloat, ) CB200_DECL_CUM_RUNS(dfloat, ) CB200_DECL_CUM_RUNS(int32, ) CB200_DECL_CUM_RUNS(int64, )
+CB200_DECL_CUM_RUNS(sfloat, _nan) CB200_DECL_CUM_RUNS(dfloat, _nan)
+
 /* Bit#where / where2, reference: gen/tmpl_bit/where.c:11-12, where_kernel.cu:83-110.  One call of
  * cumo_bit_where_scratch_new() per result (device memory from cumo_cuda_runtime_malloc, freed by the caller with
  * cumo_cuda_runtime_free), then one launch per run of the Bit array: element i of the run (bit p + i*s of `a`, or

@@ -101,7 +101,14 @@ extern "C" void CB_MSYM(CB_T, , _reduce_kernel_launch)(char* p1, char* p2, char*
 extern "C" void CB_MSYM(CB_T, , _kernel_launch)(char* p1, char* p2, char* p3, ssize_t s1, ssize_t s2, ssize_t s3, uint64_t n) {
     launch_mulsum_each<CB_C, false>(p1, p2, p3, s1, s2, s3, n);
 }
+#define CB_MAXES_(t, sfx) cb200_##t##_mulsum##sfx##_axes_kernel_launch
+#define CB_MAXES(t, sfx) CB_MAXES_(t, sfx)
+#define CB_MAXES_ARGS char* p1, char* p2, char* p3, int n_keep, const size_t* keep_shape, const ssize_t* keep_step1, const ssize_t* keep_step2, \
+                      const ssize_t* keep_step3, int n_red, const size_t* red_shape, const ssize_t* red_step1, const ssize_t* red_step2
+#define CB_MAXES_PASS p1, p2, p3, n_keep, keep_shape, keep_step1, keep_step2, keep_step3, n_red, red_shape, red_step1, red_step2
+extern "C" void CB_MAXES(CB_T, )(CB_MAXES_ARGS) { launch_mulsum_axes<CB_C, false>(CB_MAXES_PASS); }
 #if CB_FLOAT
+extern "C" void CB_MAXES(CB_T, _nan)(CB_MAXES_ARGS) { launch_mulsum_axes<CB_C, true>(CB_MAXES_PASS); }
 extern "C" void CB_MSYM(CB_T, _nan, _reduce_kernel_launch)(char* p1, char* p2, char* p3, ssize_t s1, ssize_t s2, uint64_t n) {
     launch_mulsum_reduce<CB_C, true>(p1, p2, p3, s1, s2, n);
 }

@@ -1611,7 +1611,22 @@ cb200_na_t* cb200_na_mulsum(cb200_na_t* a, cb200_na_t* b, uint32_t axis_mask, in
         FnR fr = (FnR)sym(base + "_reduce_kernel_launch");
         FnE fe = (FnE)sym(base + "_kernel_launch");
         ok = fr && fe;
-        if (ok) {
+        int64_t outer_runs = 1;
+        for (int d = 0; d + 1 < L.nd; ++d) outer_runs *= L.n[d];
+        if (ok && outer_runs >= 64) {
+            // many runs: the whole loop in one launch instead of one launch per run
+            using FnAxes = void (*)(char*, char*, char*, int, const size_t*, const ssize_t*, const ssize_t*, const ssize_t*, int, const size_t*, const ssize_t*, const ssize_t*);
+            FnAxes fa = (FnAxes)sym(std::string("cb200_") + kTypeName[dtype] + "_mulsum" + ((nan && is_float_type(dtype)) ? "_nan" : "") + "_axes_kernel_launch");
+            ok = fa != nullptr;
+            if (ok) {
+                size_t kshape[kMaxD], rshape[kMaxD];
+                ssize_t k1[kMaxD], k2[kMaxD], k3[kMaxD], r1[kMaxD], r2[kMaxD];
+                for (int i = 0; i < rp.n_keep; ++i) { kshape[i] = (size_t)lp.shape[rp.keep[i]]; k1[i] = sx.step[rp.keep[i]]; k2[i] = sy.step[rp.keep[i]]; k3[i] = (ssize_t)out->step[i]; }
+                for (int i = 0; i < rp.n_red; ++i) { rshape[i] = (size_t)lp.shape[rp.red[i]]; r1[i] = sx.step[rp.red[i]]; r2[i] = sy.step[rp.red[i]]; }
+                fa(sx.ptr, sy.ptr, data_ptr(out), rp.n_keep, kshape, k1, k2, k3, rp.n_red, rshape, r1, r2);
+                ok = launch_ok();
+            }
+        } else if (ok) {
             const int in = L.nd - 1;
             for_outer(L, 3, [&](const int64_t* off) {
                 char* p1 = sx.ptr + off[0];

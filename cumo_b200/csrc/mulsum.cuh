@@ -128,3 +128,187 @@ void launch_mulsum_each(char* p1, char* p2, char* p3, ssize_t s1, ssize_t s2, ss
 }
 
 }  // namespace cb200
+
+// ---- many outputs in one launch ----------------------------------------------------------------------------------------------
+// `a.mulsum(b, axis: k)` of arrays with other dimensions is one sum of products per output element.  The reference's
+// ndloop calls its iterator once per innermost run (gen/tmpl/accum_binary.c:9-46): the integer `dot` of two matrices,
+// which is a mulsum over a new axis (lib/cumo/narray/extra.rb:1145-1196), is one launch per element of the result.
+// Here the whole loop is one launch: the kept dimensions with the byte steps of both inputs and of the output, the summed
+// dimensions with the byte steps of both inputs; each output gets the sum added to it.
+namespace cb200 {
+
+struct MulSumAxes {
+    int n_keep, n_red;
+    int64_t outputs, reduced;
+    int64_t kshape[kMaxDim], ks1[kMaxDim], ks2[kMaxDim], ks3[kMaxDim];
+    int64_t rshape[kMaxDim], rs1[kMaxDim], rs2[kMaxDim];
+};
+
+__device__ __forceinline__ void mulsum_output_of(const MulSumAxes& c, int64_t o, int64_t* o1, int64_t* o2, int64_t* o3) {
+    int64_t a = 0, b = 0, q = 0, r = o;
+    for (int d = c.n_keep - 1; d >= 0; --d) {
+        const int64_t n = c.kshape[d];
+        const int64_t k = d > 0 ? r % n : r;
+        r = d > 0 ? r / n : 0;
+        a += k * c.ks1[d]; b += k * c.ks2[d]; q += k * c.ks3[d];
+    }
+    *o1 = a; *o2 = b; *o3 = q;
+}
+
+__device__ __forceinline__ void mulsum_reduced_of(const MulSumAxes& c, int64_t j, int upto, int64_t* o1, int64_t* o2) {
+    int64_t a = 0, b = 0, r = j;
+    for (int d = upto; d >= 0; --d) {
+        const int64_t n = c.rshape[d];
+        const int64_t k = d > 0 ? r % n : r;
+        r = d > 0 ? r / n : 0;
+        a += k * c.rs1[d]; b += k * c.rs2[d];
+    }
+    *o1 = a; *o2 = b;
+}
+
+// ROWS: the innermost summed dimension is long: G threads per output (a warp, or the whole CTA for long sums) stride over it
+template <typename T, bool NAN_SKIP, int G>
+__global__ void __launch_bounds__(kBlock)
+mulsum_rows_kernel(const MulSumAxes c, const char* __restrict__ p1, const char* __restrict__ p2, char* p3) {
+    using R = MulSumR<T, NAN_SKIP>;
+    __shared__ T smem[kWarpsPerBlock];
+    R r;
+    const int last = c.n_red - 1;
+    const int64_t run = c.rshape[last];
+    const int64_t runs = c.reduced / run;
+    const int64_t s1 = c.rs1[last], s2 = c.rs2[last];
+    const int member = threadIdx.x % G;
+    const int64_t group = ((int64_t)blockIdx.x * kBlock + threadIdx.x) / G;
+    const int64_t n_groups = (int64_t)gridDim.x * kBlock / G;
+    for (int64_t o = group; o < c.outputs; o += n_groups) {
+        int64_t o1, o2, o3;
+        mulsum_output_of(c, o, &o1, &o2, &o3);
+        T acc = 0;
+        for (int64_t j = 0; j < runs; ++j) {
+            int64_t a = 0, b = 0;
+            if (last > 0) mulsum_reduced_of(c, j, last - 1, &a, &b);
+            const char* q1 = p1 + o1 + a;
+            const char* q2 = p2 + o2 + b;
+            for (int64_t e0 = member; e0 < run; e0 += (int64_t)G * 4) {
+                T x[4], y[4];
+#pragma unroll
+                for (int u = 0; u < 4; ++u) {
+                    const int64_t e = e0 + (int64_t)u * G;
+                    if (e < run) { x[u] = ld_one<T>(q1 + e * s1); y[u] = ld_one<T>(q2 + e * s2); }
+                }
+#pragma unroll
+                for (int u = 0; u < 4; ++u)
+                    if (e0 + (int64_t)u * G < run) R::fma_into(x[u], y[u], acc);
+            }
+        }
+        if (G == 32) acc = warp_fold(r, acc);
+        else { acc = group_fold<R, kBlock>(r, acc, smem); __syncthreads(); }
+        if (member == 0) {
+            T* z = reinterpret_cast<T*>(p3 + o3);
+            *z = *z + acc;
+        }
+    }
+}
+
+// COLUMNS: a thread per (slice, output) walking its part of the summed elements in order; consecutive threads are consecutive
+// outputs.  With one slice the sum is added to the output; with more the partial sums go to `partial` for the fold below.
+template <typename T, bool NAN_SKIP>
+__global__ void __launch_bounds__(kBlock)
+mulsum_columns_kernel(const MulSumAxes c, const char* __restrict__ p1, const char* __restrict__ p2, char* p3, int64_t slice_len, int64_t slices, T* partial) {
+    using R = MulSumR<T, NAN_SKIP>;
+    const int64_t total = slices * c.outputs;
+    for (int64_t t = (int64_t)blockIdx.x * kBlock + threadIdx.x; t < total; t += (int64_t)gridDim.x * kBlock) {
+        const int64_t sl = t / c.outputs, o = t - sl * c.outputs;
+        int64_t o1, o2, o3;
+        mulsum_output_of(c, o, &o1, &o2, &o3);
+        const int64_t j_begin = sl * slice_len;
+        const int64_t j_end = j_begin + slice_len < c.reduced ? j_begin + slice_len : c.reduced;
+        T acc = 0;
+        for (int64_t j0 = j_begin; j0 < j_end; j0 += 4) {
+            T x[4], y[4];
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+                if (j0 + u >= j_end) break;
+                int64_t a, b;
+                if (c.n_red == 1) { a = (j0 + u) * c.rs1[0]; b = (j0 + u) * c.rs2[0]; }
+                else mulsum_reduced_of(c, j0 + u, c.n_red - 1, &a, &b);
+                x[u] = ld_one<T>(p1 + o1 + a);
+                y[u] = ld_one<T>(p2 + o2 + b);
+            }
+#pragma unroll
+            for (int u = 0; u < 4; ++u)
+                if (j0 + u < j_end) R::fma_into(x[u], y[u], acc);
+        }
+        if (partial) partial[t] = acc;
+        else { T* z = reinterpret_cast<T*>(p3 + o3); *z = *z + acc; }
+    }
+}
+
+template <typename T>
+__global__ void __launch_bounds__(kBlock)
+mulsum_slices_fold_kernel(const MulSumAxes c, const T* __restrict__ partial, int64_t slices, char* p3) {
+    for (int64_t o = (int64_t)blockIdx.x * kBlock + threadIdx.x; o < c.outputs; o += (int64_t)gridDim.x * kBlock) {
+        int64_t o1, o2, o3;
+        mulsum_output_of(c, o, &o1, &o2, &o3);
+        T acc = partial[o];
+        for (int64_t sl = 1; sl < slices; ++sl) acc += partial[sl * c.outputs + o];         // slice order: the same sum every run
+        T* z = reinterpret_cast<T*>(p3 + o3);
+        *z = *z + acc;
+    }
+}
+
+template <typename T, bool NAN_SKIP>
+void launch_mulsum_axes(char* p1, char* p2, char* p3, int n_keep, const size_t* kshape, const ssize_t* ks1, const ssize_t* ks2, const ssize_t* ks3,
+                        int n_red, const size_t* rshape, const ssize_t* rs1, const ssize_t* rs2) {
+    CB200_TRACE_LAUNCH();
+    if (n_keep < 0 || n_red < 0 || n_keep > kMaxDim || n_red > kMaxDim) return;
+    MulSumAxes c;
+    c.n_keep = 0; c.n_red = 0; c.outputs = 1; c.reduced = 1;
+    for (int d = 0; d < kMaxDim; ++d) { c.kshape[d] = c.rshape[d] = 1; c.ks1[d] = c.ks2[d] = c.ks3[d] = c.rs1[d] = c.rs2[d] = 0; }
+    for (int d = 0; d < n_keep; ++d) {
+        if (kshape[d] == 0) return;
+        if (kshape[d] == 1) continue;
+        c.kshape[c.n_keep] = (int64_t)kshape[d]; c.ks1[c.n_keep] = ks1[d]; c.ks2[c.n_keep] = ks2[d]; c.ks3[c.n_keep] = ks3[d];
+        c.outputs *= c.kshape[c.n_keep++];
+    }
+    for (int d = 0; d < n_red; ++d) {
+        if (rshape[d] == 0) return;                         // an empty sum adds nothing
+        if (rshape[d] == 1) continue;
+        c.rshape[c.n_red] = (int64_t)rshape[d]; c.rs1[c.n_red] = rs1[d]; c.rs2[c.n_red] = rs2[d];
+        c.reduced *= c.rshape[c.n_red++];
+    }
+    if (c.n_red == 0) c.n_red = 1;                          // every output is one product
+    cudaStream_t st = current_stream();
+    const int last = c.n_red - 1;
+    int launches = 1;
+    // rows only when the lanes' consecutive elements are consecutive in memory (or repeated) in both inputs; a summed
+    // dimension with a long step is better walked by one thread per output, whose neighbours then share each line
+    constexpr int64_t ES = sizeof(T);
+    const bool along = (c.rs1[last] == ES || c.rs1[last] == 0) && (c.rs2[last] == ES || c.rs2[last] == 0);
+    if (along && c.rshape[last] >= 64) {
+        if (c.rshape[last] >= 8192) mulsum_rows_kernel<T, NAN_SKIP, kBlock><<<grid_for(c.outputs, 8), kBlock, 0, st>>>(c, p1, p2, p3);
+        else mulsum_rows_kernel<T, NAN_SKIP, 32><<<grid_for((c.outputs + kBlock / 32 - 1) / (kBlock / 32), 8), kBlock, 0, st>>>(c, p1, p2, p3);
+    } else {
+        const int64_t wanted = (int64_t)sm_count() * 2048;
+        int64_t slices = (wanted + c.outputs - 1) / c.outputs;
+        if (slices > c.reduced / 64) slices = c.reduced / 64;
+        if (slices < 1) slices = 1;
+        const int64_t slice_len = (c.reduced + slices - 1) / slices;
+        slices = (c.reduced + slice_len - 1) / slice_len;
+        T* partial = nullptr;
+        if (slices > 1) {
+            partial = reinterpret_cast<T*>(cumo_cuda_runtime_malloc(sizeof(T) * (size_t)(slices * c.outputs)));
+            if (!partial) return;
+        }
+        mulsum_columns_kernel<T, NAN_SKIP><<<grid_for((slices * c.outputs + kBlock - 1) / kBlock, 8), kBlock, 0, st>>>(c, p1, p2, p3, slice_len, slices, partial);
+        if (partial) {
+            mulsum_slices_fold_kernel<T><<<grid_for((c.outputs + kBlock - 1) / kBlock, 8), kBlock, 0, st>>>(c, partial, slices, p3);
+            cumo_cuda_runtime_free(reinterpret_cast<char*>(partial));
+            ++launches;
+        }
+    }
+    count_launch(launches);
+    cumo_cuda_runtime_check_kernel_launch();
+}
+
+}  // namespace cb200

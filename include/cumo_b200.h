@@ -230,6 +230,16 @@ const char* cb200_version(void);
     void cumo_##T##_mulsum##sfx##_reduce_kernel_launch(char* p1, char* p2, char* p3, ssize_t s1, ssize_t s2, uint64_t n); \
     void cumo_##T##_mulsum##sfx##_kernel_launch(char* p1, char* p2, char* p3, ssize_t s1, ssize_t s2, ssize_t s3, uint64_t n);
 
+/* mulsum over a whole loop in one launch: output k = (k_0 ..) gets sum over r of x*y ADDED to it, x at
+ * p1 + sum k_i*keep_step1[i] + sum r_j*red_step1[j], y likewise with the *2 steps, the output at p3 + sum k_i*keep_step3[i]
+ * (all byte steps; host arrays).  NOT in the reference, whose ndloop calls the two functions above once per innermost run
+ * (gen/tmpl/accum_binary.c:9-46) -- one launch per element of the result of an integer `dot`. */
+#define CB200_DECL_MULSUM_AXES(T, sfx) \
+    void cb200_##T##_mulsum##sfx##_axes_kernel_launch(char* p1, char* p2, char* p3, int n_keep, const size_t* keep_shape, const ssize_t* keep_step1, \
+        const ssize_t* keep_step2, const ssize_t* keep_step3, int n_red, const size_t* red_shape, const ssize_t* red_step1, const ssize_t* red_step2);
+CB200_DECL_MULSUM_AXES(sfloat, ) CB200_DECL_MULSUM_AXES(dfloat, ) CB200_DECL_MULSUM_AXES(int32, ) CB200_DECL_MULSUM_AXES(int64, )
+CB200_DECL_MULSUM_AXES(sfloat, _nan) CB200_DECL_MULSUM_AXES(dfloat, _nan)
+
 /* store / cast from another element type (also the plain strided copy when the types
  * match), reference: gen/tmpl/store_from.c:2, store_from_kernel.cu:38-53.  NOTE the
  * argument order: a1 is the DESTINATION, a2 the source. */

@@ -363,10 +363,17 @@ __global__ void __launch_bounds__(kBlock)
 scan_columns_carry_kernel(int64_t runs, int64_t segs, T* partial) {
     for (int64_t r = (int64_t)blockIdx.x * kBlock + threadIdx.x; r < runs; r += (int64_t)gridDim.x * kBlock) {
         T acc = partial[r];
-        for (int64_t seg = 1; seg < segs; ++seg) {
-            const T mine = partial[seg * runs + r];
-            partial[seg * runs + r] = acc;                 // everything before this segment
-            acc = Op::combine(acc, mine);
+        for (int64_t seg0 = 1; seg0 < segs; seg0 += kColAhead) {
+            T mine[kColAhead];                              // the loads do not depend on the chain of combines: fetch ahead
+#pragma unroll
+            for (int k = 0; k < kColAhead; ++k)
+                if (seg0 + k < segs) mine[k] = partial[(seg0 + k) * runs + r];
+#pragma unroll
+            for (int k = 0; k < kColAhead; ++k) {
+                if (seg0 + k >= segs) break;
+                partial[(seg0 + k) * runs + r] = acc;      // everything before this segment
+                acc = Op::combine(acc, mine[k]);
+            }
         }
     }
 }

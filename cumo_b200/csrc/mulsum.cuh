@@ -167,7 +167,9 @@ __device__ __forceinline__ void mulsum_reduced_of(const MulSumAxes& c, int64_t j
 }
 
 // ROWS: the innermost summed dimension is long: G threads per output (a warp, or the whole CTA for long sums) stride over it
-template <typename T, bool NAN_SKIP, int G>
+// VEC: both inputs contiguous along the summed dimension with every run starting on a 16-byte boundary and holding whole
+// packets: 16-byte loads, two packets per input in flight per thread.
+template <typename T, bool NAN_SKIP, int G, bool VEC>
 __global__ void __launch_bounds__(kBlock)
 mulsum_rows_kernel(const MulSumAxes c, const char* __restrict__ p1, const char* __restrict__ p2, char* p3) {
     using R = MulSumR<T, NAN_SKIP>;
@@ -189,6 +191,25 @@ mulsum_rows_kernel(const MulSumAxes c, const char* __restrict__ p1, const char* 
             if (last > 0) mulsum_reduced_of(c, j, last - 1, &a, &b);
             const char* q1 = p1 + o1 + a;
             const char* q2 = p2 + o2 + b;
+            if constexpr (VEC) {
+                constexpr int V = 16 / (int)sizeof(T);
+                const int64_t packets = run / V;
+                for (int64_t k0 = member; k0 < packets; k0 += (int64_t)G * 2) {
+                    Pack<T> x[2], y[2];
+#pragma unroll
+                    for (int u = 0; u < 2; ++u) {
+                        const int64_t k = k0 + (int64_t)u * G;
+                        if (k < packets) { x[u] = ld_pack<T>(q1 + k * 16); y[u] = ld_pack<T>(q2 + k * 16); }
+                    }
+#pragma unroll
+                    for (int u = 0; u < 2; ++u) {
+                        if (k0 + (int64_t)u * G >= packets) break;
+#pragma unroll
+                        for (int e = 0; e < V; ++e) R::fma_into(x[u].v[e], y[u].v[e], acc);
+                    }
+                }
+                continue;
+            }
             for (int64_t e0 = member; e0 < run; e0 += (int64_t)G * 4) {
                 T x[4], y[4];
 #pragma unroll
@@ -286,8 +307,17 @@ void launch_mulsum_axes(char* p1, char* p2, char* p3, int n_keep, const size_t* 
     constexpr int64_t ES = sizeof(T);
     const bool along = (c.rs1[last] == ES || c.rs1[last] == 0) && (c.rs2[last] == ES || c.rs2[last] == 0);
     if (along && c.rshape[last] >= 64) {
-        if (c.rshape[last] >= 8192) mulsum_rows_kernel<T, NAN_SKIP, kBlock><<<grid_for(c.outputs, 8), kBlock, 0, st>>>(c, p1, p2, p3);
-        else mulsum_rows_kernel<T, NAN_SKIP, 32><<<grid_for((c.outputs + kBlock / 32 - 1) / (kBlock / 32), 8), kBlock, 0, st>>>(c, p1, p2, p3);
+        bool vec = c.rs1[last] == ES && c.rs2[last] == ES && aligned16(p1) && aligned16(p2) && c.rshape[last] % (16 / ES) == 0;
+        for (int d = 0; d < c.n_keep && vec; ++d) vec = mult16(c.ks1[d]) && mult16(c.ks2[d]);
+        for (int d = 0; d < last && vec; ++d) vec = mult16(c.rs1[d]) && mult16(c.rs2[d]);
+        const unsigned g_cta = grid_for(c.outputs, 8), g_warp = grid_for((c.outputs + kBlock / 32 - 1) / (kBlock / 32), 8);
+        if (c.rshape[last] >= 8192) {
+            if (vec) mulsum_rows_kernel<T, NAN_SKIP, kBlock, true><<<g_cta, kBlock, 0, st>>>(c, p1, p2, p3);
+            else mulsum_rows_kernel<T, NAN_SKIP, kBlock, false><<<g_cta, kBlock, 0, st>>>(c, p1, p2, p3);
+        } else {
+            if (vec) mulsum_rows_kernel<T, NAN_SKIP, 32, true><<<g_warp, kBlock, 0, st>>>(c, p1, p2, p3);
+            else mulsum_rows_kernel<T, NAN_SKIP, 32, false><<<g_warp, kBlock, 0, st>>>(c, p1, p2, p3);
+        }
     } else {
         const int64_t wanted = (int64_t)sm_count() * 2048;
         int64_t slices = (wanted + c.outputs - 1) / c.outputs;

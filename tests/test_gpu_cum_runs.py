@@ -62,3 +62,28 @@ def test_scans_along_an_axis_of_views():
     for what, (view, ref) in cases.items():
         for axis in (0, 1):
             assert np.array_equal(view.cumsum(axis=axis).to_numpy(), np.cumsum(ref, axis=axis)), (what, axis)
+
+
+@pytest.mark.parametrize("n", [64 * 4096, 64 * 4096 + 1, (1 << 22) + 5, 3_000_017])
+def test_long_flat_scans(n):
+    """Flat runs of 64 tiles and more (the three-launch plan): exact for integers, NaN rules kept, strided and reversed runs."""
+    import cumo_b200 as xp
+
+    rng = np.random.default_rng(n)
+    host = rng.integers(-9, 10, size=n).astype(np.int64)
+    a = xp.Int64.from_numpy(host)
+    assert np.array_equal(a.cumsum().to_numpy(), np.cumsum(host))
+    assert np.array_equal(a[::-1].cumsum().to_numpy(), np.cumsum(host[::-1]))
+    h32 = host.astype(np.int32)
+    assert np.array_equal(xp.Int32.from_numpy(h32).cumsum().to_numpy(), np.cumsum(h32, dtype=np.int32))
+    wide = xp.Int32.from_numpy(np.repeat(h32[: n // 2], 2))[::2]                       # a strided run
+    assert np.array_equal(wide.cumsum().to_numpy(), np.cumsum(h32[: n // 2], dtype=np.int32))
+    f = (rng.integers(-64, 65, size=n) / 8.0).astype(np.float32)
+    f[::4099] = np.nan
+    got = xp.SFloat.from_numpy(f).cumsum(nan=True).to_numpy()
+    want = np.cumsum(np.where(np.isnan(f), 0, f).astype(np.float64))
+    seen = np.cumsum(~np.isnan(f)) > 0
+    assert np.array_equal(np.isnan(got), ~seen) and np.allclose(got[seen], want[seen], rtol=0, atol=1e-5 * np.abs(f[~np.isnan(f)]).sum())
+    ones = np.where(rng.random(n) < 0.001, 2.0, 1.0)
+    ones[rng.random(n) < 0.001] = 0.5
+    assert np.allclose(xp.DFloat.from_numpy(ones).cumprod().to_numpy(), np.cumprod(ones), rtol=1e-12)

@@ -302,26 +302,53 @@ scan_rows_kernel(const ScanRuns o, const char* __restrict__ p1, int64_t s1, char
 // COLUMNS: a thread per run, in element order; consecutive threads are consecutive runs, so when the runs lie side by
 // side in memory (a scan along an outer axis) every step of a warp is one coalesced access.  Loads run kColAhead
 // elements ahead of the dependent chain of combines.
+// V > 1: V runs that lie side by side per thread, one 16-byte packet of them per step (the launch checks the alignment).
 constexpr int kColAhead = 8;
-template <typename T, typename Op>
+
+template <typename T, int V>
+__device__ __forceinline__ void load_group(const char* q, T (&x)[V]) {
+    if constexpr (V > 1) {
+        const Pack<T> v = ld_pack<T>(q);
+#pragma unroll
+        for (int e = 0; e < V; ++e) x[e] = v.v[e];
+    } else {
+        x[0] = *reinterpret_cast<const T*>(q);
+    }
+}
+template <typename T, int V>
+__device__ __forceinline__ void store_group(char* q, const T (&x)[V]) {
+    if constexpr (V > 1) {
+        Pack<T> v;
+#pragma unroll
+        for (int e = 0; e < V; ++e) v.v[e] = x[e];
+        st_pack<T>(q, v);
+    } else {
+        *reinterpret_cast<T*>(q) = x[0];
+    }
+}
+
+template <typename T, typename Op, int V>
 __global__ void __launch_bounds__(kBlock)
 scan_columns_kernel(const ScanRuns o, const char* __restrict__ p1, int64_t s1, char* p2, int64_t s2, int64_t n) {
-    for (int64_t r = (int64_t)blockIdx.x * kBlock + threadIdx.x; r < o.runs; r += (int64_t)gridDim.x * kBlock) {
+    constexpr int AHEAD = V > 1 ? kColAhead / 2 : kColAhead;
+    const int64_t groups = o.runs / V;
+    for (int64_t g = (int64_t)blockIdx.x * kBlock + threadIdx.x; g < groups; g += (int64_t)gridDim.x * kBlock) {
         int64_t off1, off2;
-        run_offsets(o, r, &off1, &off2);
+        run_offsets(o, g * V, &off1, &off2);
         const char* src = p1 + off1;
         char* dst = p2 + off2;
-        T acc = T();
-        for (int64_t j0 = 0; j0 < n; j0 += kColAhead) {
-            T x[kColAhead];
+        T acc[V];
+        for (int64_t j0 = 0; j0 < n; j0 += AHEAD) {
+            T x[AHEAD][V];
 #pragma unroll
-            for (int k = 0; k < kColAhead; ++k)
-                if (j0 + k < n) x[k] = *reinterpret_cast<const T*>(src + (j0 + k) * s1);
+            for (int k = 0; k < AHEAD; ++k)
+                if (j0 + k < n) load_group<T, V>(src + (j0 + k) * s1, x[k]);
 #pragma unroll
-            for (int k = 0; k < kColAhead; ++k) {
+            for (int k = 0; k < AHEAD; ++k) {
                 if (j0 + k >= n) break;
-                acc = (j0 + k == 0) ? x[k] : Op::combine(acc, x[k]);
-                *reinterpret_cast<T*>(dst + (j0 + k) * s2) = acc;
+#pragma unroll
+                for (int e = 0; e < V; ++e) acc[e] = (j0 + k == 0) ? x[k][e] : Op::combine(acc[e], x[k][e]);
+                store_group<T, V>(dst + (j0 + k) * s2, acc);
             }
         }
     }
@@ -331,30 +358,34 @@ scan_columns_kernel(const ScanRuns o, const char* __restrict__ p1, int64_t s1, c
 // the GPU idle, so every run is cut into `segs` segments of `seg_len` elements and a thread takes one (segment, run):
 // (1) fold of each segment, (2) per run, the folds become the fold of everything before each segment, (3) the scan of
 // each segment starting from that.  Consecutive threads are still consecutive runs, so every access stays coalesced.
-template <typename T, typename Op>
+template <typename T, typename Op, int V>
 __global__ void __launch_bounds__(kBlock)
 scan_columns_fold_kernel(const ScanRuns o, const char* __restrict__ p1, int64_t s1, int64_t n, int64_t seg_len, int64_t segs, T* partial) {
-    const int64_t total = segs * o.runs;
+    constexpr int AHEAD = V > 1 ? kColAhead / 2 : kColAhead;
+    const int64_t groups = o.runs / V;
+    const int64_t total = segs * groups;
     for (int64_t t = (int64_t)blockIdx.x * kBlock + threadIdx.x; t < total; t += (int64_t)gridDim.x * kBlock) {
-        const int64_t seg = t / o.runs, r = t - seg * o.runs;
+        const int64_t seg = t / groups, r = (t - seg * groups) * V;
         int64_t off1, off2;
         run_offsets(o, r, &off1, &off2);
         const char* src = p1 + off1;
         const int64_t j_begin = seg * seg_len;
         const int64_t j_end = j_begin + seg_len < n ? j_begin + seg_len : n;
-        T acc = T();
-        for (int64_t j0 = j_begin; j0 < j_end; j0 += kColAhead) {
-            T x[kColAhead];
+        T acc[V];
+        for (int64_t j0 = j_begin; j0 < j_end; j0 += AHEAD) {
+            T x[AHEAD][V];
 #pragma unroll
-            for (int k = 0; k < kColAhead; ++k)
-                if (j0 + k < j_end) x[k] = *reinterpret_cast<const T*>(src + (j0 + k) * s1);
+            for (int k = 0; k < AHEAD; ++k)
+                if (j0 + k < j_end) load_group<T, V>(src + (j0 + k) * s1, x[k]);
 #pragma unroll
-            for (int k = 0; k < kColAhead; ++k) {
+            for (int k = 0; k < AHEAD; ++k) {
                 if (j0 + k >= j_end) break;
-                acc = (j0 + k == j_begin) ? x[k] : Op::combine(acc, x[k]);
+#pragma unroll
+                for (int e = 0; e < V; ++e) acc[e] = (j0 + k == j_begin) ? x[k][e] : Op::combine(acc[e], x[k][e]);
             }
         }
-        partial[t] = acc;
+#pragma unroll
+        for (int e = 0; e < V; ++e) partial[seg * o.runs + r + e] = acc[e];
     }
 }
 
@@ -378,13 +409,15 @@ scan_columns_carry_kernel(int64_t runs, int64_t segs, T* partial) {
     }
 }
 
-template <typename T, typename Op>
+template <typename T, typename Op, int V>
 __global__ void __launch_bounds__(kBlock)
 scan_columns_write_kernel(const ScanRuns o, const char* __restrict__ p1, int64_t s1, char* p2, int64_t s2, int64_t n, int64_t seg_len, int64_t segs,
                           const T* __restrict__ partial) {
-    const int64_t total = segs * o.runs;
+    constexpr int AHEAD = V > 1 ? kColAhead / 2 : kColAhead;
+    const int64_t groups = o.runs / V;
+    const int64_t total = segs * groups;
     for (int64_t t = (int64_t)blockIdx.x * kBlock + threadIdx.x; t < total; t += (int64_t)gridDim.x * kBlock) {
-        const int64_t seg = t / o.runs, r = t - seg * o.runs;
+        const int64_t seg = t / groups, r = (t - seg * groups) * V;
         int64_t off1, off2;
         run_offsets(o, r, &off1, &off2);
         const char* src = p1 + off1;
@@ -392,17 +425,20 @@ scan_columns_write_kernel(const ScanRuns o, const char* __restrict__ p1, int64_t
         const int64_t j_begin = seg * seg_len;
         const int64_t j_end = j_begin + seg_len < n ? j_begin + seg_len : n;
         const bool have_carry = seg > 0;
-        T acc = have_carry ? partial[t] : T();
-        for (int64_t j0 = j_begin; j0 < j_end; j0 += kColAhead) {
-            T x[kColAhead];
+        T acc[V];
 #pragma unroll
-            for (int k = 0; k < kColAhead; ++k)
-                if (j0 + k < j_end) x[k] = *reinterpret_cast<const T*>(src + (j0 + k) * s1);
+        for (int e = 0; e < V; ++e) acc[e] = have_carry ? partial[seg * o.runs + r + e] : T();
+        for (int64_t j0 = j_begin; j0 < j_end; j0 += AHEAD) {
+            T x[AHEAD][V];
 #pragma unroll
-            for (int k = 0; k < kColAhead; ++k) {
+            for (int k = 0; k < AHEAD; ++k)
+                if (j0 + k < j_end) load_group<T, V>(src + (j0 + k) * s1, x[k]);
+#pragma unroll
+            for (int k = 0; k < AHEAD; ++k) {
                 if (j0 + k >= j_end) break;
-                acc = (j0 + k == j_begin && !have_carry) ? x[k] : Op::combine(acc, x[k]);
-                *reinterpret_cast<T*>(dst + (j0 + k) * s2) = acc;
+#pragma unroll
+                for (int e = 0; e < V; ++e) acc[e] = (j0 + k == j_begin && !have_carry) ? x[k][e] : Op::combine(acc[e], x[k][e]);
+                store_group<T, V>(dst + (j0 + k) * s2, acc);
             }
         }
     }
@@ -435,25 +471,34 @@ cudaError_t launch_scan_runs(char* p1, char* p2, ssize_t s1, ssize_t s2, uint64_
         const bool packed_out = s2 == (ssize_t)sizeof(T) && aligned16(p2) && steps16;
         scan_rows_kernel<T, Op><<<grid_for(o.runs, sizeof(T) <= 4 ? 4 : 3), kBlock, 0, st>>>(o, p1, s1, p2, s2, n, packed_in, packed_out);
     } else {
+        // groups of V runs that lie side by side go by 16-byte packets when every access stays aligned
+        constexpr int VMAX = 16 / (int)sizeof(T);
+        bool wide = side_by_side && o.shape[o.nd - 1] % VMAX == 0 && aligned16(p1) && aligned16(p2) && mult16(s1) && mult16(s2);
+        for (int d = 0; d + 1 < o.nd && wide; ++d) wide = mult16(o.step1[d]) && mult16(o.step2[d]);
+        const int64_t groups = wide ? o.runs / VMAX : o.runs;
         // enough threads to fill the GPU: cut the runs into segments of at least 64 elements when the runs alone are too few
         const int64_t wanted = (int64_t)sm_count() * 2048;
-        int64_t segs = (wanted + o.runs - 1) / o.runs;
+        int64_t segs = (wanted + groups - 1) / groups;
         if (segs > n / 64) segs = n / 64;
         if (segs >= 2) {
             const int64_t seg_len = (n + segs - 1) / segs;
             segs = (n + seg_len - 1) / seg_len;
-            const int64_t total = segs * o.runs;
-            T* partial = reinterpret_cast<T*>(cumo_cuda_runtime_malloc(sizeof(T) * (size_t)total));
+            const int64_t total = segs * groups;
+            T* partial = reinterpret_cast<T*>(cumo_cuda_runtime_malloc(sizeof(T) * (size_t)(segs * o.runs)));
             if (!partial) return cudaErrorMemoryAllocation;
-            scan_columns_fold_kernel<T, Op><<<grid_for((total + kBlock - 1) / kBlock, 8), kBlock, 0, st>>>(o, p1, s1, n, seg_len, segs, partial);
+            const unsigned grid = grid_for((total + kBlock - 1) / kBlock, 8);
+            if (wide) scan_columns_fold_kernel<T, Op, VMAX><<<grid, kBlock, 0, st>>>(o, p1, s1, n, seg_len, segs, partial);
+            else scan_columns_fold_kernel<T, Op, 1><<<grid, kBlock, 0, st>>>(o, p1, s1, n, seg_len, segs, partial);
             scan_columns_carry_kernel<T, Op><<<grid_for((o.runs + kBlock - 1) / kBlock, 8), kBlock, 0, st>>>(o.runs, segs, partial);
-            scan_columns_write_kernel<T, Op><<<grid_for((total + kBlock - 1) / kBlock, 8), kBlock, 0, st>>>(o, p1, s1, p2, s2, n, seg_len, segs, partial);
+            if (wide) scan_columns_write_kernel<T, Op, VMAX><<<grid, kBlock, 0, st>>>(o, p1, s1, p2, s2, n, seg_len, segs, partial);
+            else scan_columns_write_kernel<T, Op, 1><<<grid, kBlock, 0, st>>>(o, p1, s1, p2, s2, n, seg_len, segs, partial);
             count_launch(3);
             const cudaError_t e = cudaGetLastError();
             cumo_cuda_runtime_free(reinterpret_cast<char*>(partial));     // stream-ordered reuse: later kernels queue behind these
             return e;
         }
-        scan_columns_kernel<T, Op><<<grid_for((o.runs + kBlock - 1) / kBlock, 8), kBlock, 0, st>>>(o, p1, s1, p2, s2, n);
+        if (wide) scan_columns_kernel<T, Op, VMAX><<<grid_for((groups + kBlock - 1) / kBlock, 8), kBlock, 0, st>>>(o, p1, s1, p2, s2, n);
+        else scan_columns_kernel<T, Op, 1><<<grid_for((groups + kBlock - 1) / kBlock, 8), kBlock, 0, st>>>(o, p1, s1, p2, s2, n);
     }
     count_launch();
     return cudaGetLastError();

@@ -231,37 +231,55 @@ mulsum_rows_kernel(const MulSumAxes c, const char* __restrict__ p1, const char* 
     }
 }
 
-// COLUMNS: a thread per (slice, output) walking its part of the summed elements in order; consecutive threads are consecutive
-// outputs.  With one slice the sum is added to the output; with more the partial sums go to `partial` for the fold below.
-template <typename T, bool NAN_SKIP>
+// COLUMNS: a thread per (slice, V consecutive outputs) walking its part of the summed elements in order; consecutive threads
+// are consecutive outputs.  V > 1 when the innermost kept dimension is contiguous (or repeated) in both inputs and in the
+// output and everything is 16-byte aligned: one packet of each input per step.  With one slice the sums are added to the
+// outputs; with more the partial sums go to `partial` (V per thread, side by side) for the fold below.
+template <typename T, bool NAN_SKIP, int V>
 __global__ void __launch_bounds__(kBlock)
 mulsum_columns_kernel(const MulSumAxes c, const char* __restrict__ p1, const char* __restrict__ p2, char* p3, int64_t slice_len, int64_t slices, T* partial) {
     using R = MulSumR<T, NAN_SKIP>;
-    const int64_t total = slices * c.outputs;
+    const int64_t groups = c.outputs / V;
+    const int64_t total = slices * groups;
+    const bool wide1 = V > 1 && c.ks1[c.n_keep - 1] != 0, wide2 = V > 1 && c.ks2[c.n_keep - 1] != 0;
     for (int64_t t = (int64_t)blockIdx.x * kBlock + threadIdx.x; t < total; t += (int64_t)gridDim.x * kBlock) {
-        const int64_t sl = t / c.outputs, o = t - sl * c.outputs;
+        const int64_t sl = t / groups, o = (t - sl * groups) * V;
         int64_t o1, o2, o3;
         mulsum_output_of(c, o, &o1, &o2, &o3);
         const int64_t j_begin = sl * slice_len;
         const int64_t j_end = j_begin + slice_len < c.reduced ? j_begin + slice_len : c.reduced;
-        T acc = 0;
+        T acc[V];
+#pragma unroll
+        for (int e = 0; e < V; ++e) acc[e] = 0;
         for (int64_t j0 = j_begin; j0 < j_end; j0 += 4) {
-            T x[4], y[4];
+            Pack<T> x[4], y[4];
 #pragma unroll
             for (int u = 0; u < 4; ++u) {
                 if (j0 + u >= j_end) break;
                 int64_t a, b;
                 if (c.n_red == 1) { a = (j0 + u) * c.rs1[0]; b = (j0 + u) * c.rs2[0]; }
                 else mulsum_reduced_of(c, j0 + u, c.n_red - 1, &a, &b);
-                x[u] = ld_one<T>(p1 + o1 + a);
-                y[u] = ld_one<T>(p2 + o2 + b);
+                if (wide1) x[u] = ld_pack<T>(p1 + o1 + a);
+                else { const T v = ld_one<T>(p1 + o1 + a);
+#pragma unroll
+                       for (int e = 0; e < V; ++e) x[u].v[e] = v; }
+                if (wide2) y[u] = ld_pack<T>(p2 + o2 + b);
+                else { const T v = ld_one<T>(p2 + o2 + b);
+#pragma unroll
+                       for (int e = 0; e < V; ++e) y[u].v[e] = v; }
             }
 #pragma unroll
-            for (int u = 0; u < 4; ++u)
-                if (j0 + u < j_end) R::fma_into(x[u], y[u], acc);
+            for (int u = 0; u < 4; ++u) {
+                if (j0 + u >= j_end) break;
+#pragma unroll
+                for (int e = 0; e < V; ++e) R::fma_into(x[u].v[e], y[u].v[e], acc[e]);
+            }
         }
-        if (partial) partial[t] = acc;
-        else { T* z = reinterpret_cast<T*>(p3 + o3); *z = *z + acc; }
+#pragma unroll
+        for (int e = 0; e < V; ++e) {
+            if (partial) partial[sl * c.outputs + o + e] = acc[e];
+            else { T* z = reinterpret_cast<T*>(p3 + o3) + e; *z = *z + acc[e]; }
+        }
     }
 }
 
@@ -330,7 +348,14 @@ void launch_mulsum_axes(char* p1, char* p2, char* p3, int n_keep, const size_t* 
             partial = reinterpret_cast<T*>(cumo_cuda_runtime_malloc(sizeof(T) * (size_t)(slices * c.outputs)));
             if (!partial) return;
         }
-        mulsum_columns_kernel<T, NAN_SKIP><<<grid_for((slices * c.outputs + kBlock - 1) / kBlock, 8), kBlock, 0, st>>>(c, p1, p2, p3, slice_len, slices, partial);
+        constexpr int VMAX = 16 / (int)ES;
+        const int lk = c.n_keep - 1;
+        bool wide = lk >= 0 && c.ks3[lk] == ES && (c.ks1[lk] == ES || c.ks1[lk] == 0) && (c.ks2[lk] == ES || c.ks2[lk] == 0) &&
+                    (c.ks1[lk] != 0 || c.ks2[lk] != 0) && c.kshape[lk] % VMAX == 0 && aligned16(p1) && aligned16(p2) && aligned16(p3);
+        for (int d = 0; d < lk && wide; ++d) wide = mult16(c.ks1[d]) && mult16(c.ks2[d]) && mult16(c.ks3[d]);
+        for (int d = 0; d < c.n_red && wide; ++d) wide = mult16(c.rs1[d]) && mult16(c.rs2[d]);
+        if (wide) mulsum_columns_kernel<T, NAN_SKIP, VMAX><<<grid_for((slices * (c.outputs / VMAX) + kBlock - 1) / kBlock, 8), kBlock, 0, st>>>(c, p1, p2, p3, slice_len, slices, partial);
+        else mulsum_columns_kernel<T, NAN_SKIP, 1><<<grid_for((slices * c.outputs + kBlock - 1) / kBlock, 8), kBlock, 0, st>>>(c, p1, p2, p3, slice_len, slices, partial);
         if (partial) {
             mulsum_slices_fold_kernel<T><<<grid_for((c.outputs + kBlock - 1) / kBlock, 8), kBlock, 0, st>>>(c, partial, slices, p3);
             cumo_cuda_runtime_free(reinterpret_cast<char*>(partial));

@@ -122,9 +122,104 @@ void launch_bincount(char* p1, ssize_t s1, size_t* idx1, uint64_t count, char* p
     cumo_cuda_runtime_check_kernel_launch();
 }
 
+// ---- counting and sizing in one pass ---------------------------------------------------------------------------------------
+// The output of bincount is as long as the largest value says, so the reference reads the run twice: a min/max reduction to
+// size the output (bincount.c:99-131), then the counting kernel.  This probe does both at once for the common case of small
+// values: it counts every value in [0, kProbeBins) into a fixed histogram and records the extremes of ALL values.  A host that
+// finds 0 <= min and max < kProbeBins has its counts; otherwise it falls back to the two passes.  Values below kProbeFast go
+// to per-CTA histograms in shared memory (eight copies picked by lane), the rest of the range to global atomics.
+constexpr int kProbeBins = 8192;
+constexpr int kProbeFast = 1024;
+constexpr int kProbeCopies = 8;
+
+__global__ void bincount_probe_init_kernel(uint32_t* hist, long long* extremes) {
+    for (int b = blockIdx.x * blockDim.x + threadIdx.x; b < kProbeBins; b += gridDim.x * blockDim.x) hist[b] = 0u;
+    if (blockIdx.x == 0 && threadIdx.x == 0) { extremes[0] = 0x7fffffffffffffffLL; extremes[1] = -0x7fffffffffffffffLL - 1; }
+}
+
+template <typename TI>
+__global__ void __launch_bounds__(kBlock)
+bincount_probe_kernel(const char* __restrict__ p1, int64_t s1, uint64_t count, uint32_t* hist, long long* extremes) {
+    __shared__ uint32_t local[kProbeFast * kProbeCopies];
+    __shared__ long long lo_s[kWarpsPerBlock], hi_s[kWarpsPerBlock];
+    for (int b = threadIdx.x; b < kProbeFast * kProbeCopies; b += kBlock) local[b] = 0u;
+    __syncthreads();
+    uint32_t* mine = local + (threadIdx.x % kProbeCopies) * kProbeFast;
+    long long lo = 0x7fffffffffffffffLL, hi = -0x7fffffffffffffffLL - 1;
+    auto add = [&](TI x) {
+        const long long v = (long long)x;
+        lo = v < lo ? v : lo;
+        hi = v > hi ? v : hi;
+        if (v >= 0 && v < kProbeFast) atomicAdd(mine + v, 1u);
+        else if (v >= kProbeFast && v < kProbeBins) atomicAdd(hist + v, 1u);
+    };
+    constexpr int V = 16 / sizeof(TI);
+    const bool packed = s1 == (int64_t)sizeof(TI) && (reinterpret_cast<uintptr_t>(p1) & 15) == 0;
+    const uint64_t per_cta = (uint64_t)kBlock * kBinsPerThreadLoads;
+    for (uint64_t base = (uint64_t)blockIdx.x * per_cta; base < count; base += (uint64_t)gridDim.x * per_cta) {
+        if (packed && base + per_cta <= count) {
+            Pack<TI> v[kBinsPerThreadLoads / V];
+#pragma unroll
+            for (int j = 0; j < kBinsPerThreadLoads / V; ++j)
+                v[j] = ld_pack<TI>(p1 + (base + ((uint64_t)j * kBlock + threadIdx.x) * V) * sizeof(TI));
+#pragma unroll
+            for (int j = 0; j < kBinsPerThreadLoads / V; ++j)
+#pragma unroll
+                for (int e = 0; e < V; ++e) add(v[j].v[e]);
+        } else {
+            for (int j = 0; j < kBinsPerThreadLoads; ++j) {
+                const uint64_t i = base + (uint64_t)j * kBlock + threadIdx.x;
+                if (i < count) add(*reinterpret_cast<const TI*>(p1 + (int64_t)i * s1));
+            }
+        }
+    }
+#pragma unroll
+    for (int d = 16; d > 0; d >>= 1) {
+        const long long ol = __shfl_xor_sync(0xffffffffu, lo, d), oh = __shfl_xor_sync(0xffffffffu, hi, d);
+        lo = ol < lo ? ol : lo;
+        hi = oh > hi ? oh : hi;
+    }
+    if ((threadIdx.x & 31) == 0) { lo_s[threadIdx.x >> 5] = lo; hi_s[threadIdx.x >> 5] = hi; }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        for (int w = 1; w < kWarpsPerBlock; ++w) { lo = lo_s[w] < lo ? lo_s[w] : lo; hi = hi_s[w] > hi ? hi_s[w] : hi; }
+        atomicMin(extremes, lo);
+        atomicMax(extremes + 1, hi);
+    }
+    for (int b = threadIdx.x; b < kProbeFast; b += kBlock) {
+        uint32_t c = 0;
+#pragma unroll
+        for (int r = 0; r < kProbeCopies; ++r) c += local[r * kProbeFast + b];
+        if (c) atomicAdd(hist + b, c);
+    }
+}
+
+template <typename TI>
+void launch_bincount_probe(char* p1, ssize_t s1, uint64_t count, uint32_t* hist, long long* extremes) {
+    CB200_TRACE_LAUNCH();
+    cudaStream_t st = current_stream();
+    bincount_probe_init_kernel<<<8, 256, 0, st>>>(hist, extremes);
+    int launches = 1;
+    if (count > 0) {
+        const uint64_t per_cta = (uint64_t)kBlock * kBinsPerThreadLoads;
+        bincount_probe_kernel<TI><<<grid_for((int64_t)((count + per_cta - 1) / per_cta), 8), kBlock, 0, st>>>(p1, s1, count, hist, extremes);
+        ++launches;
+    }
+    count_launch(launches);
+    cumo_cuda_runtime_check_kernel_launch();
+}
+
 }  // namespace cb200
 
 using namespace cb200;
+
+extern "C" int cb200_bincount_probe_bins(void) { return kProbeBins; }
+extern "C" void cb200_int32_bincount_probe_kernel_launch(char* p1, ssize_t s1, uint64_t count, uint32_t* hist, long long* extremes) {
+    launch_bincount_probe<int32_t>(p1, s1, count, hist, extremes);
+}
+extern "C" void cb200_int64_bincount_probe_kernel_launch(char* p1, ssize_t s1, uint64_t count, uint32_t* hist, long long* extremes) {
+    launch_bincount_probe<int64_t>(p1, s1, count, hist, extremes);
+}
 
 #define CB200_DEF_BINCOUNT(T, C)                                                                                                   \
     extern "C" void cumo_iter_##T##_bincount_32_kernel_launch(char* p1, ssize_t s1, size_t* idx1, uint64_t count, char* p2,        \

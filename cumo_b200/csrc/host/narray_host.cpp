@@ -1053,6 +1053,42 @@ cb200_na_t* cb200_na_bincount(cb200_na_t* a, cb200_na_t* weight, int64_t minleng
         return (cb200_na*)fail("ShapeError", last_ok ? "weights of a different shape are not on this path" : "size mismatch along last axis between self and weight");
     }
     int64_t length = 0;
+    // one unweighted run of small values: counted and sized in the same pass
+    if (!w && a->ndim == 1 && size_of(a) > 0) {
+        using FnProbe = void (*)(char*, ssize_t, uint64_t, uint32_t*, long long*);
+        using FnBins = int (*)();
+        FnProbe fp = (FnProbe)sym(std::string("cb200_") + kTypeName[a->dtype] + "_bincount_probe_kernel_launch");
+        FnBins fb = (FnBins)sym("cb200_bincount_probe_bins");
+        if (!fp || !fb) return nullptr;
+        const int bins = fb();
+        static thread_local char* probe_dev = nullptr;          // hist[bins] then extremes[2]
+        static thread_local long long* probe_host = nullptr;
+        if (!probe_dev) {
+            if (!cuda_ok(cudaMalloc((void**)&probe_dev, sizeof(uint32_t) * bins + 16), "cudaMalloc")) { probe_dev = nullptr; return nullptr; }
+            if (!cuda_ok(cudaHostAlloc((void**)&probe_host, 16, cudaHostAllocDefault), "cudaHostAlloc")) { cudaFree(probe_dev); probe_dev = nullptr; return nullptr; }
+        }
+        uint32_t* hist = reinterpret_cast<uint32_t*>(probe_dev);
+        long long* extremes = reinterpret_cast<long long*>(probe_dev + sizeof(uint32_t) * bins);
+        cudaStream_t st = cb200::current_stream();
+        fp(data_ptr(a), (ssize_t)a->step[0], (uint64_t)a->shape[0], hist, extremes);
+        if (!launch_ok()) return nullptr;
+        if (!cuda_ok(cudaMemcpyAsync(probe_host, extremes, 16, cudaMemcpyDeviceToHost, st), "cudaMemcpyAsync") ||
+            !cuda_ok(cudaStreamSynchronize(st), "cudaStreamSynchronize")) return nullptr;
+        const long long vlo = probe_host[0], vhi = probe_host[1];
+        if (vlo < 0) return (cb200_na*)fail("ArgumentError", "array items must be non-negative");
+        int64_t len = vhi + 1;
+        if (minlength > len) len = minlength;
+        if (vhi < bins && len <= bins) {
+            cb200_na* out = make(CB200_UINT32, 1, &len, false);
+            if (!out) return nullptr;
+            if (!cuda_ok(cudaMemcpyAsync(data_ptr(out), hist, sizeof(uint32_t) * (size_t)len, cudaMemcpyDeviceToDevice, st), "cudaMemcpyAsync")) {
+                cb200_na_release(out);
+                return nullptr;
+            }
+            return out;
+        }
+        length = vhi + 1;                                       // large values: the extremes are known, count with the output-sized kernel
+    } else
     if (size_of(a) > 0) {
         cb200_na *lo = nullptr, *hi = nullptr;
         if (cb200_na_minmax(a, 0, 0, 0, &lo, &hi)) { drop_w(); return nullptr; }

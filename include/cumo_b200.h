@@ -326,6 +326,16 @@ CB200_DECL_MODF_FREXP(sfloat) CB200_DECL_MODF_FREXP(dfloat)
 CB200_DECL_BINCOUNT(int32)
 CB200_DECL_BINCOUNT(int64)
 
+/* Counting and sizing in one pass (unweighted).  NOT in the reference, whose method reads the run twice: a min/max reduction
+ * that sizes the output (gen/tmpl/bincount.c:99-131), then the counting launch above.  The probe clears `hist`
+ * (cb200_bincount_probe_bins() uint32_t counters, device memory), counts every element of the run with a value inside
+ * [0, bins) and leaves the smallest and the largest value of ALL elements in extremes[0], extremes[1] (device memory).  A
+ * caller that reads back 0 <= min and max < bins has the counts of the run in hist[0 .. max]; any other caller falls back
+ * to the two passes. */
+int cb200_bincount_probe_bins(void);
+void cb200_int32_bincount_probe_kernel_launch(char* p1, ssize_t s1, uint64_t count, uint32_t* hist, long long* extremes);
+void cb200_int64_bincount_probe_kernel_launch(char* p1, ssize_t s1, uint64_t count, uint32_t* hist, long long* extremes);
+
 /* cumsum / cumprod along one run, reference: gen/tmpl/cum.c:3, cum_kernel.cu:56-80 (thrust::inclusive_scan there).
  * out[i] = x[0] op ... op x[i] for i < n; p1/p2 with byte steps s1/s2 of any sign.  `_nan` (float types): a NaN
  * accumulator is replaced by the next value, a NaN value is skipped (real_accum_kernel.h:12-26).  Returns the launch

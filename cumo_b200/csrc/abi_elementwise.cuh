@@ -10,6 +10,7 @@
 #include "elementwise.cuh"
 #include "divmod_scalar.cuh"
 #include "multi.cuh"
+#include "poly_eye.cuh"
 
 using namespace cb200;
 
@@ -174,6 +175,12 @@ extern "C" void CB_ITER(seq, _kernel_launch)(cumo_na_iarray_t* a1, cumo_na_index
     op::SeqParams<CB_C> prm;
     prm.beg = beg; prm.step = step; prm.count = count;
     launch_multi<op::Seq<CB_C>>(a, ix, prm, nullptr);
+}
+extern "C" void CB_ITER(poly, _kernel_launch)(cumo_na_iarray_t* x, cumo_na_iarray_t* coef, int ncoef, cumo_na_iarray_t* z, cumo_na_indexer_t* ix) {
+    launch_poly<CB_C>(x, coef, ncoef, z, ix);
+}
+extern "C" void CB_ITER(eye, _stride_kernel_launch)(char* ptr, ssize_t s0, ssize_t s1, ssize_t kofs, CB_C data, uint64_t n0, uint64_t n1) {
+    launch_eye<CB_C>(ptr, s0, s1, kofs, data, n0, n1);
 }
 extern "C" void CB_ITER(divmod, _kernel_launch)(cumo_na_iarray_t* a1, cumo_na_iarray_t* a2, cumo_na_iarray_t* a3, cumo_na_iarray_t* a4,
         cumo_na_indexer_t* ix, int* divzero) {

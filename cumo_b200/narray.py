@@ -12,7 +12,7 @@ reads one back.
 from __future__ import annotations
 
 import ctypes
-from ctypes import byref, c_char_p, c_int64, c_void_p
+from ctypes import byref, c_char_p, c_double, c_float, c_int, c_int32, c_int64, c_ssize_t, c_uint64, c_void_p
 
 import numpy as np
 
@@ -539,6 +539,72 @@ class NArray:
             return 1, None, f, i
         lo, hi = bound(min), bound(max)
         return NArray._from_handle(_lib.load().cb200_na_clip(self._h, *lo, *hi))
+
+    def _repeated_to(self, shape):
+        """A view of this array repeated to `shape` (extents of 1 and missing leading dimensions get step 0), as ndloop
+        lines an operand up with the loop (ndloop.c:494-516)."""
+        oshp, ostp = self.shape, self.steps
+        if self.size == 1:
+            oshp, ostp = (), ()
+        if len(oshp) > len(shape):
+            raise ShapeError(f"an operand of shape {oshp} does not fit a loop of shape {tuple(shape)}")
+        steps = []
+        for d in range(len(shape)):
+            od = d - (len(shape) - len(oshp))
+            if od < 0 or oshp[od] == 1:
+                steps.append(0)
+            elif oshp[od] == shape[d]:
+                steps.append(ostp[od])
+            else:
+                raise ShapeError(f"an operand of shape {oshp} does not fit a loop of shape {tuple(shape)}")
+        return self._view(list(shape), steps, 0)
+
+    def poly(self, *coefs):
+        """`x.poly(a0, a1, ..., an)` = a0 + a1*x + ... + an*x**n by Horner's rule in one launch (gen/tmpl/poly.c:46-88);
+        a coefficient is a number or an array repeated to x's shape; no coefficient answers x."""
+        T = type(self)
+        ops = []
+        for c in coefs:
+            if not isinstance(c, NArray):
+                c = T.cast(c if isinstance(c, (list, tuple, np.ndarray)) else [c])
+            elif c.dtype_code != self.dtype_code:
+                c = T.cast(c)
+            ops.append(c._repeated_to(self.shape))
+        out = T(*self.shape)
+        if self.size == 0:
+            return out
+        lib = _lib.load()
+        fn = getattr(lib, f"cumo_iter_{self._tname}_poly_kernel_launch")
+        fn.restype = None
+        ix, dx = self._descriptors()
+        _, dz = out._descriptors()
+        arr = (_lib.NaIArray * max(1, len(ops)))()
+        for i, c in enumerate(ops):
+            _, dc = c._descriptors()
+            arr[i] = dc
+        fn(byref(dx), arr, c_int(len(ops)), byref(dz), byref(ix))
+        _check_launch()
+        return out
+
+    def eye(self, element=1, offset=0):
+        """`a.eye(element, offset)` (gen/tmpl/eye.c:58-104): every matrix of the last two dimensions gets `element` on the
+        diagonal `offset` above (below, if negative) the main one and zero elsewhere.  Returns self."""
+        shp, stp = self.shape, self.steps
+        if len(shp) < 2:
+            raise ShapeError("less than 2-d array")
+        if (offset >= 0 and offset >= shp[-1]) or (offset < 0 and -offset >= shp[-2]):
+            raise ValueError(f"invalid diagonal offset({offset})")
+        lib = _lib.load()
+        fn = getattr(lib, f"cumo_iter_{self._tname}_eye_stride_kernel_launch")
+        fn.restype = None
+        f, i = self._numeric(element)
+        ctype = {SFLOAT: c_float, DFLOAT: c_double, INT32: c_int32, INT64: c_int64}[self.dtype_code]
+        value = ctype(f if self.dtype_code in (SFLOAT, DFLOAT) else i)
+        for lead in np.ndindex(*shp[:-2]):                     # one launch per matrix, as ndloop walks the leading dimensions
+            ptr = self.data_ptr + sum(k * s for k, s in zip(lead, stp[:-2]))
+            fn(c_void_p(ptr), c_ssize_t(stp[-2]), c_ssize_t(stp[-1]), c_ssize_t(offset), value, c_uint64(shp[-2]), c_uint64(shp[-1]))
+        _check_launch()
+        return self
 
     def divmod(self, other):
         """`a.divmod(b)` (gen/tmpl/binary2.c:58-95): quotient and remainder of one pass, both in the upcast type."""

@@ -193,6 +193,14 @@ const char* cb200_version(void);
     void cumo_iter_##T##_seq_kernel_launch(cumo_na_iarray_t* a1, cumo_na_indexer_t* indexer, D beg, D step, double count); \
     void cumo_iter_##T##_divmod_kernel_launch(cumo_na_iarray_t* a1, cumo_na_iarray_t* a2, cumo_na_iarray_t* a3, cumo_na_iarray_t* a4, cumo_na_indexer_t* indexer, int* divzero);
 
+/* poly, reference: gen/tmpl/poly.c:2, poly_kernel.cu:22-44.  z = coef[0] + coef[1]*x + ... by Horner's rule; `coef` is a HOST
+ * array of ncoef descriptors (a numeric coefficient arrives as an array whose steps are all 0); no coefficient: z = x.
+ * eye, reference: gen/tmpl/eye.c:2, eye_kernel.cu:12-19.  The n0 x n1 matrix at ptr (byte steps s0, s1) gets `data` where
+ * row + kofs == column and zero elsewhere. */
+#define CB200_DECL_POLY_EYE(T, C) \
+    void cumo_iter_##T##_poly_kernel_launch(cumo_na_iarray_t* x, cumo_na_iarray_t* coef, int ncoef, cumo_na_iarray_t* z, cumo_na_indexer_t* indexer); \
+    void cumo_iter_##T##_eye_stride_kernel_launch(char* ptr, ssize_t s0, ssize_t s1, ssize_t kofs, C data, uint64_t n0, uint64_t n1);
+
 /* modf, reference: gen/tmpl/unary_ret2.c:2, unary_ret2_kernel.cu:16-31: a2 = fractional part, a3 = integral part.
  * frexp, reference: gen/tmpl/frexp.c:2, frexp_kernel.cu:15-31: a2 = mantissa, a3 = exponent (an Int32 array). */
 #define CB200_DECL_MODF_FREXP(T) \
@@ -312,6 +320,7 @@ CB200_DECL_CLIP(sfloat, float) CB200_DECL_CLIP(dfloat, double) CB200_DECL_CLIP(i
 CB200_DECL_FILL_SEQ_DIVMOD(sfloat, float, float) CB200_DECL_FILL_SEQ_DIVMOD(dfloat, double, double)
 CB200_DECL_FILL_SEQ_DIVMOD(int32, int32_t, double) CB200_DECL_FILL_SEQ_DIVMOD(int64, int64_t, double)
 CB200_DECL_MODF_FREXP(sfloat) CB200_DECL_MODF_FREXP(dfloat)
+CB200_DECL_POLY_EYE(sfloat, float) CB200_DECL_POLY_EYE(dfloat, double) CB200_DECL_POLY_EYE(int32, int32_t) CB200_DECL_POLY_EYE(int64, int64_t)
 
 /* bincount along one run (integer types only), reference: gen/tmpl/bincount.c:18,70, bincount_kernel.cu:32-97.
  * The output run (n elements, byte step s2/s3) is cleared, then every element x of the input run (count elements

@@ -33,7 +33,7 @@ DEFAULT_REF = Path(os.environ.get("CUMO_REFERENCE_ROOT") or HERE.parent.parent /
 # templates (by erb_base) expanded per element type: the hot path and the rows next to it
 VALUE_TEMPLATES = {"binary", "binary_s", "unary", "unary_s", "unary2", "cond_binary", "cond_unary", "pow", "ewcomp",
                    "store_from", "accum", "accum_index", "accum_arg", "accum_binary", "bincount", "cum",
-                   "clip", "fill", "seq", "binary2", "unary_ret2", "frexp", "store_bit"}
+                   "clip", "fill", "seq", "binary2", "unary_ret2", "frexp", "store_bit", "poly", "eye"}
 BIT_TEMPLATES = {"bit_count", "where", "mask", "binary", "unary", "bit_reduce", "store_from", "store_bit", "fill"}
 TYPES = ("sfloat", "dfloat", "int32", "int64", "bit")
 

@@ -1959,4 +1959,28 @@ def case_bit_value_conversions(xp):
         assert xp.Bit.cast(T[0.0, -0.0, NAN, INF, 1e-30, -2.5]).to_a() == [0, 0, 1, 1, 1, 1]
 
 
+# ---- test/narray_test.rb:1943-1965 "poly"; 996-1002 "eye" -------------------------------------------------------------------
+def case_poly_and_eye(xp):
+    x = xp.DFloat.new(4).seq(1)
+    assert x.poly(1.0, 2.0).to_a() == [3.0, 5.0, 7.0, 9.0]
+    assert x.poly(1.0, 2.0, 3.0).to_a() == [6.0, 17.0, 34.0, 57.0]
+    assert x.poly(3.0).to_a() == [3.0, 3.0, 3.0, 3.0]
+    assert x.poly().to_a() == [1.0, 2.0, 3.0, 4.0]
+    assert xp.DFloat[2.0].poly(1.0, 2.0).to_a() == [5.0]
+    assert x.poly(xp.DFloat[1, 1, 1, 1], xp.DFloat[2, 2, 2, 2]).to_a() == [3.0, 5.0, 7.0, 9.0]
+    assert xp.SFloat.new(4).seq(1).poly(1.0, 2.0).to_a() == [3.0, 5.0, 7.0, 9.0]
+    assert xp.Int32.new(4).seq(1).poly(1, 2).to_a() == [3, 5, 7, 9]
+    # over views and with a coefficient per column
+    m = _nd(xp.Int64, list(range(12)), [3, 4])
+    assert m.transpose().poly(1, 2).to_a() == [[1 + 2 * (r * 4 + c) for r in range(3)] for c in range(4)]
+    assert m.poly(xp.Int64[1, 2, 3, 4], 10).to_a() == [[(c + 1) + 10 * (r * 4 + c) for c in range(4)] for r in range(3)]
+    for T in value_types(xp):
+        assert T.new(3, 3).eye(1).to_a() == [[1, 0, 0], [0, 1, 0], [0, 0, 1]]
+        assert T.new(3, 3).eye(2).to_a() == [[2, 0, 0], [0, 2, 0], [0, 0, 2]]
+        assert T.new(3, 3).eye(1, 1).to_a() == [[0, 1, 0], [0, 0, 1], [0, 0, 0]]
+        assert T.new(3, 3).eye(1, -1).to_a() == [[0, 0, 0], [1, 0, 0], [0, 1, 0]]
+        assert T.new(2, 2, 2).eye(1).to_a() == [[[1, 0], [0, 1]], [[1, 0], [0, 1]]]
+        assert T.new(3, 1).eye(1).to_a() == [[1], [0], [0]]
+
+
 ALL_CASES = [v for k, v in sorted(globals().items()) if k.startswith("case_")]

@@ -94,6 +94,27 @@ class ONArray:
             return self
         return self._wrap(res)
 
+    def poly(self, *coefs):
+        """Horner's rule with the oracle's own multiply and add (gen/tmpl/poly_kernel.cu:9-16)."""
+        if not coefs:
+            return self._wrap(np.array(self.a))
+        cs = [np.broadcast_to(self._bound(c), self.a.shape) for c in coefs]
+        y = np.ascontiguousarray(cs[-1])
+        for c in reversed(cs[:-1]):
+            y, _ = orc.binary("mul", self.a, y)
+            y, _ = orc.binary("add", y, np.ascontiguousarray(c))
+        return self._wrap(y)
+
+    def eye(self, element=1, offset=0):
+        if self.a.ndim < 2:
+            raise ShapeErrorO("less than 2-d array")
+        n0, n1 = self.a.shape[-2:]
+        if (offset >= 0 and offset >= n1) or (offset < 0 and -offset >= n0):
+            raise ValueError("invalid diagonal offset")
+        rows, cols = np.indices((n0, n1))
+        self.a[...] = np.where(rows + offset == cols, np.array(element, dtype=self.a.dtype), np.array(0, dtype=self.a.dtype))
+        return self
+
     def divmod(self, o):
         x, y = self._operand(o)
         if not isinstance(y, np.ndarray):

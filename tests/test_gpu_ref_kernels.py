@@ -934,3 +934,40 @@ def test_bit_value_conversions_and_fill_word_for_word(libs):
             return [out]
         (a,), (b,) = run_both(libs, run)
         assert torch.equal(a, b), y
+
+
+@pytest.mark.parametrize("tname", TYPES)
+def test_poly_and_eye_bit_for_bit(libs, tname):
+    """Horner over array and repeated coefficients on several layouts, and the diagonal fill through a strided matrix."""
+    import torch
+    import abi_call as ac
+    from cumo_b200 import _lib
+
+    g = torch.Generator(device="cuda").manual_seed(77)
+    kind = "unit" if tname not in FLOATS else "normal"
+    for layout in ("flat", "transposed", "view3d"):
+        x, c_full, shape = operands(tname, layout, g, kind)
+        scalar_c = values(tname, (1,), g, kind)
+        row_c = values(tname, (shape[-1],), g, kind)
+        for ncoef in (0, 1, 2, 4):
+            coefs = [c_full, scalar_c, row_c, scalar_c][:ncoef]
+
+            def run(L):
+                out = torch.full(shape, 77, device="cuda", dtype=x.dtype)
+                arr = (_lib.NaIArray * max(1, ncoef))()
+                for i, c in enumerate(coefs):
+                    arr[i] = ac.iarray(c, shape)
+                ac.fn(L, f"cumo_iter_{tname}_poly_kernel_launch")(byref(ac.iarray(x, shape)), arr, c_int(ncoef), byref(ac.iarray(out)), byref(ac.indexer(shape)))
+                return [out]
+            (a,), (b,) = run_both(libs, run)
+            assert ac.bits_equal(a, b), (tname, layout, ncoef)
+    for kofs in (0, 1, -2, 5):
+        def run(L):
+            base = torch.full((40, 2 * 37), 77, device="cuda", dtype=ac.torch_dtype(tname))
+            m = base[3:33, ::2]                                             # 30 x 37, columns two elements apart
+            es = base.element_size()
+            ac.fn(L, f"cumo_iter_{tname}_eye_stride_kernel_launch")(c_void_p(m.data_ptr()), c_ssize_t(m.stride(0) * es), c_ssize_t(m.stride(1) * es),
+                                                                      c_ssize_t(kofs), ac.scalar(tname, 3), c_uint64(30), c_uint64(37))
+            return [base]
+        (a,), (b,) = run_both(libs, run)
+        assert ac.bits_equal(a, b), (tname, kofs)

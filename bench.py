@@ -910,6 +910,7 @@ def build_cases(xp, torch, mib: int):
         "count_true_axis0": (lambda: (lambda m=(i32().reshape(rows32, cols) > 0): m.count_true(axis=0)), n32 // 8 + cols * 8),
         "bits_to_f32": (lambda: (lambda m=(i32() > 0): xp.SFloat.cast(m)), n32 // 8 + n32 * 4),
         "i32_to_bits": (lambda: (lambda a=i32(): xp.Bit.cast(a)), n32 * 4 + n32 // 8),
+        "poly3_f32": (lambda: (lambda a=f32(): a.poly(1.0, 2.0, 3.0)), 2 * n32 * 4),
         "clip_scalars_f32": (lambda: (lambda a=f32(): a.clip(-0.5, 0.5)), 2 * n32 * 4),
         "clip_arrays_f32": (lambda: (lambda a=f32(), lo=f32() * 0.5 - 0.5, hi=f32() * 0.5 + 0.5: a.clip(lo, hi)), 4 * n32 * 4),
         "divmod_f32": (lambda: (lambda a=f32(), b=f32() * 0.5 + 1.0: a.divmod(b)), 4 * n32 * 4),

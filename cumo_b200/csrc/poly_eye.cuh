@@ -51,6 +51,49 @@ poly_kernel(const PolyPlan p, const PolyOperand* __restrict__ coef, int ncoef) {
     }
 }
 
+// FLAT: x and z contiguous, every coefficient either contiguous like them or one repeated element, everything 16-byte
+// aligned, at most kPolyFlatMax coefficients.  A thread keeps the repeated coefficients in registers and takes two packets
+// of x (and of each array coefficient) per round.
+constexpr int kPolyFlatMax = 8;
+struct PolyFlat {
+    int ncoef;
+    const char* ptr[kPolyFlatMax];
+    bool is_array[kPolyFlatMax];
+};
+
+template <typename T>
+__global__ void __launch_bounds__(kBlock)
+poly_flat_kernel(const char* __restrict__ x, char* z, int64_t n_packets, const PolyFlat c) {
+    constexpr int V = 16 / (int)sizeof(T);
+    T held[kPolyFlatMax];
+#pragma unroll
+    for (int k = 0; k < kPolyFlatMax; ++k) held[k] = (k < c.ncoef && !c.is_array[k]) ? *reinterpret_cast<const T*>(c.ptr[k]) : T(0);
+    for (int64_t q = (int64_t)blockIdx.x * kBlock + threadIdx.x; q < n_packets; q += (int64_t)gridDim.x * kBlock) {
+        const Pack<T> xv = ld_pack<T>(x + q * 16);
+        Pack<T> y;
+        if (c.ncoef == 0) {
+            y = xv;
+        } else {
+#pragma unroll
+            for (int k = kPolyFlatMax - 1; k >= 0; --k) {
+                if (k >= c.ncoef) continue;
+                Pack<T> cv;
+                if (c.is_array[k]) cv = ld_pack<T>(c.ptr[k] + q * 16);
+                else {
+#pragma unroll
+                    for (int e = 0; e < V; ++e) cv.v[e] = held[k];
+                }
+                if (k == c.ncoef - 1) y = cv;
+                else {
+#pragma unroll
+                    for (int e = 0; e < V; ++e) { T t = xv.v[e] * y.v[e]; y.v[e] = t + cv.v[e]; }
+                }
+            }
+        }
+        st_pack<T>(z + q * 16, y);
+    }
+}
+
 template <typename T>
 void launch_poly(const cumo_na_iarray_t* x, const cumo_na_iarray_t* coef, int ncoef, const cumo_na_iarray_t* z, const cumo_na_indexer_t* ix) {
     CB200_TRACE_LAUNCH();
@@ -83,6 +126,32 @@ void launch_poly(const cumo_na_iarray_t* x, const cumo_na_iarray_t* coef, int nc
     p.x = plan[0];
     p.z = plan[1];
     cudaStream_t st = current_stream();
+    constexpr int64_t ES = sizeof(T);
+    constexpr int V = 16 / (int)sizeof(T);
+    bool flat = p.nd <= 1 && ncoef <= kPolyFlatMax && p.total >= V && (p.nd == 0 || (plan[0].step[0] == ES && plan[1].step[0] == ES)) &&
+                aligned16(plan[0].ptr) && aligned16(plan[1].ptr);
+    PolyFlat fc;
+    fc.ncoef = ncoef;
+    for (int c = 0; c < kPolyFlatMax; ++c) { fc.ptr[c] = nullptr; fc.is_array[c] = false; }
+    for (int c = 0; c < ncoef && flat; ++c) {
+        const int64_t stp = p.nd == 0 ? 0 : plan[2 + c].step[0];
+        fc.ptr[c] = plan[2 + c].ptr;
+        fc.is_array[c] = stp != 0;
+        if (stp != 0 && (stp != ES || !aligned16(plan[2 + c].ptr))) flat = false;
+    }
+    if (flat) {
+        const int64_t n_packets = p.total / V;
+        poly_flat_kernel<T><<<grid_for((n_packets + kBlock - 1) / kBlock, 16), kBlock, 0, st>>>(plan[0].ptr, const_cast<char*>(plan[1].ptr), n_packets, fc);
+        count_launch();
+        const int64_t done = n_packets * V;
+        if (done == p.total) { cumo_cuda_runtime_check_kernel_launch(); return; }
+        // the few elements after the last whole packet: the general kernel on the shifted operands
+        for (int o = 0; o < nops; ++o) plan[o].ptr += done * plan[o].step[0];
+        p.total -= done;
+        p.shape[0] = p.total;
+        p.x = plan[0];
+        p.z = plan[1];
+    }
     PolyOperand* d_coef = reinterpret_cast<PolyOperand*>(cumo_cuda_runtime_malloc(sizeof(PolyOperand) * (size_t)(ncoef > 0 ? ncoef : 1)));
     if (!d_coef) return;
     if (ncoef > 0) cudaMemcpyAsync(d_coef, plan.data() + 2, sizeof(PolyOperand) * (size_t)ncoef, cudaMemcpyHostToDevice, st);

@@ -563,12 +563,19 @@ class NArray:
         """`x.poly(a0, a1, ..., an)` = a0 + a1*x + ... + an*x**n by Horner's rule in one launch (gen/tmpl/poly.c:46-88);
         a coefficient is a number or an array repeated to x's shape; no coefficient answers x."""
         T = type(self)
-        ops = []
+        numbers = [c for c in coefs if not isinstance(c, (NArray, list, tuple, np.ndarray))]
+        held = T(len(numbers)) if numbers else None              # numeric coefficients: filled on the device, nothing to wait for
+        for k, c in enumerate(numbers):
+            held[k:k + 1].fill(c)
+        ops, taken = [], 0
         for c in coefs:
-            if not isinstance(c, NArray):
-                c = T.cast(c if isinstance(c, (list, tuple, np.ndarray)) else [c])
-            elif c.dtype_code != self.dtype_code:
+            if isinstance(c, NArray):
+                c = c if c.dtype_code == self.dtype_code else T.cast(c)
+            elif isinstance(c, (list, tuple, np.ndarray)):
                 c = T.cast(c)
+            else:
+                c = held[taken:taken + 1]
+                taken += 1
             ops.append(c._repeated_to(self.shape))
         out = T(*self.shape)
         if self.size == 0:

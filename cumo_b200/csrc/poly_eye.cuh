@@ -61,36 +61,58 @@ struct PolyFlat {
     bool is_array[kPolyFlatMax];
 };
 
-template <typename T>
+template <typename T, int NC>
 __global__ void __launch_bounds__(kBlock)
 poly_flat_kernel(const char* __restrict__ x, char* z, int64_t n_packets, const PolyFlat c) {
     constexpr int V = 16 / (int)sizeof(T);
-    T held[kPolyFlatMax];
+    constexpr int U = 2;                                   // packets per thread, all loads issued before the first use
+    T held[NC > 0 ? NC : 1];
 #pragma unroll
-    for (int k = 0; k < kPolyFlatMax; ++k) held[k] = (k < c.ncoef && !c.is_array[k]) ? *reinterpret_cast<const T*>(c.ptr[k]) : T(0);
-    for (int64_t q = (int64_t)blockIdx.x * kBlock + threadIdx.x; q < n_packets; q += (int64_t)gridDim.x * kBlock) {
-        const Pack<T> xv = ld_pack<T>(x + q * 16);
-        Pack<T> y;
-        if (c.ncoef == 0) {
-            y = xv;
-        } else {
+    for (int k = 0; k < NC; ++k) held[k] = c.is_array[k] ? T(0) : *reinterpret_cast<const T*>(c.ptr[k]);
+    for (int64_t tile = blockIdx.x; tile * (kBlock * U) < n_packets; tile += gridDim.x) {
+        int64_t q[U];
+        Pack<T> xv[U], cv[U][NC > 0 ? NC : 1];
 #pragma unroll
-            for (int k = kPolyFlatMax - 1; k >= 0; --k) {
-                if (k >= c.ncoef) continue;
-                Pack<T> cv;
-                if (c.is_array[k]) cv = ld_pack<T>(c.ptr[k] + q * 16);
-                else {
+        for (int u = 0; u < U; ++u) {
+            q[u] = tile * (kBlock * U) + u * kBlock + threadIdx.x;
+            if (q[u] >= n_packets) continue;
+            xv[u] = ld_pack<T>(x + q[u] * 16);
 #pragma unroll
-                    for (int e = 0; e < V; ++e) cv.v[e] = held[k];
-                }
-                if (k == c.ncoef - 1) y = cv;
-                else {
+            for (int k = 0; k < NC; ++k)
+                if (c.is_array[k]) cv[u][k] = ld_pack<T>(c.ptr[k] + q[u] * 16);
+        }
 #pragma unroll
-                    for (int e = 0; e < V; ++e) { T t = xv.v[e] * y.v[e]; y.v[e] = t + cv.v[e]; }
+        for (int u = 0; u < U; ++u) {
+            if (q[u] >= n_packets) continue;
+            Pack<T> y = xv[u];                             // no coefficient at all answers x itself
+#pragma unroll
+            for (int k = NC - 1; k >= 0; --k) {
+#pragma unroll
+                for (int e = 0; e < V; ++e) {
+                    const T ck = c.is_array[k] ? cv[u][k].v[e] : held[k];
+                    if (k == NC - 1) y.v[e] = ck;
+                    else { const T t = xv[u].v[e] * y.v[e]; y.v[e] = t + ck; }
                 }
             }
+            st_pack<T>(z + q[u] * 16, y);
         }
-        st_pack<T>(z + q * 16, y);
+    }
+}
+
+template <typename T>
+void launch_poly_flat(const char* x, char* z, int64_t n_packets, const PolyFlat& c, cudaStream_t st) {
+    const int64_t tiles = (n_packets + kBlock * 2 - 1) / (kBlock * 2);
+    const unsigned grid = (unsigned)(tiles > 0x7fffffffLL ? 0x7fffffffLL : tiles);
+    switch (c.ncoef) {
+    case 0: poly_flat_kernel<T, 0><<<grid, kBlock, 0, st>>>(x, z, n_packets, c); break;
+    case 1: poly_flat_kernel<T, 1><<<grid, kBlock, 0, st>>>(x, z, n_packets, c); break;
+    case 2: poly_flat_kernel<T, 2><<<grid, kBlock, 0, st>>>(x, z, n_packets, c); break;
+    case 3: poly_flat_kernel<T, 3><<<grid, kBlock, 0, st>>>(x, z, n_packets, c); break;
+    case 4: poly_flat_kernel<T, 4><<<grid, kBlock, 0, st>>>(x, z, n_packets, c); break;
+    case 5: poly_flat_kernel<T, 5><<<grid, kBlock, 0, st>>>(x, z, n_packets, c); break;
+    case 6: poly_flat_kernel<T, 6><<<grid, kBlock, 0, st>>>(x, z, n_packets, c); break;
+    case 7: poly_flat_kernel<T, 7><<<grid, kBlock, 0, st>>>(x, z, n_packets, c); break;
+    default: poly_flat_kernel<T, 8><<<grid, kBlock, 0, st>>>(x, z, n_packets, c); break;
     }
 }
 
@@ -141,7 +163,7 @@ void launch_poly(const cumo_na_iarray_t* x, const cumo_na_iarray_t* coef, int nc
     }
     if (flat) {
         const int64_t n_packets = p.total / V;
-        poly_flat_kernel<T><<<grid_for((n_packets + kBlock - 1) / kBlock, 16), kBlock, 0, st>>>(plan[0].ptr, const_cast<char*>(plan[1].ptr), n_packets, fc);
+        launch_poly_flat<T>(plan[0].ptr, const_cast<char*>(plan[1].ptr), n_packets, fc, st);
         count_launch();
         const int64_t done = n_packets * V;
         if (done == p.total) { cumo_cuda_runtime_check_kernel_launch(); return; }

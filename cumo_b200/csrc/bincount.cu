@@ -12,6 +12,7 @@
 // last bits may differ from run to run.
 #include "common.cuh"
 
+#include <limits>
 #include <type_traits>
 
 namespace cb200 {
@@ -145,13 +146,16 @@ bincount_probe_kernel(const char* __restrict__ p1, int64_t s1, uint64_t count, u
     for (int b = threadIdx.x; b < kProbeFast * kProbeCopies; b += kBlock) local[b] = 0u;
     __syncthreads();
     uint32_t* mine = local + (threadIdx.x % kProbeCopies) * kProbeFast;
-    long long lo = 0x7fffffffffffffffLL, hi = -0x7fffffffffffffffLL - 1;
+    // extremes in the element type (one min and one max instruction per element for 32-bit items); range tests as unsigned,
+    // so that a negative value fails both
+    using TU = typename std::make_unsigned<TI>::type;
+    TI lo_t = std::numeric_limits<TI>::max(), hi_t = std::numeric_limits<TI>::min();
     auto add = [&](TI x) {
-        const long long v = (long long)x;
-        lo = v < lo ? v : lo;
-        hi = v > hi ? v : hi;
-        if (v >= 0 && v < kProbeFast) atomicAdd(mine + v, 1u);
-        else if (v >= kProbeFast && v < kProbeBins) atomicAdd(hist + v, 1u);
+        lo_t = x < lo_t ? x : lo_t;
+        hi_t = x > hi_t ? x : hi_t;
+        const TU u = (TU)x;
+        if (u < (TU)kProbeFast) atomicAdd(mine + u, 1u);
+        else if (u < (TU)kProbeBins) atomicAdd(hist + u, 1u);
     };
     constexpr int V = 16 / sizeof(TI);
     const bool packed = s1 == (int64_t)sizeof(TI) && (reinterpret_cast<uintptr_t>(p1) & 15) == 0;
@@ -173,6 +177,7 @@ bincount_probe_kernel(const char* __restrict__ p1, int64_t s1, uint64_t count, u
             }
         }
     }
+    long long lo = (long long)lo_t, hi = (long long)hi_t;
 #pragma unroll
     for (int d = 16; d > 0; d >>= 1) {
         const long long ol = __shfl_xor_sync(0xffffffffu, lo, d), oh = __shfl_xor_sync(0xffffffffu, hi, d);

@@ -299,6 +299,58 @@ scan_rows_kernel(const ScanRuns o, const char* __restrict__ p1, int64_t s1, char
     }
 }
 
+// SHORT ROWS: runs of fewer than 256 elements that do not lie side by side (a scan along the contiguous axis of a matrix
+// with short rows).  G lanes per run (the smallest power of two that covers the run, at most a warp), 32/G runs per warp at
+// a time; the lanes of a group take consecutive elements, so a warp's loads and stores are consecutive memory when the rows
+// are; runs longer than a warp go in chunks of 32 with the fold so far carried along.  Every chunk of a lane is loaded
+// before the first shuffle.  No shared memory, no barrier.
+constexpr int kShortMax = 256;
+template <typename T, typename Op, int G, int CH>
+__global__ void __launch_bounds__(kBlock)
+scan_short_rows_kernel(const ScanRuns o, const char* __restrict__ p1, int64_t s1, char* p2, int64_t s2, int64_t n) {
+    constexpr int R = 32 / G;                              // runs per warp and slot
+    constexpr int U = 8 / CH;                              // slots per round: eight loads per lane in flight either way
+    const int lane = threadIdx.x & 31, sub = lane % G;
+    const int64_t warp = ((int64_t)blockIdx.x * kBlock + threadIdx.x) >> 5;
+    const int64_t n_warps = ((int64_t)gridDim.x * kBlock) >> 5;
+    for (int64_t r0 = warp * (R * U); r0 < o.runs; r0 += n_warps * (R * U)) {
+        T x[U][CH];
+        int64_t off2[U];
+        bool live[U];
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+            const int64_t r = r0 + u * R + lane / G;
+            live[u] = r < o.runs;
+            int64_t off1 = 0;
+            off2[u] = 0;
+            if (live[u]) run_offsets(o, r, &off1, &off2[u]);
+#pragma unroll
+            for (int k = 0; k < CH; ++k) {
+                const int64_t j = (int64_t)k * G + sub;
+                x[u][k] = (live[u] && j < n) ? *reinterpret_cast<const T*>(p1 + off1 + j * s1) : T();
+            }
+        }
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+            T carry = T();
+#pragma unroll
+            for (int k = 0; k < CH; ++k) {
+                if ((int64_t)k * G >= n) break;            // the same for every lane
+                const int64_t j = (int64_t)k * G + sub;
+                T v = x[u][k];
+#pragma unroll
+                for (int d = 1; d < G; d <<= 1) {
+                    const T before = __shfl_up_sync(0xffffffffu, v, d, G);
+                    if (sub >= d) v = Op::combine(before, v);
+                }
+                if (k > 0) v = Op::combine(carry, v);
+                if (live[u] && j < n) *reinterpret_cast<T*>(p2 + off2[u] + j * s2) = v;
+                carry = __shfl_sync(0xffffffffu, v, G - 1, G);  // a chunk that is followed by another is a whole one
+            }
+        }
+    }
+}
+
 // COLUMNS: a thread per run, in element order; consecutive threads are consecutive runs, so when the runs lie side by
 // side in memory (a scan along an outer axis) every step of a warp is one coalesced access.  Loads run kColAhead
 // elements ahead of the dependent chain of combines.
@@ -466,7 +518,27 @@ cudaError_t launch_scan_runs(char* p1, char* p2, ssize_t s1, ssize_t s2, uint64_
     const int64_t n = (int64_t)n64;
     cudaStream_t st = current_stream();
     if (o.runs == 1) return launch_scan<T, PROD, NANSKIP>(p1, p2, s1, s2, n64);
-    if (!side_by_side && n >= 256) {
+    if (!side_by_side && n < kShortMax) {
+        int g = 1;
+        while (g < 32 && g < n) g <<= 1;
+        const int chunks = g < 32 ? 1 : (int)((n + 31) / 32);
+        const int ch = chunks <= 1 ? 1 : chunks <= 2 ? 2 : chunks <= 4 ? 4 : 8;
+        const int64_t per_warp = (int64_t)(32 / g) * (8 / ch);
+        const int64_t warps = (o.runs + per_warp - 1) / per_warp;
+        const unsigned grid = grid_for((warps + kBlock / 32 - 1) / (kBlock / 32), 8);
+        switch (g) {
+        case 1: case 2: scan_short_rows_kernel<T, Op, 2, 1><<<grid, kBlock, 0, st>>>(o, p1, s1, p2, s2, n); break;
+        case 4:  scan_short_rows_kernel<T, Op, 4, 1><<<grid, kBlock, 0, st>>>(o, p1, s1, p2, s2, n); break;
+        case 8:  scan_short_rows_kernel<T, Op, 8, 1><<<grid, kBlock, 0, st>>>(o, p1, s1, p2, s2, n); break;
+        case 16: scan_short_rows_kernel<T, Op, 16, 1><<<grid, kBlock, 0, st>>>(o, p1, s1, p2, s2, n); break;
+        default:
+            if (ch == 1)      scan_short_rows_kernel<T, Op, 32, 1><<<grid, kBlock, 0, st>>>(o, p1, s1, p2, s2, n);
+            else if (ch == 2) scan_short_rows_kernel<T, Op, 32, 2><<<grid, kBlock, 0, st>>>(o, p1, s1, p2, s2, n);
+            else if (ch == 4) scan_short_rows_kernel<T, Op, 32, 4><<<grid, kBlock, 0, st>>>(o, p1, s1, p2, s2, n);
+            else              scan_short_rows_kernel<T, Op, 32, 8><<<grid, kBlock, 0, st>>>(o, p1, s1, p2, s2, n);
+            break;
+        }
+    } else if (!side_by_side && n >= 256) {
         const bool packed_in = s1 == (ssize_t)sizeof(T) && aligned16(p1) && steps16;
         const bool packed_out = s2 == (ssize_t)sizeof(T) && aligned16(p2) && steps16;
         scan_rows_kernel<T, Op><<<grid_for(o.runs, sizeof(T) <= 4 ? 4 : 3), kBlock, 0, st>>>(o, p1, s1, p2, s2, n, packed_in, packed_out);

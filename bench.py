@@ -904,6 +904,8 @@ def build_cases(xp, torch, mib: int):
         "sum_i32": (lambda: (lambda a=i32(): a.sum()), n32 * 4),
         "mulsum_axis1_f32": (lambda: (lambda a=f32().reshape(rows32, cols), b=(f32() * 0.5).reshape(rows32, cols): a.mulsum(b, axis=1)), 2 * n32 * 4),
         "mulsum_axis0_f32": (lambda: (lambda a=f32().reshape(rows32, cols), b=(f32() * 0.5).reshape(rows32, cols): a.mulsum(b, axis=0)), 2 * n32 * 4),
+        "mulsum_axis1_short_f32": (lambda: (lambda a=f32().reshape(rows32 * cols // 16, 16), b=(f32() * 0.5).reshape(rows32 * cols // 16, 16): a.mulsum(b, axis=1)), 2 * n32 * 4 + n32 // 4),
+        "sum_axis1_short_f32": (lambda: (lambda a=f32().reshape(rows32 * cols // 16, 16): a.sum(axis=1)), n32 * 4 + n32 // 4),
         "cumsum_axis1_short_f32": (lambda: (lambda a=f32().reshape(rows32 * cols // 64, 64): a.cumsum(axis=1)), 2 * n32 * 4),
         "cumsum_axis1_f32": (lambda: (lambda a=f32().reshape(rows32, cols): a.cumsum(axis=1)), 2 * n32 * 4),
         "cumsum_axis0_f32": (lambda: (lambda a=f32().reshape(rows32, cols): a.cumsum(axis=0)), 2 * n32 * 4),

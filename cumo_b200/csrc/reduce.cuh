@@ -120,9 +120,18 @@ __device__ __forceinline__ typename R::Acc warp_fold(const R& r, typename R::Acc
     return a;                                // lane 0 holds the warp's result
 }
 
-// Result valid in thread 0 of the group.  G == 32: a warp; G == kBlock: the CTA.
+// Result valid in thread 0 of the group.  G < 32: G neighbouring lanes of a warp; G == 32: a warp; G == kBlock: the CTA.
 template <typename R, int G>
 __device__ __forceinline__ typename R::Acc group_fold(const R& r, typename R::Acc a, typename R::Acc* smem) {
+    if constexpr (G < 32) {
+        // lane i folds in lane i+d for d < G: the first lane of a group only ever reaches lanes of its own group
+#pragma unroll
+        for (int d = 1; d < G; d <<= 1) {
+            typename R::Acc b = shfl_down_acc(a, d);
+            a = r.combine(a, b);
+        }
+        return a;
+    }
     a = warp_fold(r, a);
     if (G == 32) return a;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -686,9 +695,22 @@ void launch_reduce(const cumo_na_reduction_arg_t* arg, const cumo_na_iarray_t* o
             if (vec) red_row_kernel<R, VMAX, kBlock><<<red_grid(items), kBlock, 0, st>>>(p, r, q, in, out, out2, partial);
             else     red_row_kernel<R, 1, kBlock><<<red_grid(items), kBlock, 0, st>>>(p, r, q, in, out, out2, partial);
         } else {
-            const unsigned grid = red_grid((items + kWarpsPerBlock - 1) / kWarpsPerBlock);
-            if (vec) red_row_kernel<R, VMAX, 32><<<grid, kBlock, 0, st>>>(p, r, q, in, out, out2, partial);
-            else     red_row_kernel<R, 1, 32><<<grid, kBlock, 0, st>>>(p, r, q, in, out, out2, partial);
+            // short rows: 4 or 16 lanes per row instead of a warp (a warp per 16-element row leaves 28 lanes idle and pays a
+            // five-step fold per 64 bytes); the lanes of a group take neighbouring packets, the groups of a warp neighbouring rows
+            const int64_t units = vec ? (L + VMAX - 1) / VMAX : L;
+            if (units <= 4 && q.n_split == 1) {
+                const unsigned grid = red_grid((items + kBlock / 4 - 1) / (kBlock / 4));
+                if (vec) red_row_kernel<R, VMAX, 4><<<grid, kBlock, 0, st>>>(p, r, q, in, out, out2, partial);
+                else     red_row_kernel<R, 1, 4><<<grid, kBlock, 0, st>>>(p, r, q, in, out, out2, partial);
+            } else if (units <= 16 && q.n_split == 1) {
+                const unsigned grid = red_grid((items + kBlock / 16 - 1) / (kBlock / 16));
+                if (vec) red_row_kernel<R, VMAX, 16><<<grid, kBlock, 0, st>>>(p, r, q, in, out, out2, partial);
+                else     red_row_kernel<R, 1, 16><<<grid, kBlock, 0, st>>>(p, r, q, in, out, out2, partial);
+            } else {
+                const unsigned grid = red_grid((items + kWarpsPerBlock - 1) / kWarpsPerBlock);
+                if (vec) red_row_kernel<R, VMAX, 32><<<grid, kBlock, 0, st>>>(p, r, q, in, out, out2, partial);
+                else     red_row_kernel<R, 1, 32><<<grid, kBlock, 0, st>>>(p, r, q, in, out, out2, partial);
+            }
         }
     } else if (col) {
         const int od_in = p.n_od - 1;

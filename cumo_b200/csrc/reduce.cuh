@@ -695,17 +695,18 @@ void launch_reduce(const cumo_na_reduction_arg_t* arg, const cumo_na_iarray_t* o
             if (vec) red_row_kernel<R, VMAX, kBlock><<<red_grid(items), kBlock, 0, st>>>(p, r, q, in, out, out2, partial);
             else     red_row_kernel<R, 1, kBlock><<<red_grid(items), kBlock, 0, st>>>(p, r, q, in, out, out2, partial);
         } else {
-            // short rows: 4 or 16 lanes per row instead of a warp (a warp per 16-element row leaves 28 lanes idle and pays a
-            // five-step fold per 64 bytes); the lanes of a group take neighbouring packets, the groups of a warp neighbouring rows
+            // short rows: one lane (up to 4 packets) or 4 lanes (up to 16) per row instead of a warp (a warp per 16-element row
+            // leaves 28 lanes idle and pays a five-step fold per 64 bytes); every lane then has up to four loads in flight and
+            // a warp covers 32 or 8 neighbouring rows
             const int64_t units = vec ? (L + VMAX - 1) / VMAX : L;
             if (units <= 4 && q.n_split == 1) {
+                const unsigned grid = red_grid((items + kBlock - 1) / kBlock);
+                if (vec) red_row_kernel<R, VMAX, 1><<<grid, kBlock, 0, st>>>(p, r, q, in, out, out2, partial);
+                else     red_row_kernel<R, 1, 1><<<grid, kBlock, 0, st>>>(p, r, q, in, out, out2, partial);
+            } else if (units <= 16 && q.n_split == 1) {
                 const unsigned grid = red_grid((items + kBlock / 4 - 1) / (kBlock / 4));
                 if (vec) red_row_kernel<R, VMAX, 4><<<grid, kBlock, 0, st>>>(p, r, q, in, out, out2, partial);
                 else     red_row_kernel<R, 1, 4><<<grid, kBlock, 0, st>>>(p, r, q, in, out, out2, partial);
-            } else if (units <= 16 && q.n_split == 1) {
-                const unsigned grid = red_grid((items + kBlock / 16 - 1) / (kBlock / 16));
-                if (vec) red_row_kernel<R, VMAX, 16><<<grid, kBlock, 0, st>>>(p, r, q, in, out, out2, partial);
-                else     red_row_kernel<R, 1, 16><<<grid, kBlock, 0, st>>>(p, r, q, in, out, out2, partial);
             } else {
                 const unsigned grid = red_grid((items + kWarpsPerBlock - 1) / kWarpsPerBlock);
                 if (vec) red_row_kernel<R, VMAX, 32><<<grid, kBlock, 0, st>>>(p, r, q, in, out, out2, partial);

@@ -283,6 +283,37 @@ mulsum_columns_kernel(const MulSumAxes c, const char* __restrict__ p1, const cha
     }
 }
 
+// SHORT ROWS: one summed dimension, contiguous in both inputs, of fewer than 64 elements in whole 16-byte packets: a thread per
+// output reading its own run by packets, four of each input in flight (a warp then covers 32 neighbouring rows).
+template <typename T, bool NAN_SKIP>
+__global__ void __launch_bounds__(kBlock)
+mulsum_shortrows_kernel(const MulSumAxes c, const char* __restrict__ p1, const char* __restrict__ p2, char* p3) {
+    using R = MulSumR<T, NAN_SKIP>;
+    constexpr int V = 16 / (int)sizeof(T);
+    const int64_t packets = c.rshape[0] / V;
+    for (int64_t o = (int64_t)blockIdx.x * kBlock + threadIdx.x; o < c.outputs; o += (int64_t)gridDim.x * kBlock) {
+        int64_t o1, o2, o3;
+        mulsum_output_of(c, o, &o1, &o2, &o3);
+        const char* q1 = p1 + o1;
+        const char* q2 = p2 + o2;
+        T acc = 0;
+        for (int64_t k0 = 0; k0 < packets; k0 += 4) {
+            Pack<T> x[4], y[4];
+#pragma unroll
+            for (int u = 0; u < 4; ++u)
+                if (k0 + u < packets) { x[u] = ld_pack<T>(q1 + (k0 + u) * 16); y[u] = ld_pack<T>(q2 + (k0 + u) * 16); }
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+                if (k0 + u >= packets) break;
+#pragma unroll
+                for (int e = 0; e < V; ++e) R::fma_into(x[u].v[e], y[u].v[e], acc);
+            }
+        }
+        T* z = reinterpret_cast<T*>(p3 + o3);
+        *z = *z + acc;
+    }
+}
+
 template <typename T>
 __global__ void __launch_bounds__(kBlock)
 mulsum_slices_fold_kernel(const MulSumAxes c, const T* __restrict__ partial, int64_t slices, char* p3) {
@@ -336,6 +367,11 @@ void launch_mulsum_axes(char* p1, char* p2, char* p3, int n_keep, const size_t* 
             if (vec) mulsum_rows_kernel<T, NAN_SKIP, 32, true><<<g_warp, kBlock, 0, st>>>(c, p1, p2, p3);
             else mulsum_rows_kernel<T, NAN_SKIP, 32, false><<<g_warp, kBlock, 0, st>>>(c, p1, p2, p3);
         }
+    } else if (along && c.n_red == 1 && c.rs1[0] == ES && c.rs2[0] == ES && c.rshape[0] % (16 / ES) == 0 && aligned16(p1) && aligned16(p2) &&
+               c.outputs >= (int64_t)sm_count() * 512 && [&] {
+                   for (int d = 0; d < c.n_keep; ++d) if (!mult16(c.ks1[d]) || !mult16(c.ks2[d])) return false;
+                   return true; }()) {
+        mulsum_shortrows_kernel<T, NAN_SKIP><<<grid_for((c.outputs + kBlock - 1) / kBlock, 8), kBlock, 0, st>>>(c, p1, p2, p3);
     } else {
         const int64_t wanted = (int64_t)sm_count() * 2048;
         int64_t slices = (wanted + c.outputs - 1) / c.outputs;

@@ -7,7 +7,8 @@ pytestmark = pytest.mark.gpu
 
 CASES = [((300, 2048), (300, 2048), 1), ((300, 2048), (300, 2048), 0), ((300, 2048), (1, 2048), 1), ((300, 2048), (300, 1), 0),
          ((7, 33, 130), (7, 33, 130), (0, 2)), ((7, 33, 130), (7, 33, 130), 1), ((7, 33, 130), (33, 130), (1, 2)),
-         ((5000, 9), (5000, 9), 1), ((70, 20_000), (70, 20_000), 1), ((20_000, 70), (20_000, 70), 0), ((100_000, 3), (100_000, 3), 0)]
+         ((5000, 9), (5000, 9), 1), ((70, 20_000), (70, 20_000), 1), ((20_000, 70), (20_000, 70), 0), ((100_000, 3), (100_000, 3), 0),
+         ((200_000, 16), (200_000, 16), 1), ((100_000, 32), (100_000, 32), 1), ((90_000, 8), (90_000, 8), 1), ((80_000, 60), (80_000, 60), 1)]
 
 
 @pytest.mark.parametrize("sa,sb,axis", CASES)

@@ -351,6 +351,38 @@ scan_short_rows_kernel(const ScanRuns o, const char* __restrict__ p1, int64_t s1
     }
 }
 
+// ... and when such short rows are contiguous, whole packets long and 16-byte aligned, a thread per run reading and writing
+// its own run by packets, four at a time: a warp then has 32 neighbouring rows in flight instead of one to sixteen.
+template <typename T, typename Op>
+__global__ void __launch_bounds__(kBlock)
+scan_thread_rows_kernel(const ScanRuns o, const char* __restrict__ p1, char* p2, int64_t n) {
+    constexpr int V = 16 / (int)sizeof(T);
+    const int64_t packets = n / V;
+    for (int64_t r = (int64_t)blockIdx.x * kBlock + threadIdx.x; r < o.runs; r += (int64_t)gridDim.x * kBlock) {
+        int64_t off1, off2;
+        run_offsets(o, r, &off1, &off2);
+        const char* src = p1 + off1;
+        char* dst = p2 + off2;
+        T acc = T();
+        for (int64_t k0 = 0; k0 < packets; k0 += 4) {
+            Pack<T> x[4];
+#pragma unroll
+            for (int u = 0; u < 4; ++u)
+                if (k0 + u < packets) x[u] = ld_pack<T>(src + (k0 + u) * 16);
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+                if (k0 + u >= packets) break;
+#pragma unroll
+                for (int e = 0; e < V; ++e) {
+                    acc = (k0 + u == 0 && e == 0) ? x[u].v[e] : Op::combine(acc, x[u].v[e]);
+                    x[u].v[e] = acc;
+                }
+                st_pack<T>(dst + (k0 + u) * 16, x[u]);
+            }
+        }
+    }
+}
+
 // COLUMNS: a thread per run, in element order; consecutive threads are consecutive runs, so when the runs lie side by
 // side in memory (a scan along an outer axis) every step of a warp is one coalesced access.  Loads run kColAhead
 // elements ahead of the dependent chain of combines.
@@ -518,7 +550,10 @@ cudaError_t launch_scan_runs(char* p1, char* p2, ssize_t s1, ssize_t s2, uint64_
     const int64_t n = (int64_t)n64;
     cudaStream_t st = current_stream();
     if (o.runs == 1) return launch_scan<T, PROD, NANSKIP>(p1, p2, s1, s2, n64);
-    if (!side_by_side && n < kShortMax) {
+    if (!side_by_side && n < kShortMax && s1 == (ssize_t)sizeof(T) && s2 == (ssize_t)sizeof(T) && n % (16 / (int64_t)sizeof(T)) == 0 && steps16 &&
+        aligned16(p1) && aligned16(p2) && o.runs >= (int64_t)sm_count() * 512) {
+        scan_thread_rows_kernel<T, Op><<<grid_for((o.runs + kBlock - 1) / kBlock, 8), kBlock, 0, st>>>(o, p1, p2, n);
+    } else if (!side_by_side && n < kShortMax) {
         int g = 1;
         while (g < 32 && g < n) g <<= 1;
         const int chunks = g < 32 ? 1 : (int)((n + 31) / 32);

@@ -7,7 +7,7 @@ pytestmark = pytest.mark.gpu
 
 SHAPES = [((300, 2048), 1), ((300, 2047), 1), ((2048, 300), 0), ((7, 33, 130), 1), ((7, 33, 130), 0), ((7, 33, 130), 2), ((5000, 9), 1),
           ((3, 10_000), 1), ((4, 3, 5000), 2), ((2, 3, 4, 700), 3), ((9000, 2), 0),
-          ((1000, 1), 1), ((1000, 2), 1), ((777, 5), 1), ((3000, 31), 1), ((3000, 32), 1), ((3000, 33), 1), ((500, 255), 1), ((40, 50, 64), 2)]
+          ((1000, 1), 1), ((1000, 2), 1), ((777, 5), 1), ((3000, 31), 1), ((3000, 32), 1), ((3000, 33), 1), ((500, 255), 1), ((40, 50, 64), 2), ((100_000, 16), 1), ((90_000, 64), 1), ((80_000, 4), 1)]
 
 
 @pytest.mark.parametrize("shape,axis", SHAPES)
